@@ -1,0 +1,95 @@
+// C ABI of the sm_100a kernel library.  Every function takes raw device pointers and
+// a CUDA stream (as void*), launches asynchronously, allocates nothing unless stated,
+// and returns a cudaError_t value as int (0 = launched).  Device-side problems
+// (expired waits, failed bounds checks) are reported through the caller's 4-int
+// `status` block: {code, kernel id, detail, observed value}; see common.cuh.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GEEPS_MAX_RANKS 8
+
+enum GeepsTableMode { GEEPS_TABLE_ADDITIVE = 0, GEEPS_TABLE_SGD_MOMENTUM = 1 };
+
+// ---------------- row ops (row = 128 fp32) ----------------
+// index: array of {int64 id0, int64 id1} pairs ("double index": id0 = position in the
+// application buffer, id1 = position in the cache / oplog).
+int geeps_row_gather(float* dst, const float* src, const void* index, long long num_rows,
+                     long long dst_off, long long src_off, long long num_vals_limit,
+                     long long dst_rows, long long src_rows, int* status, void* stream);
+int geeps_row_scatter(float* dst, const float* src, const void* index, long long num_rows,
+                      long long dst_off, long long src_off, long long num_vals_limit,
+                      long long dst_rows, long long src_rows, int* status, void* stream);
+int geeps_row_scatter_add(float* dst, const float* src, const void* index, long long num_rows,
+                          long long dst_off, long long src_off, long long num_vals_limit,
+                          long long dst_rows, long long src_rows, int* status, void* stream);
+int geeps_axpy(float* y, const float* x, float alpha, long long n, void* stream);
+
+// ---------------- parameter-server fabric ----------------
+typedef struct GeepsPushApplyParams {
+  const float* upd[GEEPS_MAX_RANKS];   // each worker's update buffer (full-table layout)
+  float* cache[GEEPS_MAX_RANKS];       // each worker's fp32 parameter cache (full table) or NULL
+  void* cache16[GEEPS_MAX_RANKS];      // each worker's bf16 compute copy (full table) or NULL
+  int* data_age[GEEPS_MAX_RANKS];      // each worker's data_age[n_ranks] flag array or NULL
+  float* master;                       // this shard's rows, compact [n_owned][128]
+  float* momentum;                     // same shape; SGD tables only
+  const int* push_ready;               // local flags [n_ranks] written by the workers, or NULL
+  int* global_clock;                   // local flag: this shard applied clock_stamp (may be NULL)
+  int* cta_counter;                    // one zero-initialised int of scratch
+  int* status;                         // 4 ints or NULL
+  long long n_owned, row_start, row_stride, total_rows;
+  unsigned long long wait_budget_ns;
+  int n_ranks, rank, clock_stamp, mode, publish;
+  float lr, momentum_coef, weight_decay, grad_scale;
+} GeepsPushApplyParams;
+int geeps_ps_push_apply(const GeepsPushApplyParams* p, int max_ctas, void* stream);
+
+typedef struct GeepsPullParams {
+  const float* master[GEEPS_MAX_RANKS];  // each shard's compact master rows (peer pointers)
+  const int* global_clock[GEEPS_MAX_RANKS];  // each shard's applied-clock flag or NULL (no wait)
+  long long n_owned[GEEPS_MAX_RANKS], row_start[GEEPS_MAX_RANKS], row_stride[GEEPS_MAX_RANKS];
+  float* cache;        // local fp32 cache or NULL
+  void* cache16;       // local bf16 copy or NULL
+  int* data_age_local; // local data_age[n_ranks] or NULL
+  int* cta_counter;
+  int* status;
+  long long total_rows;
+  unsigned long long wait_budget_ns;
+  int n_ranks, rank, needed_stamp;
+} GeepsPullParams;
+int geeps_ps_pull(const GeepsPullParams* p, int max_ctas, void* stream);
+
+typedef struct GeepsFlagList { int* ptr[GEEPS_MAX_RANKS]; int n; } GeepsFlagList;
+int geeps_flag_signal(const GeepsFlagList* list, int index, int stamp, void* stream);
+int geeps_flag_wait(const int* flags, int n, int stamp, unsigned long long budget_ns, int* status,
+                    void* stream);
+int geeps_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+
+// ---------------- GEMM (bf16 x bf16 -> fp32 accumulate) ----------------
+// C[M,N] = alpha * A[M,K] * B[N,K]^T + beta * C + bias, optional ReLU.
+//   a_mn_major = 0: A is stored [M][lda] (K contiguous); 1: stored [K][lda] (M contiguous)
+//   b_mn_major = 0: B is stored [N][ldb] (K contiguous); 1: stored [K][ldb] (N contiguous)
+//   out_fp32   = 0: C is bf16; 1: C is fp32.   ldc in elements.
+//   bias_mode  = 0 none, 1 bias[n], 2 bias[m] (fp32)
+//   split_k > 1: partial sums are added into fp32 C with red.global.add (C must hold the
+//                beta-scaled initial value already; relu is not applied).
+typedef struct GeepsGemmParams {
+  const void* A; const void* B; void* C; const float* bias;
+  long long M, N, K, lda, ldb, ldc;
+  float alpha, beta;
+  int a_mn_major, b_mn_major, out_fp32, bias_mode, relu, split_k;
+  int block_n;     // 0 = auto, else 64 / 128 / 256
+  int* status;
+} GeepsGemmParams;
+int geeps_gemm_bf16(const GeepsGemmParams* p, void* stream);       // tcgen05 + TMA + TMEM
+int geeps_gemm_bf16_simt(const GeepsGemmParams* p, void* stream);  // plain SIMT fallback / cross-check
+int geeps_gemm_tc_supported(const GeepsGemmParams* p);             // 1 if the tcgen05 path accepts p
+// C[m][n] = beta * C[m][n] (exactly 0 when beta == 0) over an M x N view with pitch ldc
+int geeps_scale_matrix_f32(float* c, long long M, long long N, long long ldc, float beta, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,713 @@
+// Training ops around the tensor-core GEMM, all on NHWC bf16 activations with fp32
+// arithmetic: layout conversion, im2col / col2im (conv forward, data- and weight-gradient
+// run as GEMMs on the patch matrix), BatchNorm, ReLU, LRN, max / average pooling,
+// softmax cross-entropy, column sums (bias gradients) and dropout.
+//
+// The reference ships none of these (its Caffe application is an un-fetched submodule,
+// .gitmodules:1-4 of the reference); layer maths follows the usual Caffe definitions so that
+// the AlexNet / Inception-BN configurations behave as the originals did.
+#include "common.cuh"
+#include "nn_ops.h"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float bf(const bf16 v) { return __bfloat162float(v); }
+
+struct alignas(16) Bf8 { bf16 v[8]; };
+__device__ __forceinline__ Bf8 ld8(const bf16* p) { Bf8 r; *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p); return r; }
+__device__ __forceinline__ void st8(bf16* p, const Bf8& r) { *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r); }
+
+inline int grid_1d(long long n, int block = 256, int cap = 148 * 16) {
+  long long b = (n + block - 1) / block;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+// ---------------- layout conversion ----------------
+__global__ void __launch_bounds__(256)
+nchw_f32_to_nhwc_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int C, int H, int W, int Cpad) {
+  const long long total = (long long)B * H * W * Cpad;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % Cpad);
+    long long p = i / Cpad;
+    const int w = (int)(p % W); p /= W;
+    const int h = (int)(p % H);
+    const int b = (int)(p / H);
+    y[i] = c < C ? __float2bfloat16(x[(((long long)b * C + c) * H + h) * W + w]) : __float2bfloat16(0.f);
+  }
+}
+
+// ---------------- im2col / col2im (NHWC, one channel group) ----------------
+// col[(b,oh,ow)][(kh,kw,c)] = x[b][oh*s-p+kh][ow*s-p+kw][c0+c]; row pitch ldcol >= KH*KW*Cg.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, const GeepsConvGeom g) {
+  const int cv = g.Cg / VEC;
+  const long long per_row = (long long)g.KH * g.KW * cv;
+  const long long total = (long long)g.B * g.OH * g.OW * per_row;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long row = i / per_row;
+    int r = (int)(i % per_row);
+    const int c = (r % cv) * VEC; r /= cv;
+    const int kw = r % g.KW;
+    const int kh = r / g.KW;
+    long long p = row;
+    const int ow = (int)(p % g.OW); p /= g.OW;
+    const int oh = (int)(p % g.OH);
+    const int b = (int)(p / g.OH);
+    const int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
+    bf16* dst = col + row * g.ldcol + (long long)(kh * g.KW + kw) * g.Cg + c;
+    const bool in = ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
+    const bf16* src = x + (((long long)b * g.H + ih) * g.W + iw) * g.C + g.c0 + c;
+    if (VEC == 8) {
+      Bf8 v;
+      if (in) v = ld8(src); else *reinterpret_cast<uint4*>(&v) = make_uint4(0, 0, 0, 0);
+      st8(dst, v);
+    } else if (VEC == 4) {
+      uint2 v = in ? *reinterpret_cast<const uint2*>(src) : make_uint2(0, 0);
+      *reinterpret_cast<uint2*>(dst) = v;
+    } else {
+      *dst = in ? *src : __float2bfloat16(0.f);
+    }
+  }
+}
+
+// Zero the pad columns [Kd, ldcol) of the patch matrix once (TMA reads them as K).
+__global__ void zero_col_pad_kernel(bf16* col, long long rows, int kd, int ldcol) {
+  const int padw = ldcol - kd;
+  const long long total = rows * padw;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+    col[(i / padw) * ldcol + kd + (i % padw)] = __float2bfloat16(0.f);
+}
+
+// dx[b][ih][iw][c0+c] (+)= sum over (kh,kw) windows covering (ih,iw) of dcol[(b,oh,ow)][(kh,kw,c)]
+// Gather form: no atomics, deterministic.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+col2im_kernel(const bf16* __restrict__ dcol, bf16* __restrict__ dx, const GeepsConvGeom g, int accumulate) {
+  const int cv = g.Cg / VEC;
+  const long long total = (long long)g.B * g.H * g.W * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * VEC;
+    long long p = i / cv;
+    const int iw = (int)(p % g.W); p /= g.W;
+    const int ih = (int)(p % g.H);
+    const int b = (int)(p / g.H);
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      const int th = ih + g.pad - kh;
+      if (th < 0 || th % g.stride) continue;
+      const int oh = th / g.stride;
+      if (oh >= g.OH) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        const int tw = iw + g.pad - kw;
+        if (tw < 0 || tw % g.stride) continue;
+        const int ow = tw / g.stride;
+        if (ow >= g.OW) continue;
+        const bf16* src = dcol + (((long long)b * g.OH + oh) * g.OW + ow) * g.ldcol +
+                          (long long)(kh * g.KW + kw) * g.Cg + c;
+        if (VEC == 8) {
+          Bf8 v = ld8(src);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += bf(v.v[e]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[e] += bf(src[e]);
+        }
+      }
+    }
+    bf16* dst = dx + (((long long)b * g.H + ih) * g.W + iw) * g.C + g.c0 + c;
+    if (VEC == 8) {
+      Bf8 o;
+      if (accumulate) { Bf8 old = ld8(dst);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
+      st8(dst, o);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) dst[e] = __float2bfloat16(acc[e] + (accumulate ? bf(dst[e]) : 0.f));
+    }
+  }
+}
+
+// ---------------- per-channel reductions over a [P][C] (pitch ld) bf16 matrix ----------------
+// MODE 0: out[c] += sum x, out[C+c] += sum x^2                  (BN forward statistics)
+// MODE 1: out[c] += sum dy', out[C+c] += sum dy' * xhat          (BN backward; dy' = dy masked by y>0 if relu)
+// MODE 2: out[c] += scale * sum x                                (bias gradient)
+template <int MODE>
+__global__ void __launch_bounds__(256)
+channel_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                      const float* __restrict__ mean_rstd, float* __restrict__ out, long long P, int C,
+                      long long ldx, long long lddy, int relu, float scale) {
+  extern __shared__ float sacc[];  // [2*C]
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sacc[i] = 0.f;
+  __syncthreads();
+  const int cv = C >> 3;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long groups = nthreads / cv;  // pixel lanes: each owns one 8-channel slot
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid < groups * cv) {
+    const int c = (int)(tid % cv) * 8;
+    float a0[8], a1[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { a0[e] = 0.f; a1[e] = 0.f; }
+    float mu[8], rs[8];
+    if (MODE == 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { mu[e] = mean_rstd[c + e]; rs[e] = mean_rstd[C + c + e]; }
+    }
+    for (long long p = tid / cv; p < P; p += groups) {
+      if (MODE == 0 || MODE == 2) {
+        Bf8 v = ld8(x + p * ldx + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { float f = bf(v.v[e]); a0[e] += f; if (MODE == 0) a1[e] += f * f; }
+      } else {
+        Bf8 xv = ld8(x + p * ldx + c), dv = ld8(dy + p * lddy + c), yv;
+        if (relu) yv = ld8(y + p * lddy + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float d = bf(dv.v[e]);
+          if (relu && !(bf(yv.v[e]) > 0.f)) d = 0.f;
+          a0[e] += d;
+          a1[e] += d * (bf(xv.v[e]) - mu[e]) * rs[e];
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      atomicAdd(&sacc[c + e], a0[e]);
+      if (MODE != 2) atomicAdd(&sacc[C + c + e], a1[e]);
+    }
+  }
+  __syncthreads();
+  const int nout = MODE == 2 ? C : 2 * C;
+  for (int i = threadIdx.x; i < nout; i += blockDim.x) {
+    const float v = sacc[i];
+    if (v != 0.f) atomicAdd(out + i, MODE == 2 ? v * scale : v);
+  }
+}
+
+// any C, any pitch: one thread per column (small P: FC bias gradients with odd widths)
+__global__ void colsum_simple_kernel(const bf16* __restrict__ x, float* __restrict__ out, long long P, int C,
+                                     long long ldx, float scale, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float a = 0.f;
+  for (long long p = 0; p < P; ++p) a += bf(x[p * ldx + c]);
+  out[c] = a * scale + (accumulate ? out[c] : 0.f);
+}
+
+// sums -> mean / rstd (+ running statistics with Caffe-style moving average)
+__global__ void bn_finalize_kernel(const float* __restrict__ sums, float* __restrict__ mean_rstd,
+                                   float* running_mean, float* running_var, int C, float inv_count, float eps,
+                                   float momentum) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float m = sums[c] * inv_count;
+  float var = sums[C + c] * inv_count - m * m;
+  var = fmaxf(var, 0.f);
+  mean_rstd[c] = m;
+  mean_rstd[C + c] = rsqrtf(var + eps);
+  if (running_mean) {
+    running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * m;
+    running_var[c] = (1.f - momentum) * running_var[c] + momentum * var;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ mean_rstd,
+                const float* __restrict__ gamma, const float* __restrict__ beta, long long P, int C,
+                long long ldx, long long ldy, int relu) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long p = i / cv;
+    Bf8 v = ld8(x + p * ldx + c), o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float f = (bf(v.v[e]) - mean_rstd[c + e]) * mean_rstd[C + c + e] * gamma[c + e] + beta[c + e];
+      if (relu) f = fmaxf(f, 0.f);
+      o.v[e] = __float2bfloat16(f);
+    }
+    st8(y + p * ldy + c, o);
+  }
+}
+
+// dx = gamma * rstd * (dy' - sum_dy/P - xhat * sum_dy_xhat/P); also emits dgamma, dbeta (scaled).
+__global__ void __launch_bounds__(256)
+bn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                   bf16* __restrict__ dx, const float* __restrict__ mean_rstd, const float* __restrict__ gamma,
+                   const float* __restrict__ sums, float* dgamma, float* dbeta, long long P, int C,
+                   long long ldx, long long lddy, long long lddx, int relu, float grad_scale) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float invP = 1.f / (float)P;
+  const long long tid0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid0 < C) {
+    if (dbeta) dbeta[tid0] = sums[tid0] * grad_scale;
+    if (dgamma) dgamma[tid0] = sums[C + tid0] * grad_scale;
+  }
+  for (long long i = tid0; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long p = i / cv;
+    Bf8 xv = ld8(x + p * ldx + c), dv = ld8(dy + p * lddy + c), yv, o;
+    if (relu) yv = ld8(y + p * lddy + c);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float d = bf(dv.v[e]);
+      if (relu && !(bf(yv.v[e]) > 0.f)) d = 0.f;
+      const float rs = mean_rstd[C + c + e];
+      const float xhat = (bf(xv.v[e]) - mean_rstd[c + e]) * rs;
+      o.v[e] = __float2bfloat16(gamma[c + e] * rs * (d - sums[c + e] * invP - xhat * sums[C + c + e] * invP));
+    }
+    st8(dx + p * lddx + c, o);
+  }
+}
+
+// ---------------- ReLU backward / dropout ----------------
+__global__ void __launch_bounds__(256)
+relu_backward_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx, long long n8) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    Bf8 d = ld8(dy + i * 8), v = ld8(y + i * 8), o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o.v[e] = bf(v.v[e]) > 0.f ? d.v[e] : __float2bfloat16(0.f);
+    st8(dx + i * 8, o);
+  }
+}
+
+__device__ __forceinline__ uint32_t mix32(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return (uint32_t)((z ^ (z >> 31)) >> 32);
+}
+// y = x * keep(seed, idx) / (1 - p); the same call with dy as input gives dx.
+__global__ void __launch_bounds__(256)
+dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, float p, unsigned long long seed) {
+  const float inv = 1.f / (1.f - p);
+  const uint32_t thresh = (uint32_t)(p * 4294967296.0);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = mix32(seed * 0x100000001B3ull + (uint64_t)i) >= thresh ? __float2bfloat16(bf(x[i]) * inv) : __float2bfloat16(0.f);
+}
+
+// ---------------- LRN across channels ----------------
+__global__ void __launch_bounds__(256)
+lrn_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __restrict__ scale, long long P, int C,
+                   int size, float alpha, float beta, float k) {
+  const long long total = P * C;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int half = size / 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % C);
+    const bf16* row = x + (i - c);
+    float s = 0.f;
+    const int lo = max(0, c - half), hi = min(C - 1, c + half);
+    for (int j = lo; j <= hi; ++j) { float f = bf(row[j]); s += f * f; }
+    const float sc = k + alpha / (float)size * s;
+    scale[i] = sc;
+    y[i] = __float2bfloat16(bf(row[c]) * __powf(sc, -beta));
+  }
+}
+__global__ void __launch_bounds__(256)
+lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ scale,
+                    const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
+                    float beta) {
+  const long long total = P * C;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int half = size / 2;
+  const float coef = 2.f * alpha * beta / (float)size;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % C);
+    const long long base = i - c;
+    float acc = 0.f;
+    const int lo = max(0, c - half), hi = min(C - 1, c + half);
+    for (int j = lo; j <= hi; ++j) acc += bf(dy[base + j]) * bf(y[base + j]) / scale[base + j];
+    dx[i] = __float2bfloat16(bf(dy[i]) * __powf(scale[i], -beta) - coef * bf(x[i]) * acc);
+  }
+}
+
+// ---------------- pooling (NHWC, 8 channels per thread) ----------------
+// Output may be a channel slice of a wider tensor (pitch ldy, offset applied by the caller).
+__global__ void __launch_bounds__(256)
+maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ argmax,
+                       const GeepsPoolGeom g) {
+  const int cv = g.C >> 3;
+  const long long total = (long long)g.B * g.OH * g.OW * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    long long p = i / cv;
+    const int ow = (int)(p % g.OW); p /= g.OW;
+    const int oh = (int)(p % g.OH);
+    const int b = (int)(p / g.OH);
+    float best[8]; int arg[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { best[e] = -3.0e38f; arg[e] = 255; }
+    for (int kh = 0; kh < g.K; ++kh) {
+      const int ih = oh * g.stride - g.pad + kh;
+      if (ih < 0 || ih >= g.H) continue;
+      for (int kw = 0; kw < g.K; ++kw) {
+        const int iw = ow * g.stride - g.pad + kw;
+        if (iw < 0 || iw >= g.W) continue;
+        Bf8 v = ld8(x + (((long long)b * g.H + ih) * g.W + iw) * g.ldx + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { float f = bf(v.v[e]); if (f > best[e]) { best[e] = f; arg[e] = kh * g.K + kw; } }
+      }
+    }
+    const long long opix = ((long long)b * g.OH + oh) * g.OW + ow;
+    Bf8 o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(best[e]);
+    st8(y + opix * g.ldy + c, o);
+    uint2 pk;
+    pk.x = (uint32_t)arg[0] | ((uint32_t)arg[1] << 8) | ((uint32_t)arg[2] << 16) | ((uint32_t)arg[3] << 24);
+    pk.y = (uint32_t)arg[4] | ((uint32_t)arg[5] << 8) | ((uint32_t)arg[6] << 16) | ((uint32_t)arg[7] << 24);
+    *reinterpret_cast<uint2*>(argmax + opix * g.C + c) = pk;
+  }
+}
+__global__ void __launch_bounds__(256)
+maxpool_backward_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ argmax, bf16* __restrict__ dx,
+                        const GeepsPoolGeom g, int accumulate) {
+  const int cv = g.C >> 3;
+  const long long total = (long long)g.B * g.H * g.W * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    long long p = i / cv;
+    const int iw = (int)(p % g.W); p /= g.W;
+    const int ih = (int)(p % g.H);
+    const int b = (int)(p / g.H);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int kh = 0; kh < g.K; ++kh) {
+      const int th = ih + g.pad - kh;
+      if (th < 0 || th % g.stride) continue;
+      const int oh = th / g.stride;
+      if (oh >= g.OH) continue;
+      for (int kw = 0; kw < g.K; ++kw) {
+        const int tw = iw + g.pad - kw;
+        if (tw < 0 || tw % g.stride) continue;
+        const int ow = tw / g.stride;
+        if (ow >= g.OW) continue;
+        const long long opix = ((long long)b * g.OH + oh) * g.OW + ow;
+        const uint2 pk = *reinterpret_cast<const uint2*>(argmax + opix * g.C + c);
+        Bf8 d = ld8(dy + opix * g.ldy + c);
+        const int code = kh * g.K + kw;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int a = (int)(((e < 4 ? pk.x : pk.y) >> ((e & 3) * 8)) & 0xff);
+          if (a == code) acc[e] += bf(d.v[e]);
+        }
+      }
+    }
+    bf16* dst = dx + (((long long)b * g.H + ih) * g.W + iw) * g.ldx + c;
+    Bf8 o;
+    if (accumulate) { Bf8 old = ld8(dst);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
+    st8(dst, o);
+  }
+}
+
+// Caffe average pooling: divisor is the window area clipped to the padded extent.
+__device__ __forceinline__ int avg_area(int o, int stride, int pad, int K, int size) {
+  const int s = o * stride - pad;
+  const int e = min(s + K, size + pad);
+  return e - s;
+}
+__global__ void __launch_bounds__(256)
+avgpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const GeepsPoolGeom g) {
+  const int cv = g.C >> 3;
+  const long long total = (long long)g.B * g.OH * g.OW * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    long long p = i / cv;
+    const int ow = (int)(p % g.OW); p /= g.OW;
+    const int oh = (int)(p % g.OH);
+    const int b = (int)(p / g.OH);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int kh = 0; kh < g.K; ++kh) {
+      const int ih = oh * g.stride - g.pad + kh;
+      if (ih < 0 || ih >= g.H) continue;
+      for (int kw = 0; kw < g.K; ++kw) {
+        const int iw = ow * g.stride - g.pad + kw;
+        if (iw < 0 || iw >= g.W) continue;
+        Bf8 v = ld8(x + (((long long)b * g.H + ih) * g.W + iw) * g.ldx + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += bf(v.v[e]);
+      }
+    }
+    const float inv = 1.f / (float)(avg_area(oh, g.stride, g.pad, g.K, g.H) * avg_area(ow, g.stride, g.pad, g.K, g.W));
+    Bf8 o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e] * inv);
+    st8(y + (((long long)b * g.OH + oh) * g.OW + ow) * g.ldy + c, o);
+  }
+}
+__global__ void __launch_bounds__(256)
+avgpool_backward_kernel(const bf16* __restrict__ dy, bf16* __restrict__ dx, const GeepsPoolGeom g, int accumulate) {
+  const int cv = g.C >> 3;
+  const long long total = (long long)g.B * g.H * g.W * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    long long p = i / cv;
+    const int iw = (int)(p % g.W); p /= g.W;
+    const int ih = (int)(p % g.H);
+    const int b = (int)(p / g.H);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int kh = 0; kh < g.K; ++kh) {
+      const int th = ih + g.pad - kh;
+      if (th < 0 || th % g.stride) continue;
+      const int oh = th / g.stride;
+      if (oh >= g.OH) continue;
+      for (int kw = 0; kw < g.K; ++kw) {
+        const int tw = iw + g.pad - kw;
+        if (tw < 0 || tw % g.stride) continue;
+        const int ow = tw / g.stride;
+        if (ow >= g.OW) continue;
+        const float inv = 1.f / (float)(avg_area(oh, g.stride, g.pad, g.K, g.H) * avg_area(ow, g.stride, g.pad, g.K, g.W));
+        Bf8 d = ld8(dy + (((long long)b * g.OH + oh) * g.OW + ow) * g.ldy + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += bf(d.v[e]) * inv;
+      }
+    }
+    bf16* dst = dx + (((long long)b * g.H + ih) * g.W + iw) * g.ldx + c;
+    Bf8 o;
+    if (accumulate) { Bf8 old = ld8(dst);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
+    st8(dst, o);
+  }
+}
+
+// ---------------- softmax cross-entropy (one CTA per sample) ----------------
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float t = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, t) : v + t;
+  }
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    v = lane < (int)(blockDim.x >> 5) ? sh[lane] : (is_max ? -3.0e38f : 0.f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float t = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, t) : v + t;
+    }
+    if (lane == 0) sh[0] = v;
+  }
+  __syncthreads();
+  return sh[0];
+}
+// loss_sum += -log softmax(logits[b])[label[b]] * loss_scale;  dlogits = (softmax - onehot) * grad_scale
+__global__ void __launch_bounds__(256)
+softmax_ce_kernel(const float* __restrict__ logits, const long long* __restrict__ labels, float* loss_sum,
+                  float* __restrict__ per_sample, bf16* __restrict__ dlogits, int C, long long ldl, long long ldd,
+                  float loss_scale, float grad_scale, int* status) {
+  __shared__ float sh[32];
+  const int b = blockIdx.x;
+  const float* row = logits + (long long)b * ldl;
+  float mx = -3.0e38f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) mx = fmaxf(mx, row[c]);
+  mx = block_reduce(mx, true, sh);
+  float s = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) s += __expf(row[c] - mx);
+  s = block_reduce(s, false, sh);
+  long long lab = labels[b];
+  if (lab < 0 || lab >= C) {
+    if (threadIdx.x == 0) geeps_report(status, GEEPS_ERR_BOUNDS, 30, b, (int)lab);
+    lab = 0;
+  }
+  const float inv = 1.f / s;
+  if (dlogits != nullptr) {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float pr = __expf(row[c] - mx) * inv;
+      dlogits[(long long)b * ldd + c] = __float2bfloat16((pr - (c == lab ? 1.f : 0.f)) * grad_scale);
+    }
+  }
+  if (threadIdx.x == 0) {
+    const float l = -(row[lab] - mx - __logf(s));
+    if (per_sample) per_sample[b] = l;
+    if (loss_sum) atomicAdd(loss_sum, l * loss_scale);
+  }
+}
+
+}  // namespace
+
+#define CK() ((int)cudaGetLastError())
+
+extern "C" {
+
+int geeps_nchw_f32_to_nhwc_bf16(const float* x, void* y, int B, int C, int H, int W, int Cpad, void* stream) {
+  const long long n = (long long)B * H * W * Cpad;
+  nchw_f32_to_nhwc_bf16_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H, W, Cpad);
+  return CK();
+}
+
+int geeps_im2col(const void* x, void* col, const GeepsConvGeom* g, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long rows = (long long)g->B * g->OH * g->OW;
+  const int kd = g->KH * g->KW * g->Cg;
+  if (g->ldcol > kd)
+    zero_col_pad_kernel<<<grid_1d(rows * (g->ldcol - kd)), 256, 0, st>>>((bf16*)col, rows, kd, g->ldcol);
+  const bool a8 = (g->Cg % 8 == 0) && (g->C % 8 == 0) && (g->c0 % 8 == 0) && (g->ldcol % 8 == 0);
+  const bool a4 = (g->Cg % 4 == 0) && (g->C % 4 == 0) && (g->c0 % 4 == 0) && (g->ldcol % 4 == 0);
+  if (a8) im2col_kernel<8><<<grid_1d(rows * g->KH * g->KW * (g->Cg / 8)), 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
+  else if (a4) im2col_kernel<4><<<grid_1d(rows * g->KH * g->KW * (g->Cg / 4)), 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
+  else im2col_kernel<1><<<grid_1d(rows * kd), 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
+  return CK();
+}
+
+int geeps_col2im(const void* dcol, void* dx, const GeepsConvGeom* g, int accumulate, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long pix = (long long)g->B * g->H * g->W;
+  const bool a8 = (g->Cg % 8 == 0) && (g->C % 8 == 0) && (g->c0 % 8 == 0) && (g->ldcol % 8 == 0);
+  if (a8) col2im_kernel<8><<<grid_1d(pix * (g->Cg / 8)), 256, 0, st>>>((const bf16*)dcol, (bf16*)dx, *g, accumulate);
+  else col2im_kernel<1><<<grid_1d(pix * g->Cg), 256, 0, st>>>((const bf16*)dcol, (bf16*)dx, *g, accumulate);
+  return CK();
+}
+
+static int reduce_grid(long long P, int C) {
+  long long want = (P * (C / 8) + 255) / 256;
+  if (want > 148 * 4) want = 148 * 4;
+  long long min_blocks = ((long long)(C / 8) + 255) / 256;
+  if (want < min_blocks) want = min_blocks;
+  return (int)(want < 1 ? 1 : want);
+}
+
+int geeps_bn_forward(const void* x, void* y, const float* gamma, const float* beta, float* sums,
+                     float* mean_rstd, float* running_mean, float* running_var, long long P, int C,
+                     long long ldx, long long ldy, float eps, float momentum, int relu, void* stream) {
+  if (C % 8) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st);
+  channel_reduce_kernel<0><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
+      (const bf16*)x, nullptr, nullptr, nullptr, sums, P, C, ldx, 0, 0, 1.f);
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, mean_rstd, running_mean, running_var, C,
+                                                      1.f / (float)P, eps, momentum);
+  bn_apply_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (bf16*)y, mean_rstd, gamma, beta, P, C, ldx,
+                                                        ldy, relu);
+  return CK();
+}
+
+int geeps_bn_backward(const void* x, const void* dy, const void* y, void* dx, const float* mean_rstd,
+                      const float* gamma, float* sums, float* dgamma, float* dbeta, long long P, int C,
+                      long long ldx, long long lddy, long long lddx, int relu, float grad_scale, void* stream) {
+  if (C % 8) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st);
+  channel_reduce_kernel<1><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
+      (const bf16*)x, (const bf16*)dy, (const bf16*)y, mean_rstd, sums, P, C, ldx, lddy, relu, 1.f);
+  bn_backward_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y,
+                                                           (bf16*)dx, mean_rstd, gamma, sums, dgamma, dbeta, P, C,
+                                                           ldx, lddy, lddx, relu, grad_scale);
+  return CK();
+}
+
+int geeps_colsum(const void* x, float* out, long long P, int C, long long ldx, float scale, int zero_first,
+                 void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((C % 8) || (ldx % 8) || C > 4096) {
+    colsum_simple_kernel<<<(C + 127) / 128, 128, 0, st>>>((const bf16*)x, out, P, C, ldx, scale, !zero_first);
+    return CK();
+  }
+  if (zero_first) cudaMemsetAsync(out, 0, sizeof(float) * C, st);
+  channel_reduce_kernel<2><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
+      (const bf16*)x, nullptr, nullptr, nullptr, out, P, C, ldx, 0, 0, scale);
+  return CK();
+}
+
+int geeps_relu_backward(const void* dy, const void* y, void* dx, long long n, void* stream) {
+  if (n % 8) return (int)cudaErrorInvalidValue;
+  relu_backward_kernel<<<grid_1d(n / 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)y, (bf16*)dx, n / 8);
+  return CK();
+}
+
+int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream) {
+  dropout_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, p, seed);
+  return CK();
+}
+
+int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, int size, float alpha, float beta,
+                      float k, void* stream) {
+  lrn_forward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, scale, P, C, size,
+                                                                      alpha, beta, k);
+  return CK();
+}
+int geeps_lrn_backward(const void* x, const void* y, const float* scale, const void* dy, void* dx, long long P,
+                       int C, int size, float alpha, float beta, void* stream) {
+  lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, scale,
+                                                                       (const bf16*)dy, (bf16*)dx, P, C, size, alpha,
+                                                                       beta);
+  return CK();
+}
+
+int geeps_maxpool_forward(const void* x, void* y, void* argmax, const GeepsPoolGeom* g, void* stream) {
+  if (g->C % 8 || g->ldx % 8 || g->ldy % 8 || g->K * g->K > 255) return (int)cudaErrorInvalidValue;
+  const long long n = (long long)g->B * g->OH * g->OW * (g->C / 8);
+  maxpool_forward_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, (uint8_t*)argmax, *g);
+  return CK();
+}
+int geeps_maxpool_backward(const void* dy, const void* argmax, void* dx, const GeepsPoolGeom* g, int accumulate,
+                           void* stream) {
+  if (g->C % 8 || g->ldx % 8 || g->ldy % 8) return (int)cudaErrorInvalidValue;
+  const long long n = (long long)g->B * g->H * g->W * (g->C / 8);
+  maxpool_backward_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const uint8_t*)argmax,
+                                                                       (bf16*)dx, *g, accumulate);
+  return CK();
+}
+int geeps_avgpool_forward(const void* x, void* y, const GeepsPoolGeom* g, void* stream) {
+  if (g->C % 8 || g->ldx % 8 || g->ldy % 8) return (int)cudaErrorInvalidValue;
+  const long long n = (long long)g->B * g->OH * g->OW * (g->C / 8);
+  avgpool_forward_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, *g);
+  return CK();
+}
+int geeps_avgpool_backward(const void* dy, void* dx, const GeepsPoolGeom* g, int accumulate, void* stream) {
+  if (g->C % 8 || g->ldx % 8 || g->ldy % 8) return (int)cudaErrorInvalidValue;
+  const long long n = (long long)g->B * g->H * g->W * (g->C / 8);
+  avgpool_backward_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (bf16*)dx, *g, accumulate);
+  return CK();
+}
+
+int geeps_softmax_ce(const float* logits, const long long* labels, float* loss_sum, float* per_sample,
+                     void* dlogits, int B, int C, long long ldl, long long ldd, float loss_scale, float grad_scale,
+                     int zero_loss, int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (zero_loss && loss_sum) cudaMemsetAsync(loss_sum, 0, sizeof(float), st);
+  softmax_ce_kernel<<<B, 256, 0, st>>>(logits, labels, loss_sum, per_sample, (bf16*)dlogits, C, ldl, ldd, loss_scale,
+                                       grad_scale, status);
+  return CK();
+}
+
+}  // extern "C"

@@ -1,0 +1,53 @@
+// C ABI of the training-op kernels (NHWC bf16 activations, fp32 parameters and
+// statistics).  Same calling conventions as kernels.h.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct GeepsConvGeom {
+  int B, H, W, C;       // input tensor [B][H][W][C]
+  int c0, Cg;           // channel group [c0, c0+Cg) taken by this call
+  int KH, KW, stride, pad, OH, OW;
+  int ldcol;            // row pitch of the patch matrix, >= KH*KW*Cg, multiple of 8
+} GeepsConvGeom;
+
+typedef struct GeepsPoolGeom {
+  int B, H, W, C, K, stride, pad, OH, OW;
+  int ldx, ldy;         // channel pitch of input / output pixels (>= C; concat slices)
+} GeepsPoolGeom;
+
+int geeps_nchw_f32_to_nhwc_bf16(const float* x, void* y, int B, int C, int H, int W, int Cpad, void* stream);
+int geeps_im2col(const void* x, void* col, const GeepsConvGeom* g, void* stream);
+int geeps_col2im(const void* dcol, void* dx, const GeepsConvGeom* g, int accumulate, void* stream);
+
+// sums: 2*C floats of scratch; mean_rstd: 2*C floats saved for backward.
+int geeps_bn_forward(const void* x, void* y, const float* gamma, const float* beta, float* sums,
+                     float* mean_rstd, float* running_mean, float* running_var, long long P, int C,
+                     long long ldx, long long ldy, float eps, float momentum, int relu, void* stream);
+int geeps_bn_backward(const void* x, const void* dy, const void* y, void* dx, const float* mean_rstd,
+                      const float* gamma, float* sums, float* dgamma, float* dbeta, long long P, int C,
+                      long long ldx, long long lddy, long long lddx, int relu, float grad_scale, void* stream);
+// out[c] (+)= scale * sum_p x[p][c]
+int geeps_colsum(const void* x, float* out, long long P, int C, long long ldx, float scale, int zero_first,
+                 void* stream);
+int geeps_relu_backward(const void* dy, const void* y, void* dx, long long n, void* stream);
+int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream);
+int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, int size, float alpha, float beta,
+                      float k, void* stream);
+int geeps_lrn_backward(const void* x, const void* y, const float* scale, const void* dy, void* dx, long long P,
+                       int C, int size, float alpha, float beta, void* stream);
+int geeps_maxpool_forward(const void* x, void* y, void* argmax, const GeepsPoolGeom* g, void* stream);
+int geeps_maxpool_backward(const void* dy, const void* argmax, void* dx, const GeepsPoolGeom* g, int accumulate,
+                           void* stream);
+int geeps_avgpool_forward(const void* x, void* y, const GeepsPoolGeom* g, void* stream);
+int geeps_avgpool_backward(const void* dy, void* dx, const GeepsPoolGeom* g, int accumulate, void* stream);
+int geeps_softmax_ce(const float* logits, const long long* labels, float* loss_sum, float* per_sample,
+                     void* dlogits, int B, int C, long long ldl, long long ldd, float loss_scale, float grad_scale,
+                     int zero_loss, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

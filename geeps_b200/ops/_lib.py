@@ -1,0 +1,113 @@
+"""ctypes view of the native kernel ABI (csrc/kernels/kernels.h, nn_ops.h)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native
+
+MAX_RANKS = 8
+TABLE_ADDITIVE = 0
+TABLE_SGD_MOMENTUM = 1
+
+STATUS_CODES = {0: "ok", 1: "timeout", 2: "bounds", 3: "align"}
+
+
+class GemmParams(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("bias", C.c_void_p),
+        ("M", C.c_longlong), ("N", C.c_longlong), ("K", C.c_longlong),
+        ("lda", C.c_longlong), ("ldb", C.c_longlong), ("ldc", C.c_longlong),
+        ("alpha", C.c_float), ("beta", C.c_float),
+        ("a_mn_major", C.c_int), ("b_mn_major", C.c_int), ("out_fp32", C.c_int),
+        ("bias_mode", C.c_int), ("relu", C.c_int), ("split_k", C.c_int),
+        ("block_n", C.c_int), ("status", C.c_void_p),
+    ]
+
+
+class PushApplyParams(C.Structure):
+    _fields_ = [
+        ("upd", C.c_void_p * MAX_RANKS), ("cache", C.c_void_p * MAX_RANKS),
+        ("cache16", C.c_void_p * MAX_RANKS), ("data_age", C.c_void_p * MAX_RANKS),
+        ("master", C.c_void_p), ("momentum", C.c_void_p), ("push_ready", C.c_void_p),
+        ("global_clock", C.c_void_p), ("cta_counter", C.c_void_p), ("status", C.c_void_p),
+        ("n_owned", C.c_longlong), ("row_start", C.c_longlong), ("row_stride", C.c_longlong),
+        ("total_rows", C.c_longlong), ("wait_budget_ns", C.c_ulonglong),
+        ("n_ranks", C.c_int), ("rank", C.c_int), ("clock_stamp", C.c_int), ("mode", C.c_int),
+        ("publish", C.c_int),
+        ("lr", C.c_float), ("momentum_coef", C.c_float), ("weight_decay", C.c_float),
+        ("grad_scale", C.c_float),
+    ]
+
+
+class PullParams(C.Structure):
+    _fields_ = [
+        ("master", C.c_void_p * MAX_RANKS), ("global_clock", C.c_void_p * MAX_RANKS),
+        ("n_owned", C.c_longlong * MAX_RANKS), ("row_start", C.c_longlong * MAX_RANKS),
+        ("row_stride", C.c_longlong * MAX_RANKS),
+        ("cache", C.c_void_p), ("cache16", C.c_void_p), ("data_age_local", C.c_void_p),
+        ("cta_counter", C.c_void_p), ("status", C.c_void_p),
+        ("total_rows", C.c_longlong), ("wait_budget_ns", C.c_ulonglong),
+        ("n_ranks", C.c_int), ("rank", C.c_int), ("needed_stamp", C.c_int),
+    ]
+
+
+class FlagList(C.Structure):
+    _fields_ = [("ptr", C.c_void_p * MAX_RANKS), ("n", C.c_int)]
+
+
+class ConvGeom(C.Structure):
+    _fields_ = [(n, C.c_int) for n in
+                ("B", "H", "W", "C", "c0", "Cg", "KH", "KW", "stride", "pad", "OH", "OW", "ldcol")]
+
+
+class PoolGeom(C.Structure):
+    _fields_ = [(n, C.c_int) for n in
+                ("B", "H", "W", "C", "K", "stride", "pad", "OH", "OW", "ldx", "ldy")]
+
+
+_lib = None
+_launches = 0
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = _native.load()
+    return _lib
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise RuntimeError("geeps_b200 kernels need a CUDA device (sm_100a); none is visible")
+
+
+def stream_ptr(stream=None) -> C.c_void_p:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def ptr(t) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def check(err: int, what: str) -> None:
+    global _launches
+    _launches += 1
+    if err != 0:
+        raise RuntimeError(f"{what}: CUDA launch error {err}")
+
+
+def launch_count() -> int:
+    """Number of native kernel-launching calls made by this process so far."""
+    return _launches
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def read_status(status: torch.Tensor) -> dict:
+    s = status.tolist()
+    return {"code": s[0], "name": STATUS_CODES.get(s[0], "?"), "kernel": s[1], "detail": s[2], "seen": s[3]}

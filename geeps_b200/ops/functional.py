@@ -1,0 +1,211 @@
+"""Functional wrappers: one Python function per native kernel, on torch tensors.
+
+Activations are NHWC bf16 (2-D views [pixels, channels] with a channel pitch), parameters
+and statistics fp32.  Nothing here falls back to a torch implementation: without the
+native library or without a GPU these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+from ._lib import ConvGeom, GemmParams, PoolGeom, check, lib, ptr, stream_ptr
+
+bf16 = torch.bfloat16
+
+
+def _ld(t: torch.Tensor) -> int:
+    """Row pitch (elements) of a 2-D tensor whose last dim is contiguous."""
+    assert t.dim() == 2 and (t.stride(1) == 1 or t.shape[1] == 1), "need a row-major 2-D view"
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         bias: torch.Tensor | None = None, bias_mode: int = 1, relu: bool = False, alpha: float = 1.0,
+         beta: float = 0.0, split_k: int = 1, block_n: int = 0, status: torch.Tensor | None = None,
+         impl: str = "auto") -> torch.Tensor:
+    """out[M,N] = alpha * A[M,K] @ B[N,K]^T + beta*out + bias  (bf16 operands, fp32 accumulate).
+
+    a_mn / b_mn: the operand is stored transposed ([K, M] / [K, N] row-major).
+    out is bf16 or fp32 and may be a column slice of a wider matrix.
+    impl: "auto" (tcgen05 when the layout allows, else SIMT), "tc", or "simt".
+    """
+    L.require_cuda()
+    assert a.dtype == bf16 and b.dtype == bf16 and out.dtype in (bf16, torch.float32)
+    M, N = out.shape
+    K = a.shape[0] if a_mn else a.shape[1]
+    assert (a.shape == (K, M)) if a_mn else (a.shape == (M, K)), (a.shape, M, K, a_mn)
+    assert (b.shape == (K, N)) if b_mn else (b.shape == (N, K)), (b.shape, N, K, b_mn)
+    p = GemmParams()
+    p.A, p.B, p.C, p.bias = a.data_ptr(), b.data_ptr(), out.data_ptr(), (bias.data_ptr() if bias is not None else None)
+    p.M, p.N, p.K = M, N, K
+    p.lda, p.ldb, p.ldc = _ld(a), _ld(b), _ld(out)
+    p.alpha, p.beta = alpha, beta
+    p.a_mn_major, p.b_mn_major = int(a_mn), int(b_mn)
+    p.out_fp32 = int(out.dtype == torch.float32)
+    p.bias_mode = bias_mode if bias is not None else 0
+    p.relu = int(relu)
+    p.split_k = split_k
+    p.block_n = block_n
+    p.status = status.data_ptr() if status is not None else None
+    if bias is not None:
+        assert bias.dtype == torch.float32
+    use_tc = impl == "tc" or (impl == "auto" and lib().geeps_gemm_tc_supported(C.byref(p)))
+    if use_tc:
+        check(lib().geeps_gemm_bf16(C.byref(p), stream_ptr()), "gemm_bf16(tcgen05)")
+    else:
+        if split_k != 1:
+            p.split_k = 1
+        check(lib().geeps_gemm_bf16_simt(C.byref(p), stream_ptr()), "gemm_bf16(simt)")
+    return out
+
+
+def nchw_to_nhwc_bf16(x: torch.Tensor, cpad: int | None = None) -> torch.Tensor:
+    L.require_cuda()
+    B, Cc, H, W = x.shape
+    cpad = cpad or Cc
+    y = torch.empty((B, H, W, cpad), dtype=bf16, device=x.device)
+    check(lib().geeps_nchw_f32_to_nhwc_bf16(ptr(x), ptr(y), B, Cc, H, W, cpad, stream_ptr()), "nchw_to_nhwc")
+    return y
+
+
+def conv_geom(x_shape, c0: int, cg: int, kh: int, kw: int, stride: int, pad: int, ldcol: int) -> ConvGeom:
+    B, H, W, Cc = x_shape
+    g = ConvGeom()
+    g.B, g.H, g.W, g.C, g.c0, g.Cg = B, H, W, Cc, c0, cg
+    g.KH, g.KW, g.stride, g.pad = kh, kw, stride, pad
+    g.OH = (H + 2 * pad - kh) // stride + 1
+    g.OW = (W + 2 * pad - kw) // stride + 1
+    g.ldcol = ldcol
+    return g
+
+
+def im2col(x: torch.Tensor, col: torch.Tensor, g: ConvGeom) -> None:
+    check(lib().geeps_im2col(ptr(x), ptr(col), C.byref(g), stream_ptr()), "im2col")
+
+
+def col2im(dcol: torch.Tensor, dx: torch.Tensor, g: ConvGeom, accumulate: bool = False) -> None:
+    check(lib().geeps_col2im(ptr(dcol), ptr(dx), C.byref(g), int(accumulate), stream_ptr()), "col2im")
+
+
+def bn_forward(x2d, y2d, gamma, beta, sums, mean_rstd, running_mean, running_var, eps=1e-5, momentum=0.1,
+               relu=False) -> None:
+    P, Cc = x2d.shape
+    check(lib().geeps_bn_forward(ptr(x2d), ptr(y2d), ptr(gamma), ptr(beta), ptr(sums), ptr(mean_rstd),
+                                 ptr(running_mean), ptr(running_var), C.c_longlong(P), Cc,
+                                 C.c_longlong(_ld(x2d)), C.c_longlong(_ld(y2d)), C.c_float(eps),
+                                 C.c_float(momentum), int(relu), stream_ptr()), "bn_forward")
+
+
+def bn_backward(x2d, dy2d, y2d, dx2d, mean_rstd, gamma, sums, dgamma, dbeta, relu=False, grad_scale=1.0) -> None:
+    P, Cc = x2d.shape
+    check(lib().geeps_bn_backward(ptr(x2d), ptr(dy2d), ptr(y2d), ptr(dx2d), ptr(mean_rstd), ptr(gamma), ptr(sums),
+                                  ptr(dgamma), ptr(dbeta), C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)),
+                                  C.c_longlong(_ld(dy2d)), C.c_longlong(_ld(dx2d)), int(relu),
+                                  C.c_float(grad_scale), stream_ptr()), "bn_backward")
+
+
+def colsum(x2d, out, scale=1.0, zero_first=True) -> None:
+    P, Cc = x2d.shape
+    check(lib().geeps_colsum(ptr(x2d), ptr(out), C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)), C.c_float(scale),
+                             int(zero_first), stream_ptr()), "colsum")
+
+
+def relu_backward(dy, y, dx) -> None:
+    assert dy.is_contiguous() and y.is_contiguous() and dx.is_contiguous()
+    check(lib().geeps_relu_backward(ptr(dy), ptr(y), ptr(dx), C.c_longlong(dy.numel()), stream_ptr()), "relu_backward")
+
+
+def dropout(x, y, p: float, seed: int) -> None:
+    assert x.is_contiguous() and y.is_contiguous()
+    check(lib().geeps_dropout(ptr(x), ptr(y), C.c_longlong(x.numel()), C.c_float(p), C.c_ulonglong(seed),
+                              stream_ptr()), "dropout")
+
+
+def lrn_forward(x2d, y2d, scale, size=5, alpha=1e-4, beta=0.75, k=1.0) -> None:
+    P, Cc = x2d.shape
+    assert x2d.is_contiguous() and y2d.is_contiguous()
+    check(lib().geeps_lrn_forward(ptr(x2d), ptr(y2d), ptr(scale), C.c_longlong(P), Cc, size, C.c_float(alpha),
+                                  C.c_float(beta), C.c_float(k), stream_ptr()), "lrn_forward")
+
+
+def lrn_backward(x2d, y2d, scale, dy2d, dx2d, size=5, alpha=1e-4, beta=0.75) -> None:
+    P, Cc = x2d.shape
+    check(lib().geeps_lrn_backward(ptr(x2d), ptr(y2d), ptr(scale), ptr(dy2d), ptr(dx2d), C.c_longlong(P), Cc, size,
+                                   C.c_float(alpha), C.c_float(beta), stream_ptr()), "lrn_backward")
+
+
+def pool_geom(x_shape, k: int, stride: int, pad: int, ldx: int, ldy: int, ceil_mode: bool = True) -> PoolGeom:
+    B, H, W, Cc = x_shape
+    g = PoolGeom()
+    g.B, g.H, g.W, g.C, g.K, g.stride, g.pad = B, H, W, Cc, k, stride, pad
+
+    def osz(n):
+        num = n + 2 * pad - k
+        o = (-(-num // stride) if ceil_mode else num // stride) + 1
+        if pad > 0 and (o - 1) * stride >= n + pad:
+            o -= 1
+        return o
+
+    g.OH, g.OW = osz(H), osz(W)
+    g.ldx, g.ldy = ldx, ldy
+    return g
+
+
+def maxpool_forward(x, y, argmax, g: PoolGeom) -> None:
+    check(lib().geeps_maxpool_forward(ptr(x), ptr(y), ptr(argmax), C.byref(g), stream_ptr()), "maxpool_forward")
+
+
+def maxpool_backward(dy, argmax, dx, g: PoolGeom, accumulate=False) -> None:
+    check(lib().geeps_maxpool_backward(ptr(dy), ptr(argmax), ptr(dx), C.byref(g), int(accumulate), stream_ptr()),
+          "maxpool_backward")
+
+
+def avgpool_forward(x, y, g: PoolGeom) -> None:
+    check(lib().geeps_avgpool_forward(ptr(x), ptr(y), C.byref(g), stream_ptr()), "avgpool_forward")
+
+
+def avgpool_backward(dy, dx, g: PoolGeom, accumulate=False) -> None:
+    check(lib().geeps_avgpool_backward(ptr(dy), ptr(dx), C.byref(g), int(accumulate), stream_ptr()), "avgpool_backward")
+
+
+def softmax_ce(logits, labels, loss_sum, dlogits, per_sample=None, loss_scale=1.0, grad_scale=1.0, zero_loss=True,
+               status=None) -> None:
+    B, Cc = logits.shape
+    assert logits.dtype == torch.float32 and labels.dtype == torch.int64
+    check(lib().geeps_softmax_ce(ptr(logits), ptr(labels), ptr(loss_sum), ptr(per_sample), ptr(dlogits), B, Cc,
+                                 C.c_longlong(_ld(logits)), C.c_longlong(_ld(dlogits) if dlogits is not None else 0),
+                                 C.c_float(loss_scale), C.c_float(grad_scale), int(zero_loss), ptr(status),
+                                 stream_ptr()), "softmax_ce")
+
+
+def f32_to_bf16(src, dst) -> None:
+    check(lib().geeps_f32_to_bf16(ptr(src), ptr(dst), C.c_longlong(src.numel()), stream_ptr()), "f32_to_bf16")
+
+
+def axpy(y, x, alpha: float) -> None:
+    check(lib().geeps_axpy(ptr(y), ptr(x), C.c_float(alpha), C.c_longlong(y.numel()), stream_ptr()), "axpy")
+
+
+def _row_op(fn, name, dst, src, index, dst_off, src_off, num_vals_limit, status):
+    n = index.shape[0]
+    lim = num_vals_limit if num_vals_limit is not None else (1 << 62)
+    check(fn(ptr(dst), ptr(src), ptr(index), C.c_longlong(n), C.c_longlong(dst_off), C.c_longlong(src_off),
+             C.c_longlong(lim), C.c_longlong(dst.shape[0]), C.c_longlong(src.shape[0]), ptr(status), stream_ptr()), name)
+
+
+def row_gather(dst, src, index, dst_off=0, src_off=0, num_vals_limit=None, status=None) -> None:
+    """dst[id0 + dst_off] = src[id1 + src_off] for each (id0, id1) in index (int64 [n,2])."""
+    _row_op(lib().geeps_row_gather, "row_gather", dst, src, index, dst_off, src_off, num_vals_limit, status)
+
+
+def row_scatter(dst, src, index, dst_off=0, src_off=0, num_vals_limit=None, status=None) -> None:
+    """dst[id1 + dst_off] = src[id0 + src_off]."""
+    _row_op(lib().geeps_row_scatter, "row_scatter", dst, src, index, dst_off, src_off, num_vals_limit, status)
+
+
+def row_scatter_add(dst, src, index, dst_off=0, src_off=0, num_vals_limit=None, status=None) -> None:
+    """dst[id1 + dst_off] += src[id0 + src_off]."""
+    _row_op(lib().geeps_row_scatter_add, "row_scatter_add", dst, src, index, dst_off, src_off, num_vals_limit, status)
