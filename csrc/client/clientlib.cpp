@@ -1,0 +1,380 @@
+// ClientLib: construction, communication bring-up, foreground access calls.
+#include "clientlib.hpp"
+
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <unistd.h>
+
+#include <fstream>
+
+namespace geeps_b200 {
+
+// ---------------- OpMemBufferPool ----------------
+void OpMemBufferPool::init(size_t entries, size_t rows, MemType type) {
+  std::lock_guard<std::mutex> lk(mu_);
+  all_.clear();
+  free_.clear();
+  for (size_t i = 0; i < entries; ++i) {
+    all_.emplace_back(new FlatOps());
+    all_.back()->data.init(rows, type);
+    free_.push_back(all_.back().get());
+  }
+}
+
+FlatOps* OpMemBufferPool::get(size_t budget_ms) {
+  std::unique_lock<std::mutex> lk(mu_);
+  const double t0 = now_seconds();
+  while (free_.empty()) {
+    if (cv_.wait_for(lk, std::chrono::seconds(kWatchdogSeconds)) == std::cv_status::timeout)
+      fprintf(stderr, "[geeps] oplog pool: all %zu entries in flight, still waiting\n", all_.size());
+    if (budget_ms && (now_seconds() - t0) * 1000.0 > (double)budget_ms) return nullptr;
+  }
+  FlatOps* e = free_.front();
+  free_.erase(free_.begin());
+  return e;
+}
+
+void OpMemBufferPool::put(FlatOps* e) {
+  { std::lock_guard<std::mutex> lk(mu_); e->flag = FlatOps::NONE; e->clock = -1; free_.push_back(e); }
+  cv_.notify_all();
+}
+
+// ---------------- construction ----------------
+ClientLib::ClientLib(uint process_id, const GeePsConfig& config) : process_id_(process_id), config_(config) {
+  num_processes_ = config.num_workers_override > 0 ? (uint)config.num_workers_override
+                                                   : (uint)(config.host_list.empty() ? 1 : config.host_list.size());
+  gpu_ = config.device == GeePsConfig::DEVICE_CUDA && Mem::cuda_available();
+  if (config.device == GeePsConfig::DEVICE_CUDA && !gpu_)
+    fprintf(stderr, "[geeps] no CUDA device visible: caches and staging live in host memory\n");
+  nvlink_ = gpu_ && config.transport == GeePsConfig::TRANSPORT_NVLINK;
+  if (config.transport == GeePsConfig::TRANSPORT_NVLINK && !gpu_)
+    set_error(ERR_TRANSPORT, "NVLINK transport needs a CUDA device");
+  if (gpu_) {
+    if (config.cuda_device >= 0) cudaSetDevice(config.cuda_device);
+    cudaStream_t s0, s1;
+    cudaStreamCreateWithFlags(&s0, cudaStreamNonBlocking);
+    cudaStreamCreateWithFlags(&s1, cudaStreamNonBlocking);
+    default_stream_ = s0;
+    swap_stream_ = s1;
+  }
+  PlanConfig pc;
+  pc.gpu_memory_capacity = config.gpu_memory_capacity;
+  pc.mm_warning_level = config.mm_warning_level;
+  pc.read_my_writes = config.read_my_writes;
+  pc.num_shards = (int)num_processes_;
+  pc.partitioner = config.partitioner;
+  pc.num_tables = config.num_tables;
+  pc.device_is_gpu = gpu_;
+  pc.allow_direct = nvlink_;
+  pc.update_ring = nvlink_;
+  compiler_.reset(new PlanCompiler(pc));
+  last_heartbeat_.assign(num_processes_, now_seconds());
+  peer_clock_.assign(num_processes_, 0);
+  peer_dead_.assign(num_processes_, 0);
+  std::string err;
+  if (!init_comm(&err)) set_error(ERR_TRANSPORT, err);
+}
+
+ClientLib::~ClientLib() {
+  shutdown();
+  for (void* p : op_index_dev_) if (p) cudaFree(p);
+  for (auto& kv : tables_)
+    for (ShardRows& sr : kv.second->shards) if (sr.gpu_index_dev) cudaFree(sr.gpu_index_dev);
+  fabric_teardown();
+  if (default_stream_) cudaStreamDestroy((cudaStream_t)default_stream_);
+  if (swap_stream_) cudaStreamDestroy((cudaStream_t)swap_stream_);
+}
+
+void ClientLib::set_error(int code, const std::string& what) {
+  int expected = 0;
+  if (error_code_.compare_exchange_strong(expected, code)) {
+    std::lock_guard<std::mutex> lk(error_mu_);
+    error_text_ = what;
+    fprintf(stderr, "[geeps worker %u] error %d: %s\n", process_id_, code, what.c_str());
+  }
+  // wake every host-side waiter so that it can observe the error
+  for (auto& kv : tables_) kv.second->cv.notify_all();
+  global_cv_.notify_all();
+}
+
+std::string ClientLib::last_error_string() {
+  std::lock_guard<std::mutex> lk(error_mu_);
+  return error_text_;
+}
+
+bool ClientLib::init_comm(std::string* err) {
+  // every process hosts a server shard (channel 0 carries the control plane as well)
+  server_.reset(new ServerThreadEntry(0, config_.num_comm_channels, process_id_, num_processes_, config_));
+  if (!server_->start(err)) return false;
+  ClientLib* self = this;
+  server_->decoder()->control_hook = [self](const std::string& src, Message& msg) {
+    switch (msg[0].cmd()) {
+      case CMD_HEARTBEAT: { heartbeat_msg_t h; if (msg[0].unpack(&h)) self->heartbeat_cbk(h.id, h.counter, h.clock); break; }
+      case CMD_BARRIER: { barrier_msg_t h; if (msg[0].unpack(&h)) self->barrier_cbk(h.id, h.epoch); break; }
+      case CMD_IPC_EXCHANGE: self->ipc_exchange_cbk(msg); break;
+      case CMD_PEER_LOST: self->peer_lost_cbk(src); break;
+      default: break;
+    }
+  };
+  router_.reset(new RouterHandler("client-" + std::to_string(process_id_)));
+  if (config_.local_opt) {
+    router_->set_local_peer(server_->router().get());
+    server_->router()->set_local_peer(router_.get());
+  }
+  for (uint s = 0; s < num_processes_; ++s) {
+    if (config_.local_opt && s == process_id_) continue;
+    const std::string host = s < config_.host_list.size() ? config_.host_list[s] : "127.0.0.1";
+    const unsigned port = ServerThreadEntry::port_for(config_, s, 0);
+    if (!router_->connect_to("tablet-" + std::to_string(s), host, port, 60000, err)) return false;
+  }
+  encoder_.reset(new ClientServerEncode(router_, num_processes_, process_id_, config_));
+  decoder_.reset(new ServerClientDecode(this));
+  ServerClientDecode* dec = decoder_.get();
+  router_->start_handler_thread([dec](const std::string& src, Message& msg) { dec->router_callback(src, msg); });
+  const uint nch = config_.num_comm_channels ? config_.num_comm_channels : 1;
+  for (uint c = 0; c < nch; ++c) {
+    bg_workers_.emplace_back(new BackgroundWorker());
+    bg_workers_.back()->add_callback(kIterateCmd, [self](std::vector<char>& args) { self->cbk_iterate(args); });
+    bg_workers_.back()->start();
+  }
+  if (num_processes_ > 1) heartbeat_thread_ = std::thread([self] { self->heartbeat_loop(); });
+  return true;
+}
+
+void ClientLib::shutdown() {
+  if (shut_down_) return;
+  shut_down_ = true;
+  if (gpu_) cudaDeviceSynchronize();
+  for (auto& w : bg_workers_) w->stop();
+  // leave together: a rank that tears its sockets down early would look like a failure to the rest
+  if (num_processes_ > 1 && error_code_.load() == 0) host_barrier(10000);
+  stop_heartbeat_ = true;
+  if (heartbeat_thread_.joinable()) heartbeat_thread_.join();
+  if (router_) router_->stop_handler_thread();
+  if (server_) server_->stop();
+}
+
+// ---------------- virtual iteration (recording) ----------------
+int ClientLib::virtual_read_batch(size_t table, const std::vector<size_t>& rows, int slack) {
+  OpInfo op; op.type = OP_READ; op.table = table; op.rows = rows; op.slack = slack;
+  return compiler_->record(op);
+}
+int ClientLib::virtual_postread_batch(int prestep) {
+  OpInfo op; op.type = OP_POST_READ; op.prestep = prestep;
+  return compiler_->record(op);
+}
+int ClientLib::virtual_preupdate_batch(size_t table, const std::vector<size_t>& rows) {
+  OpInfo op; op.type = OP_PRE_UPDATE; op.table = table; op.rows = rows;
+  return compiler_->record(op);
+}
+int ClientLib::virtual_update_batch(int prestep) {
+  OpInfo op; op.type = OP_UPDATE; op.prestep = prestep;
+  return compiler_->record(op);
+}
+int ClientLib::virtual_localaccess_batch(const std::vector<size_t>& rows, bool fetch) {
+  OpInfo op; op.type = OP_LOCAL_ACCESS; op.table = kLocalTableId; op.rows = rows; op.local = true; op.fetch = fetch;
+  return compiler_->record(op);
+}
+int ClientLib::virtual_postlocalaccess_batch(int prestep, bool keep) {
+  OpInfo op; op.type = OP_POST_LOCAL_ACCESS; op.prestep = prestep; op.local = true; op.keep = keep;
+  return compiler_->record(op);
+}
+int ClientLib::virtual_clock() {
+  OpInfo op; op.type = OP_CLOCK;
+  return compiler_->record(op);
+}
+
+// ---------------- foreground access ----------------
+bool ClientLib::check_order(int handle, OpType want) {
+  if (!vi_finished_ || handle < 0 || handle >= (int)plan_.ops.size() || plan_.ops[handle].type != want) {
+    set_error(ERR_ORDER, "handle " + std::to_string(handle) + " is not a valid handle for this call");
+    return false;
+  }
+  if (started_ && !plan_.ops[handle].one_off) {
+    // after StartIterations the calls must come in exactly the declared order
+    if (handle != last_handle_ + 1) {
+      set_error(ERR_ORDER, "call with handle " + std::to_string(handle) + " after handle " +
+                               std::to_string(last_handle_) + " breaks the declared order");
+      return false;
+    }
+    last_handle_ = handle;
+  }
+  return true;
+}
+
+RowData* ClientLib::staging_ptr(const OpInfo& op) {
+  const size_t copy = plan_.staging_copies > 1 ? (size_t)(clock_ & 1) : 0;
+  return thread_cache_.at(copy * plan_.staging_rows + op.staging_offset);
+}
+
+bool ClientLib::read_batch(int handle, RowData** buf, void* stream, bool async) {
+  const double t0 = now_seconds();
+  *buf = nullptr;
+  if (!check_order(handle, OP_READ)) return false;
+  const OpInfo& op = plan_.ops[handle];
+  void* st = op_stream(stream);
+  bool ok = true;
+  if (nvlink_) {
+    CachedTable& ct = *tables_[(uint)op.table];
+    fabric_wait_data_age(ct, (uint)op.table, clock_ - op.slack - 1, st);
+    if (op.direct) {
+      *buf = reinterpret_cast<RowData*>(fabric_cache_ptr((uint)op.table, (int)process_id_)) + op.store_offset;
+    } else {
+      *buf = staging_ptr(op);
+      ok = read_row_batch_param_cache(op, *buf, st);
+    }
+    if (!async) { cudaStreamSynchronize((cudaStream_t)st); ok = fabric_check_status(true) && ok; }
+  } else {
+    *buf = staging_ptr(op);
+    ok = read_row_batch_param_cache(op, *buf, st);
+  }
+  accessed_clock_[handle] = clock_;
+  stats_.nr_read++;
+  stats_.rows_read += op.rows.size();
+  stats_.read_time += now_seconds() - t0;
+  return ok && error_code_.load() == 0;
+}
+
+void* ClientLib::read_bf16(int handle) {
+  if (!nvlink_ || !config_.bf16_compute_cache || handle < 0 || handle >= (int)plan_.ops.size()) return nullptr;
+  const OpInfo& op = plan_.ops[handle];
+  if (op.type != OP_READ || !op.direct) return nullptr;
+  const TableArena& ta = fabric_.tables[op.table];
+  return fabric_.base + ta.cache16_off + op.store_offset * (size_t)kRowFloats * 2;
+}
+
+void ClientLib::postread_batch(int handle) { postread_batch(handle, nullptr); }
+
+void ClientLib::postread_batch(int handle, void* stream) {
+  const double t0 = now_seconds();
+  if (!check_order(handle, OP_POST_READ)) return;
+  swap_release(plan_.ops[handle].prestep, op_stream(stream), false);
+  stats_.nr_postread++;
+  stats_.postread_time += now_seconds() - t0;
+}
+
+void ClientLib::preupdate_batch(int handle, RowOpVal** buf, void* stream) {
+  const double t0 = now_seconds();
+  *buf = nullptr;
+  if (!check_order(handle, OP_PRE_UPDATE)) return;
+  const OpInfo& op = plan_.ops[handle];
+  if (nvlink_) {
+    // the ring slot of this clock is free again once every shard consumed clock - (slack+1):
+    // the same condition a read of this clock waits for
+    CachedTable& ct = *tables_[(uint)op.table];
+    fabric_wait_data_age(ct, (uint)op.table, clock_ - ct.plan->slack - 1, op_stream(stream));
+    if (ct.has_indirect_updates && ct.ring_zeroed_clock != clock_) {
+      // staged updates are accumulated into the ring slot: it has to start the clock at zero
+      cudaMemsetAsync(fabric_ring_ptr((uint)op.table, (int)process_id_, clock_), 0, ct.plan->rows.size() * kRowBytes,
+                      (cudaStream_t)op_stream(stream));
+      ct.ring_zeroed_clock = clock_;
+    }
+    if (op.direct) {
+      *buf = reinterpret_cast<RowOpVal*>(fabric_ring_ptr((uint)op.table, (int)process_id_, clock_)) + op.store_offset;
+      stats_.nr_preupdate++;
+      stats_.preupdate_time += now_seconds() - t0;
+      return;
+    }
+  }
+  *buf = staging_ptr(op);
+  accessed_clock_[handle] = clock_;
+  stats_.nr_preupdate++;
+  stats_.preupdate_time += now_seconds() - t0;
+}
+
+void ClientLib::update_batch(int handle, void* stream, bool async) {
+  const double t0 = now_seconds();
+  if (!check_order(handle, OP_UPDATE)) return;
+  const OpInfo& op = plan_.ops[handle];
+  const OpInfo& pre = plan_.ops[op.prestep];
+  void* st = op_stream(stream);
+  if (!pre.direct) { update_batch_param_cache(pre, staging_ptr(pre), st); swap_release(op.prestep, st, false); }
+  stats_.nr_update++;
+  stats_.rows_updated += pre.rows.size();
+  // after StartIterations the last write of a table in the clock signals that table's clock at
+  // once, so its push overlaps the rest of the iteration; during bootstrap Clock() signals all
+  if (started_ && op.table_last_write) clock_table(clock_, (uint)op.table, false, false);
+  if (nvlink_ && !async && started_ && op.table_last_write) { /* device work stays queued; errors surface in Clock */ }
+  (void)st;
+  stats_.update_time += now_seconds() - t0;
+}
+
+bool ClientLib::localaccess_batch(int handle, RowData** buf, void* stream) {
+  const double t0 = now_seconds();
+  *buf = nullptr;
+  if (!check_order(handle, OP_LOCAL_ACCESS)) return false;
+  const OpInfo& op = plan_.ops[handle];
+  if (op.direct) {
+    *buf = (op.location == LOC_GPU ? local_.gpu.data() : local_.cpu.data()) + op.store_offset;
+  } else {
+    *buf = staging_ptr(op);
+    accessed_clock_[handle] = clock_;
+    if (op.fetch) read_batch_local(op, *buf, op_stream(stream));
+  }
+  stats_.nr_localaccess++;
+  stats_.localaccess_time += now_seconds() - t0;
+  return true;
+}
+
+void ClientLib::postlocalaccess_batch(int handle, void* stream) {
+  const double t0 = now_seconds();
+  if (!check_order(handle, OP_POST_LOCAL_ACCESS)) return;
+  const OpInfo& op = plan_.ops[handle];
+  const OpInfo& pre = plan_.ops[op.prestep];
+  if (!pre.direct) {
+    if (op.keep) update_batch_local(pre, staging_ptr(pre), op_stream(stream));
+    else swap_release(op.prestep, op_stream(stream), false);
+  }
+  stats_.localaccess_time += now_seconds() - t0;
+}
+
+void ClientLib::start_opseq() {
+  if (!vi_finished_) { set_error(ERR_ORDER, "StartIterations before FinishVirtualIteration"); return; }
+  started_ = true;
+  last_handle_ = -1;
+}
+
+void ClientLib::iterate() {
+  const double t0 = now_seconds();
+  if (!vi_finished_) { set_error(ERR_ORDER, "Clock before FinishVirtualIteration"); return; }
+  if (started_ && last_handle_ != plan_.clock_handle - 1)
+    set_error(ERR_ORDER, "Clock called before all declared accesses of the iteration");
+  if (!started_) clock_all(clock_, clock_ == kInitialClock);   // bootstrap: signal every table now
+  clock_++;
+  last_handle_ = -1;
+  stats_.nr_clock++;
+  if (nvlink_) fabric_check_status();
+  if (config_.snapshot_interval > 0 && !config_.snapshot_dir.empty() && clock_ % config_.snapshot_interval == 0)
+    save_snapshot(config_.snapshot_dir);
+  if (config_.log_interval > 0 && clock_ % config_.log_interval == 0)
+    fprintf(stderr, "[geeps worker %u] clock %d stats %s\n", process_id_, clock_, stats_.to_json().c_str());
+  stats_.clock_time += now_seconds() - t0;
+}
+
+std::string ClientLib::json_stats() {
+  // ask the co-located shard for its counters and wait (bounded) for the reply
+  {
+    std::lock_guard<std::mutex> lk(global_mu_);
+    server_stats_.erase(process_id_);
+  }
+  if (encoder_) encoder_->get_stats(process_id_);
+  std::string server_json = "{}";
+  {
+    std::unique_lock<std::mutex> lk(global_mu_);
+    global_cv_.wait_for(lk, std::chrono::seconds(5), [&] { return server_stats_.count(process_id_) > 0; });
+    if (server_stats_.count(process_id_)) server_json = server_stats_[process_id_];
+  }
+  std::string out = "{\"process_id\":" + std::to_string(process_id_) + ",\"clock\":" + std::to_string(clock_) +
+                    ",\"transport\":\"" + (nvlink_ ? "nvlink" : "tcp") + "\",\"device\":\"" + (gpu_ ? "cuda" : "cpu") +
+                    "\",\"client\":" + stats_.to_json() + ",\"bgthread\":" + bg_stats_.to_json() +
+                    ",\"router\":" + (router_ ? router_->stats.to_json() : std::string("{}")) +
+                    ",\"server_router\":" + (server_ ? server_->router()->stats.to_json() : std::string("{}")) +
+                    ",\"server\":" + server_json + "}";
+  if (!config_.output_dir.empty()) {
+    std::ofstream f(config_.output_dir + "/json_stats." + std::to_string(process_id_), std::ios::app);
+    f << out << "\n";
+  }
+  return out;
+}
+
+}  // namespace geeps_b200

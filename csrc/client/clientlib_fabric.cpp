@@ -1,0 +1,243 @@
+// ClientLib NVLINK transport: every rank owns one device arena with the same layout (parameter
+// cache, bf16 compute copy, update ring, shard master + momentum, clock flags per table), maps the
+// other ranks' arenas through CUDA IPC (handles travel over the TCP control plane), and drives the
+// sm_100a push / apply / publish kernels of kernels/ps_fabric.cu.
+//
+// This path replaces, per clock and table, the reference's D2H + ZeroMQ push
+// (src/client/clientlib-data.cpp:436-522), the host apply (src/server/tablet-server.cpp:119-134), the
+// whole-shard broadcast (src/server/tablet-server.cpp:147-163) and the pinned-bounce install
+// (src/client/clientlib-data.cpp:110-151).  Peer memory is only touched with plain loads/stores and
+// flag words; no TMA and no multicast object is involved.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+#include <unistd.h>
+
+#include "clientlib.hpp"
+#include "kernels/kernels.h"
+
+namespace geeps_b200 {
+
+namespace {
+struct IpcBlob {
+  uint32_t pid;
+  int32_t device;
+  cudaIpcMemHandle_t handle;
+  uint64_t raw_ptr;
+  uint64_t bytes;
+};
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+constexpr size_t kFlagBytes = 256;
+constexpr size_t kPushReadyOff = 0, kDataAgeOff = 32, kGlobalClockOff = 64, kCtaCounterOff = 68;
+}  // namespace
+
+float* ClientLib::fabric_cache_ptr(uint table_id, int rank) const {
+  return reinterpret_cast<float*>(fabric_.peer_base[rank] + fabric_.tables[table_id].cache_off);
+}
+
+float* ClientLib::fabric_ring_ptr(uint table_id, int rank, iter_t clock) const {
+  const TableArena& ta = fabric_.tables[table_id];
+  const size_t slot = (size_t)(clock % ta.ring_slots);
+  return reinterpret_cast<float*>(fabric_.peer_base[rank] + ta.ring_off + slot * ta.rows * kRowBytes);
+}
+
+bool ClientLib::fabric_setup(std::string* err) {
+  // ---- layout (identical on every rank: it only depends on the plan) ----
+  size_t off = 0;
+  fabric_.tables.assign(config_.num_tables, TableArena());
+  for (auto& kv : plan_.tables) {
+    const TablePlan& tp = kv.second;
+    TableArena& ta = fabric_.tables[tp.table_id];
+    ta.rows = tp.rows.size();
+    ta.ring_slots = tp.num_oplog_entries;
+    for (const ShardRange& r : tp.shard_ranges) ta.max_owned = std::max(ta.max_owned, r.count);
+    ta.cache_off = off; off = align_up(off + ta.rows * kRowBytes, 256);
+    if (config_.bf16_compute_cache) { ta.cache16_off = off; off = align_up(off + ta.rows * kRowBytes / 2, 256); }
+    ta.ring_off = off; off = align_up(off + (size_t)ta.ring_slots * ta.rows * kRowBytes, 256);
+    ta.master_off = off; off = align_up(off + ta.max_owned * kRowBytes, 256);
+    ta.momentum_off = off; off = align_up(off + ta.max_owned * kRowBytes, 256);
+    ta.flags_off = off; off += kFlagBytes;
+  }
+  fabric_.status_off = off;
+  off += 256;
+  fabric_.bytes = off;
+  void* base = nullptr;
+  cudaError_t e = cudaMalloc(&base, fabric_.bytes);
+  if (e != cudaSuccess) { *err = std::string("arena cudaMalloc: ") + cudaGetErrorString(e); cudaGetLastError(); return false; }
+  cudaMemset(base, 0, fabric_.bytes);
+  cudaDeviceSynchronize();
+  fabric_.base = static_cast<char*>(base);
+  fabric_.peer_base.assign(num_processes_, nullptr);
+  fabric_.peer_base[process_id_] = fabric_.base;
+
+  // ---- exchange arena handles over the control plane ----
+  if (num_processes_ > 1) {
+    IpcBlob mine;
+    memset(&mine, 0, sizeof(mine));
+    mine.pid = (uint32_t)getpid();
+    cudaGetDevice(&mine.device);
+    mine.raw_ptr = (uint64_t)(uintptr_t)base;
+    mine.bytes = fabric_.bytes;
+    e = cudaIpcGetMemHandle(&mine.handle, base);
+    if (e != cudaSuccess) { *err = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e); cudaGetLastError(); return false; }
+    std::vector<char> blob(sizeof(mine));
+    memcpy(blob.data(), &mine, sizeof(mine));
+    encoder_->ipc_exchange(blob);
+    {
+      std::unique_lock<std::mutex> lk(global_mu_);
+      const bool got = global_cv_.wait_for(lk, std::chrono::seconds(120), [&] {
+        return ipc_blobs_.size() >= num_processes_ || error_code_.load() != 0;
+      });
+      if (!got || error_code_.load()) { *err = "timed out exchanging arena handles with the other ranks"; return false; }
+    }
+    for (uint r = 0; r < num_processes_; ++r) {
+      if (r == process_id_) continue;
+      IpcBlob theirs;
+      {
+        std::lock_guard<std::mutex> lk(global_mu_);
+        if (ipc_blobs_[r].size() != sizeof(IpcBlob)) { *err = "bad arena handle from rank " + std::to_string(r); return false; }
+        memcpy(&theirs, ipc_blobs_[r].data(), sizeof(theirs));
+      }
+      if (theirs.bytes != fabric_.bytes) { *err = "rank " + std::to_string(r) + " compiled a different plan"; return false; }
+      if (theirs.pid == mine.pid) {
+        // ranks living in one process (threads): plain pointers, peer access enabled explicitly
+        if (theirs.device != mine.device) {
+          cudaError_t pe = cudaDeviceEnablePeerAccess(theirs.device, 0);
+          if (pe != cudaSuccess && pe != cudaErrorPeerAccessAlreadyEnabled) {
+            *err = std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(pe);
+            cudaGetLastError();
+            return false;
+          }
+          cudaGetLastError();
+        }
+        fabric_.peer_base[r] = reinterpret_cast<char*>((uintptr_t)theirs.raw_ptr);
+      } else {
+        void* p = nullptr;
+        e = cudaIpcOpenMemHandle(&p, theirs.handle, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) { *err = std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e); cudaGetLastError(); return false; }
+        fabric_.peer_base[r] = static_cast<char*>(p);
+      }
+    }
+    if (!host_barrier(120000) || error_code_.load()) { *err = "barrier after arena mapping failed"; return false; }
+  }
+  cudaStream_t cs;
+  cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
+  fabric_.comm_stream = cs;
+  cudaHostAlloc(reinterpret_cast<void**>(&fabric_.host_status), 4 * sizeof(int), cudaHostAllocDefault);
+  memset(fabric_.host_status, 0, 4 * sizeof(int));
+  fabric_.active = true;
+  return true;
+}
+
+void ClientLib::fabric_teardown() {
+  if (!fabric_.base) return;
+  cudaDeviceSynchronize();
+  const uint32_t pid = (uint32_t)getpid();
+  for (uint r = 0; r < num_processes_; ++r) {
+    if (r == process_id_ || !fabric_.peer_base[r]) continue;
+    bool same_process = false;
+    {
+      std::lock_guard<std::mutex> lk(global_mu_);
+      if (ipc_blobs_[r].size() == sizeof(IpcBlob)) {
+        IpcBlob b;
+        memcpy(&b, ipc_blobs_[r].data(), sizeof(b));
+        same_process = b.pid == pid;
+      }
+    }
+    if (!same_process) cudaIpcCloseMemHandle(fabric_.peer_base[r]);
+  }
+  if (fabric_.comm_stream) cudaStreamDestroy((cudaStream_t)fabric_.comm_stream);
+  if (fabric_.host_status) cudaFreeHost(fabric_.host_status);
+  cudaFree(fabric_.base);
+  fabric_.base = nullptr;
+  fabric_.active = false;
+}
+
+// Device-side SSP wait: the stream stalls (bounded) until every shard stamped data_age >= needed+1.
+void ClientLib::fabric_wait_data_age(CachedTable& ct, uint table_id, iter_t needed_age, void* stream) {
+  const iter_t stamp = needed_age + 1;
+  if (stamp <= 0 || stamp <= ct.waited_stamp) return;
+  const TableArena& ta = fabric_.tables[table_id];
+  const int* flags = reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kDataAgeOff);
+  geeps_flag_wait(flags, (int)num_processes_, stamp, (unsigned long long)config_.device_wait_budget_us * 1000ull,
+                  reinterpret_cast<int*>(fabric_.base + fabric_.status_off), stream);
+  ct.waited_stamp = stamp;
+}
+
+// Push of (clock, table): announce "my update is complete" to every shard on the application's
+// stream, then - on the comm stream - wait for all workers' announcements and run the fused
+// reduce + apply + publish kernel for the rows this rank owns.
+void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* stream) {
+  CachedTable& ct = *tables_[table_id];
+  const TableArena& ta = fabric_.tables[table_id];
+  const int stamp = clock + 1;
+  int* status = reinterpret_cast<int*>(fabric_.base + fabric_.status_off);
+  if (!withhold_push_signal_) {
+    GeepsFlagList list;
+    memset(&list, 0, sizeof(list));
+    list.n = (int)num_processes_;
+    for (uint r = 0; r < num_processes_; ++r)
+      list.ptr[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kPushReadyOff);
+    geeps_flag_signal(&list, (int)process_id_, stamp, stream);
+  }
+  void* cs = fabric_.comm_stream;
+  const unsigned long long budget = (unsigned long long)config_.device_wait_budget_us * 1000ull;
+  geeps_flag_wait(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_, stamp,
+                  budget, status, cs);
+  GeepsPushApplyParams p;
+  memset(&p, 0, sizeof(p));
+  for (uint r = 0; r < num_processes_; ++r) {
+    p.upd[r] = fabric_ring_ptr(table_id, (int)r, clock);
+    p.cache[r] = fabric_cache_ptr(table_id, (int)r);
+    p.cache16[r] = config_.bf16_compute_cache ? (void*)(fabric_.peer_base[r] + ta.cache16_off) : nullptr;
+    p.data_age[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kDataAgeOff);
+  }
+  const ShardRange& own = ct.plan->shard_ranges[process_id_];
+  p.master = reinterpret_cast<float*>(fabric_.base + ta.master_off);
+  p.momentum = reinterpret_cast<float*>(fabric_.base + ta.momentum_off);
+  p.push_ready = nullptr;   // already awaited by the one-warp wait kernel above, which occupies no SM worth of CTAs
+  p.global_clock = reinterpret_cast<int*>(fabric_.base + ta.flags_off + kGlobalClockOff);
+  p.cta_counter = reinterpret_cast<int*>(fabric_.base + ta.flags_off + kCtaCounterOff);
+  p.status = status;
+  p.n_owned = (long long)own.count;
+  p.row_start = (long long)own.start;
+  p.row_stride = (long long)own.stride;
+  p.total_rows = (long long)ta.rows;
+  p.wait_budget_ns = budget;
+  p.n_ranks = (int)num_processes_;
+  p.rank = (int)process_id_;
+  p.clock_stamp = stamp;
+  p.mode = is_init ? GEEPS_TABLE_ADDITIVE : ct.mode;
+  p.publish = 1;
+  p.lr = config_.learning_rate;
+  p.momentum_coef = config_.momentum;
+  p.weight_decay = config_.weight_decay;
+  p.grad_scale = config_.grad_scale;
+  geeps_ps_push_apply(&p, 0, cs);
+  bg_stats_.nr_push++;
+  bg_stats_.bytes_pushed += ta.rows * kRowBytes;
+}
+
+// Errors recorded by kernels (expired waits, failed bounds checks) surface here.  The device block
+// is mirrored into pinned memory asynchronously, so a problem is seen at most one clock late
+// without ever synchronising the streams.
+bool ClientLib::fabric_check_status(bool sync) {
+  if (!fabric_.active) return true;
+  bool ok = true;
+  if (sync)   // the caller has synchronised the streams: read the block itself
+    cudaMemcpy(fabric_.host_status, fabric_.base + fabric_.status_off, 4 * sizeof(int), cudaMemcpyDeviceToHost);
+  if (fabric_.host_status[0] != 0) {
+    ok = false;
+    const int code = fabric_.host_status[0];
+    if (code == 1) stats_.device_wait_timeouts++;
+    set_error(code == 1 ? ERR_DEVICE_TIMEOUT : ERR_CUDA,
+              std::string(code == 1 ? "device-side wait expired" : "device-side check failed") + " (kernel " +
+                  std::to_string(fabric_.host_status[1]) + ", detail " + std::to_string(fabric_.host_status[2]) +
+                  ", seen " + std::to_string(fabric_.host_status[3]) + ")");
+  }
+  cudaMemcpyAsync(fabric_.host_status, fabric_.base + fabric_.status_off, 4 * sizeof(int), cudaMemcpyDeviceToHost,
+                  (cudaStream_t)fabric_.comm_stream);
+  return ok;
+}
+
+}  // namespace geeps_b200

@@ -1,0 +1,222 @@
+"""Python binding of the native parameter-server runtime (the C++ GeePs class).
+
+Method names follow the C++ API (include/geeps.hpp) in snake_case.  Buffers handed out by
+read / pre_update / local_access are returned as tensors that alias the runtime's memory:
+device memory on a CUDA worker, host memory on a CPU worker.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+
+import numpy as np
+import torch
+
+from .. import _native
+from ..utils.config import DEVICE_CUDA, GeePsConfig
+
+ROW_FLOATS = 128
+
+ERRORS = {0: "none", 1: "plan", 2: "order", 3: "host_timeout", 4: "device_timeout", 5: "peer_lost",
+          6: "protocol", 7: "transport", 8: "memory", 9: "cuda", 10: "snapshot"}
+
+
+class GeePsError(RuntimeError):
+    def __init__(self, code: int, text: str):
+        super().__init__(f"geeps error {code} ({ERRORS.get(code, '?')}): {text}")
+        self.code = code
+
+
+class _CudaView:
+    """Minimal __cuda_array_interface__ carrier so torch can alias runtime-owned device memory."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _lib():
+    lib = _native.load()
+    if not getattr(lib, "_geeps_ps_typed", False):
+        lib.geeps_config_new.restype = C.c_void_p
+        lib.geeps_new.restype = C.c_void_p
+        lib.geeps_new.argtypes = [C.c_uint, C.c_void_p]
+        lib.geeps_read_bf16.restype = C.c_void_p
+        lib.geeps_planner_new.restype = C.c_void_p
+        lib.geeps_mtcache_new.restype = C.c_void_p
+        lib.geeps_ringcache_new.restype = C.c_void_p
+        for name in ("geeps_mtcache_get", "geeps_mtcache_used", "geeps_ringcache_get"):
+            getattr(lib, name).restype = C.c_longlong
+        lib._geeps_ps_typed = True
+    return lib
+
+
+def _rows(rows):
+    arr = (C.c_longlong * len(rows))(*[int(r) for r in rows])
+    return arr, len(rows)
+
+
+class GeePs:
+    def __init__(self, process_id: int, config: GeePsConfig):
+        self._l = _lib()
+        self.config = config
+        self.process_id = process_id
+        cfg = C.c_void_p(self._l.geeps_config_new())
+        for i, h in enumerate(config.host_list):
+            port = config.port_list[i] if i < len(config.port_list) else 0
+            self._l.geeps_config_add_host(cfg, h.encode(), int(port))
+        for k in GeePsConfig._NUMERIC:
+            self._l.geeps_config_set(cfg, k.encode(), C.c_double(float(getattr(config, k))))
+        for k in GeePsConfig._STRING:
+            self._l.geeps_config_set_str(cfg, k.encode(), getattr(config, k).encode())
+        for t, m in config.table_modes.items():
+            self._l.geeps_config_set_table_mode(cfg, int(t), int(m))
+        self._g = C.c_void_p(self._l.geeps_new(process_id, cfg))
+        self._l.geeps_config_delete(cfg)
+        self._ops = {}      # handle -> (kind, num_rows)
+        self._cuda = config.device == DEVICE_CUDA and torch.cuda.is_available()
+        self.check()
+
+    # ---- errors / info ----
+    def last_error(self) -> int:
+        return self._l.geeps_last_error(self._g)
+
+    def _string(self, fn) -> str:
+        need = fn(self._g, None, 0)
+        buf = C.create_string_buffer(need + 16)
+        fn(self._g, buf, need + 16)
+        return buf.value.decode()
+
+    def last_error_string(self) -> str:
+        return self._string(self._l.geeps_last_error_string)
+
+    def check(self) -> None:
+        code = self.last_error()
+        if code:
+            raise GeePsError(code, self.last_error_string())
+
+    def get_stats(self) -> dict:
+        return json.loads(self._string(self._l.geeps_get_stats))
+
+    def plan(self) -> dict:
+        return json.loads(self._string(self._l.geeps_plan_json))
+
+    @property
+    def clock_value(self) -> int:
+        return self._l.geeps_current_clock(self._g)
+
+    # ---- virtual iteration ----
+    def virtual_read(self, table: int, rows, slack: int = 0) -> int:
+        a, n = _rows(rows)
+        h = self._l.geeps_virtual_read(self._g, C.c_longlong(table), a, n, slack)
+        self._ops[h] = ("read", n)
+        return h
+
+    def virtual_post_read(self, prestep: int) -> int:
+        return self._l.geeps_virtual_post_read(self._g, prestep)
+
+    def virtual_pre_update(self, table: int, rows) -> int:
+        a, n = _rows(rows)
+        h = self._l.geeps_virtual_pre_update(self._g, C.c_longlong(table), a, n)
+        self._ops[h] = ("pre_update", n)
+        return h
+
+    def virtual_update(self, prestep: int) -> int:
+        return self._l.geeps_virtual_update(self._g, prestep)
+
+    def virtual_local_access(self, rows, fetch: bool) -> int:
+        a, n = _rows(rows)
+        h = self._l.geeps_virtual_local_access(self._g, a, n, int(fetch))
+        self._ops[h] = ("local", n)
+        return h
+
+    def virtual_post_local_access(self, prestep: int, keep: bool) -> int:
+        return self._l.geeps_virtual_post_local_access(self._g, prestep, int(keep))
+
+    def virtual_clock(self) -> int:
+        return self._l.geeps_virtual_clock(self._g)
+
+    def finish_virtual_iteration(self) -> None:
+        self._l.geeps_finish_virtual_iteration(self._g)
+        self.check()
+
+    def start_iterations(self) -> None:
+        self._l.geeps_start_iterations(self._g)
+        self.check()
+
+    # ---- real access ----
+    def _stream(self, stream):
+        if not self._cuda:
+            return C.c_void_p(0)
+        s = stream if stream is not None else torch.cuda.current_stream()
+        return C.c_void_p(s.cuda_stream)
+
+    def _wrap(self, ptr: int, nrows: int, dtype=torch.float32) -> torch.Tensor:
+        if not ptr:
+            self.check()
+            raise GeePsError(-1, "runtime returned no buffer")
+        if self._cuda:
+            ts = "<f4" if dtype == torch.float32 else "<u2"
+            t = torch.as_tensor(_CudaView(ptr, (nrows, ROW_FLOATS), ts), device="cuda")
+            return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+        buf = (C.c_float * (nrows * ROW_FLOATS)).from_address(ptr)
+        return torch.from_numpy(np.frombuffer(buf, dtype=np.float32).reshape(nrows, ROW_FLOATS))
+
+    def read(self, handle: int, stream=None, asynchronous: bool = True) -> torch.Tensor:
+        p = C.c_void_p()
+        ok = self._l.geeps_read(self._g, handle, C.byref(p), self._stream(stream), int(asynchronous))
+        if not ok:
+            self.check()
+        return self._wrap(p.value, self._ops[handle][1])
+
+    def read_bf16(self, handle: int):
+        p = self._l.geeps_read_bf16(self._g, handle)
+        return self._wrap(p, self._ops[handle][1], torch.bfloat16) if p else None
+
+    def post_read(self, handle: int, stream=None) -> None:
+        self._l.geeps_post_read(self._g, handle, self._stream(stream))
+
+    def pre_update(self, handle: int, stream=None) -> torch.Tensor:
+        p = C.c_void_p()
+        self._l.geeps_pre_update(self._g, handle, C.byref(p), self._stream(stream))
+        return self._wrap(p.value, self._ops[handle][1])
+
+    def update(self, handle: int, stream=None, asynchronous: bool = True) -> None:
+        self._l.geeps_update(self._g, handle, self._stream(stream), int(asynchronous))
+
+    def local_access(self, handle: int, stream=None) -> torch.Tensor:
+        p = C.c_void_p()
+        self._l.geeps_local_access(self._g, handle, C.byref(p), self._stream(stream))
+        return self._wrap(p.value, self._ops[handle][1])
+
+    def post_local_access(self, handle: int, stream=None) -> None:
+        self._l.geeps_post_local_access(self._g, handle, self._stream(stream))
+
+    def clock(self) -> None:
+        self._l.geeps_clock(self._g)
+        self.check()
+
+    # ---- snapshots / lifecycle / test hooks ----
+    def save_snapshot(self, directory: str) -> bool:
+        return bool(self._l.geeps_save_snapshot(self._g, directory.encode()))
+
+    def load_snapshot(self, directory: str) -> bool:
+        return bool(self._l.geeps_load_snapshot(self._g, directory.encode()))
+
+    def inject(self, what: int, value: int) -> None:
+        self._l.geeps_inject(self._g, what, value)
+
+    def shutdown(self) -> None:
+        if self._g:
+            self._l.geeps_shutdown(self._g)
+
+    def close(self) -> None:
+        if self._g:
+            self._l.geeps_delete(self._g)
+            self._g = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,133 @@
+#ifndef GEEPS_B200_GEEPS_HPP_
+#define GEEPS_B200_GEEPS_HPP_
+// Public C++ API of the B200-native GPU parameter server.
+//
+// The class and the first thirteen GeePsConfig fields are source-compatible with the
+// reference's include/geeps.hpp:42-98: an application written against that header compiles
+// against this one.  Everything after `read_my_writes` in the config, the *Async calls, the
+// snapshot calls and the error accessors are additions.
+//
+// Life cycle: construct -> Virtual* calls (declare one iteration's accesses, get handles) ->
+// FinishVirtualIteration() (compiles the memory + communication plan) -> optional bootstrap
+// accesses in any order + Clock() -> StartIterations() -> the declared accesses in exactly the
+// declared order, every clock.
+#include <limits>
+#include <string>
+#include <vector>
+
+#include "geeps-user-defined-types.hpp"
+
+using std::string;
+using std::vector;
+
+struct GeePsConfig {
+  uint num_tables;
+  std::vector<std::string> host_list;
+  std::vector<uint> port_list;   /* per-process TCP port (honoured; lets several processes share a host) */
+  uint tcp_base_port;
+  uint num_comm_channels;
+  std::string output_dir;
+  iter_t log_interval;
+  int pp_policy;
+  int local_opt;
+  size_t gpu_memory_capacity;
+  int mm_warning_level;
+      /* 0: no warning
+       * 1: guarantee double buffering for the staging pool
+       * 2: make sure all local data is in GPU memory
+       * 3: make sure the whole parameter cache is in GPU memory */
+  int pinned_cpu_memory;
+  int read_my_writes;
+
+  /* ---- additions ---- */
+  enum Device { DEVICE_CPU = 0, DEVICE_CUDA = 1 };
+  enum Transport { TRANSPORT_TCP = 0, TRANSPORT_NVLINK = 1 };
+  enum Partitioner { PARTITION_RANGE = 0, PARTITION_ROUND_ROBIN = 1 };
+  enum TableMode { TABLE_ADDITIVE = 0, TABLE_SGD_MOMENTUM = 1 };
+  int device;                 /* where caches and staging live */
+  int cuda_device;            /* CUDA ordinal for DEVICE_CUDA (-1: current device) */
+  int transport;              /* TCP: host-staged messages; NVLINK: in-kernel peer loads/stores */
+  int partitioner;
+  int table_mode;             /* default mode of every table */
+  std::vector<int> table_modes;  /* optional per-table override */
+  float learning_rate, momentum, weight_decay;
+  float grad_scale;           /* multiplies the reduced update before the optimizer (e.g. 1/workers) */
+  int bf16_compute_cache;     /* also keep a bf16 copy of the parameter cache (NVLINK transport) */
+  size_t device_wait_budget_us;  /* bound of every device-side flag wait */
+  size_t host_wait_budget_ms;    /* bound of every host-side blocking wait (0 = wait forever, log every 12 s) */
+  std::string snapshot_dir;
+  iter_t snapshot_interval;
+  int num_workers_override;   /* 0: one worker per host_list entry */
+
+  GeePsConfig() :
+    num_tables(1),
+    tcp_base_port(9090),
+    num_comm_channels(1),
+    output_dir(""), log_interval(0),
+    pp_policy(0), local_opt(1),
+    gpu_memory_capacity(std::numeric_limits<size_t>::max()),
+    mm_warning_level(1),
+    pinned_cpu_memory(1),
+    read_my_writes(0),
+    device(DEVICE_CUDA), cuda_device(-1), transport(TRANSPORT_TCP),
+    partitioner(PARTITION_RANGE), table_mode(TABLE_ADDITIVE),
+    learning_rate(0.01f), momentum(0.9f), weight_decay(0.f), grad_scale(1.f),
+    bf16_compute_cache(0),
+    device_wait_budget_us(30u * 1000u * 1000u), host_wait_budget_ms(0),
+    snapshot_dir(""), snapshot_interval(0), num_workers_override(0) {}
+};
+
+namespace geeps_b200 { class ClientLib; }
+
+class GeePs {
+ public:
+  GeePs(uint process_id, const GeePsConfig& config);
+  ~GeePs();
+  void Shutdown();
+  std::string GetStats();
+  void StartIterations();
+
+  /* Interfaces for virtual iteration */
+  int VirtualRead(size_t table_id, const vector<size_t>& row_ids, int slack);
+  int VirtualPostRead(int prestep_handle);
+  int VirtualPreUpdate(size_t table_id, const vector<size_t>& row_ids);
+  int VirtualUpdate(int prestep_handle);
+  int VirtualLocalAccess(const vector<size_t>& row_ids, bool fetch);
+  int VirtualPostLocalAccess(int prestep_handle, bool keep);
+  int VirtualClock();
+  void FinishVirtualIteration();
+
+  /* Interfaces for real access */
+  bool Read(int handle, RowData **buffer_ptr);
+  void PostRead(int handle);
+  void PreUpdate(int handle, RowOpVal **buffer_ptr);
+  void Update(int handle);
+  bool LocalAccess(int handle, RowData **buffer_ptr);
+  void PostLocalAccess(int handle);
+  void Clock();
+
+  /* ---- additions ---- */
+  /* Stream-aware variants: enqueue the work (and any device-side SSP wait) on `cuda_stream`
+   * and return without synchronising the host. */
+  bool ReadAsync(int handle, RowData **buffer_ptr, void *cuda_stream);
+  void UpdateAsync(int handle, void *cuda_stream);
+  /* bf16 view of a Read buffer when bf16_compute_cache is on and the batch is cache-contiguous */
+  void *ReadBf16(int handle);
+  /* 0 when healthy; otherwise the first error (expired wait, dead peer, ...) and its text */
+  int LastError() const;
+  std::string LastErrorString() const;
+  /* Table snapshots */
+  bool SaveSnapshot(const std::string& dir);
+  bool LoadSnapshot(const std::string& dir);
+  /* The compiled plan as JSON (placement, offsets, indices, per-shard ranges) */
+  std::string PlanJson() const;
+  iter_t CurrentClock() const;
+  geeps_b200::ClientLib* impl() { return impl_; }
+
+ private:
+  GeePs(const GeePs&);
+  GeePs& operator=(const GeePs&);
+  geeps_b200::ClientLib* impl_;
+};
+
+#endif  // GEEPS_B200_GEEPS_HPP_

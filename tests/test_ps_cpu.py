@@ -1,0 +1,188 @@
+"""Parameter-server semantics on CPU over TCP loopback (no GPU): the helloworld-shaped run with
+2 workers + 2 shards, SSP slack 0 and 1, additive and optimizer tables, read-my-writes,
+round-robin partitioning, snapshots."""
+import multiprocessing as mp
+import os
+import random
+
+import pytest
+import torch
+
+from geeps_b200.parallel.ps import GeePs, GeePsError
+from geeps_b200.utils.config import (DEVICE_CPU, PARTITION_ROUND_ROBIN, TABLE_SGD_MOMENTUM, GeePsConfig)
+
+from ps_workers import helloworld_worker
+
+_port = [20000 + (os.getpid() % 500) * 40]
+
+
+def next_port():
+    _port[0] += 40
+    return _port[0]
+
+
+def run_workers(target, world, args, timeout=180):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=target, args=(r, world) + args + (q,) + ()) for r in range(world)]
+    return ctx, q, procs
+
+
+def _run_hello(world, slack, clocks, **kw):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = next_port()
+    kw.setdefault("device", DEVICE_CPU)
+    procs = [ctx.Process(target=helloworld_worker, args=(r, world, port, slack, clocks, q, kw)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for o in out:
+        assert o[1] == "ok", o[2]
+    return sorted(out)
+
+
+@pytest.mark.parametrize("slack", [0, 1])
+def test_helloworld_two_workers_two_shards(slack):
+    clocks = 100
+    out = _run_hello(2, slack, clocks)
+    for rank, _, final, seen, max_stale, stats in out:
+        assert final == (200.0, 200.0), final
+        assert max_stale <= slack
+        for clock, lo, hi in seen:
+            # a read in clock c holds at least every worker's updates of clocks <= c - slack - 1
+            # (clock 0 is the zero bootstrap) and at most everything issued so far
+            c_updates = min(clock - 1, clocks)
+            need = 2.0 * max(0, min(clock - slack - 1, clocks))
+            assert lo >= need - 1e-6, (clock, lo, need)
+            assert hi <= 2.0 * c_updates + 1e-6
+        assert stats["server"]["storage"]["nr_errors"] == 0
+
+
+def test_round_robin_partition_and_read_my_writes():
+    out = _run_hello(2, 1, 20, partitioner=PARTITION_ROUND_ROBIN, read_my_writes=1)
+    for rank, _, final, seen, max_stale, stats in out:
+        assert final == (40.0, 40.0)
+        assert stats["bgthread"]["nr_rmw_replay"] >= 0
+
+
+def _single(cfg_kw, rows=(0, 1, 2, 3)):
+    cfg = GeePsConfig(device=DEVICE_CPU, tcp_base_port=next_port(), **cfg_kw)
+    return GeePs(0, cfg)
+
+
+def test_optimizer_table_matches_momentum_sgd():
+    g = _single(dict(table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.1, momentum=0.9, weight_decay=0.01))
+    rows = [5, 6, 7]
+    r = g.virtual_read(0, rows, 0)
+    u = g.virtual_pre_update(0, rows)
+    pr = g.virtual_post_read(r)
+    up = g.virtual_update(u)
+    g.virtual_clock()
+    g.finish_virtual_iteration()
+    torch.manual_seed(0)
+    w0 = torch.randn(3, 128)
+    g.pre_update(u).copy_(w0)     # bootstrap update = initial values (always additive)
+    g.update(up)
+    g.clock()
+    g.start_iterations()
+    p, v = w0.clone(), torch.zeros_like(w0)
+    for c in range(6):
+        x = g.read(r, asynchronous=False).clone()
+        assert torch.allclose(x, p, atol=1e-6), c
+        grad = torch.randn(3, 128)
+        b = g.pre_update(u)
+        g.post_read(pr)
+        b.copy_(grad)
+        g.update(up)
+        g.clock()
+        v = 0.9 * v + 0.1 * (grad + 0.01 * p)
+        p = p - v
+    g.shutdown()
+    g.close()
+
+
+def test_call_order_is_enforced_and_reported():
+    g = _single({})
+    r = g.virtual_read(0, [0], 0)
+    u = g.virtual_pre_update(0, [0])
+    pr = g.virtual_post_read(r)
+    up = g.virtual_update(u)
+    g.virtual_clock()
+    g.finish_virtual_iteration()
+    g.pre_update(u).zero_()
+    g.update(up)
+    g.clock()
+    g.start_iterations()
+    with pytest.raises(GeePsError) as e:
+        g.pre_update(u)          # declared order starts with the read
+        g.check()
+    assert e.value.code == 2
+    g.shutdown()
+    g.close()
+
+
+def test_plan_errors_surface():
+    g = _single({})
+    g.virtual_read(0, [0], 0)
+    g.virtual_clock()
+    with pytest.raises(GeePsError):
+        g.finish_virtual_iteration()   # read never released, table never updated
+    g.close()
+
+
+def test_local_access_keeps_and_discards():
+    g = _single({})
+    u = g.virtual_pre_update(0, [0])
+    up = g.virtual_update(u)
+    la = g.virtual_local_access([100, 101], True)
+    pla = g.virtual_post_local_access(la, True)
+    g.virtual_clock()
+    g.finish_virtual_iteration()
+    g.pre_update(u).zero_(); g.update(up); g.clock()
+    g.start_iterations()
+    for c in range(3):
+        g.pre_update(u).zero_(); g.update(up)
+        buf = g.local_access(la)
+        assert float(buf[0, 0]) == float(c)      # survives across clocks
+        buf += 1.0
+        g.post_local_access(pla)
+        g.clock()
+    g.shutdown(); g.close()
+
+
+def test_snapshot_roundtrip(tmp_path):
+    def build(port):
+        cfg = GeePsConfig(device=DEVICE_CPU, tcp_base_port=port, table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.05)
+        g = GeePs(0, cfg)
+        rows = list(range(16))
+        r = g.virtual_read(0, rows, 0); u = g.virtual_pre_update(0, rows)
+        pr = g.virtual_post_read(r); up = g.virtual_update(u); g.virtual_clock()
+        g.finish_virtual_iteration()
+        return g, r, u, pr, up
+
+    def step(g, r, u, pr, up, seed):
+        x = g.read(r, asynchronous=False).clone()
+        b = g.pre_update(u); g.post_read(pr)
+        b.copy_(torch.randn(16, 128, generator=torch.Generator().manual_seed(seed)))
+        g.update(up); g.clock()
+        return x
+
+    g, r, u, pr, up = build(next_port())
+    g.pre_update(u).copy_(torch.ones(16, 128)); g.update(up); g.clock()
+    g.start_iterations()
+    for s in range(3):
+        step(g, r, u, pr, up, s)
+    assert g.save_snapshot(str(tmp_path))
+    after = [step(g, r, u, pr, up, 10 + s) for s in range(3)]
+    g.shutdown(); g.close()
+
+    g2, r, u, pr, up = build(next_port())
+    assert g2.load_snapshot(str(tmp_path))
+    g2.start_iterations()
+    again = [step(g2, r, u, pr, up, 10 + s) for s in range(3)]
+    for a, b in zip(after, again):
+        assert torch.equal(a, b)      # parameters AND momentum came back
+    g2.shutdown(); g2.close()
