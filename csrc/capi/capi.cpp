@@ -65,6 +65,7 @@ int geeps_config_set(void* c, const char* key, double v) {
   else if (k == "bf16_compute_cache") cfg->bf16_compute_cache = (int)v;
   else if (k == "device_wait_budget_us") cfg->device_wait_budget_us = (size_t)v;
   else if (k == "host_wait_budget_ms") cfg->host_wait_budget_ms = (size_t)v;
+  else if (k == "heartbeat_timeout_ms") cfg->heartbeat_timeout_ms = (size_t)v;
   else if (k == "snapshot_interval") cfg->snapshot_interval = (iter_t)v;
   else if (k == "num_workers_override") cfg->num_workers_override = (int)v;
   else return -1;

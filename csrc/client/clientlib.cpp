@@ -262,6 +262,7 @@ void ClientLib::preupdate_batch(int handle, RowOpVal** buf, void* stream) {
     // the ring slot of this clock is free again once every shard consumed clock - (slack+1):
     // the same condition a read of this clock waits for
     CachedTable& ct = *tables_[(uint)op.table];
+    ct.last_stream = op_stream(stream);
     fabric_wait_data_age(ct, (uint)op.table, clock_ - ct.plan->slack - 1, op_stream(stream));
     if (ct.has_indirect_updates && ct.ring_zeroed_clock != clock_) {
       // staged updates are accumulated into the ring slot: it has to start the clock at zero
@@ -293,9 +294,9 @@ void ClientLib::update_batch(int handle, void* stream, bool async) {
   stats_.rows_updated += pre.rows.size();
   // after StartIterations the last write of a table in the clock signals that table's clock at
   // once, so its push overlaps the rest of the iteration; during bootstrap Clock() signals all
-  if (started_ && op.table_last_write) clock_table(clock_, (uint)op.table, false, false);
-  if (nvlink_ && !async && started_ && op.table_last_write) { /* device work stays queued; errors surface in Clock */ }
-  (void)st;
+  if (!pre.local) tables_[(uint)op.table]->last_stream = st;
+  if (started_ && op.table_last_write) clock_table(clock_, (uint)op.table, false, false, st);
+  (void)async;
   stats_.update_time += now_seconds() - t0;
 }
 

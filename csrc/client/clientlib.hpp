@@ -90,6 +90,7 @@ struct CachedTable {
   int mode = 0;
   bool has_indirect_updates = false;   // some PreUpdate of this table goes through staging
   iter_t ring_zeroed_clock = -1;       // NVLINK: clock whose ring slot has been zeroed
+  void* last_stream = nullptr;         // stream of the application's latest PreUpdate/Update on this table
   std::mutex mu;
   std::condition_variable cv;
 };
@@ -201,7 +202,7 @@ class ClientLib {
   void swap_prefetch_after(int handle);
   void swap_release(int pre_handle, void* stream, bool after_swap_stream);
   // background (clientlib_bg.cpp)
-  void clock_table(iter_t signalled_clock, uint table_id, bool is_init, bool synchronous);
+  void clock_table(iter_t signalled_clock, uint table_id, bool is_init, bool synchronous, void* stream);
   void clock_all(iter_t signalled_clock, bool is_init);
   void cbk_iterate(std::vector<char>& args);
   void heartbeat_loop();

@@ -92,20 +92,25 @@ void ClientLib::swap_release(int pre_handle, void* stream, bool) {
 // ---------------- clock signalling ----------------
 // "Signal clock c of table t": this worker's updates of clock c are complete.  On the host-staged
 // path the push worker sends them; on NVLINK the push kernels are enqueued right here.
-void ClientLib::clock_table(iter_t signalled_clock, uint table_id, bool is_init, bool synchronous) {
+void ClientLib::clock_table(iter_t signalled_clock, uint table_id, bool is_init, bool synchronous, void* stream) {
   auto it = tables_.find(table_id);
   if (it == tables_.end()) return;
   CachedTable& ct = *it->second;
   if (signalled_clock <= ct.signalled_clock) return;
   ct.signalled_clock = signalled_clock;
-  if (nvlink_) { fabric_push(signalled_clock, table_id, is_init, default_stream_); return; }
+  if (nvlink_) {
+    // the announcement has to follow the application's update writes in stream order
+    void* st = stream ? stream : (ct.last_stream ? ct.last_stream : default_stream_);
+    fabric_push(signalled_clock, table_id, is_init, st);
+    return;
+  }
   if (synchronous) { push_updates_param_cache(signalled_clock, table_id, is_init); return; }
   IterateArgs a{signalled_clock, table_id, is_init ? 1 : 0};
   bg_workers_[table_id % bg_workers_.size()]->pusher()->push_work(kIterateCmd, a);
 }
 
 void ClientLib::clock_all(iter_t signalled_clock, bool is_init) {
-  for (auto& kv : tables_) clock_table(signalled_clock, kv.first, is_init, true);
+  for (auto& kv : tables_) clock_table(signalled_clock, kv.first, is_init, true, nullptr);
 }
 
 void ClientLib::cbk_iterate(std::vector<char>& args) {
@@ -120,7 +125,11 @@ void ClientLib::cbk_iterate(std::vector<char>& args) {
 // ---------------- failure detection ----------------
 void ClientLib::heartbeat_loop() {
   uint64_t counter = 0;
-  const double timeout_s = 10.0;
+  const double timeout_s = (double)config_.heartbeat_timeout_ms / 1000.0;
+  {
+    std::lock_guard<std::mutex> lk(peers_mu_);
+    for (double& t : last_heartbeat_) t = now_seconds();
+  }
   while (!stop_heartbeat_) {
     if (!skip_heartbeats_ && encoder_) encoder_->heartbeat(++counter, clock_);
     {

@@ -290,6 +290,38 @@ relu_backward_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf
   }
 }
 
+// 2-D variant with row pitches (channel slices of concat tensors)
+__global__ void __launch_bounds__(256)
+relu_backward_2d_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx, long long P,
+                        int C, long long lddy, long long ldy, long long lddx) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long p = i / cv;
+    Bf8 d = ld8(dy + p * lddy + c), v = ld8(y + p * ldy + c), o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o.v[e] = bf(v.v[e]) > 0.f ? d.v[e] : __float2bfloat16(0.f);
+    st8(dx + p * lddx + c, o);
+  }
+}
+// dst += src over 2-D views (sum of branch gradients)
+__global__ void __launch_bounds__(256)
+add_2d_kernel(bf16* __restrict__ dst, const bf16* __restrict__ src, long long P, int C, long long ldd, long long lds) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long p = i / cv;
+    Bf8 a = ld8(dst + p * ldd + c), b = ld8(src + p * lds + c), o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(bf(a.v[e]) + bf(b.v[e]));
+    st8(dst + p * ldd + c, o);
+  }
+}
+
 __device__ __forceinline__ uint32_t mix32(uint64_t z) {
   z += 0x9E3779B97F4A7C15ull;
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -651,6 +683,19 @@ int geeps_colsum(const void* x, float* out, long long P, int C, long long ldx, f
 int geeps_relu_backward(const void* dy, const void* y, void* dx, long long n, void* stream) {
   if (n % 8) return (int)cudaErrorInvalidValue;
   relu_backward_kernel<<<grid_1d(n / 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)y, (bf16*)dx, n / 8);
+  return CK();
+}
+
+int geeps_relu_backward_2d(const void* dy, const void* y, void* dx, long long P, int C, long long lddy, long long ldy,
+                           long long lddx, void* stream) {
+  if (C % 8 || lddy % 8 || ldy % 8 || lddx % 8) return (int)cudaErrorInvalidValue;
+  relu_backward_2d_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)y,
+                                                                                 (bf16*)dx, P, C, lddy, ldy, lddx);
+  return CK();
+}
+int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long ldd, long long lds, void* stream) {
+  if (C % 8 || ldd % 8 || lds % 8) return (int)cudaErrorInvalidValue;
+  add_2d_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>((bf16*)dst, (const bf16*)src, P, C, ldd, lds);
   return CK();
 }
 

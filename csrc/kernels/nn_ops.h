@@ -34,6 +34,9 @@ int geeps_bn_backward(const void* x, const void* dy, const void* y, void* dx, co
 int geeps_colsum(const void* x, float* out, long long P, int C, long long ldx, float scale, int zero_first,
                  void* stream);
 int geeps_relu_backward(const void* dy, const void* y, void* dx, long long n, void* stream);
+int geeps_relu_backward_2d(const void* dy, const void* y, void* dx, long long P, int C, long long lddy, long long ldy,
+                           long long lddx, void* stream);
+int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long ldd, long long lds, void* stream);
 int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream);
 int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, int size, float alpha, float beta,
                       float k, void* stream);

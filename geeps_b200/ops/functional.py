@@ -118,6 +118,18 @@ def relu_backward(dy, y, dx) -> None:
     check(lib().geeps_relu_backward(ptr(dy), ptr(y), ptr(dx), C.c_longlong(dy.numel()), stream_ptr()), "relu_backward")
 
 
+def relu_backward_2d(dy2d, y2d, dx2d) -> None:
+    P, Cc = dy2d.shape
+    check(lib().geeps_relu_backward_2d(ptr(dy2d), ptr(y2d), ptr(dx2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dy2d)),
+                                       C.c_longlong(_ld(y2d)), C.c_longlong(_ld(dx2d)), stream_ptr()), "relu_backward_2d")
+
+
+def add_2d(dst2d, src2d) -> None:
+    P, Cc = dst2d.shape
+    check(lib().geeps_add_bf16_2d(ptr(dst2d), ptr(src2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dst2d)),
+                                  C.c_longlong(_ld(src2d)), stream_ptr()), "add_bf16_2d")
+
+
 def dropout(x, y, p: float, seed: int) -> None:
     assert x.is_contiguous() and y.is_contiguous()
     check(lib().geeps_dropout(ptr(x), ptr(y), C.c_longlong(x.numel()), C.c_float(p), C.c_ulonglong(seed),

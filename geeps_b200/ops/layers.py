@@ -1,0 +1,380 @@
+"""Caffe-style layers with explicit forward / backward on the native kernels.
+
+Activations are NHWC bf16 tensors with static shapes; every buffer is allocated once at
+setup and reused each step.  Parameters are NOT owned by the layers: the parameter-server
+module binds, per step, fp32 views of the rows it Read (`p32`), bf16 compute copies (`p16`) and
+fp32 views of the PreUpdate buffers the gradients are written into (`g32`).
+
+The reference's layer code lived in its (absent) Caffe application; layer definitions here
+follow Caffe's AlexNet / Inception-BN usage: conv with groups, LRN across channels, ceil-mode
+max pooling, BatchNorm + scale, inner product, softmax loss.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import functional as F
+
+BF = torch.bfloat16
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+@dataclass
+class ParamSpec:
+    name: str
+    shape: tuple          # stored shape (may include K padding)
+    init: str             # "gaussian:<std>", "msra:<fan_in>", "const:<v>"
+    valid_cols: int = 0   # for 2-D weights: columns [valid_cols, shape[1]) are padding and stay zero
+    decay: bool = True
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def initial(self, gen: torch.Generator) -> torch.Tensor:
+        kind, _, arg = self.init.partition(":")
+        if kind == "const":
+            return torch.full(self.shape, float(arg))
+        std = float(arg) if kind == "gaussian" else math.sqrt(2.0 / float(arg))
+        t = torch.randn(self.shape, generator=gen) * std
+        if self.valid_cols and len(self.shape) == 2:
+            t[:, self.valid_cols:] = 0
+        return t
+
+
+class Layer:
+    name = "layer"
+
+    def __init__(self):
+        self.p32, self.p16, self.g32 = {}, {}, {}
+        self.training = True
+
+    def param_specs(self) -> list:
+        return []
+
+    def setup(self, in_shape, device):
+        raise NotImplementedError
+
+    def forward(self, x):
+        raise NotImplementedError
+
+    def backward(self, dy):
+        raise NotImplementedError
+
+
+class Input(Layer):
+    """fp32 NCHW batch -> NHWC bf16 (optionally zero-padding the channel count)."""
+
+    def __init__(self, cpad: int | None = None):
+        super().__init__()
+        self.cpad = cpad
+
+    def setup(self, in_shape, device):
+        B, C, H, W = in_shape
+        self.out_shape = (B, H, W, self.cpad or C)
+        return self.out_shape
+
+    def forward(self, x):
+        return F.nchw_to_nhwc_bf16(x, self.cpad)
+
+    def backward(self, dy):
+        return None
+
+
+class Conv2d(Layer):
+    def __init__(self, name, cout, k, stride=1, pad=0, groups=1, relu=False, bias=True, std=0.01, bias_value=0.0,
+                 need_dx=True, cin_valid=None):
+        super().__init__()
+        self.name, self.cout, self.k, self.stride, self.pad, self.groups = name, cout, k, stride, pad, groups
+        self.relu, self.has_bias, self.std, self.bias_value, self.need_dx = relu, bias, std, bias_value, need_dx
+        self.cin_valid = cin_valid
+
+    def setup(self, in_shape, device):
+        B, H, W, C = in_shape
+        self.in_shape = in_shape
+        G = self.groups
+        self.cg, self.og = C // G, self.cout // G
+        self.kd = self.k * self.k * self.cg
+        self.ld = _pad8(self.kd)
+        self.geoms = [F.conv_geom(in_shape, g * self.cg, self.cg, self.k, self.k, self.stride, self.pad, self.ld)
+                      for g in range(G)]
+        self.OH, self.OW = self.geoms[0].OH, self.geoms[0].OW
+        self.M = B * self.OH * self.OW
+        self.pointwise = self.k == 1 and self.stride == 1 and self.pad == 0 and G == 1 and C % 8 == 0
+        if not self.pointwise:
+            self.cols = [torch.empty(self.M, self.ld, dtype=BF, device=device) for _ in range(G)]
+            self.dcol = torch.empty(self.M, self.ld, dtype=BF, device=device) if self.need_dx else None
+        self.y = None
+        self.dx = torch.empty(in_shape, dtype=BF, device=device) if self.need_dx else None
+        self.out_shape = (B, self.OH, self.OW, self.cout)
+        self.device = device
+        return self.out_shape
+
+    def param_specs(self):
+        fan_in = self.kd
+        specs = [ParamSpec("weight", (self.cout, self.ld), f"gaussian:{self.std}" if self.std > 0 else f"msra:{fan_in}",
+                           valid_cols=self.kd)]
+        if self.has_bias:
+            specs.append(ParamSpec("bias", (self.cout,), f"const:{self.bias_value}", decay=False))
+        return specs
+
+    def bind_output(self, y2d):
+        """Write the output into a channel slice of a wider (concat) tensor."""
+        self.y = y2d
+
+    def forward(self, x):
+        self.x = x
+        if self.y is None:
+            self.y = torch.empty(self.M, self.cout, dtype=BF, device=self.device)
+        w16 = self.p16["weight"]
+        bias = self.p32.get("bias")
+        for g in range(self.groups):
+            if self.pointwise:
+                a = x.view(self.M, -1)
+            else:
+                F.im2col(x, self.cols[g], self.geoms[g])
+                a = self.cols[g]
+            F.gemm(a, w16[g * self.og:(g + 1) * self.og], self.y[:, g * self.og:(g + 1) * self.og],
+                   bias=None if bias is None else bias[g * self.og:(g + 1) * self.og], relu=self.relu)
+        return self.y
+
+    def backward(self, dy):
+        # dy: [M, cout] bf16 (possibly a slice view of a wider tensor)
+        if dy.dim() != 2:
+            dy = dy.view(self.M, self.cout)
+        if self.relu:
+            dy = self._relu_mask(dy)
+        gw = self.g32["weight"]
+        if self.has_bias:
+            F.colsum(dy, self.g32["bias"])
+        w16 = self.p16["weight"]
+        for g in range(self.groups):
+            dyg = dy[:, g * self.og:(g + 1) * self.og]
+            a = self.x.view(self.M, -1) if self.pointwise else self.cols[g]
+            # dW_g[og, ld] = dy_g^T @ col_g      (both operands stored K-outermost)
+            F.gemm(dyg, a, gw[g * self.og:(g + 1) * self.og], a_mn=True, b_mn=True, split_k=0)
+            if self.need_dx:
+                wg = w16[g * self.og:(g + 1) * self.og]
+                if self.pointwise:
+                    F.gemm(dyg, wg, self.dx.view(self.M, -1), b_mn=True)
+                else:
+                    F.gemm(dyg, wg, self.dcol, b_mn=True)
+                    F.col2im(self.dcol, self.dx, self.geoms[g])
+        return self.dx
+
+    def _relu_mask(self, dy):
+        if not hasattr(self, "_dy_masked"):
+            self._dy_masked = torch.empty(self.M, self.cout, dtype=BF, device=self.device)
+        F.relu_backward_2d(dy, self.y, self._dy_masked)
+        return self._dy_masked
+
+
+class Linear(Layer):
+    def __init__(self, name, out_features, relu=False, std=0.01, bias_value=0.0, need_dx=True, fp32_out=False):
+        super().__init__()
+        self.name, self.out, self.relu, self.std, self.bias_value = name, out_features, relu, std, bias_value
+        self.need_dx, self.fp32_out = need_dx, fp32_out
+
+    def setup(self, in_shape, device):
+        self.in_shape = in_shape
+        B = in_shape[0]
+        self.B = B
+        self.k_in = 1
+        for s in in_shape[1:]:
+            self.k_in *= s
+        self.ld = _pad8(self.k_in)
+        assert self.ld == self.k_in, "Linear input width must be a multiple of 8"
+        self.out_ld = _pad8(self.out)
+        ybuf = torch.zeros(B, self.out_ld, dtype=torch.float32 if self.fp32_out else BF, device=device)
+        self.y = ybuf[:, :self.out]
+        self.dx = torch.empty(B, self.k_in, dtype=BF, device=device) if self.need_dx else None
+        self.device = device
+        self.out_shape = (B, self.out)
+        return self.out_shape
+
+    def param_specs(self):
+        return [ParamSpec("weight", (self.out, self.ld), f"gaussian:{self.std}", valid_cols=self.k_in),
+                ParamSpec("bias", (self.out,), f"const:{self.bias_value}", decay=False)]
+
+    def forward(self, x):
+        self.x = x.reshape(self.B, self.k_in)
+        F.gemm(self.x, self.p16["weight"], self.y, bias=self.p32["bias"], relu=self.relu)
+        return self.y
+
+    def backward(self, dy):
+        if self.relu:
+            if not hasattr(self, "_dym"):
+                self._dym = torch.empty(self.B, self.out_ld, dtype=BF, device=self.device)[:, :self.out]
+            F.relu_backward_2d(dy, self.y, self._dym)
+            dy = self._dym
+        F.colsum(dy, self.g32["bias"])
+        # dW[out, in] = dy^T @ x ; dx[B, in] = dy @ W
+        F.gemm(dy, self.x, self.g32["weight"], a_mn=True, b_mn=True, split_k=0)
+        if self.need_dx:
+            F.gemm(dy, self.p16["weight"], self.dx, b_mn=True)
+            return self.dx.view(self.in_shape)
+        return None
+
+
+class BatchNorm(Layer):
+    def __init__(self, name, relu=False, eps=1e-5, momentum=0.1):
+        super().__init__()
+        self.name, self.relu, self.eps, self.momentum = name, relu, eps, momentum
+
+    def setup(self, in_shape, device):
+        self.in_shape = in_shape
+        self.C = in_shape[-1]
+        self.P = 1
+        for s in in_shape[:-1]:
+            self.P *= s
+        self.sums = torch.empty(2 * self.C, device=device)
+        self.mean_rstd = torch.empty(2 * self.C, device=device)
+        self.running_mean = torch.zeros(self.C, device=device)
+        self.running_var = torch.ones(self.C, device=device)
+        self.y = torch.empty(self.P, self.C, dtype=BF, device=device)
+        self.dx = torch.empty(self.P, self.C, dtype=BF, device=device)
+        self.out_shape = in_shape
+        return in_shape
+
+    def param_specs(self):
+        return [ParamSpec("gamma", (self.C,), "const:1.0", decay=False),
+                ParamSpec("beta", (self.C,), "const:0.0", decay=False)]
+
+    def bind_output(self, y2d):
+        self.y = y2d
+
+    def forward(self, x):
+        self.x = x if x.dim() == 2 else x.view(self.P, self.C)
+        F.bn_forward(self.x, self.y, self.p32["gamma"], self.p32["beta"], self.sums, self.mean_rstd, self.running_mean,
+                     self.running_var, eps=self.eps, momentum=self.momentum, relu=self.relu)
+        return self.y
+
+    def backward(self, dy):
+        if dy.dim() != 2:
+            dy = dy.view(self.P, self.C)
+        F.bn_backward(self.x, dy, self.y, self.dx, self.mean_rstd, self.p32["gamma"], self.sums, self.g32["gamma"],
+                      self.g32["beta"], relu=self.relu)
+        return self.dx
+
+
+class LRN(Layer):
+    def __init__(self, size=5, alpha=1e-4, beta=0.75, k=1.0):
+        super().__init__()
+        self.size, self.alpha, self.beta, self.k = size, alpha, beta, k
+
+    def setup(self, in_shape, device):
+        self.C = in_shape[-1]
+        self.P = 1
+        for s in in_shape[:-1]:
+            self.P *= s
+        self.y = torch.empty(self.P, self.C, dtype=BF, device=device)
+        self.scale = torch.empty(self.P, self.C, device=device)
+        self.dx = torch.empty(self.P, self.C, dtype=BF, device=device)
+        self.out_shape = in_shape
+        return in_shape
+
+    def forward(self, x):
+        self.x = x.reshape(self.P, self.C)
+        F.lrn_forward(self.x, self.y, self.scale, self.size, self.alpha, self.beta, self.k)
+        return self.y
+
+    def backward(self, dy):
+        F.lrn_backward(self.x, self.y, self.scale, dy.reshape(self.P, self.C), self.dx, self.size, self.alpha, self.beta)
+        return self.dx
+
+
+class Pool(Layer):
+    def __init__(self, kind, k, stride, pad=0, ceil_mode=True):
+        super().__init__()
+        self.kind, self.k, self.stride, self.pad, self.ceil_mode = kind, k, stride, pad, ceil_mode
+
+    def setup(self, in_shape, device):
+        B, H, W, C = in_shape
+        self.in_shape = in_shape
+        k = H if self.k == 0 else self.k      # k = 0: global pooling
+        self.g = F.pool_geom(in_shape, k, self.stride, self.pad, C, C, self.ceil_mode)
+        self.out_shape = (B, self.g.OH, self.g.OW, C)
+        self.y = None
+        self.argmax = torch.empty(self.out_shape, dtype=torch.uint8, device=device) if self.kind == "max" else None
+        self.dx = torch.empty(in_shape, dtype=BF, device=device)
+        self.device = device
+        return self.out_shape
+
+    def bind_output(self, y2d, ldy):
+        self.y = y2d
+        self.g.ldy = ldy
+
+    def forward(self, x):
+        if self.y is None:
+            self.y = torch.empty(self.out_shape, dtype=BF, device=self.device)
+        self.g.ldx = x.stride(-2) if x.dim() >= 2 else self.g.C
+        if self.kind == "max":
+            F.maxpool_forward(x, self.y, self.argmax, self.g)
+        else:
+            F.avgpool_forward(x, self.y, self.g)
+        return self.y
+
+    def backward(self, dy):
+        ldx = self.g.ldx
+        self.g.ldx = self.g.C       # dx is a dense tensor of the input shape
+        if self.kind == "max":
+            F.maxpool_backward(dy, self.argmax, self.dx, self.g)
+        else:
+            F.avgpool_backward(dy, self.dx, self.g)
+        self.g.ldx = ldx
+        return self.dx
+
+
+class Dropout(Layer):
+    def __init__(self, p=0.5, seed=1234):
+        super().__init__()
+        self.p, self.seed, self.step = p, seed, 0
+
+    def setup(self, in_shape, device):
+        self.y = torch.empty(in_shape, dtype=BF, device=device)
+        self.dx = torch.empty(in_shape, dtype=BF, device=device)
+        self.out_shape = in_shape
+        return in_shape
+
+    def forward(self, x):
+        self.step += 1
+        if not self.training:
+            return x
+        F.dropout(x.contiguous(), self.y, self.p, self.seed + self.step)
+        return self.y
+
+    def backward(self, dy):
+        if not self.training:
+            return dy
+        F.dropout(dy.contiguous(), self.dx, self.p, self.seed + self.step)
+        return self.dx
+
+
+class SoftmaxLoss(Layer):
+    """Mean softmax cross-entropy over the batch; backward seeds dlogits = (softmax - onehot) / B."""
+
+    def setup(self, in_shape, device):
+        B, C = in_shape
+        self.B, self.C = B, C
+        self.loss = torch.zeros(1, device=device)
+        self.dlogits = torch.zeros(B, _pad8(C), dtype=BF, device=device)[:, :C]
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.out_shape = (1,)
+        return self.out_shape
+
+    def forward(self, logits, labels):
+        F.softmax_ce(logits, labels, self.loss, self.dlogits, loss_scale=1.0 / self.B, grad_scale=1.0 / self.B,
+                     status=self.status)
+        return self.loss
+
+    def backward(self, dy=None):
+        return self.dlogits

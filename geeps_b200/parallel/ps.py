@@ -74,6 +74,7 @@ class GeePs:
         self._g = C.c_void_p(self._l.geeps_new(process_id, cfg))
         self._l.geeps_config_delete(cfg)
         self._ops = {}      # handle -> (kind, num_rows)
+        self._views = {}    # (ptr, rows, dtype) -> tensor aliasing runtime memory
         self._cuda = config.device == DEVICE_CUDA and torch.cuda.is_available()
         self.check()
 
@@ -149,16 +150,22 @@ class GeePs:
         if not self._cuda:
             return C.c_void_p(0)
         s = stream if stream is not None else torch.cuda.current_stream()
-        return C.c_void_p(s.cuda_stream)
+        # handle 0 means "the runtime's own stream" to the C API; CUDA's legacy default stream is 0x1
+        return C.c_void_p(s.cuda_stream or 1)
 
     def _wrap(self, ptr: int, nrows: int, dtype=torch.float32) -> torch.Tensor:
         if not ptr:
             self.check()
             raise GeePsError(-1, "runtime returned no buffer")
         if self._cuda:
-            ts = "<f4" if dtype == torch.float32 else "<u2"
-            t = torch.as_tensor(_CudaView(ptr, (nrows, ROW_FLOATS), ts), device="cuda")
-            return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+            key = (ptr, nrows, dtype)
+            t = self._views.get(key)
+            if t is None:
+                ts = "<f4" if dtype == torch.float32 else "<u2"
+                t = torch.as_tensor(_CudaView(ptr, (nrows, ROW_FLOATS), ts), device="cuda")
+                t = t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+                self._views[key] = t
+            return t
         buf = (C.c_float * (nrows * ROW_FLOATS)).from_address(ptr)
         return torch.from_numpy(np.frombuffer(buf, dtype=np.float32).reshape(nrows, ROW_FLOATS))
 

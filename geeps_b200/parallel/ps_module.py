@@ -1,0 +1,140 @@
+"""PSModule: trains a Net through the parameter server.
+
+Every parameterised layer owns one table (its parameters packed row after row, each padded to
+whole 128-float rows).  One fwd/bwd is declared to the runtime as a virtual iteration:
+    Read(table_l) before layer l's forward ... then, walking the layers backwards,
+    PreUpdate(table_l) -> layer l's backward writes its gradients straight into that buffer ->
+    PostRead(table_l) -> Update(table_l) ... Clock.
+Because a layer's Update is the last write of its table in the clock, the runtime signals that
+table's clock immediately and the push of layer l overlaps the backward pass of layers < l
+(the per-table clocks of the reference exist for exactly this: src/client/clientlib-viter.cpp:773-797).
+
+Stands in for the solver glue of the reference's (absent) Caffe application.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import functional as F
+from ..ops.layers import BF, ParamSpec
+from ..utils.config import TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK, GeePsConfig
+from .ps import ROW_FLOATS, GeePs
+
+
+def _rows_for(numel: int) -> int:
+    return (numel + ROW_FLOATS - 1) // ROW_FLOATS
+
+
+class _Table:
+    def __init__(self, table_id, layer):
+        self.table_id = table_id
+        self.layer = layer
+        self.specs = layer.param_specs()
+        self.offsets = []
+        off = 0
+        for sp in self.specs:
+            self.offsets.append(off)
+            off += _rows_for(sp.numel) * ROW_FLOATS
+        self.rows = off // ROW_FLOATS
+        self.h_read = self.h_post = self.h_pre = self.h_upd = -1
+        self.p16_buf = None
+
+    def views(self, buf: torch.Tensor) -> dict:
+        flat = buf.view(-1)
+        return {sp.name: flat[o:o + sp.numel].view(sp.shape) for sp, o in zip(self.specs, self.offsets)}
+
+
+class PSModule:
+    def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
+                 slack: int = 0, seed: int = 0):
+        self.net, self.rank, self.world, self.slack = net, rank, world, slack
+        self.device = torch.device(device)
+        net.setup(in_shape, self.device)
+        self.tables = [_Table(i, l) for i, l in enumerate(net.param_layers())]
+        by_layer = {id(t.layer): t for t in self.tables}
+        # tables grouped by top-level layer (a Concat module holds several parameterised layers)
+        self.groups = []
+        for l in net.layers:
+            subs = list(l.sublayers()) if hasattr(l, "sublayers") else [l]
+            self.groups.append((l, [by_layer[id(s)] for s in subs if id(s) in by_layer]))
+        ps_config.num_tables = len(self.tables)
+        self.direct16 = ps_config.transport == TRANSPORT_NVLINK and ps_config.bf16_compute_cache
+        self.ps = GeePs(rank, ps_config)
+        self._declare()
+        self._bootstrap(seed)
+        self.ps.start_iterations()
+        self.steps = 0
+
+    # one virtual iteration = the exact call sequence of step()
+    def _declare(self):
+        ps = self.ps
+        for _, tabs in self.groups:
+            for t in tabs:
+                t.h_read = ps.virtual_read(t.table_id, range(t.rows), self.slack)
+        for _, tabs in reversed(self.groups):
+            for t in reversed(tabs):
+                t.h_pre = ps.virtual_pre_update(t.table_id, range(t.rows))
+            for t in reversed(tabs):
+                t.h_post = ps.virtual_post_read(t.h_read)
+                t.h_upd = ps.virtual_update(t.h_pre)
+        ps.virtual_clock()
+        ps.finish_virtual_iteration()
+
+    def _bootstrap(self, seed):
+        # the bootstrap update carries the initial values; updates add up over workers, so only rank 0
+        # sends non-zero values
+        gen = torch.Generator().manual_seed(seed)
+        for t in [t for _, tabs in reversed(self.groups) for t in reversed(tabs)]:
+            buf = self.ps.pre_update(t.h_pre)
+            buf.zero_()
+            views = t.views(buf)
+            for sp in t.specs:
+                init = sp.initial(gen)
+                if self.rank == 0:
+                    views[sp.name].copy_(init.to(buf.device))
+            self.ps.update(t.h_upd)
+        self.ps.clock()
+
+    def _bind_read(self, t):
+        buf = self.ps.read(t.h_read)
+        t.layer.p32 = t.views(buf)
+        b16 = self.ps.read_bf16(t.h_read) if self.direct16 else None
+        if b16 is None:
+            if t.p16_buf is None:
+                t.p16_buf = torch.empty(t.rows, ROW_FLOATS, dtype=BF, device=self.device)
+            F.f32_to_bf16(buf, t.p16_buf)
+            b16 = t.p16_buf
+        t.layer.p16 = t.views(b16)
+
+    def step(self, x: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """One clock: forward, backward, push.  Returns the mean loss as a 1-element device tensor."""
+        net = self.net
+        h = net.input_layer.forward(x)
+        for l, tabs in self.groups:
+            for t in tabs:
+                self._bind_read(t)
+            h = l.forward(h)
+        loss = net.loss_layer.forward(h, labels)
+        g = net.loss_layer.backward()
+        for l, tabs in reversed(self.groups):
+            for t in reversed(tabs):
+                t.layer.g32 = t.views(self.ps.pre_update(t.h_pre))
+            g = l.backward(g)
+            for t in reversed(tabs):
+                self.ps.post_read(t.h_post)
+                self.ps.update(t.h_upd)
+        self.ps.clock()
+        self.steps += 1
+        return loss
+
+    def params_fp32(self) -> dict:
+        """Current parameter values as seen by this worker's last Read (for tests)."""
+        out = {}
+        for t in self.tables:
+            for name, v in t.layer.p32.items():
+                out[f"{t.layer.name}.{name}"] = v
+        return out
+
+    def close(self):
+        self.ps.shutdown()
+        self.ps.close()

@@ -40,6 +40,7 @@ class GeePsConfig:
     bf16_compute_cache: int = 0
     device_wait_budget_us: int = 30_000_000
     host_wait_budget_ms: int = 0
+    heartbeat_timeout_ms: int = 30000
     snapshot_dir: str = ""
     snapshot_interval: int = 0
     num_workers_override: int = 0
@@ -48,5 +49,5 @@ class GeePsConfig:
                 "gpu_memory_capacity", "mm_warning_level", "pinned_cpu_memory", "read_my_writes", "device",
                 "cuda_device", "transport", "partitioner", "table_mode", "learning_rate", "momentum",
                 "weight_decay", "grad_scale", "bf16_compute_cache", "device_wait_budget_us",
-                "host_wait_budget_ms", "snapshot_interval", "num_workers_override")
+                "host_wait_budget_ms", "heartbeat_timeout_ms", "snapshot_interval", "num_workers_override")
     _STRING = ("output_dir", "snapshot_dir")

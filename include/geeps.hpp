@@ -55,6 +55,7 @@ struct GeePsConfig {
   int bf16_compute_cache;     /* also keep a bf16 copy of the parameter cache (NVLINK transport) */
   size_t device_wait_budget_us;  /* bound of every device-side flag wait */
   size_t host_wait_budget_ms;    /* bound of every host-side blocking wait (0 = wait forever, log every 12 s) */
+  size_t heartbeat_timeout_ms;   /* a peer silent for this long is declared lost */
   std::string snapshot_dir;
   iter_t snapshot_interval;
   int num_workers_override;   /* 0: one worker per host_list entry */
@@ -73,7 +74,7 @@ struct GeePsConfig {
     partitioner(PARTITION_RANGE), table_mode(TABLE_ADDITIVE),
     learning_rate(0.01f), momentum(0.9f), weight_decay(0.f), grad_scale(1.f),
     bf16_compute_cache(0),
-    device_wait_budget_us(30u * 1000u * 1000u), host_wait_budget_ms(0),
+    device_wait_budget_us(30u * 1000u * 1000u), host_wait_budget_ms(0), heartbeat_timeout_ms(30000),
     snapshot_dir(""), snapshot_interval(0), num_workers_override(0) {}
 };
 
