@@ -114,7 +114,7 @@ push_apply_kernel(const GeepsPushApplyParams p) {
         const uint2 h = make_uint2(pack_bf16x2(w.x, w.y), pack_bf16x2(w.z, w.w));
         for (int q = 0; q < p.n_ranks; ++q) {
           if (p.cache[q] != nullptr) st_f4(p.cache[q] + goff, w);
-          if (p.cache16[q] != nullptr) *reinterpret_cast<uint2*>(p.cache16[q] + goff) = h;
+          if (p.cache16[q] != nullptr) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.cache16[q]) + goff) = h;
         }
       }
     }
@@ -166,7 +166,7 @@ pull_kernel(const GeepsPullParams p) {
       const long long goff = grow * GEEPS_ROW_FLOATS + lane * 4;
       if (p.cache != nullptr) st_f4(p.cache + goff, w);
       if (p.cache16 != nullptr)
-        *reinterpret_cast<uint2*>(p.cache16 + goff) =
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.cache16) + goff) =
             make_uint2(pack_bf16x2(w.x, w.y), pack_bf16x2(w.z, w.w));
     }
   }

@@ -58,6 +58,8 @@ class Concat(Layer):
         return self.y
 
     def backward(self, dy):
+        if dy.dim() != 2:
+            dy = dy.view(self.P, -1)
         off = 0
         total = None
         for br, w in zip(self.branches, self.widths):

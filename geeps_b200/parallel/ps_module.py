@@ -46,7 +46,7 @@ class _Table:
 
 class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
-                 slack: int = 0, seed: int = 0):
+                 slack: int = 0, seed: int = 0, keep_init: bool = False):
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
         net.setup(in_shape, self.device)
@@ -60,6 +60,8 @@ class PSModule:
         ps_config.num_tables = len(self.tables)
         self.direct16 = ps_config.transport == TRANSPORT_NVLINK and ps_config.bf16_compute_cache
         self.ps = GeePs(rank, ps_config)
+        self.initial_params = {} if keep_init else None
+        self.captured = None
         self._declare()
         self._bootstrap(seed)
         self.ps.start_iterations()
@@ -92,6 +94,8 @@ class PSModule:
                 init = sp.initial(gen)
                 if self.rank == 0:
                     views[sp.name].copy_(init.to(buf.device))
+                if self.initial_params is not None:
+                    self.initial_params[f"{t.layer.name}.{sp.name}"] = init.clone()
             self.ps.update(t.h_upd)
         self.ps.clock()
 
@@ -105,10 +109,16 @@ class PSModule:
             F.f32_to_bf16(buf, t.p16_buf)
             b16 = t.p16_buf
         t.layer.p16 = t.views(b16)
+        if self.captured is not None:
+            # stream-ordered copy of what this clock's Read delivered (tests)
+            for name, v in t.layer.p32.items():
+                self.captured[f"{t.layer.name}.{name}"] = v.clone()
 
-    def step(self, x: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
-        """One clock: forward, backward, push.  Returns the mean loss as a 1-element device tensor."""
+    def step(self, x: torch.Tensor, labels: torch.Tensor, capture: bool = False) -> torch.Tensor:
+        """One clock: forward, backward, push.  Returns the mean loss as a 1-element device tensor.
+        capture=True keeps clones of the parameters this clock read in `self.captured`."""
         net = self.net
+        self.captured = {} if capture else None
         h = net.input_layer.forward(x)
         for l, tabs in self.groups:
             for t in tabs:

@@ -1,0 +1,111 @@
+"""End-to-end training steps through the parameter server on one GPU: the layer stack against a
+PyTorch fp32 reference of the same network, and loss going down on a fixed batch."""
+import pytest
+import torch
+import torch.nn.functional as TF
+
+pytestmark = pytest.mark.gpu
+
+from geeps_b200.models.alexnet import alexnet
+from geeps_b200.models.inception_bn import inception_bn_small
+from geeps_b200.ops.layers import Conv2d, Linear, Pool, LRN, Input
+from geeps_b200.models.net import Net
+from geeps_b200.parallel.ps_module import PSModule
+from geeps_b200.utils.config import (DEVICE_CUDA, TABLE_ADDITIVE, TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK, TRANSPORT_TCP,
+                                     GeePsConfig)
+
+_port = [26000]
+
+
+def cfg(transport, **kw):
+    _port[0] += 20
+    base = dict(device=DEVICE_CUDA, cuda_device=0, transport=transport, table_mode=TABLE_SGD_MOMENTUM,
+                tcp_base_port=_port[0], bf16_compute_cache=1, learning_rate=0.01, momentum=0.9)
+    base.update(kw)
+    return GeePsConfig(**base)
+
+
+def tiny_net():
+    layers = [Conv2d("c1", 16, 3, pad=1, relu=True, std=0.1, need_dx=False), LRN(5, 1e-2, 0.75, 1.0), Pool("max", 3, 2),
+              Conv2d("c2", 32, 3, pad=1, groups=2, relu=True, std=0.1), Pool("max", 3, 2),
+              Linear("f1", 64, relu=True, std=0.05), Linear("f2", 10, std=0.05, fp32_out=True)]
+    return Net("tiny", Input(cpad=8), layers)
+
+
+@pytest.mark.parametrize("transport", [TRANSPORT_NVLINK, TRANSPORT_TCP])
+def test_tiny_net_gradients_match_torch(transport):
+    torch.manual_seed(0)
+    dev = torch.device("cuda:0")
+    B = 16
+    with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+        mod = PSModule(tiny_net(), (B, 3, 16, 16), cfg(transport, learning_rate=1.0, momentum=0.0), device=dev,
+                       keep_init=True)
+        x = torch.randn(B, 3, 16, 16, device=dev)
+        y = torch.randint(0, 10, (B,), device=dev)
+        loss = mod.step(x, y).item()                     # clock 1: update = -lr * grad with lr 1, momentum 0
+        mod.step(x, y, capture=True)                     # clock 2 reads p1 = p0 - grad(p0)
+        torch.cuda.synchronize()
+        before = {k: v.to(dev) for k, v in mod.initial_params.items()}
+        after = mod.captured
+        grads = {k: (before[k] - after[k]) for k in before}
+        # ---- the same network in plain PyTorch fp32 on the bf16-rounded parameters ----
+        p = {k: v.to(torch.bfloat16).float().requires_grad_(True) for k, v in before.items()}
+        xb = torch.zeros(B, 8, 16, 16, device=dev)
+        xb[:, :3] = x.to(torch.bfloat16).float()
+
+        def conv_w(w, cin, k):
+            return w[:, :k * k * cin].view(w.shape[0], k, k, cin).permute(0, 3, 1, 2)
+
+        def q(t):   # activations are stored as bf16 between layers (differentiable rounding)
+            return t.to(torch.bfloat16).float()
+
+        h = q(torch.relu(TF.conv2d(xb, conv_w(p["c1.weight"], 8, 3), p["c1.bias"], padding=1)))
+        h = q(TF.local_response_norm(h, 5, alpha=1e-2, beta=0.75, k=1.0))
+        h = TF.max_pool2d(h, 3, 2, ceil_mode=True)
+        h = q(torch.relu(TF.conv2d(h, conv_w(p["c2.weight"], 8, 3), p["c2.bias"], padding=1, groups=2)))
+        h = TF.max_pool2d(h, 3, 2, ceil_mode=True)
+        h = h.permute(0, 2, 3, 1).reshape(B, -1)          # NHWC flatten order
+        h = q(torch.relu(h @ p["f1.weight"].t() + p["f1.bias"]))
+        logits = h @ p["f2.weight"][:, :64].t() + p["f2.bias"]
+        ref_loss = TF.cross_entropy(logits, y)
+        ref_loss.backward()
+        assert abs(loss - ref_loss.item()) < 3e-2 * max(1.0, abs(ref_loss.item())), (loss, ref_loss.item())
+        for k in ("f2.weight", "f1.weight", "c2.weight", "c1.weight", "f2.bias", "c1.bias"):
+            g_ref = p[k].grad
+            g = grads[k]
+            # Frobenius-relative error: a ReLU unit whose pre-activation sits within bf16 rounding of zero
+            # may flip between the two computations and move single entries by one sample's contribution
+            err = ((g - g_ref).norm() / (g_ref.norm() + 1e-12)).item()
+            assert err < 8e-2, (k, err)
+        mod.close()
+
+
+def test_inception_small_loss_decreases():
+    torch.manual_seed(1)
+    dev = torch.device("cuda:0")
+    B = 100
+    with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+        mod = PSModule(inception_bn_small(), (B, 3, 32, 32), cfg(TRANSPORT_NVLINK, learning_rate=0.01), device=dev)
+        x = torch.randn(B, 3, 32, 32, device=dev)
+        y = torch.randint(0, 10, (B,), device=dev)
+        losses = [mod.step(x, y).item() for _ in range(12)]
+        assert all(l == l for l in losses), losses
+        assert losses[-1] < losses[0] - 0.05 and losses == sorted(losses, reverse=True), losses
+        mod.close()
+
+
+def test_alexnet_step_runs_and_learns():
+    torch.manual_seed(2)
+    dev = torch.device("cuda:0")
+    B = 16
+    with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+        net = alexnet(dropout=0.0)
+        mod = PSModule(net, (B, 3, 227, 227), cfg(TRANSPORT_NVLINK, learning_rate=0.01), device=dev)
+        x = torch.randn(B, 3, 227, 227, device=dev)
+        y = torch.randint(0, 1000, (B,), device=dev)
+        losses = [mod.step(x, y).item() for _ in range(8)]
+        assert all(l == l for l in losses), losses
+        assert abs(losses[0] - 6.9) < 0.3, losses       # ln(1000) at random init
+        assert losses[-1] < losses[0], losses
+        assert mod.ps.last_error() == 0
+        mod.close()
