@@ -50,3 +50,79 @@ def helloworld_worker(rank, world, base_port, slack, clocks, q, kw):
         q.put((rank, "ok", final, seen, stats["client"]["max_staleness"], stats))
     except Exception as e:  # pragma: no cover
         q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
+
+
+def nvlink_hello_worker(rank, world, base_port, slack, clocks, q, kw):
+    """Same helloworld-shaped run on the NVLINK transport: one GPU per rank, device-side clocks."""
+    try:
+        import torch
+        from geeps_b200.parallel.ps import GeePs
+        from geeps_b200.utils.config import DEVICE_CUDA, TRANSPORT_NVLINK
+        torch.cuda.set_device(rank)
+        kw = dict(kw)
+        nrows = kw.pop("_rows", 1000)
+        cfg = make_cfg(world, base_port, device=DEVICE_CUDA, cuda_device=rank, transport=TRANSPORT_NVLINK, **kw)
+        stream = torch.cuda.Stream(device=rank)
+        with torch.cuda.stream(stream):
+            g = GeePs(rank, cfg)
+            rows = list(range(nrows))
+            r = g.virtual_read(0, rows, slack)
+            u = g.virtual_pre_update(0, rows)
+            pr = g.virtual_post_read(r)
+            up = g.virtual_update(u)
+            g.virtual_clock()
+            g.finish_virtual_iteration()
+            b = g.pre_update(u)
+            b.zero_()
+            g.update(up)
+            g.clock()
+            g.start_iterations()
+            mins, maxs = [], []
+            extra = slack + 1
+            for c in range(clocks + extra):
+                x = g.read(r)
+                mins.append(x.min().clone())
+                maxs.append(x.max().clone())
+                b = g.pre_update(u)
+                g.post_read(pr)
+                b.fill_(1.0 if c < clocks else 0.0)
+                g.update(up)
+                g.clock()
+            x = g.read(r, asynchronous=False)
+            final = (float(x.min()), float(x.max()))
+            torch.cuda.synchronize()
+            seen = [(i + 1, float(a), float(b)) for i, (a, b) in enumerate(zip(mins, maxs))]
+            err = g.last_error()
+            stats = g.get_stats()
+            g.shutdown()
+            g.close()
+        q.put((rank, "ok" if err == 0 else "error", final if err == 0 else f"runtime error {err}", seen, 0, stats))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
+
+
+def nvlink_train_worker(rank, world, base_port, steps, q, kw):
+    """Data-parallel training of the small Inception-BN through the NVLINK parameter server."""
+    try:
+        import torch
+        from geeps_b200.models.inception_bn import inception_bn_small
+        from geeps_b200.parallel.ps_module import PSModule
+        from geeps_b200.utils.config import DEVICE_CUDA, TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK
+        torch.cuda.set_device(rank)
+        cfg = make_cfg(world, base_port, device=DEVICE_CUDA, cuda_device=rank, transport=TRANSPORT_NVLINK,
+                       table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.02, momentum=0.9, grad_scale=1.0 / world,
+                       bf16_compute_cache=1, **kw)
+        dev = torch.device("cuda", rank)
+        with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+            mod = PSModule(inception_bn_small(), (50, 3, 32, 32), cfg, rank=rank, world=world, device=dev, seed=3)
+            gen = torch.Generator(device=dev).manual_seed(100 + rank)
+            x = torch.randn(50, 3, 32, 32, device=dev, generator=gen)
+            y = torch.randint(0, 10, (50,), device=dev, generator=gen)
+            losses = [mod.step(x, y, capture=(i == steps - 1)).item() for i in range(steps)]
+            torch.cuda.synchronize()
+            digest = {k: float(v.double().sum()) for k, v in list(mod.captured.items())[:6]}
+            err = mod.ps.last_error()
+            mod.close()
+        q.put((rank, "ok" if err == 0 else "error", losses, digest, err, None))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))

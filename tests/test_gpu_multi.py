@@ -1,0 +1,56 @@
+"""Multi-GPU parameter server over NVLink peer memory: one process per GPU."""
+import multiprocessing as mp
+import os
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+from ps_workers import nvlink_hello_worker, nvlink_train_worker
+
+_port = [31000 + (os.getpid() % 300) * 40]
+
+
+def _spawn(target, world, args):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    _port[0] += 100
+    procs = [ctx.Process(target=target, args=(r, world, _port[0]) + args + (q,) + ({},)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for o in out:
+        assert o[1] == "ok", o[2]
+    return sorted(out)
+
+
+def _world():
+    import torch
+    n = torch.cuda.device_count()
+    return 8 if n >= 8 else 4 if n >= 4 else 2
+
+
+@pytest.mark.parametrize("slack", [0, 1])
+def test_nvlink_helloworld(slack):
+    world, clocks = _world(), 50
+    out = _spawn(nvlink_hello_worker, world, (slack, clocks))
+    for rank, _, final, seen, _, stats in out:
+        assert final == (float(world * clocks),) * 2, final
+        for clock, lo, hi in seen:
+            need = world * max(0, min(clock - slack - 1, clocks))
+            most = min(clock - 1, clocks) + (world - 1) * min(clock + slack, clocks)
+            assert lo >= need - 1e-6, (clock, lo, need)
+            assert hi <= most + 1e-6, (clock, hi, most)
+
+
+def test_nvlink_data_parallel_training_is_consistent():
+    world = _world()
+    out = _spawn(nvlink_train_worker, world, (10,))
+    digests = [o[3] for o in out]
+    for d in digests[1:]:
+        assert d == digests[0]          # every worker reads bit-identical parameters
+    for o in out:
+        losses = o[2]
+        assert all(l == l for l in losses) and losses[-1] < losses[0], losses
