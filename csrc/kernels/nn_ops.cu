@@ -756,3 +756,80 @@ int geeps_softmax_ce(const float* logits, const long long* labels, float* loss_s
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// BatchNorm forward for callers that must not allocate device memory.
+//
+// geeps_bn_forward needs 2*C floats of scratch for the per-channel sums and leaves it to the
+// caller to provide them.  Two kinds of callers of this library cannot do that: code running
+// under the parameter server's memory plan, where every byte of the GPU budget has been handed
+// out before the first clock and no allocator exists in steady state, and plain C/C++ hosts that
+// link the library without any device allocator of their own and must not pay cudaMalloc's
+// device-wide synchronisation inside their step loop.  For them the scratch lives in the
+// library image itself: a fixed array in device memory, sized for GEEPS_BN_NOALLOC_MAX_CHANNELS
+// channels (32 KB), that every GPU loading the library holds until the process exits.
+//
+// The array is shared by all calls and keeps whatever the previous call left in it, so the
+// entry point clears the part it uses on the caller's stream before the reduction.  Two calls
+// whose kernels can overlap on the GPU (different streams, no ordering between them) race on it.
+// ---------------------------------------------------------------------------------------------
+#include <stdio.h>
+#include <mutex>
+
+#define GEEPS_BN_NOALLOC_MAX_CHANNELS_IMPL 4096
+static __device__ __align__(256) float g_bn_noalloc_scratch[2 * GEEPS_BN_NOALLOC_MAX_CHANNELS_IMPL];
+
+namespace {
+constexpr int kNoallocMaxDevices = 64;
+float* g_bn_noalloc_ptr[kNoallocMaxDevices] = {};
+std::mutex g_bn_noalloc_mu;
+
+// Device address of the scratch array on the current device.  In host code the array's name is
+// only a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress,
+// looked up once per device with that device current.
+int bn_noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoallocMaxDevices) return (int)cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lk(g_bn_noalloc_mu);
+  if (g_bn_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_bn_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_bn_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_bn_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+int geeps_bn_noalloc_max_channels() { return GEEPS_BN_NOALLOC_MAX_CHANNELS_IMPL; }
+
+int geeps_bn_forward_noalloc(const void* x, void* y, const float* gamma, const float* beta, float* mean_rstd,
+                             float* running_mean, float* running_var, long long P, int C, long long ldx,
+                             long long ldy, float eps, float momentum, int relu, void* stream) {
+  if (C <= 0 || C % 8) return (int)cudaErrorInvalidValue;
+  if (C > GEEPS_BN_NOALLOC_MAX_CHANNELS_IMPL) {
+    fprintf(stderr, "geeps_bn_forward_noalloc: %d channels exceed the built-in scratch of %d channels; "
+                    "use geeps_bn_forward with caller-provided scratch\n", C, GEEPS_BN_NOALLOC_MAX_CHANNELS_IMPL);
+    return GEEPS_ERR_NOALLOC_TOO_LARGE;
+  }
+  float* sums = nullptr;
+  const int rc = bn_noalloc_scratch(&sums);   // first call on a device resolves the address
+  if (rc != 0) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st);   // the array keeps the last call's sums
+  if (e != cudaSuccess) return (int)e;
+  channel_reduce_kernel<0><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
+      (const bf16*)x, nullptr, nullptr, nullptr, sums, P, C, ldx, 0, 0, 1.f);
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, mean_rstd, running_mean, running_var, C,
+                                                      1.f / (float)P, eps, momentum);
+  bn_apply_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (bf16*)y, mean_rstd, gamma, beta, P, C, ldx,
+                                                        ldy, relu);
+  return CK();
+}
+
+}  // extern "C"

@@ -51,6 +51,27 @@ int geeps_softmax_ce(const float* logits, const long long* labels, float* loss_s
                      void* dlogits, int B, int C, long long ldl, long long ldd, float loss_scale, float grad_scale,
                      int zero_loss, int* status, void* stream);
 
+// ---- allocation-free BatchNorm forward (no counterpart in the reference, which has no layer kernels) ----
+// Same result as geeps_bn_forward, but the 2*C floats of reduction scratch come from a fixed device
+// array inside the library (GEEPS_BN_NOALLOC_MAX_CHANNELS channels, 32 KB per GPU, held until exit)
+// instead of from the caller.  It is meant for callers that cannot allocate: code under the parameter
+// server's fully planned GPU budget, and hosts without a device allocator that must keep cudaMalloc's
+// device-wide synchronisation out of their step loop.  The call itself never calls cudaMalloc / cudaFree
+// or any allocating library routine.
+//  * C must be a multiple of 8 and <= GEEPS_BN_NOALLOC_MAX_CHANNELS; a larger C is rejected with
+//    GEEPS_ERR_NOALLOC_TOO_LARGE (and a message on stderr) without launching anything.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+//    device current); make that first call before any stream capture begins.
+//  * All calls share the one array, which keeps the previous call's contents; the part in use is cleared
+//    on `stream` first.  Calls whose kernels may overlap on the GPU race on it: keep them on one stream
+//    or order them with events.
+#define GEEPS_BN_NOALLOC_MAX_CHANNELS 4096
+#define GEEPS_ERR_NOALLOC_TOO_LARGE (-2)
+int geeps_bn_noalloc_max_channels(void);
+int geeps_bn_forward_noalloc(const void* x, void* y, const float* gamma, const float* beta, float* mean_rstd,
+                             float* running_mean, float* running_var, long long P, int C, long long ldx,
+                             long long ldy, float eps, float momentum, int relu, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
