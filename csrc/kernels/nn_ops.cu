@@ -374,6 +374,112 @@ lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, cons
   }
 }
 
+// Vector forms: one thread owns 8 consecutive channels of a pixel and slides the window over the
+// 24 channels around them (window half-width <= 8); each squared value / ratio is computed once.
+__global__ void __launch_bounds__(256)
+lrn_forward_v8_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __restrict__ scale, long long P, int C,
+                      int size, float alpha, float beta, float k) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int half = size / 2;
+  const float a_n = alpha / (float)size;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long base = (i / cv) * C;
+    float sq[24];
+#pragma unroll
+    for (int v = 0; v < 3; ++v) {
+      const int cc = c + (v - 1) * 8;
+      if (cc >= 0 && cc < C) {
+        Bf8 t = ld8(x + base + cc);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { float f = bf(t.v[e]); sq[v * 8 + e] = v == 1 ? f : f * f; }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sq[v * 8 + e] = 0.f;
+      }
+    }
+    float xv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { xv[e] = sq[8 + e]; sq[8 + e] = xv[e] * xv[e]; }
+    Bf8 o;
+    float sc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 24; ++j)
+        if (j >= 8 + e - half && j <= 8 + e + half) s += sq[j];
+      sc[e] = k + a_n * s;
+      o.v[e] = __float2bfloat16(xv[e] * __powf(sc[e], -beta));
+    }
+    st8(y + base + c, o);
+    st_f4(scale + base + c, make_float4(sc[0], sc[1], sc[2], sc[3]));
+    st_f4(scale + base + c + 4, make_float4(sc[4], sc[5], sc[6], sc[7]));
+  }
+}
+__global__ void __launch_bounds__(256)
+lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ scale,
+                       const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
+                       float beta) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int half = size / 2;
+  const float coef = 2.f * alpha * beta / (float)size;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long base = (i / cv) * C;
+    float ratio[24], dyc[8], scc[8];
+#pragma unroll
+    for (int v = 0; v < 3; ++v) {
+      const int cc = c + (v - 1) * 8;
+      if (cc >= 0 && cc < C) {
+        Bf8 d = ld8(dy + base + cc), yy = ld8(y + base + cc);
+        const float4 s0 = ld_f4(scale + base + cc), s1 = ld_f4(scale + base + cc + 4);
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          ratio[v * 8 + e] = __fdividef(bf(d.v[e]) * bf(yy.v[e]), sv[e]);
+          if (v == 1) { dyc[e] = bf(d.v[e]); scc[e] = sv[e]; }
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ratio[v * 8 + e] = 0.f;
+      }
+    }
+    Bf8 xv = ld8(x + base + c), o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 24; ++j)
+        if (j >= 8 + e - half && j <= 8 + e + half) acc += ratio[j];
+      o.v[e] = __float2bfloat16(dyc[e] * __powf(scc[e], -beta) - coef * bf(xv.v[e]) * acc);
+    }
+    st8(dx + base + c, o);
+  }
+}
+
+// NCHW fp32 -> NHWC bf16, one thread per pixel: reads are coalesced along W in every channel plane
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_pix_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int C, int HW, int Cpad) {
+  const long long total = (long long)B * HW;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long b = i / HW, p = i % HW;
+    const float* src = x + b * C * HW + p;
+    bf16* dst = y + i * Cpad;
+    for (int c0 = 0; c0 < Cpad; c0 += 4) {
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = (c0 + e < C) ? src[(long long)(c0 + e) * HW] : 0.f;
+      *reinterpret_cast<uint2*>(dst + c0) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+    }
+  }
+}
+
 // ---------------- pooling (NHWC, 8 channels per thread) ----------------
 // Output may be a channel slice of a wider tensor (pitch ldy, offset applied by the caller).
 __global__ void __launch_bounds__(256)
@@ -603,7 +709,10 @@ extern "C" {
 
 int geeps_nchw_f32_to_nhwc_bf16(const float* x, void* y, int B, int C, int H, int W, int Cpad, void* stream) {
   const long long n = (long long)B * H * W * Cpad;
-  nchw_f32_to_nhwc_bf16_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H, W, Cpad);
+  if (Cpad % 4 == 0)
+    nchw_to_nhwc_pix_kernel<<<grid_1d((long long)B * H * W), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H * W, Cpad);
+  else
+    nchw_f32_to_nhwc_bf16_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H, W, Cpad);
   return CK();
 }
 
@@ -706,15 +815,23 @@ int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long lo
 
 int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, int size, float alpha, float beta,
                       float k, void* stream) {
-  lrn_forward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, scale, P, C, size,
-                                                                      alpha, beta, k);
+  if (C % 8 == 0 && size / 2 <= 8)
+    lrn_forward_v8_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, scale, P, C,
+                                                                                size, alpha, beta, k);
+  else
+    lrn_forward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, scale, P, C, size,
+                                                                        alpha, beta, k);
   return CK();
 }
 int geeps_lrn_backward(const void* x, const void* y, const float* scale, const void* dy, void* dx, long long P,
                        int C, int size, float alpha, float beta, void* stream) {
-  lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, scale,
-                                                                       (const bf16*)dy, (bf16*)dx, P, C, size, alpha,
-                                                                       beta);
+  if (C % 8 == 0 && size / 2 <= 8)
+    lrn_backward_v8_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
+        (const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
+  else
+    lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, scale,
+                                                                         (const bf16*)dy, (bf16*)dx, P, C, size, alpha,
+                                                                         beta);
   return CK();
 }
 

@@ -42,8 +42,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0) {
-      if (*abort_flag) return false;
-      if (geeps_globaltimer() - t0 > budget_ns) { *abort_flag = 1; return false; }
+      // give up only if the phase really did not complete: every waiter of one phase must reach the
+      // same verdict, because the epilogue warps meet at a named barrier afterwards
+      if (*abort_flag) return mbar_try_wait(bar, parity);
+      if (geeps_globaltimer() - t0 > budget_ns) { *abort_flag = 1; return mbar_try_wait(bar, parity); }
     }
   }
 }
@@ -57,6 +59,26 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
 }
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+// Tiled 2-D store / reduce-add from swizzled smem to global (bulk async group of the issuing thread).
+// Coordinates must be non-negative; x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// wait until at most N of this thread's bulk groups still READ their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// wait until at most N of this thread's bulk groups are incomplete (writes performed)
+template <int N>
+__device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 // Make generic-proxy smem writes (st.shared) visible to the async proxy (UMMA reads).
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -1,0 +1,107 @@
+"""Kernel micro-benchmarks: python -m geeps_b200.utils.microbench [gemm|ps|rows|all]
+
+Every number is a CUDA-event time on the launching stream after warm-up, with a buffer larger than
+L2 written between timed launches.  GEMM lines also give cuBLAS (torch.matmul) on the same shape and
+the fraction of the measured bf16 peak (MEASURED_PEAKS.json if present, else 1590 TFLOP/s)."""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+
+from ..ops import functional as F
+
+BF = torch.bfloat16
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+def timeit(fn, iters=10, flush=None):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1.0)          # 256 MB write: evicts L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(shapes=None):
+    dev = torch.device("cuda")
+    peak, _, src = _peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    shapes = shapes or [
+        ("square 8192", 8192, 8192, 8192, False, False, False),
+        ("square 4096", 4096, 4096, 4096, False, False, False),
+        ("conv1 fwd", 774400, 96, 488, False, False, False),
+        ("conv2 fwd (1 group)", 186624, 128, 1200, False, False, False),
+        ("conv3 fwd", 43264, 384, 2304, False, False, False),
+        ("conv3 dgrad", 43264, 2304, 384, False, True, False),
+        ("conv3 wgrad", 384, 2304, 43264, True, True, True),
+        ("conv2 dgrad (1 group)", 186624, 1200, 128, False, True, False),
+        ("fc6 fwd", 256, 4096, 9216, False, False, False),
+        ("fc6 dgrad", 256, 9216, 4096, False, True, False),
+        ("fc6 wgrad", 4096, 9216, 256, True, True, True),
+    ]
+    rows = []
+    for name, M, N, K, a_mn, b_mn, f32 in shapes:
+        a = (torch.randn((K, M) if a_mn else (M, K), device=dev) * 0.1).to(BF)
+        b = (torch.randn((K, N) if b_mn else (N, K), device=dev) * 0.1).to(BF)
+        out = torch.empty(M, N, dtype=torch.float32 if f32 else BF, device=dev)
+        t = timeit(lambda: F.gemm(a, b, out, a_mn=a_mn, b_mn=b_mn, split_k=0 if f32 else 1), flush=flush)
+        A = a.t() if a_mn else a
+        Bm = b if b_mn else b.t()
+        t_ref = timeit(lambda: torch.matmul(A, Bm), flush=flush)
+        tf = 2.0 * M * N * K / t / 1e9
+        rows.append({"shape": name, "M": M, "N": N, "K": K, "ms": round(t, 4), "tflops": round(tf, 1),
+                     "frac_of_peak": round(tf / peak, 3), "peak_source": src, "cublas_ms": round(t_ref, 4),
+                     "cublas_tflops": round(2.0 * M * N * K / t_ref / 1e9, 1)})
+        print(json.dumps(rows[-1]), flush=True)
+        del a, b, out
+    return rows
+
+
+def bench_rows():
+    dev = torch.device("cuda")
+    _, hbm, src = _peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    n = 1 << 20   # 512 MB of rows
+    cache = torch.randn(n, 128, device=dev)
+    buf = torch.empty(n, 128, device=dev)
+    idx = torch.stack([torch.arange(n, device=dev), torch.randperm(n, device=dev)], 1).contiguous()
+    for name, fn, nbytes in (("row_gather", lambda: F.row_gather(buf, cache, idx), 2 * n * 512),
+                             ("row_scatter_add", lambda: F.row_scatter_add(cache, buf, idx), 3 * n * 512)):
+        t = timeit(fn, flush=flush)
+        gbs = nbytes / t / 1e6
+        print(json.dumps({"kernel": name, "rows": n, "ms": round(t, 4), "gb_s": round(gbs, 1),
+                          "frac_of_hbm": round(gbs / hbm, 3), "peak_source": src}), flush=True)
+
+
+def main():
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("gemm", "all"):
+        bench_gemm()
+    if what in ("rows", "all"):
+        bench_rows()
+
+
+if __name__ == "__main__":
+    main()
