@@ -121,6 +121,7 @@ def main() -> None:
     from geeps_b200.models.inception_bn import inception_bn_22k, inception_bn_small
     from geeps_b200.ops import _lib as L
     from geeps_b200.parallel.ps_module import PSModule
+    from geeps_b200.utils.feeder import HostFeeder, LossMailbox
     from geeps_b200.utils.config import (DEVICE_CUDA, TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK, TRANSPORT_TCP, GeePsConfig)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -155,9 +156,6 @@ def main() -> None:
         y_dev = torch.randint(0, classes, (B,), device=dev, generator=gen)
         x_host = torch.randn((B,) + image).pin_memory()
         y_host = torch.randint(0, classes, (B,)).pin_memory()
-        x_in = torch.empty_like(x_dev)
-        y_in = torch.empty_like(y_dev)
-        loss_host = torch.zeros(1).pin_memory()
 
         def barrier():
             torch.cuda.synchronize(dev)
@@ -193,13 +191,21 @@ def main() -> None:
         def step_device():
             return mod.step(x_dev, y_dev)
 
+        feeder = HostFeeder((B,) + image, (B,), dev)
+        mailbox = LossMailbox(dev)
+        feeder.submit(x_host, y_host)
+
         def step_e2e():
-            x_in.copy_(x_host, non_blocking=True)
-            y_in.copy_(y_host, non_blocking=True)
-            loss = mod.step(x_in, y_in)
-            loss_host.copy_(loss, non_blocking=True)
-            stream.synchronize()             # the caller reads the loss every step
-            return loss_host
+            # every step: this step's batch comes from pinned host memory (its copy was started one step
+            # earlier on the copy stream), the next batch's copy starts now, and the loss goes back to the
+            # host; the host reads each step's loss one step later, so the launch queue never drains
+            xb, yb, slot = feeder.next(stream)
+            feeder.submit(x_host, y_host)
+            loss = mod.step(xb, yb)
+            feeder.release(slot, stream)
+            mailbox.post(loss, stream)
+            mailbox.collect(lag=1)
+            return loss
 
         for _ in range(max(args.warmup, 3)):
             step_device()
@@ -210,7 +216,7 @@ def main() -> None:
                 step_e2e()
             ms_e, _, _, _ = timed(step_e2e, args.steps)
             e2e = {"value": B * world * args.steps / (ms_e / 1e3), "unit": "images/s",
-                   "h2d_bytes_per_step": x_host.numel() * 4 + y_host.numel() * 8, "d2h_bytes_per_step": 4,
+                   "h2d_bytes_per_step": feeder.bytes_per_batch, "d2h_bytes_per_step": mailbox.bytes_per_step,
                    "ms_per_step": ms_e / args.steps}
         stats = mod.ps.get_stats()
         # kernels launched inside the runtime (flag signal + flag wait + push/apply per table per clock,

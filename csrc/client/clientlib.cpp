@@ -25,9 +25,15 @@ FlatOps* OpMemBufferPool::get(size_t budget_ms) {
   std::unique_lock<std::mutex> lk(mu_);
   const double t0 = now_seconds();
   while (free_.empty()) {
-    if (cv_.wait_for(lk, std::chrono::seconds(kWatchdogSeconds)) == std::cv_status::timeout)
+    double wait_ms = kWatchdogSeconds * 1000.0;
+    if (budget_ms) {
+      const double left = (double)budget_ms - (now_seconds() - t0) * 1000.0;
+      if (left <= 0) return nullptr;
+      if (left < wait_ms) wait_ms = left;
+    }
+    if (cv_.wait_for(lk, std::chrono::microseconds((long long)(wait_ms * 1000))) == std::cv_status::timeout &&
+        wait_ms >= kWatchdogSeconds * 1000.0)
       fprintf(stderr, "[geeps] oplog pool: all %zu entries in flight, still waiting\n", all_.size());
-    if (budget_ms && (now_seconds() - t0) * 1000.0 > (double)budget_ms) return nullptr;
   }
   FlatOps* e = free_.front();
   free_.erase(free_.begin());

@@ -176,11 +176,17 @@ size_t MultithreadedCacheHelper::get(size_t count, bool wait, int tag, size_t bu
   for (;;) {
     size_t s = try_get_locked(count, tag);
     if (s != (size_t)-1 || !wait) return s;
-    if (cv_.wait_for(lk, std::chrono::seconds(kWatchdogSeconds)) == std::cv_status::timeout) {
+    double wait_ms = kWatchdogSeconds * 1000.0;
+    if (budget_ms) {
+      const double left = (double)budget_ms - (now_seconds() - t0) * 1000.0;
+      if (left <= 0) return (size_t)-1;
+      if (left < wait_ms) wait_ms = left;
+    }
+    if (cv_.wait_for(lk, std::chrono::microseconds((long long)(wait_ms * 1000))) == std::cv_status::timeout &&
+        wait_ms >= kWatchdogSeconds * 1000.0) {
       fprintf(stderr, "[geeps] staging pool: tag %d still waiting for %zu rows (%zu of %zu used)\n", tag, count,
               used_, size_);
     }
-    if (budget_ms && (now_seconds() - t0) * 1000.0 > (double)budget_ms) return (size_t)-1;
   }
 }
 

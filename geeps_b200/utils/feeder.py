@@ -1,0 +1,71 @@
+"""Host -> device input pipeline: double-buffered asynchronous copies from pinned host memory on a
+copy stream, so the transfer of batch i+1 overlaps the training step of batch i, and a pinned
+mailbox through which the loss of every step is read back without stalling the launch queue."""
+from __future__ import annotations
+
+import torch
+
+
+class HostFeeder:
+    def __init__(self, x_shape, y_shape, device, depth: int = 2):
+        self.device = torch.device(device)
+        self.copy_stream = torch.cuda.Stream(device=self.device)
+        self.x = [torch.empty(x_shape, device=self.device) for _ in range(depth)]
+        self.y = [torch.empty(y_shape, dtype=torch.int64, device=self.device) for _ in range(depth)]
+        self.ready = [torch.cuda.Event() for _ in range(depth)]
+        self.free = [torch.cuda.Event() for _ in range(depth)]
+        self.depth, self.put_i, self.get_i = depth, 0, 0
+        self.bytes_per_batch = self.x[0].numel() * 4 + self.y[0].numel() * 8
+        for e in self.free:
+            e.record(torch.cuda.current_stream(self.device))
+
+    def submit(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """Start copying one batch (pinned host tensors) into the next device slot."""
+        s = self.put_i % self.depth
+        self.copy_stream.wait_event(self.free[s])      # the step that used this slot has finished with it
+        with torch.cuda.stream(self.copy_stream):
+            self.x[s].copy_(x_host, non_blocking=True)
+            self.y[s].copy_(y_host, non_blocking=True)
+            self.ready[s].record(self.copy_stream)
+        self.put_i += 1
+
+    def next(self, stream=None):
+        """Device tensors of the oldest submitted batch; `stream` waits for its copy."""
+        stream = stream or torch.cuda.current_stream(self.device)
+        s = self.get_i % self.depth
+        stream.wait_event(self.ready[s])
+        self.get_i += 1
+        return self.x[s], self.y[s], s
+
+    def release(self, slot: int, stream=None) -> None:
+        """Call after the step that consumed `slot` has been enqueued."""
+        self.free[slot].record(stream or torch.cuda.current_stream(self.device))
+
+
+class LossMailbox:
+    """Reads a 1-element device tensor back every step through pinned memory; `collect` returns the
+    value of the previous step (already complete), so the host never waits for the step just launched."""
+
+    def __init__(self, device, depth: int = 2):
+        self.host = [torch.zeros(1).pin_memory() for _ in range(depth)]
+        self.done = [torch.cuda.Event() for _ in range(depth)]
+        self.depth, self.i = depth, 0
+        self.bytes_per_step = 4
+
+    def post(self, loss: torch.Tensor, stream=None) -> None:
+        s = self.i % self.depth
+        self.host[s].copy_(loss, non_blocking=True)
+        self.done[s].record(stream or torch.cuda.current_stream(loss.device))
+        self.i += 1
+
+    def collect(self, lag: int = 1):
+        if self.i - 1 - lag < 0:
+            return None
+        s = (self.i - 1 - lag) % self.depth
+        self.done[s].synchronize()
+        return float(self.host[s][0])
+
+    def last(self) -> float:
+        s = (self.i - 1) % self.depth
+        self.done[s].synchronize()
+        return float(self.host[s][0])

@@ -126,3 +126,45 @@ def nvlink_train_worker(rank, world, base_port, steps, q, kw):
         q.put((rank, "ok" if err == 0 else "error", losses, digest, err, None))
     except Exception as e:  # pragma: no cover
         q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
+
+
+def fault_worker(rank, world, base_port, mode, q, kw):
+    """Host-side fault injection (no GPU): mode 'exit' - rank 1 leaves after 3 clocks without shutdown;
+    'mute' - rank 1 stops sending heartbeats; 'drop' - rank 0 drops an inbound row batch."""
+    try:
+        import time
+        import torch
+        from geeps_b200.parallel.ps import GeePs, GeePsError
+        from geeps_b200.utils.config import DEVICE_CPU
+        cfg = make_cfg(world, base_port, device=DEVICE_CPU, **kw)
+        g = GeePs(rank, cfg)
+        rows = list(range(64))
+        r = g.virtual_read(0, rows, 0); u = g.virtual_pre_update(0, rows)
+        pr = g.virtual_post_read(r); up = g.virtual_update(u); g.virtual_clock()
+        g.finish_virtual_iteration()
+        g.pre_update(u).zero_(); g.update(up); g.clock(); g.start_iterations()
+        t0 = time.time()
+        result = ("ok", 0, "")
+        try:
+            for c in range(40):
+                if c == 3 and rank == 1 and mode == "exit":
+                    q.put((rank, "left", 0, "", 0.0))
+                    q.close(); q.join_thread()        # flush the message before dying
+                    os._exit(0)                       # dies between steps, sockets close
+                if c == 3 and rank == 1 and mode == "mute":
+                    g.inject(0, 1)
+                    time.sleep(kw.get("heartbeat_timeout_ms", 1000) / 1000.0 * 3)
+                if c == 3 and rank == 0 and mode == "drop":
+                    g.inject(2, 1)
+                x = g.read(r, asynchronous=False)
+                b = g.pre_update(u); g.post_read(pr); b.fill_(1.0); g.update(up); g.clock()
+                if mode == "mute" and rank == 1 and c > 6:
+                    break
+        except GeePsError as e:
+            result = ("error", e.code, str(e))
+        dt = time.time() - t0
+        q.put((rank, result[0], result[1], result[2], dt))
+        q.close(); q.join_thread()
+        os._exit(0)                                   # skip the coordinated shutdown: peers may be gone
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "exception", -1, repr(e) + traceback.format_exc(), 0.0))
