@@ -16,8 +16,9 @@ def main():
     ap.add_argument("--clocks", type=int, default=10)
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    dev = torch.device("cuda")
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     for mb in a.mb:
         n = int(mb * 1024 * 1024 / 4) // (128 * world) * (128 * world)

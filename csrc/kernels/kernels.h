@@ -90,6 +90,24 @@ int geeps_gemm_tc_supported(const GeepsGemmParams* p);             // 1 if the t
 // C[m][n] = beta * C[m][n] (exactly 0 when beta == 0) over an M x N view with pitch ldc
 int geeps_scale_matrix_f32(float* c, long long M, long long N, long long ldc, float beta, void* stream);
 
+// ---------------- parameter pull fused with the consuming GEMM ----------------
+// Y[M,N] = X[M,K] * W[N,K]^T + bias (+ReLU), M <= 256, K a multiple of 64.  W's rows live on the server
+// shards: shard s holds rows [n_start[s], n_start[s+1]) (n_start[n_shards] = N) as bf16 at w_shard[s]
+// (a peer pointer, row pitch ldw elements).  ready[s] (local int flag or NULL) must reach needed_stamp
+// before shard s is read.  w_local (or NULL) receives a full local copy [N][ldw] of what was pulled.
+typedef struct GeepsPullGemmParams {
+  const void* X; void* Y; const float* bias;
+  const void* w_shard[GEEPS_MAX_RANKS];
+  const int* ready[GEEPS_MAX_RANKS];
+  long long n_start[GEEPS_MAX_RANKS + 1];
+  void* w_local;
+  int* status;
+  long long M, N, K, ldx, ldw, ldy;
+  unsigned long long wait_budget_ns;
+  int n_shards, needed_stamp, relu, out_fp32, block_n;
+} GeepsPullGemmParams;
+int geeps_pull_gemm_bf16(const GeepsPullGemmParams* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -53,6 +53,20 @@ class PullParams(C.Structure):
     ]
 
 
+class PullGemmParams(C.Structure):
+    _fields_ = [
+        ("X", C.c_void_p), ("Y", C.c_void_p), ("bias", C.c_void_p),
+        ("w_shard", C.c_void_p * MAX_RANKS), ("ready", C.c_void_p * MAX_RANKS),
+        ("n_start", C.c_longlong * (MAX_RANKS + 1)),
+        ("w_local", C.c_void_p), ("status", C.c_void_p),
+        ("M", C.c_longlong), ("N", C.c_longlong), ("K", C.c_longlong),
+        ("ldx", C.c_longlong), ("ldw", C.c_longlong), ("ldy", C.c_longlong),
+        ("wait_budget_ns", C.c_ulonglong),
+        ("n_shards", C.c_int), ("needed_stamp", C.c_int), ("relu", C.c_int), ("out_fp32", C.c_int),
+        ("block_n", C.c_int),
+    ]
+
+
 class FlagList(C.Structure):
     _fields_ = [("ptr", C.c_void_p * MAX_RANKS), ("n", C.c_int)]
 

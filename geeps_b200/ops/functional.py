@@ -221,3 +221,31 @@ def row_scatter(dst, src, index, dst_off=0, src_off=0, num_vals_limit=None, stat
 def row_scatter_add(dst, src, index, dst_off=0, src_off=0, num_vals_limit=None, status=None) -> None:
     """dst[id1 + dst_off] += src[id0 + src_off]."""
     _row_op(lib().geeps_row_scatter_add, "row_scatter_add", dst, src, index, dst_off, src_off, num_vals_limit, status)
+
+
+def pull_gemm(x, w_shard_ptrs, n_start, out, *, ldw, bias=None, relu=False, ready_ptrs=None, needed_stamp=0,
+              w_local=None, status=None, wait_budget_ns=2_000_000_000, block_n=0) -> torch.Tensor:
+    """out[M,N] = x[M,K] @ W[N,K]^T (+bias, ReLU) where W's rows are pulled from the shards while the
+    GEMM runs.  w_shard_ptrs[s]: device address (local or peer) of shard s's bf16 rows
+    [n_start[s], n_start[s+1]); ready_ptrs[s]: address of the int flag that must reach needed_stamp."""
+    L.require_cuda()
+    M, K = x.shape
+    N = out.shape[1]
+    p = L.PullGemmParams()
+    p.X, p.Y, p.bias = x.data_ptr(), out.data_ptr(), (bias.data_ptr() if bias is not None else None)
+    for s, a in enumerate(w_shard_ptrs):
+        p.w_shard[s] = a
+        p.ready[s] = ready_ptrs[s] if ready_ptrs is not None else None
+    for s, v in enumerate(n_start):
+        p.n_start[s] = v
+    p.n_start[len(w_shard_ptrs)] = N
+    p.w_local = w_local.data_ptr() if w_local is not None else None
+    p.status = status.data_ptr() if status is not None else None
+    p.M, p.N, p.K = M, N, K
+    p.ldx, p.ldw, p.ldy = _ld(x), ldw, _ld(out)
+    p.wait_budget_ns = wait_budget_ns
+    p.n_shards, p.needed_stamp, p.relu = len(w_shard_ptrs), needed_stamp, int(relu)
+    p.out_fp32 = int(out.dtype == torch.float32)
+    p.block_n = block_n
+    check(lib().geeps_pull_gemm_bf16(C.byref(p), stream_ptr()), "pull_gemm_bf16")
+    return out

@@ -168,3 +168,76 @@ def fault_worker(rank, world, base_port, mode, q, kw):
         os._exit(0)                                   # skip the coordinated shutdown: peers may be gone
     except Exception as e:  # pragma: no cover
         q.put((rank, "exception", -1, repr(e) + traceback.format_exc(), 0.0))
+
+
+def nvlink_pull_gemm_worker(rank, world, base_port, M, N, K, q, kw):
+    """Fused pull+GEMM with the weight shards on different GPUs (peer pointers from torch symmetric
+    memory); returns the max error vs an fp32 reference and timings vs all_gather + matmul."""
+    try:
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        from geeps_b200.ops import functional as F
+        from geeps_b200.ops import _lib as L
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(base_port), RANK=str(rank), WORLD_SIZE=str(world))
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", device_id=dev)
+        per = (N + world - 1) // world
+        n_start = [min(s * per, N) for s in range(world)]
+        rows = [(n_start[s + 1] if s + 1 < world else N) - n_start[s] for s in range(world)]
+        shard = symm_mem.empty((per, K), dtype=torch.bfloat16, device=dev)
+        hdl = symm_mem.rendezvous(shard, dist.group.WORLD.group_name)
+        full = []
+        for s in range(world):
+            g = torch.Generator(device=dev).manual_seed(1000 + s)
+            full.append((torch.randn(per, K, device=dev, generator=g) * 0.1).to(torch.bfloat16))
+        shard.copy_(full[rank])
+        w = torch.cat([full[s][:rows[s]] for s in range(world)], 0)
+        x = (torch.randn(M, K, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * 0.3).to(torch.bfloat16)
+        ready = torch.full((world,), 3, dtype=torch.int32, device=dev)
+        out = torch.zeros(M, (N + 7) // 8 * 8, dtype=torch.float32, device=dev)[:, :N]
+        w_local = torch.zeros(N, K, dtype=torch.bfloat16, device=dev)
+        st = L.new_status(dev)
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+
+        def fused():
+            F.pull_gemm(x, [int(p) for p in hdl.buffer_ptrs], n_start, out, ldw=K,
+                        ready_ptrs=[ready.data_ptr() + 4 * s for s in range(world)], needed_stamp=3, w_local=w_local,
+                        status=st)
+
+        gathered = torch.empty(world * per, K, dtype=torch.bfloat16, device=dev)
+        out2 = torch.empty(M, world * per, dtype=torch.float32, device=dev)
+
+        def baseline():
+            dist.all_gather_into_tensor(gathered, shard)
+            torch.matmul(x, gathered.t(), out=out2.to(torch.bfloat16))
+
+        def timeit(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record(); e1.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+
+        fused()
+        torch.cuda.synchronize()
+        err = (out - x.float() @ w.float().t()).abs().max().item()
+        same = bool(torch.equal(w_local, w))
+        code = L.read_status(st)["code"]
+        t_fused = timeit(fused)
+        t_base = timeit(baseline)
+        link_ms = (world - 1) / world * N * K * 2 / 770e9 * 1e3
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok", dict(err=err, w_local_ok=same, status=code, fused_ms=t_fused, nccl_allgather_matmul_ms=t_base,
+                                nvlink_roofline_ms=link_ms, frac_of_roofline=link_ms / t_fused), None, None, None))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))

@@ -6,7 +6,7 @@ import pytest
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
-from ps_workers import nvlink_hello_worker, nvlink_train_worker
+from ps_workers import nvlink_hello_worker, nvlink_pull_gemm_worker, nvlink_train_worker
 
 _port = [31000 + (os.getpid() % 300) * 40]
 
@@ -54,3 +54,12 @@ def test_nvlink_data_parallel_training_is_consistent():
     for o in out:
         losses = o[2]
         assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+
+
+def test_pull_gemm_over_peer_memory():
+    world = _world()
+    out = _spawn(nvlink_pull_gemm_worker, world, (256, 4096, 9216))
+    for o in out:
+        r = o[2]
+        assert r["status"] == 0 and r["w_local_ok"] and r["err"] < 5e-2, r
+    print("pull_gemm fc6:", out[0][2])
