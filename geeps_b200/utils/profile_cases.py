@@ -1,0 +1,76 @@
+"""Small, self-terminating workloads for `ncu` captures: python -m geeps_b200.utils.profile_cases <case>
+
+Each case allocates well under 1 GB (but more than the 126 MB L2 where DRAM figures matter), warms up
+once and launches the kernel of interest three times.
+  gemm        conv3-forward-shaped bf16 GEMM (M=43264, N=384, K=2304), tcgen05 kernel
+  gemm_dgrad  conv3 data-gradient shape (small K, MN-major B, output-heavy)
+  push_apply  fused reduce + momentum-SGD apply + publish over a 256 MB table (1 rank)
+  lrn         LRN forward + backward on a conv1-sized activation
+  pull_gemm   fused pull + GEMM on an fc6-shaped layer (4 local shards)
+"""
+from __future__ import annotations
+
+import ctypes as C
+import sys
+
+import torch
+
+from ..ops import _lib as L
+from ..ops import functional as F
+
+BF = torch.bfloat16
+
+
+def main():
+    case = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    dev = torch.device("cuda")
+    if case in ("gemm", "gemm_dgrad"):
+        M, N, K, b_mn = (43264, 384, 2304, False) if case == "gemm" else (43264, 2304, 384, True)
+        a = (torch.randn(M, K, device=dev) * 0.1).to(BF)
+        b = (torch.randn((K, N) if b_mn else (N, K), device=dev) * 0.1).to(BF)
+        out = torch.empty(M, N, dtype=BF, device=dev)
+        for _ in range(4):
+            F.gemm(a, b, out, b_mn=b_mn)
+    elif case == "push_apply":
+        rows = 512 * 1024          # 256 MB table
+        upd = torch.randn(rows, 128, device=dev) * 0.01
+        master = torch.zeros(rows, 128, device=dev)
+        mom = torch.zeros(rows, 128, device=dev)
+        cache = torch.zeros(rows, 128, device=dev)
+        cache16 = torch.zeros(rows, 128, dtype=BF, device=dev)
+        flags = torch.zeros(64, dtype=torch.int32, device=dev)
+        p = L.PushApplyParams()
+        p.upd[0], p.cache[0], p.cache16[0] = upd.data_ptr(), cache.data_ptr(), cache16.data_ptr()
+        p.data_age[0] = flags.data_ptr() + 32
+        p.master, p.momentum = master.data_ptr(), mom.data_ptr()
+        p.push_ready, p.global_clock, p.cta_counter = None, flags.data_ptr() + 64, flags.data_ptr() + 68
+        p.status = None
+        p.n_owned, p.row_start, p.row_stride, p.total_rows = rows, 0, 1, rows
+        p.wait_budget_ns, p.n_ranks, p.rank, p.mode, p.publish = 10 ** 9, 1, 0, 1, 1
+        p.lr, p.momentum_coef, p.weight_decay, p.grad_scale = 0.01, 0.9, 5e-4, 1.0
+        for i in range(4):
+            p.clock_stamp = i + 1
+            L.check(L.lib().geeps_ps_push_apply(C.byref(p), 0, L.stream_ptr()), "push_apply")
+    elif case == "lrn":
+        P, Cc = 256 * 55 * 55, 96
+        x = torch.randn(P, Cc, device=dev).to(BF)
+        y = torch.empty_like(x); dx = torch.empty_like(x)
+        scale = torch.empty(P, Cc, device=dev)
+        for _ in range(4):
+            F.lrn_forward(x, y, scale)
+            F.lrn_backward(x, y, scale, y, dx)
+    elif case == "pull_gemm":
+        M, N, K, shards = 256, 4096, 9216, 4
+        x = (torch.randn(M, K, device=dev) * 0.3).to(BF)
+        parts = [(torch.randn(N // shards, K, device=dev) * 0.1).to(BF) for _ in range(shards)]
+        out = torch.zeros(M, N, dtype=torch.float32, device=dev)
+        for _ in range(4):
+            F.pull_gemm(x, [t.data_ptr() for t in parts], [s * (N // shards) for s in range(shards)], out, ldw=K)
+    else:
+        raise SystemExit(f"unknown case {case}")
+    torch.cuda.synchronize()
+    print("done", case)
+
+
+if __name__ == "__main__":
+    main()
