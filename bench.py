@@ -142,7 +142,8 @@ def main() -> None:
     else:
         net, image, classes = inception_bn_22k(), (3, 224, 224), 21841
     B = args.batch
-    base_port = 23000 + (int(os.environ.get("MASTER_PORT", "29500")) % 1000) * 20
+    # below the kernel's ephemeral port range (32768+), or an outgoing connection may already own the port
+    base_port = 10000 + (int(os.environ.get("MASTER_PORT", "29500")) % 500) * 40
     cfg = GeePsConfig(host_list=["127.0.0.1"] * world, port_list=[base_port + 10 * r for r in range(world)],
                       device=DEVICE_CUDA, cuda_device=local_rank,
                       transport=TRANSPORT_NVLINK if args.transport == "nvlink" else TRANSPORT_TCP,

@@ -376,13 +376,13 @@ lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, cons
 
 // Vector forms: one thread owns 8 consecutive channels of a pixel and slides the window over the
 // 24 channels around them (window half-width <= 8); each squared value / ratio is computed once.
+template <int HALF>
 __global__ void __launch_bounds__(256)
 lrn_forward_v8_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __restrict__ scale, long long P, int C,
                       int size, float alpha, float beta, float k) {
   const int cv = C >> 3;
   const long long total = P * cv;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  const int half = size / 2;
   const float a_n = alpha / (float)size;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int c = (int)(i % cv) * 8;
@@ -406,19 +406,21 @@ lrn_forward_v8_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* _
     Bf8 o;
     float sc[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float s = 0.f;
+    float s = 0.f;       // sliding window over the 2*HALF+1 channels around output e
 #pragma unroll
-      for (int j = 0; j < 24; ++j)
-        if (j >= 8 + e - half && j <= 8 + e + half) s += sq[j];
+    for (int j = 8 - HALF; j <= 8 + HALF; ++j) s += sq[j];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
       sc[e] = k + a_n * s;
       o.v[e] = __float2bfloat16(xv[e] * __powf(sc[e], -beta));
+      if (e < 7) s += sq[8 + e + HALF + 1] - sq[8 + e - HALF];
     }
     st8(y + base + c, o);
     st_f4(scale + base + c, make_float4(sc[0], sc[1], sc[2], sc[3]));
     st_f4(scale + base + c + 4, make_float4(sc[4], sc[5], sc[6], sc[7]));
   }
 }
+template <int HALF>
 __global__ void __launch_bounds__(256)
 lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ scale,
                        const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
@@ -426,7 +428,6 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
   const int cv = C >> 3;
   const long long total = P * cv;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  const int half = size / 2;
   const float coef = 2.f * alpha * beta / (float)size;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int c = (int)(i % cv) * 8;
@@ -451,12 +452,13 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
     }
     Bf8 xv = ld8(x + base + c), o;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float acc = 0.f;
+    float acc = 0.f;
 #pragma unroll
-      for (int j = 0; j < 24; ++j)
-        if (j >= 8 + e - half && j <= 8 + e + half) acc += ratio[j];
+    for (int j = 8 - HALF; j <= 8 + HALF; ++j) acc += ratio[j];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
       o.v[e] = __float2bfloat16(dyc[e] * __powf(scc[e], -beta) - coef * bf(xv.v[e]) * acc);
+      if (e < 7) acc += ratio[8 + e + HALF + 1] - ratio[8 + e - HALF];
     }
     st8(dx + base + c, o);
   }
@@ -815,9 +817,14 @@ int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long lo
 
 int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, int size, float alpha, float beta,
                       float k, void* stream) {
-  if (C % 8 == 0 && size / 2 <= 8)
-    lrn_forward_v8_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, scale, P, C,
-                                                                                size, alpha, beta, k);
+  const int g8 = grid_1d(P * (C / 8));
+  cudaStream_t st8 = (cudaStream_t)stream;
+  if (C % 8 == 0 && size == 5)
+    lrn_forward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, scale, P, C, size, alpha, beta, k);
+  else if (C % 8 == 0 && size == 3)
+    lrn_forward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, scale, P, C, size, alpha, beta, k);
+  else if (C % 8 == 0 && size == 7)
+    lrn_forward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, scale, P, C, size, alpha, beta, k);
   else
     lrn_forward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, scale, P, C, size,
                                                                         alpha, beta, k);
@@ -825,9 +832,14 @@ int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, 
 }
 int geeps_lrn_backward(const void* x, const void* y, const float* scale, const void* dy, void* dx, long long P,
                        int C, int size, float alpha, float beta, void* stream) {
-  if (C % 8 == 0 && size / 2 <= 8)
-    lrn_backward_v8_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>(
-        (const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
+  const int g8 = grid_1d(P * (C / 8));
+  cudaStream_t st8 = (cudaStream_t)stream;
+  if (C % 8 == 0 && size == 5)
+    lrn_backward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
+  else if (C % 8 == 0 && size == 3)
+    lrn_backward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
+  else if (C % 8 == 0 && size == 7)
+    lrn_backward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
   else
     lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, scale,
                                                                          (const bf16*)dy, (bf16*)dx, P, C, size, alpha,

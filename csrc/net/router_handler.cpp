@@ -81,7 +81,12 @@ bool RouterHandler::bind(const std::string& host, unsigned port, std::string* er
   addr.sin_addr.s_addr = htonl(INADDR_ANY);
   if (!host.empty() && host != "*" && inet_pton(AF_INET, host.c_str(), &addr.sin_addr) != 1)
     addr.sin_addr.s_addr = htonl(INADDR_ANY);
-  if (::bind(listen_fd_, (sockaddr*)&addr, sizeof(addr)) != 0 || ::listen(listen_fd_, 64) != 0) {
+  int rc = -1;
+  for (int attempt = 0; attempt < 30 && rc != 0; ++attempt) {   // a port in TIME_WAIT frees up within seconds
+    rc = ::bind(listen_fd_, (sockaddr*)&addr, sizeof(addr));
+    if (rc != 0) std::this_thread::sleep_for(std::chrono::milliseconds(100));
+  }
+  if (rc != 0 || ::listen(listen_fd_, 64) != 0) {
     if (err) *err = "bind/listen on port " + std::to_string(port) + " failed: " + strerror(errno);
     ::close(listen_fd_);
     listen_fd_ = -1;

@@ -34,14 +34,14 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    port = 27000 + (int(os.environ.get("MASTER_PORT", "29500")) % 500) * 40
+    port = 10000 + (int(os.environ.get("MASTER_PORT", "29500")) % 10) * 2000   # below the ephemeral range
     run = 0
     for mb in a.mb:
         for slack in a.slack:
             run += 1
             rows = max(world, int(mb * 1024 * 1024 / 512))
             cfg = GeePsConfig(host_list=["127.0.0.1"] * world,
-                              port_list=[port + run * 1000 % 20000 + 10 * r for r in range(world)],
+                              port_list=[port + (run % 19) * 100 + 10 * r for r in range(world)],
                               device=DEVICE_CUDA, cuda_device=local,
                               transport=TRANSPORT_NVLINK if a.transport == "nvlink" else TRANSPORT_TCP,
                               partitioner=PARTITION_ROUND_ROBIN, table_mode=TABLE_SGD_MOMENTUM, grad_scale=1.0 / world)

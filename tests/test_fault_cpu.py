@@ -7,7 +7,7 @@ import pytest
 
 from ps_workers import fault_worker
 
-_port = [34000 + (os.getpid() % 300) * 40]
+_port = [26000 + (os.getpid() % 50) * 100]
 
 
 def _run(mode, kw, expect):

@@ -13,7 +13,7 @@ from geeps_b200.utils.config import (DEVICE_CPU, PARTITION_ROUND_ROBIN, TABLE_SG
 
 from ps_workers import helloworld_worker
 
-_port = [20000 + (os.getpid() % 500) * 40]
+_port = [12000 + (os.getpid() % 300) * 40]   # below the ephemeral port range
 
 
 def next_port():
