@@ -18,6 +18,7 @@ import torch
 from ..ops import functional as F
 from ..ops.layers import BF, ParamSpec
 from ..utils.config import TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK, GeePsConfig
+from ..utils.trace import NullTrace
 from .ps import ROW_FLOATS, GeePs
 
 
@@ -46,9 +47,10 @@ class _Table:
 
 class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
-                 slack: int = 0, seed: int = 0, keep_init: bool = False):
+                 slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None):
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
+        self.trace = trace or NullTrace()
         net.setup(in_shape, self.device)
         self.tables = [_Table(i, l) for i, l in enumerate(net.param_layers())]
         by_layer = {id(t.layer): t for t in self.tables}
@@ -117,23 +119,34 @@ class PSModule:
     def step(self, x: torch.Tensor, labels: torch.Tensor, capture: bool = False) -> torch.Tensor:
         """One clock: forward, backward, push.  Returns the mean loss as a 1-element device tensor.
         capture=True keeps clones of the parameters this clock read in `self.captured`."""
-        net = self.net
+        net, tr = self.net, self.trace
         self.captured = {} if capture else None
-        h = net.input_layer.forward(x)
+        with tr.span("input", "fwd"):
+            h = net.input_layer.forward(x)
         for l, tabs in self.groups:
-            for t in tabs:
-                self._bind_read(t)
-            h = l.forward(h)
-        loss = net.loss_layer.forward(h, labels)
-        g = net.loss_layer.backward()
+            name = getattr(l, "name", type(l).__name__)
+            if tabs:
+                with tr.span(f"read:{name}", "ps"):
+                    for t in tabs:
+                        self._bind_read(t)
+            with tr.span(f"fwd:{name}", "fwd"):
+                h = l.forward(h)
+        with tr.span("loss", "fwd"):
+            loss = net.loss_layer.forward(h, labels)
+            g = net.loss_layer.backward()
         for l, tabs in reversed(self.groups):
+            name = getattr(l, "name", type(l).__name__)
             for t in reversed(tabs):
                 t.layer.g32 = t.views(self.ps.pre_update(t.h_pre))
-            g = l.backward(g)
-            for t in reversed(tabs):
-                self.ps.post_read(t.h_post)
-                self.ps.update(t.h_upd)
-        self.ps.clock()
+            with tr.span(f"bwd:{name}", "bwd"):
+                g = l.backward(g)
+            if tabs:
+                with tr.span(f"update:{name}", "ps"):
+                    for t in reversed(tabs):
+                        self.ps.post_read(t.h_post)
+                        self.ps.update(t.h_upd)
+        with tr.span("clock", "ps", clock=self.steps):
+            self.ps.clock()
         self.steps += 1
         return loss
 

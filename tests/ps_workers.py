@@ -241,3 +241,80 @@ def nvlink_pull_gemm_worker(rank, world, base_port, M, N, K, q, kw):
                                 nvlink_roofline_ms=link_ms, frac_of_roofline=link_ms / t_fused), None, None, None))
     except Exception as e:  # pragma: no cover
         q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
+
+
+def snapshot_worker(rank, world, base_port, phase, snap_dir, q, kw):
+    """phase 'save': run 4 clocks of +1 updates, snapshot, run 2 more and report what the next read sees.
+    phase 'resume': load the snapshot (possibly with another world size), run the same 2 clocks."""
+    try:
+        import torch
+        from geeps_b200.parallel.ps import GeePs
+        from geeps_b200.utils.config import DEVICE_CPU, PARTITION_ROUND_ROBIN
+        cfg = make_cfg(world, base_port, device=DEVICE_CPU, partitioner=PARTITION_ROUND_ROBIN, **kw)
+        g = GeePs(rank, cfg)
+        rows = list(range(37))
+        r = g.virtual_read(0, rows, 0); u = g.virtual_pre_update(0, rows)
+        pr = g.virtual_post_read(r); up = g.virtual_update(u); g.virtual_clock()
+        g.finish_virtual_iteration()
+
+        def step(val):
+            x = g.read(r, asynchronous=False).clone()
+            b = g.pre_update(u); g.post_read(pr); b.fill_(val); g.update(up); g.clock()
+            return x
+
+        if phase == "save":
+            init = torch.arange(37 * 128, dtype=torch.float32).view(37, 128) if rank == 0 else torch.zeros(37, 128)
+            g.pre_update(u).copy_(init); g.update(up); g.clock(); g.start_iterations()
+            for _ in range(4):
+                step(1.0)
+            assert g.save_snapshot(snap_dir)
+        else:
+            assert g.load_snapshot(snap_dir), g.last_error_string()
+            g.start_iterations()
+        step(2.0 / world)         # the same total update regardless of the world size
+        step(0.0)
+        final = g.read(r, asynchronous=False).clone()
+        g.shutdown(); g.close()
+        q.put((rank, "ok", final.flatten().tolist(), None, None, None))   # plain list: no shared-memory handles
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
+
+
+def nvlink_leave_worker(rank, world, base_port, q, kw):
+    """NVLINK transport, 2 ranks: rank 1 leaves between steps with nothing of its own in flight; rank 0
+    must get an error code from the runtime (host-side detection or a bounded device wait), not hang."""
+    try:
+        import time
+        import torch
+        from geeps_b200.parallel.ps import GeePs, GeePsError
+        from geeps_b200.utils.config import DEVICE_CUDA, TRANSPORT_NVLINK
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        cfg = make_cfg(world, base_port, device=DEVICE_CUDA, cuda_device=rank, transport=TRANSPORT_NVLINK,
+                       device_wait_budget_us=500_000, heartbeat_timeout_ms=3000)
+        with torch.cuda.stream(torch.cuda.Stream(device=rank)):
+            g = GeePs(rank, cfg)
+            rows = list(range(256))
+            r = g.virtual_read(0, rows, 0); u = g.virtual_pre_update(0, rows)
+            pr = g.virtual_post_read(r); up = g.virtual_update(u); g.virtual_clock()
+            g.finish_virtual_iteration()
+            g.pre_update(u).zero_(); g.update(up); g.clock(); g.start_iterations()
+            t0 = time.time()
+            result = ("ok", 0)
+            try:
+                for c in range(30):
+                    if rank == 1 and c == 5:
+                        torch.cuda.synchronize()          # nothing of this rank is in flight
+                        time.sleep(0.5)                   # let the peer finish the clock that used our signals
+                        q.put((rank, "left", 0, 0.0)); q.close(); q.join_thread()
+                        os._exit(0)
+                    x = g.read(r); b = g.pre_update(u); g.post_read(pr); b.fill_(1.0); g.update(up); g.clock()
+                    torch.cuda.synchronize()
+            except GeePsError as e:
+                result = ("error", e.code)
+            torch.cuda.synchronize()
+            alive = float(torch.ones(8, device=f"cuda:{rank}").sum()) == 8.0
+            q.put((rank, result[0], result[1], time.time() - t0, alive)); q.close(); q.join_thread()
+            os._exit(0)
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "exception", repr(e) + traceback.format_exc(), 0.0, False))

@@ -6,7 +6,7 @@ import pytest
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
-from ps_workers import nvlink_hello_worker, nvlink_pull_gemm_worker, nvlink_train_worker
+from ps_workers import nvlink_hello_worker, nvlink_leave_worker, nvlink_pull_gemm_worker, nvlink_train_worker
 
 _port = [15000 + (os.getpid() % 100) * 100]
 
@@ -65,3 +65,22 @@ def test_pull_gemm_over_peer_memory():
         r = o[2]
         assert r["status"] == 0 and r["w_local_ok"] and r["err"] < 5e-2, r
     print("pull_gemm fc6:", out[0][2])
+
+
+def test_rank_leaving_between_steps_gives_an_error_not_a_hang():
+    """Host-made failure on 2 GPUs: the leaving rank has nothing in flight; no GPU is faulted."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    _port[0] += 100
+    procs = [ctx.Process(target=nvlink_leave_worker, args=(r, 2, _port[0], q, {})) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = {}
+    for _ in range(2):
+        o = q.get(timeout=180)
+        out[o[0]] = o
+    for p in procs:
+        p.join(timeout=30)
+    assert out[1][1] == "left"
+    assert out[0][1] == "error" and out[0][2] in (4, 5), out[0]     # device wait expired or peer loss seen on the host
+    assert out[0][3] < 60 and out[0][4] is True                      # bounded, and the CUDA context still works

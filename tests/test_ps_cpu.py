@@ -187,3 +187,31 @@ def test_snapshot_roundtrip(tmp_path):
     for a, b in zip(after, again):
         assert torch.equal(a, b)      # parameters AND momentum came back
     g2.shutdown(); g2.close()
+
+
+def _run_snapshot(world, phase, snap_dir):
+    from ps_workers import snapshot_worker
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = next_port()
+    procs = [ctx.Process(target=snapshot_worker, args=(r, world, port, phase, snap_dir, q, {})) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=240) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    for o in out:
+        assert o[1] == "ok", o[2]
+    return [o[2] for o in out]
+
+
+def test_snapshot_resharded_to_a_smaller_world(tmp_path):
+    """Elastic restart: a 2-worker / 2-shard job snapshots, a 1-worker job resumes from it (the rows
+    are re-partitioned on load) and continues with the same parameter values."""
+    snap = str(tmp_path)
+    two = _run_snapshot(2, "save", snap)
+    one = _run_snapshot(1, "resume", snap)
+    assert two[0] == two[1]
+    assert one[0] == two[0]
+    expect = (torch.arange(37 * 128, dtype=torch.float32) + 4 * 2 * 1.0 + 2.0).tolist()
+    assert two[0] == expect

@@ -1,0 +1,28 @@
+"""Host-only tests of the utilities: trace writer, config mirror."""
+import json
+
+from geeps_b200.utils.config import GeePsConfig
+from geeps_b200.utils.trace import ChromeTrace
+
+
+def test_chrome_trace_roundtrip(tmp_path):
+    tr = ChromeTrace("unit", nvtx=False)
+    with tr.span("fwd:conv1", "fwd", rows=3):
+        with tr.span("read:conv1", "ps"):
+            pass
+    tr.instant("clock", clock=1)
+    tr.counter("staleness", value=0)
+    path = tmp_path / "trace.json"
+    tr.save(str(path))
+    data = json.loads(path.read_text())
+    names = [e["name"] for e in data["traceEvents"]]
+    assert "fwd:conv1" in names and "read:conv1" in names and "clock" in names
+    spans = [e for e in data["traceEvents"] if e.get("ph") == "X"]
+    assert all(e["dur"] >= 0 for e in spans)
+
+
+def test_config_mirror_covers_every_numeric_field():
+    cfg = GeePsConfig()
+    for k in GeePsConfig._NUMERIC + GeePsConfig._STRING:
+        assert hasattr(cfg, k), k
+    assert cfg.tcp_base_port == 9090 and cfg.mm_warning_level == 1 and cfg.read_my_writes == 0
