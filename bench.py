@@ -109,6 +109,9 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU)
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "tcp"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cache-frac", type=float, default=None,
+                    help="manage activations through the PS memory plan and cap the GPU budget at this fraction of the working set")
+    ap.add_argument("--slack", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -151,7 +154,8 @@ def main() -> None:
                       grad_scale=1.0 / world, bf16_compute_cache=1)
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
-        mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=0, seed=1)
+        mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=args.slack, seed=1,
+                       manage_activations=args.cache_frac is not None, cache_fraction=args.cache_frac)
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
         x_dev = torch.randn((B,) + image, device=dev, generator=gen)
         y_dev = torch.randint(0, classes, (B,), device=dev, generator=gen)
@@ -230,9 +234,16 @@ def main() -> None:
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic", "impl": "ours",
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
-                           "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": 0,
+                           "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack,
                            "tables": "fp32 master rows, momentum SGD on the owning shard",
                            "l2": "inputs (158 MB/step) and activations exceed the 126 MB L2; no explicit flush"},
+                "memory_plan": ({"cache_fraction_of_activations": args.cache_frac, "budget_rows": mod.budget_rows,
+                                 "working_set_rows": mod.working_set_rows, "managed_activation_rows": mod.managed_rows,
+                                 "param_rows": mod.param_rows,
+                                 "swap_h2d_gb_per_s": stats["client"]["swap_h2d_bytes"] / max(1, mod.steps) / (ms / args.steps) / 1e6,
+                                 "swap_d2h_gb_per_s": stats["client"]["swap_d2h_bytes"] / max(1, mod.steps) / (ms / args.steps) / 1e6,
+                                 "cpu_local_rows": stats["client"]["cpu_local_rows"], "gpu_local_rows": stats["client"]["gpu_local_rows"]}
+                                if args.cache_frac is not None else None),
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches + runtime_launches, "final_loss": last_loss,
             }
             print(json.dumps(out))

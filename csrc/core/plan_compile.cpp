@@ -181,7 +181,21 @@ Plan PlanCompiler::compile() const {
     for (auto& kv : bs) if (kv.second.pinned) s += kv.second.rows;
     return s;
   };
-  const size_t cap = plan.capacity_rows;
+  // On the NVLINK transport the parameter cache, its update ring and the shard state must be device
+  // resident (peers read and write them in place), so they are carved out of the budget first; on the
+  // host-staged transport local data comes first and the parameter cache may spill to host memory.
+  size_t param_reserved = 0;
+  if (cfg_.update_ring)
+    for (auto& kv : plan.tables) param_reserved += kv.second.rows.size() * (1 + (size_t)kv.second.num_oplog_entries);
+  size_t cap = plan.capacity_rows;
+  if (gpu && cap != (size_t)-1 && param_reserved) {
+    if (param_reserved > cap) {
+      plan.error = "GPU memory budget (" + std::to_string(cap) + " rows) is smaller than the device-resident parameter state (" +
+                   std::to_string(param_reserved) + " rows)";
+      return plan;
+    }
+    cap -= param_reserved;
+  }
   if (gpu) {
     for (auto& kv : batches) kv.second.pinned = true;
     size_t peak = peak_of(ops, staged_for(batches), nullptr);
@@ -234,7 +248,7 @@ Plan PlanCompiler::compile() const {
 
   // ---- 5. parameter cache: GPU while it fits (first fit in op order), host memory after that ----
   size_t avail = (size_t)-1;
-  if (gpu && cap != (size_t)-1) {
+  if (gpu && cap != (size_t)-1 && !param_reserved) {
     const size_t taken = plan.gpu_local_rows + 2 * plan.peak_staging_rows;
     avail = cap > taken ? cap - taken : 0;
   }
@@ -321,7 +335,7 @@ Plan PlanCompiler::compile() const {
     }
   plan.staging_copies = 2;
   if (gpu && cap != (size_t)-1) {
-    const size_t fixed = plan.gpu_local_rows + used_param;
+    const size_t fixed = plan.gpu_local_rows + (param_reserved ? 0 : used_param);   // reserved rows already left `cap`
     if (fixed + 2 * plan.staging_rows > cap) {
       const std::string msg = "staging pool cannot be double buffered: need " + std::to_string(2 * plan.staging_rows) +
                               " rows, " + std::to_string(cap > fixed ? cap - fixed : 0) + " left";

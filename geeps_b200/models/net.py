@@ -49,6 +49,25 @@ class Concat(Layer):
         self.dx = None
         return self.out_shape
 
+    def out_numel(self):
+        return self.P * sum(self.widths)
+
+    def set_output(self, flat):
+        ctot = sum(self.widths)
+        self.y = flat[:self.P * ctot].view(self.P, ctot)
+        off = 0
+        for br, w in zip(self.branches, self.widths):
+            last, view = br[-1], self.y[:, off:off + w]
+            if isinstance(last, Pool):
+                last.bind_output(view, ctot)
+            else:
+                last.bind_output(view)
+            off += w
+
+    def set_input(self, x):
+        for br in self.branches:
+            br[0].set_input(x)
+
     def forward(self, x):
         x4 = x if x.dim() == 4 else x.view(self.in_shape)
         for br in self.branches:

@@ -70,6 +70,22 @@ class Layer:
     def backward(self, dy):
         raise NotImplementedError
 
+    # ---- hooks for activations managed by the parameter server's memory plan ----
+    def out_numel(self) -> int:
+        n = 1
+        for s_ in self.out_shape:
+            n *= s_
+        return n
+
+    def set_output(self, flat: "torch.Tensor") -> None:
+        """Use `flat` (bf16, >= out_numel elements) as this layer's output buffer from now on."""
+        self.y = flat[:self.out_numel()].view(-1, self.out_shape[-1])
+
+    def set_input(self, x: "torch.Tensor") -> None:
+        """The input this layer saved in forward now lives in `x` (it was evicted and fetched back)."""
+        if hasattr(self, "x"):
+            self.x = x.view(self.x.shape) if x.numel() == self.x.numel() else x
+
 
 class Input(Layer):
     """fp32 NCHW batch -> NHWC bf16 (optionally zero-padding the channel count)."""
@@ -312,6 +328,10 @@ class Pool(Layer):
     def bind_output(self, y2d, ldy):
         self.y = y2d
         self.g.ldy = ldy
+
+    def set_output(self, flat):
+        self.y = flat[:self.out_numel()].view(self.out_shape)
+        self.g.ldy = self.out_shape[-1]
 
     def forward(self, x):
         if self.y is None:

@@ -47,7 +47,8 @@ class _Table:
 
 class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
-                 slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None):
+                 slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None, manage_activations: bool = False,
+                 cache_fraction: float | None = None):
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
         self.trace = trace or NullTrace()
@@ -60,6 +61,34 @@ class PSModule:
             subs = list(l.sublayers()) if hasattr(l, "sublayers") else [l]
             self.groups.append((l, [by_layer[id(s)] for s in subs if id(s) in by_layer]))
         ps_config.num_tables = len(self.tables)
+        # Activations managed by the runtime's memory plan: the output of every large top-level layer becomes a
+        # worker-local row batch (produced in forward: no fetch / keep; consumed in backward: fetch / discard), so
+        # that under a GPU budget the plan decides which of them stay resident and which are swapped to pinned
+        # host memory through the staging pool.
+        self.managed = {}
+        if manage_activations:
+            from ..ops.layers import Dropout, Linear
+            for i, (l, _) in enumerate(self.groups):
+                nbytes = l.out_numel() * 2
+                if isinstance(l, (Linear, Dropout)) or nbytes < (1 << 20):
+                    continue
+                nrows = (nbytes + 511) // 512
+                self.managed[i] = {"rows": range(1_000_000 * (i + 1), 1_000_000 * (i + 1) + nrows), "nrows": nrows}
+        self.param_rows = sum(t.rows for t in self.tables)
+        self.managed_rows = sum(m["nrows"] for m in self.managed.values())
+        if cache_fraction is not None:
+            ring = 2 if ps_config.transport == TRANSPORT_NVLINK else 1 + int(bool(ps_config.read_my_writes))
+            param_state = self.param_rows * (1 + ring)
+            if ps_config.transport == TRANSPORT_NVLINK:
+                # peers read and write the parameter cache and the update ring in place, so that state stays
+                # device resident; the cap applies to the activation working set
+                budget_rows = param_state + int(cache_fraction * self.managed_rows)
+            else:
+                budget_rows = int(cache_fraction * (param_state + self.managed_rows))
+            self.budget_rows = budget_rows
+            self.working_set_rows = param_state + self.managed_rows
+            ps_config.gpu_memory_capacity = budget_rows * 512
+            ps_config.mm_warning_level = 0
         self.direct16 = ps_config.transport == TRANSPORT_NVLINK and ps_config.bf16_compute_cache
         self.ps = GeePs(rank, ps_config)
         self.initial_params = {} if keep_init else None
@@ -71,16 +100,28 @@ class PSModule:
 
     # one virtual iteration = the exact call sequence of step()
     def _declare(self):
-        ps = self.ps
-        for _, tabs in self.groups:
+        ps, M = self.ps, self.managed
+        n = len(self.groups)
+        for i, (_, tabs) in enumerate(self.groups):
             for t in tabs:
                 t.h_read = ps.virtual_read(t.table_id, range(t.rows), self.slack)
-        for _, tabs in reversed(self.groups):
+            if i in M:
+                M[i]["f"] = ps.virtual_local_access(M[i]["rows"], False)
+            if i - 1 in M:      # the previous output was this layer's input: release (and keep) it now
+                M[i - 1]["pf"] = ps.virtual_post_local_access(M[i - 1]["f"], True)
+        if n - 1 in M:
+            M[n - 1]["pf"] = ps.virtual_post_local_access(M[n - 1]["f"], True)
+            M[n - 1]["b"] = ps.virtual_local_access(M[n - 1]["rows"], True)
+        for i, (_, tabs) in reversed(list(enumerate(self.groups))):
+            if i - 1 in M:
+                M[i - 1]["b"] = ps.virtual_local_access(M[i - 1]["rows"], True)
             for t in reversed(tabs):
                 t.h_pre = ps.virtual_pre_update(t.table_id, range(t.rows))
             for t in reversed(tabs):
                 t.h_post = ps.virtual_post_read(t.h_read)
                 t.h_upd = ps.virtual_update(t.h_pre)
+            if i in M:
+                M[i]["pb"] = ps.virtual_post_local_access(M[i]["b"], False)
         ps.virtual_clock()
         ps.finish_virtual_iteration()
 
@@ -123,19 +164,38 @@ class PSModule:
         self.captured = {} if capture else None
         with tr.span("input", "fwd"):
             h = net.input_layer.forward(x)
-        for l, tabs in self.groups:
+        M, n = self.managed, len(self.groups)
+
+        def local(handle):
+            return self.ps.local_access(handle).view(BF).view(-1)
+
+        for i, (l, tabs) in enumerate(self.groups):
             name = getattr(l, "name", type(l).__name__)
             if tabs:
                 with tr.span(f"read:{name}", "ps"):
                     for t in tabs:
                         self._bind_read(t)
+            if i in M:
+                l.set_output(local(M[i]["f"]))
             with tr.span(f"fwd:{name}", "fwd"):
                 h = l.forward(h)
+            if i - 1 in M:
+                self.ps.post_local_access(M[i - 1]["pf"])
+        if n - 1 in M:
+            self.ps.post_local_access(M[n - 1]["pf"])
+            held = local(M[n - 1]["b"])
+            self.groups[n - 1][0].set_output(held)
         with tr.span("loss", "fwd"):
             loss = net.loss_layer.forward(h, labels)
             g = net.loss_layer.backward()
-        for l, tabs in reversed(self.groups):
+        for i, (l, tabs) in reversed(list(enumerate(self.groups))):
             name = getattr(l, "name", type(l).__name__)
+            if i - 1 in M:
+                # this layer's input was evicted after forward: fetch it back; it is also the previous
+                # layer's output, which that layer's backward (ReLU / BN / LRN) reads
+                buf = local(M[i - 1]["b"])
+                l.set_input(buf[:self.groups[i - 1][0].out_numel()])
+                self.groups[i - 1][0].set_output(buf)
             for t in reversed(tabs):
                 t.layer.g32 = t.views(self.ps.pre_update(t.h_pre))
             with tr.span(f"bwd:{name}", "bwd"):
@@ -145,6 +205,8 @@ class PSModule:
                     for t in reversed(tabs):
                         self.ps.post_read(t.h_post)
                         self.ps.update(t.h_upd)
+            if i in M:
+                self.ps.post_local_access(M[i]["pb"])
         with tr.span("clock", "ps", clock=self.steps):
             self.ps.clock()
         self.steps += 1

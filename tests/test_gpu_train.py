@@ -109,3 +109,29 @@ def test_alexnet_step_runs_and_learns():
         assert losses[-1] < losses[0], losses
         assert mod.ps.last_error() == 0
         mod.close()
+
+
+@pytest.mark.parametrize("frac", [None, 0.55])
+def test_managed_activations_match_unmanaged(frac):
+    """Activations routed through LocalAccess (and swapped to pinned host memory under a budget of 55 % of the working set) give the
+    same losses as ordinary buffers."""
+    torch.manual_seed(4)
+    dev = torch.device("cuda:0")
+    B = 64
+    losses = {}
+    for managed in (False, True):
+        with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+            mod = PSModule(inception_bn_small(), (B, 3, 32, 32), cfg(TRANSPORT_NVLINK, learning_rate=0.01), device=dev,
+                           seed=9, manage_activations=managed, cache_fraction=frac if managed else None)
+            gen = torch.Generator(device=dev).manual_seed(5)
+            x = torch.randn(B, 3, 32, 32, device=dev, generator=gen)
+            y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+            losses[managed] = [mod.step(x, y).item() for _ in range(5)]
+            if managed:
+                st = mod.ps.get_stats()["client"]
+                assert len(mod.managed) > 0
+                if frac is not None:
+                    assert st["cpu_local_rows"] > 0 and st["swap_h2d_bytes"] > 0
+            assert mod.ps.last_error() == 0
+            mod.close()
+    assert losses[True] == pytest.approx(losses[False], rel=2e-3), losses
