@@ -19,6 +19,14 @@ struct alignas(16) Bf8 { bf16 v[8]; };
 __device__ __forceinline__ Bf8 ld8(const bf16* p) { Bf8 r; *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p); return r; }
 __device__ __forceinline__ void st8(bf16* p, const Bf8& r) { *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r); }
 
+// t = q * stride exactly?  Strides 1 and 2 (every layer of the supported nets but conv1) avoid the divider.
+__device__ __forceinline__ bool div_exact(int t, int stride, int& q) {
+  if (stride == 1) { q = t; return true; }
+  if (stride == 2) { q = t >> 1; return (t & 1) == 0; }
+  q = t / stride;
+  return q * stride == t;
+}
+
 inline int grid_1d(long long n, int block = 256, int cap = 148 * 16) {
   long long b = (n + block - 1) / block;
   if (b > cap) b = cap;
@@ -43,36 +51,42 @@ nchw_f32_to_nhwc_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, 
 
 // ---------------- im2col / col2im (NHWC, one channel group) ----------------
 // col[(b,oh,ow)][(kh,kw,c)] = x[b][oh*s-p+kh][ow*s-p+kw][c0+c]; row pitch ldcol >= KH*KW*Cg.
+// One warp builds one row of the patch matrix at a time: the pixel coordinates are decoded once per row
+// and the lanes sweep the row's vectors, so the address arithmetic is two 32-bit divisions per vector.
 template <int VEC>
 __global__ void __launch_bounds__(256)
 im2col_kernel(const bf16* __restrict__ x, bf16* __restrict__ col, const GeepsConvGeom g) {
   const int cv = g.Cg / VEC;
-  const long long per_row = (long long)g.KH * g.KW * cv;
-  const long long total = (long long)g.B * g.OH * g.OW * per_row;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const long long row = i / per_row;
-    int r = (int)(i % per_row);
-    const int c = (r % cv) * VEC; r /= cv;
-    const int kw = r % g.KW;
-    const int kh = r / g.KW;
-    long long p = row;
-    const int ow = (int)(p % g.OW); p /= g.OW;
-    const int oh = (int)(p % g.OH);
-    const int b = (int)(p / g.OH);
-    const int ih = oh * g.stride - g.pad + kh, iw = ow * g.stride - g.pad + kw;
-    bf16* dst = col + row * g.ldcol + (long long)(kh * g.KW + kw) * g.Cg + c;
-    const bool in = ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
-    const bf16* src = x + (((long long)b * g.H + ih) * g.W + iw) * g.C + g.c0 + c;
-    if (VEC == 8) {
-      Bf8 v;
-      if (in) v = ld8(src); else *reinterpret_cast<uint4*>(&v) = make_uint4(0, 0, 0, 0);
-      st8(dst, v);
-    } else if (VEC == 4) {
-      uint2 v = in ? *reinterpret_cast<const uint2*>(src) : make_uint2(0, 0);
-      *reinterpret_cast<uint2*>(dst) = v;
-    } else {
-      *dst = in ? *src : __float2bfloat16(0.f);
+  const int per_kh = g.KW * cv;
+  const int per_row = g.KH * per_kh;
+  const long long rows = (long long)g.B * g.OH * g.OW;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const int ow = (int)(row % g.OW);
+    const long long t = row / g.OW;
+    const int oh = (int)(t % g.OH);
+    const int b = (int)(t / g.OH);
+    const int ih0 = oh * g.stride - g.pad, iw0 = ow * g.stride - g.pad;
+    bf16* drow = col + row * g.ldcol;
+    const bf16* xb = x + (long long)b * g.H * g.W * g.C + g.c0;
+    for (int v = lane; v < per_row; v += 32) {
+      const int kh = v / per_kh;
+      const int rem = v - kh * per_kh;
+      const int kw = rem / cv;
+      const int c = (rem - kw * cv) * VEC;
+      const int ih = ih0 + kh, iw = iw0 + kw;
+      const bool in = ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
+      bf16* dst = drow + (kh * g.KW + kw) * g.Cg + c;
+      const bf16* src = xb + ((long long)ih * g.W + iw) * g.C + c;
+      if (VEC == 8) {
+        *reinterpret_cast<uint4*>(dst) = in ? *reinterpret_cast<const uint4*>(src) : make_uint4(0, 0, 0, 0);
+      } else if (VEC == 4) {
+        *reinterpret_cast<uint2*>(dst) = in ? *reinterpret_cast<const uint2*>(src) : make_uint2(0, 0);
+      } else {
+        *dst = in ? *src : __float2bfloat16(0.f);
+      }
     }
   }
 }
@@ -105,14 +119,11 @@ col2im_kernel(const bf16* __restrict__ dcol, bf16* __restrict__ dx, const GeepsC
     for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
     for (int kh = 0; kh < g.KH; ++kh) {
       const int th = ih + g.pad - kh;
-      if (th < 0 || th % g.stride) continue;
-      const int oh = th / g.stride;
-      if (oh >= g.OH) continue;
+      int oh, ow;
+      if (th < 0 || !div_exact(th, g.stride, oh) || oh >= g.OH) continue;
       for (int kw = 0; kw < g.KW; ++kw) {
         const int tw = iw + g.pad - kw;
-        if (tw < 0 || tw % g.stride) continue;
-        const int ow = tw / g.stride;
-        if (ow >= g.OW) continue;
+        if (tw < 0 || !div_exact(tw, g.stride, ow) || ow >= g.OW) continue;
         const bf16* src = dcol + (((long long)b * g.OH + oh) * g.OW + ow) * g.ldcol +
                           (long long)(kh * g.KW + kw) * g.Cg + c;
         if (VEC == 8) {
@@ -538,14 +549,11 @@ maxpool_backward_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
     for (int kh = 0; kh < g.K; ++kh) {
       const int th = ih + g.pad - kh;
-      if (th < 0 || th % g.stride) continue;
-      const int oh = th / g.stride;
-      if (oh >= g.OH) continue;
+      int oh, ow;
+      if (th < 0 || !div_exact(th, g.stride, oh) || oh >= g.OH) continue;
       for (int kw = 0; kw < g.K; ++kw) {
         const int tw = iw + g.pad - kw;
-        if (tw < 0 || tw % g.stride) continue;
-        const int ow = tw / g.stride;
-        if (ow >= g.OW) continue;
+        if (tw < 0 || !div_exact(tw, g.stride, ow) || ow >= g.OW) continue;
         const long long opix = ((long long)b * g.OH + oh) * g.OW + ow;
         const uint2 pk = *reinterpret_cast<const uint2*>(argmax + opix * g.C + c);
         Bf8 d = ld8(dy + opix * g.ldy + c);
@@ -622,14 +630,11 @@ avgpool_backward_kernel(const bf16* __restrict__ dy, bf16* __restrict__ dx, cons
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
     for (int kh = 0; kh < g.K; ++kh) {
       const int th = ih + g.pad - kh;
-      if (th < 0 || th % g.stride) continue;
-      const int oh = th / g.stride;
-      if (oh >= g.OH) continue;
+      int oh, ow;
+      if (th < 0 || !div_exact(th, g.stride, oh) || oh >= g.OH) continue;
       for (int kw = 0; kw < g.K; ++kw) {
         const int tw = iw + g.pad - kw;
-        if (tw < 0 || tw % g.stride) continue;
-        const int ow = tw / g.stride;
-        if (ow >= g.OW) continue;
+        if (tw < 0 || !div_exact(tw, g.stride, ow) || ow >= g.OW) continue;
         const float inv = 1.f / (float)(avg_area(oh, g.stride, g.pad, g.K, g.H) * avg_area(ow, g.stride, g.pad, g.K, g.W));
         Bf8 d = ld8(dy + (((long long)b * g.OH + oh) * g.OW + ow) * g.ldy + c);
 #pragma unroll
@@ -726,9 +731,10 @@ int geeps_im2col(const void* x, void* col, const GeepsConvGeom* g, void* stream)
     zero_col_pad_kernel<<<grid_1d(rows * (g->ldcol - kd)), 256, 0, st>>>((bf16*)col, rows, kd, g->ldcol);
   const bool a8 = (g->Cg % 8 == 0) && (g->C % 8 == 0) && (g->c0 % 8 == 0) && (g->ldcol % 8 == 0);
   const bool a4 = (g->Cg % 4 == 0) && (g->C % 4 == 0) && (g->c0 % 4 == 0) && (g->ldcol % 4 == 0);
-  if (a8) im2col_kernel<8><<<grid_1d(rows * g->KH * g->KW * (g->Cg / 8)), 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
-  else if (a4) im2col_kernel<4><<<grid_1d(rows * g->KH * g->KW * (g->Cg / 4)), 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
-  else im2col_kernel<1><<<grid_1d(rows * kd), 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
+  const int wgrid = grid_1d(rows * 32);   // one warp per patch-matrix row
+  if (a8) im2col_kernel<8><<<wgrid, 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
+  else if (a4) im2col_kernel<4><<<wgrid, 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
+  else im2col_kernel<1><<<wgrid, 256, 0, st>>>((const bf16*)x, (bf16*)col, *g);
   return CK();
 }
 
