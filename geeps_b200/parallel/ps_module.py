@@ -77,12 +77,15 @@ class PSModule:
         self.param_rows = sum(t.rows for t in self.tables)
         self.managed_rows = sum(m["nrows"] for m in self.managed.values())
         if cache_fraction is not None:
-            ring = 2 if ps_config.transport == TRANSPORT_NVLINK else 1 + int(bool(ps_config.read_my_writes))
+            ring = slack + 1 if ps_config.transport == TRANSPORT_NVLINK else 1 + int(bool(ps_config.read_my_writes))
             param_state = self.param_rows * (1 + ring)
             if ps_config.transport == TRANSPORT_NVLINK:
                 # peers read and write the parameter cache and the update ring in place, so that state stays
-                # device resident; the cap applies to the activation working set
-                budget_rows = param_state + int(cache_fraction * self.managed_rows)
+                # device resident; the cap applies to the activation working set, but never goes below what
+                # one forward step needs at once (a layer's input and output)
+                sizes = [self.managed.get(i, {"nrows": 0})["nrows"] for i in range(len(self.groups))]
+                pair = max([a + b for a, b in zip(sizes, sizes[1:])] + sizes + [0])
+                budget_rows = param_state + max(int(cache_fraction * self.managed_rows), int(pair * 1.02) + 16)
             else:
                 budget_rows = int(cache_fraction * (param_state + self.managed_rows))
             self.budget_rows = budget_rows
