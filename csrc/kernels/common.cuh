@@ -85,6 +85,15 @@ __device__ __forceinline__ float4 ld_f4_nc_stream(const float* p) {
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
   return v;
 }
+// Weak 16-byte load that bypasses the (non-coherent) L1 and is served from L2 / the peer.  Correct for data
+// that was completely written before this kernel started or before a flag this kernel's stream waited on
+// (stream order and the release / acquire on the flag order those writes before this load).
+__device__ __forceinline__ float4 ld_f4_cg(const float* p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
 // Volatile-strength peer load: data written by another GPU during this kernel must
 // not be served from a stale L1 line.
 __device__ __forceinline__ float4 ld_f4_peer(const float* p) {

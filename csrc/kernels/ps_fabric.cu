@@ -47,20 +47,23 @@ __device__ __forceinline__ bool last_cta_arrive(int* counter) {
   return last;
 }
 
+// The workers' updates are complete before the push-ready flags this stream waited on, so plain weak loads
+// (L1 bypassed) are enough; with `in_kernel_wait` the flags were acquired inside this kernel by other
+// threads, and the loads have to be system-scope relaxed ones.
 template <int NR>
-__device__ __forceinline__ float4 reduce_fixed_order(const GeepsPushApplyParams& p, long long off) {
+__device__ __forceinline__ float4 reduce_fixed_order(const GeepsPushApplyParams& p, long long off, bool strong) {
   float4 v[NR];
 #pragma unroll
-  for (int w = 0; w < NR; ++w) v[w] = ld_f4_peer(p.upd[w] + off);
+  for (int w = 0; w < NR; ++w) v[w] = strong ? ld_f4_peer(p.upd[w] + off) : ld_f4_cg(p.upd[w] + off);
   float4 g = v[0];
 #pragma unroll
   for (int w = 1; w < NR; ++w) g = f4_add(g, v[w]);
   return g;
 }
 
-__device__ __forceinline__ float4 reduce_dyn(const GeepsPushApplyParams& p, long long off) {
-  float4 g = ld_f4_peer(p.upd[0] + off);
-  for (int w = 1; w < p.n_ranks; ++w) g = f4_add(g, ld_f4_peer(p.upd[w] + off));
+__device__ __forceinline__ float4 reduce_dyn(const GeepsPushApplyParams& p, long long off, bool strong) {
+  float4 g = strong ? ld_f4_peer(p.upd[0] + off) : ld_f4_cg(p.upd[0] + off);
+  for (int w = 1; w < p.n_ranks; ++w) g = f4_add(g, strong ? ld_f4_peer(p.upd[w] + off) : ld_f4_cg(p.upd[w] + off));
   return g;
 }
 
@@ -85,6 +88,7 @@ push_apply_kernel(const GeepsPushApplyParams p) {
   }
   __syncthreads();
   const bool ok = s_ok != 0;
+  const bool strong = p.push_ready != nullptr;   // flags were awaited inside this kernel
 
   if (ok) {
     const int lane = threadIdx.x & 31;
@@ -98,7 +102,7 @@ push_apply_kernel(const GeepsPushApplyParams p) {
       }
       const long long goff = grow * GEEPS_ROW_FLOATS + lane * 4;  // offset in full-table buffers
       const long long loff = i * GEEPS_ROW_FLOATS + lane * 4;     // offset in shard-local buffers
-      float4 g = (NR > 0) ? reduce_fixed_order<(NR > 0 ? NR : 1)>(p, goff) : reduce_dyn(p, goff);
+      float4 g = (NR > 0) ? reduce_fixed_order<(NR > 0 ? NR : 1)>(p, goff, strong) : reduce_dyn(p, goff, strong);
       float4 w = ld_f4(p.master + loff);
       if (p.mode == GEEPS_TABLE_SGD_MOMENTUM) {
         float4 m = ld_f4(p.momentum + loff);
