@@ -112,6 +112,8 @@ def main() -> None:
     ap.add_argument("--cache-frac", type=float, default=None,
                     help="manage activations through the PS memory plan and cap the GPU budget at this fraction of the working set")
     ap.add_argument("--slack", type=int, default=0)
+    ap.add_argument("--no-tape", action="store_true",
+                    help="re-run the Python layer code every step instead of replaying the recorded native calls")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -155,7 +157,8 @@ def main() -> None:
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=args.slack, seed=1,
-                       manage_activations=args.cache_frac is not None, cache_fraction=args.cache_frac)
+                       manage_activations=args.cache_frac is not None, cache_fraction=args.cache_frac,
+                       use_tape=not args.no_tape)
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
         x_dev = torch.randn((B,) + image, device=dev, generator=gen)
         y_dev = torch.randint(0, classes, (B,), device=dev, generator=gen)
@@ -235,6 +238,7 @@ def main() -> None:
                 "dtype": "bf16", "data": "synthetic", "impl": "ours",
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
                            "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack,
+                           "host_replay_tapes": len(mod._tapes),
                            "tables": "fp32 master rows, momentum SGD on the owning shard",
                            "l2": "inputs (158 MB/step) and activations exceed the 126 MB L2; no explicit flush"},
                 "memory_plan": ({"cache_fraction_of_activations": args.cache_frac, "budget_rows": mod.budget_rows,

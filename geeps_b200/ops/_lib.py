@@ -113,6 +113,79 @@ def check(err: int, what: str) -> None:
         raise RuntimeError(f"{what}: CUDA launch error {err}")
 
 
+class Tape:
+    """A recorded sequence of native calls (kernel launches and parameter-server calls) with their argument
+    objects.  When every pointer a training step uses is static - zero-copy parameter access, slack 0, no
+    staged buffers - the step can be replayed by walking the tape, which skips all the Python work between
+    launches (argument marshalling, shape logic, view creation)."""
+
+    def __init__(self):
+        self.ops = []          # (cfunc, args tuple, label)
+
+    def signature(self):
+        sig = []
+        for fn, args, label in self.ops:
+            row = [label]
+            for a in args:
+                obj = getattr(a, "_obj", None)       # byref(struct)
+                if obj is not None:
+                    row.append(bytes(obj))
+                elif hasattr(a, "value"):
+                    row.append(a.value)
+                else:
+                    row.append(a)
+            sig.append(tuple(row))
+        return sig
+
+    def replay(self) -> None:
+        global _launches
+        for fn, args, label in self.ops:
+            err = fn(*args)
+            if err:
+                raise RuntimeError(f"{label}: native call failed with {err} during tape replay")
+        _launches += self.kernel_launches
+
+    @property
+    def kernel_launches(self) -> int:
+        return sum(1 for _, _, label in self.ops if not label.startswith("ps:"))
+
+
+_tape = None
+
+
+def start_recording() -> Tape:
+    global _tape
+    _tape = Tape()
+    return _tape
+
+
+def stop_recording() -> Tape:
+    global _tape
+    t, _tape = _tape, None
+    return t
+
+
+def launch(fn, label: str, *args) -> None:
+    """Call a native launcher; record it when a tape is being recorded."""
+    if _tape is not None:
+        _tape.ops.append((fn, args, label))
+    check(fn(*args), label)
+
+
+def record_call(fn, label: str, *args):
+    """Call (and record) a native function whose return value is not an error code."""
+    if _tape is not None:
+        _tape.ops.append((_ignore_result(fn), args, "ps:" + label))
+    return fn(*args)
+
+
+def _ignore_result(fn):
+    def call(*a):
+        fn(*a)
+        return 0
+    return call
+
+
 def launch_count() -> int:
     """Number of native kernel-launching calls made by this process so far."""
     return _launches

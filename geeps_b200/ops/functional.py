@@ -11,7 +11,7 @@ import ctypes as C
 import torch
 
 from . import _lib as L
-from ._lib import ConvGeom, GemmParams, PoolGeom, check, lib, ptr, stream_ptr
+from ._lib import ConvGeom, GemmParams, PoolGeom, check, launch, lib, ptr, stream_ptr
 
 bf16 = torch.bfloat16
 
@@ -54,11 +54,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
         assert bias.dtype == torch.float32
     use_tc = impl == "tc" or (impl == "auto" and lib().geeps_gemm_tc_supported(C.byref(p)))
     if use_tc:
-        check(lib().geeps_gemm_bf16(C.byref(p), stream_ptr()), "gemm_bf16(tcgen05)")
+        launch(lib().geeps_gemm_bf16, "gemm_bf16(tcgen05)", C.byref(p), stream_ptr())
     else:
         if split_k != 1:
             p.split_k = 1
-        check(lib().geeps_gemm_bf16_simt(C.byref(p), stream_ptr()), "gemm_bf16(simt)")
+        launch(lib().geeps_gemm_bf16_simt, "gemm_bf16(simt)", C.byref(p), stream_ptr())
     return out
 
 
@@ -67,7 +67,7 @@ def nchw_to_nhwc_bf16(x: torch.Tensor, cpad: int | None = None) -> torch.Tensor:
     B, Cc, H, W = x.shape
     cpad = cpad or Cc
     y = torch.empty((B, H, W, cpad), dtype=bf16, device=x.device)
-    check(lib().geeps_nchw_f32_to_nhwc_bf16(ptr(x), ptr(y), B, Cc, H, W, cpad, stream_ptr()), "nchw_to_nhwc")
+    launch(lib().geeps_nchw_f32_to_nhwc_bf16, "nchw_to_nhwc", ptr(x), ptr(y), B, Cc, H, W, cpad, stream_ptr())
     return y
 
 
@@ -83,70 +83,70 @@ def conv_geom(x_shape, c0: int, cg: int, kh: int, kw: int, stride: int, pad: int
 
 
 def im2col(x: torch.Tensor, col: torch.Tensor, g: ConvGeom) -> None:
-    check(lib().geeps_im2col(ptr(x), ptr(col), C.byref(g), stream_ptr()), "im2col")
+    launch(lib().geeps_im2col, "im2col", ptr(x), ptr(col), C.byref(g), stream_ptr())
 
 
 def col2im(dcol: torch.Tensor, dx: torch.Tensor, g: ConvGeom, accumulate: bool = False) -> None:
-    check(lib().geeps_col2im(ptr(dcol), ptr(dx), C.byref(g), int(accumulate), stream_ptr()), "col2im")
+    launch(lib().geeps_col2im, "col2im", ptr(dcol), ptr(dx), C.byref(g), int(accumulate), stream_ptr())
 
 
 def bn_forward(x2d, y2d, gamma, beta, sums, mean_rstd, running_mean, running_var, eps=1e-5, momentum=0.1,
                relu=False) -> None:
     P, Cc = x2d.shape
-    check(lib().geeps_bn_forward(ptr(x2d), ptr(y2d), ptr(gamma), ptr(beta), ptr(sums), ptr(mean_rstd),
+    launch(lib().geeps_bn_forward, "bn_forward", ptr(x2d), ptr(y2d), ptr(gamma), ptr(beta), ptr(sums), ptr(mean_rstd),
                                  ptr(running_mean), ptr(running_var), C.c_longlong(P), Cc,
                                  C.c_longlong(_ld(x2d)), C.c_longlong(_ld(y2d)), C.c_float(eps),
-                                 C.c_float(momentum), int(relu), stream_ptr()), "bn_forward")
+                                 C.c_float(momentum), int(relu), stream_ptr())
 
 
 def bn_backward(x2d, dy2d, y2d, dx2d, mean_rstd, gamma, sums, dgamma, dbeta, relu=False, grad_scale=1.0) -> None:
     P, Cc = x2d.shape
-    check(lib().geeps_bn_backward(ptr(x2d), ptr(dy2d), ptr(y2d), ptr(dx2d), ptr(mean_rstd), ptr(gamma), ptr(sums),
+    launch(lib().geeps_bn_backward, "bn_backward", ptr(x2d), ptr(dy2d), ptr(y2d), ptr(dx2d), ptr(mean_rstd), ptr(gamma), ptr(sums),
                                   ptr(dgamma), ptr(dbeta), C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)),
                                   C.c_longlong(_ld(dy2d)), C.c_longlong(_ld(dx2d)), int(relu),
-                                  C.c_float(grad_scale), stream_ptr()), "bn_backward")
+                                  C.c_float(grad_scale), stream_ptr())
 
 
 def colsum(x2d, out, scale=1.0, zero_first=True) -> None:
     P, Cc = x2d.shape
-    check(lib().geeps_colsum(ptr(x2d), ptr(out), C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)), C.c_float(scale),
-                             int(zero_first), stream_ptr()), "colsum")
+    launch(lib().geeps_colsum, "colsum", ptr(x2d), ptr(out), C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)), C.c_float(scale),
+                             int(zero_first), stream_ptr())
 
 
 def relu_backward(dy, y, dx) -> None:
     assert dy.is_contiguous() and y.is_contiguous() and dx.is_contiguous()
-    check(lib().geeps_relu_backward(ptr(dy), ptr(y), ptr(dx), C.c_longlong(dy.numel()), stream_ptr()), "relu_backward")
+    launch(lib().geeps_relu_backward, "relu_backward", ptr(dy), ptr(y), ptr(dx), C.c_longlong(dy.numel()), stream_ptr())
 
 
 def relu_backward_2d(dy2d, y2d, dx2d) -> None:
     P, Cc = dy2d.shape
-    check(lib().geeps_relu_backward_2d(ptr(dy2d), ptr(y2d), ptr(dx2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dy2d)),
-                                       C.c_longlong(_ld(y2d)), C.c_longlong(_ld(dx2d)), stream_ptr()), "relu_backward_2d")
+    launch(lib().geeps_relu_backward_2d, "relu_backward_2d", ptr(dy2d), ptr(y2d), ptr(dx2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dy2d)),
+                                       C.c_longlong(_ld(y2d)), C.c_longlong(_ld(dx2d)), stream_ptr())
 
 
 def add_2d(dst2d, src2d) -> None:
     P, Cc = dst2d.shape
-    check(lib().geeps_add_bf16_2d(ptr(dst2d), ptr(src2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dst2d)),
-                                  C.c_longlong(_ld(src2d)), stream_ptr()), "add_bf16_2d")
+    launch(lib().geeps_add_bf16_2d, "add_bf16_2d", ptr(dst2d), ptr(src2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dst2d)),
+                                  C.c_longlong(_ld(src2d)), stream_ptr())
 
 
 def dropout(x, y, p: float, seed: int) -> None:
     assert x.is_contiguous() and y.is_contiguous()
-    check(lib().geeps_dropout(ptr(x), ptr(y), C.c_longlong(x.numel()), C.c_float(p), C.c_ulonglong(seed),
-                              stream_ptr()), "dropout")
+    launch(lib().geeps_dropout, "dropout", ptr(x), ptr(y), C.c_longlong(x.numel()), C.c_float(p), C.c_ulonglong(seed),
+                              stream_ptr())
 
 
 def lrn_forward(x2d, y2d, scale, size=5, alpha=1e-4, beta=0.75, k=1.0) -> None:
     P, Cc = x2d.shape
     assert x2d.is_contiguous() and y2d.is_contiguous()
-    check(lib().geeps_lrn_forward(ptr(x2d), ptr(y2d), ptr(scale), C.c_longlong(P), Cc, size, C.c_float(alpha),
-                                  C.c_float(beta), C.c_float(k), stream_ptr()), "lrn_forward")
+    launch(lib().geeps_lrn_forward, "lrn_forward", ptr(x2d), ptr(y2d), ptr(scale), C.c_longlong(P), Cc, size, C.c_float(alpha),
+                                  C.c_float(beta), C.c_float(k), stream_ptr())
 
 
 def lrn_backward(x2d, y2d, scale, dy2d, dx2d, size=5, alpha=1e-4, beta=0.75) -> None:
     P, Cc = x2d.shape
-    check(lib().geeps_lrn_backward(ptr(x2d), ptr(y2d), ptr(scale), ptr(dy2d), ptr(dx2d), C.c_longlong(P), Cc, size,
-                                   C.c_float(alpha), C.c_float(beta), stream_ptr()), "lrn_backward")
+    launch(lib().geeps_lrn_backward, "lrn_backward", ptr(x2d), ptr(y2d), ptr(scale), ptr(dy2d), ptr(dx2d), C.c_longlong(P), Cc, size,
+                                   C.c_float(alpha), C.c_float(beta), stream_ptr())
 
 
 def pool_geom(x_shape, k: int, stride: int, pad: int, ldx: int, ldy: int, ceil_mode: bool = True) -> PoolGeom:
@@ -167,45 +167,44 @@ def pool_geom(x_shape, k: int, stride: int, pad: int, ldx: int, ldy: int, ceil_m
 
 
 def maxpool_forward(x, y, argmax, g: PoolGeom) -> None:
-    check(lib().geeps_maxpool_forward(ptr(x), ptr(y), ptr(argmax), C.byref(g), stream_ptr()), "maxpool_forward")
+    launch(lib().geeps_maxpool_forward, "maxpool_forward", ptr(x), ptr(y), ptr(argmax), C.byref(g), stream_ptr())
 
 
 def maxpool_backward(dy, argmax, dx, g: PoolGeom, accumulate=False) -> None:
-    check(lib().geeps_maxpool_backward(ptr(dy), ptr(argmax), ptr(dx), C.byref(g), int(accumulate), stream_ptr()),
-          "maxpool_backward")
+    launch(lib().geeps_maxpool_backward, "maxpool_backward", ptr(dy), ptr(argmax), ptr(dx), C.byref(g), int(accumulate), stream_ptr())
 
 
 def avgpool_forward(x, y, g: PoolGeom) -> None:
-    check(lib().geeps_avgpool_forward(ptr(x), ptr(y), C.byref(g), stream_ptr()), "avgpool_forward")
+    launch(lib().geeps_avgpool_forward, "avgpool_forward", ptr(x), ptr(y), C.byref(g), stream_ptr())
 
 
 def avgpool_backward(dy, dx, g: PoolGeom, accumulate=False) -> None:
-    check(lib().geeps_avgpool_backward(ptr(dy), ptr(dx), C.byref(g), int(accumulate), stream_ptr()), "avgpool_backward")
+    launch(lib().geeps_avgpool_backward, "avgpool_backward", ptr(dy), ptr(dx), C.byref(g), int(accumulate), stream_ptr())
 
 
 def softmax_ce(logits, labels, loss_sum, dlogits, per_sample=None, loss_scale=1.0, grad_scale=1.0, zero_loss=True,
                status=None) -> None:
     B, Cc = logits.shape
     assert logits.dtype == torch.float32 and labels.dtype == torch.int64
-    check(lib().geeps_softmax_ce(ptr(logits), ptr(labels), ptr(loss_sum), ptr(per_sample), ptr(dlogits), B, Cc,
+    launch(lib().geeps_softmax_ce, "softmax_ce", ptr(logits), ptr(labels), ptr(loss_sum), ptr(per_sample), ptr(dlogits), B, Cc,
                                  C.c_longlong(_ld(logits)), C.c_longlong(_ld(dlogits) if dlogits is not None else 0),
                                  C.c_float(loss_scale), C.c_float(grad_scale), int(zero_loss), ptr(status),
-                                 stream_ptr()), "softmax_ce")
+                                 stream_ptr())
 
 
 def f32_to_bf16(src, dst) -> None:
-    check(lib().geeps_f32_to_bf16(ptr(src), ptr(dst), C.c_longlong(src.numel()), stream_ptr()), "f32_to_bf16")
+    launch(lib().geeps_f32_to_bf16, "f32_to_bf16", ptr(src), ptr(dst), C.c_longlong(src.numel()), stream_ptr())
 
 
 def axpy(y, x, alpha: float) -> None:
-    check(lib().geeps_axpy(ptr(y), ptr(x), C.c_float(alpha), C.c_longlong(y.numel()), stream_ptr()), "axpy")
+    launch(lib().geeps_axpy, "axpy", ptr(y), ptr(x), C.c_float(alpha), C.c_longlong(y.numel()), stream_ptr())
 
 
 def _row_op(fn, name, dst, src, index, dst_off, src_off, num_vals_limit, status):
     n = index.shape[0]
     lim = num_vals_limit if num_vals_limit is not None else (1 << 62)
-    check(fn(ptr(dst), ptr(src), ptr(index), C.c_longlong(n), C.c_longlong(dst_off), C.c_longlong(src_off),
-             C.c_longlong(lim), C.c_longlong(dst.shape[0]), C.c_longlong(src.shape[0]), ptr(status), stream_ptr()), name)
+    launch(fn, name, ptr(dst), ptr(src), ptr(index), C.c_longlong(n), C.c_longlong(dst_off), C.c_longlong(src_off),
+           C.c_longlong(lim), C.c_longlong(dst.shape[0]), C.c_longlong(src.shape[0]), ptr(status), stream_ptr())
 
 
 def row_gather(dst, src, index, dst_off=0, src_off=0, num_vals_limit=None, status=None) -> None:
@@ -247,5 +246,5 @@ def pull_gemm(x, w_shard_ptrs, n_start, out, *, ldw, bias=None, relu=False, read
     p.n_shards, p.needed_stamp, p.relu = len(w_shard_ptrs), needed_stamp, int(relu)
     p.out_fp32 = int(out.dtype == torch.float32)
     p.block_n = block_n
-    check(lib().geeps_pull_gemm_bf16(C.byref(p), stream_ptr()), "pull_gemm_bf16")
+    launch(lib().geeps_pull_gemm_bf16, "pull_gemm_bf16", C.byref(p), stream_ptr())
     return out

@@ -13,6 +13,7 @@ import numpy as np
 import torch
 
 from .. import _native
+from ..ops import _lib as _L
 from ..utils.config import DEVICE_CUDA, GeePsConfig
 
 ROW_FLOATS = 128
@@ -171,7 +172,7 @@ class GeePs:
 
     def read(self, handle: int, stream=None, asynchronous: bool = True) -> torch.Tensor:
         p = C.c_void_p()
-        ok = self._l.geeps_read(self._g, handle, C.byref(p), self._stream(stream), int(asynchronous))
+        ok = _L.record_call(self._l.geeps_read, "read", self._g, handle, C.byref(p), self._stream(stream), int(asynchronous))
         if not ok:
             self.check()
         return self._wrap(p.value, self._ops[handle][1])
@@ -181,15 +182,15 @@ class GeePs:
         return self._wrap(p, self._ops[handle][1], torch.bfloat16) if p else None
 
     def post_read(self, handle: int, stream=None) -> None:
-        self._l.geeps_post_read(self._g, handle, self._stream(stream))
+        _L.record_call(self._l.geeps_post_read, "post_read", self._g, handle, self._stream(stream))
 
     def pre_update(self, handle: int, stream=None) -> torch.Tensor:
         p = C.c_void_p()
-        self._l.geeps_pre_update(self._g, handle, C.byref(p), self._stream(stream))
+        _L.record_call(self._l.geeps_pre_update, "pre_update", self._g, handle, C.byref(p), self._stream(stream))
         return self._wrap(p.value, self._ops[handle][1])
 
     def update(self, handle: int, stream=None, asynchronous: bool = True) -> None:
-        self._l.geeps_update(self._g, handle, self._stream(stream), int(asynchronous))
+        _L.record_call(self._l.geeps_update, "update", self._g, handle, self._stream(stream), int(asynchronous))
 
     def local_access(self, handle: int, stream=None) -> torch.Tensor:
         p = C.c_void_p()
@@ -200,7 +201,7 @@ class GeePs:
         self._l.geeps_post_local_access(self._g, handle, self._stream(stream))
 
     def clock(self) -> None:
-        self._l.geeps_clock(self._g)
+        _L.record_call(self._l.geeps_clock, "clock", self._g)
         self.check()
 
     # ---- snapshots / lifecycle / test hooks ----

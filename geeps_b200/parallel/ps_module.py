@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import _lib as L
 from ..ops import functional as F
 from ..ops.layers import BF, ParamSpec
 from ..utils.config import TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK, GeePsConfig
@@ -48,7 +49,7 @@ class _Table:
 class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
                  slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None, manage_activations: bool = False,
-                 cache_fraction: float | None = None):
+                 cache_fraction: float | None = None, use_tape: bool = False):
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
         self.trace = trace or NullTrace()
@@ -94,6 +95,10 @@ class PSModule:
             ps_config.mm_warning_level = 0
         self.direct16 = ps_config.transport == TRANSPORT_NVLINK and ps_config.bf16_compute_cache
         self.ps = GeePs(rank, ps_config)
+        # tape replay: record two consecutive steps; if they issued identical native calls (static pointers),
+        # later steps walk the tape instead of re-running the Python layer code
+        self.use_tape = use_tape and not manage_activations
+        self._tapes, self._tape_sigs, self._tape_tries = {}, {}, {}     # keyed by (input ptr, label ptr, clock phase)
         self.initial_params = {} if keep_init else None
         self.captured = None
         self._declare()
@@ -164,6 +169,22 @@ class PSModule:
         """One clock: forward, backward, push.  Returns the mean loss as a 1-element device tensor.
         capture=True keeps clones of the parameters this clock read in `self.captured`."""
         net, tr = self.net, self.trace
+        # the update buffers a clock writes rotate through slack + 2 slots, so the calls repeat with that period
+        key = (x.data_ptr(), labels.data_ptr(), self.steps % (self.slack + 2))
+        tape = self._tapes.get(key) if self.use_tape and not capture else None
+        if tape is not None:
+            for arg, offset in tape.dropouts:      # the only arguments that change from step to step
+                arg.value = offset + self.steps
+            tape.replay()
+            self.ps.check()
+            self.steps += 1
+            for l in tape.stepped_layers:
+                l.step += 1
+            return net.loss_layer.loss
+        recording = (self.use_tape and not capture and self.steps >= 2 and self._tape_tries.get(key, 0) < 4
+                     and (key in self._tape_tries or len(self._tape_tries) < 8))
+        if recording:
+            L.start_recording()
         self.captured = {} if capture else None
         with tr.span("input", "fwd"):
             h = net.input_layer.forward(x)
@@ -212,8 +233,23 @@ class PSModule:
                 self.ps.post_local_access(M[i]["pb"])
         with tr.span("clock", "ps", clock=self.steps):
             self.ps.clock()
+        if recording:
+            self._finish_recording(L.stop_recording(), key)
         self.steps += 1
         return loss
+
+    def _finish_recording(self, tape, key):
+        """Keep the tape for this (input, label) buffer pair once two recordings of it issued the same native
+        calls with the same arguments (dropout seeds aside, which are re-derived from the step count)."""
+        import ctypes
+        self._tape_tries[key] = self._tape_tries.get(key, 0) + 1
+        tape.dropouts = [(a, a.value - self.steps) for fn, args, label in tape.ops if label == "dropout"
+                         for a in args if isinstance(a, ctypes.c_ulonglong)]
+        tape.stepped_layers = [l for l in self.net.all_layers() if hasattr(l, "seed") and hasattr(l, "step")]
+        sig = [row for row in tape.signature() if row[0] != "dropout"]
+        if self._tape_sigs.get(key) == sig:
+            self._tapes[key] = tape
+        self._tape_sigs[key] = sig
 
     def params_fp32(self) -> dict:
         """Current parameter values as seen by this worker's last Read (for tests)."""

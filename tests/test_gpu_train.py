@@ -135,3 +135,27 @@ def test_managed_activations_match_unmanaged(frac):
             assert mod.ps.last_error() == 0
             mod.close()
     assert losses[True] == pytest.approx(losses[False], rel=2e-3), losses
+
+
+def test_tape_replay_matches_python_path():
+    """Replaying the recorded native calls of a step gives the same losses as running the layer code, keeps
+    counting launches, and still advances the dropout seeds."""
+    from geeps_b200.ops import _lib as L
+    dev = torch.device("cuda:0")
+    B = 64
+    losses, launches = {}, {}
+    for tape in (False, True):
+        with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+            mod = PSModule(inception_bn_small(), (B, 3, 32, 32), cfg(TRANSPORT_NVLINK, learning_rate=0.01), device=dev,
+                           seed=9, use_tape=tape)
+            gen = torch.Generator(device=dev).manual_seed(5)
+            x = torch.randn(B, 3, 32, 32, device=dev, generator=gen)
+            y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+            n0 = L.launch_count()
+            losses[tape] = [mod.step(x, y).item() for _ in range(10)]
+            launches[tape] = L.launch_count() - n0
+            assert (len(mod._tapes) == 2) == tape
+            assert mod.ps.last_error() == 0
+            mod.close()
+    assert losses[True] == pytest.approx(losses[False], rel=2e-3), losses
+    assert launches[True] == launches[False]

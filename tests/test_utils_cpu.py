@@ -26,3 +26,32 @@ def test_config_mirror_covers_every_numeric_field():
     for k in GeePsConfig._NUMERIC + GeePsConfig._STRING:
         assert hasattr(cfg, k), k
     assert cfg.tcp_base_port == 9090 and cfg.mm_warning_level == 1 and cfg.read_my_writes == 0
+
+
+def test_tape_records_and_replays_native_calls():
+    import ctypes as C
+    from geeps_b200.ops import _lib as L
+    seen = []
+
+    def fake_kernel(a, b):
+        seen.append((a.value, b))
+        return 0
+
+    def fake_ps(a):
+        seen.append(("ps", a))
+        return 1
+
+    tape = L.start_recording()
+    seed = C.c_ulonglong(7)
+    L.launch(fake_kernel, "dropout", seed, 3)
+    assert L.record_call(fake_ps, "read", 5) == 1
+    assert L.stop_recording() is tape
+    L.launch(fake_kernel, "dropout", seed, 4)            # not recorded any more
+    assert len(tape.ops) == 2 and tape.kernel_launches == 1
+    assert tape.signature() == [("dropout", 7, 3), ("ps:read", 5)]
+    seen.clear()
+    seed.value = 8
+    n0 = L.launch_count()
+    tape.replay()
+    assert seen == [(8, 3), ("ps", 5)]
+    assert L.launch_count() - n0 == 1
