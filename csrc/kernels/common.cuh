@@ -26,7 +26,7 @@ enum GeepsStatusCode : int {
 enum GeepsKernelId : int {
   KID_ROW_GATHER = 1, KID_ROW_SCATTER = 2, KID_ROW_SCATTER_ADD = 3, KID_ROW_AXPY = 4,
   KID_PUSH_APPLY = 10, KID_PULL = 11, KID_PUSHPULL = 12, KID_FLAG_WAIT = 13,
-  KID_GEMM_TC = 20, KID_GEMM_SIMT = 21, KID_PULL_GEMM = 22,
+  KID_GEMM_TC = 20, KID_GEMM_SIMT = 21, KID_PULL_GEMM = 22, KID_CONV_TC = 23,
 };
 
 __device__ __forceinline__ void geeps_report(int* status, int code, int kid, int detail, int seen) {

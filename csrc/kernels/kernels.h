@@ -90,6 +90,22 @@ int geeps_gemm_tc_supported(const GeepsGemmParams* p);             // 1 if the t
 // C[m][n] = beta * C[m][n] (exactly 0 when beta == 0) over an M x N view with pitch ldc
 int geeps_scale_matrix_f32(float* c, long long M, long long N, long long ldc, float beta, void* stream);
 
+// ---------------- implicit-GEMM convolution, stride 1 (tcgen05 + 4-D TMA, no patch matrix) ----------------
+// NHWC bf16 activations: x is [B][H][W] pixels of x_pitch channels of which this call uses the cg channels
+// starting at x; y likewise [B][OH][OW] x y_pitch with og channels; OH = H + 2 pad - KH + 1.
+// w is [og][ldw] with column (kh * KW + kw) * cg + ci.
+//   mode 0 forward:        y = conv(x, w) + bias, optional ReLU   (w bf16, ldw % 8 == 0)
+//   mode 1 data gradient:  x = conv^T(y, w)                        (y holds dY, x receives dX)
+//   mode 2 weight gradient: w = dY^T * patches(x), fp32            (w fp32, ldw % 4 == 0; split_k 0 = auto)
+// Pointers 16-byte aligned; cg, og and the pitches multiples of 8.
+typedef struct GeepsConvTcParams {
+  void* x; void* y; void* w; const float* bias; int* status;
+  long long x_pitch, y_pitch, ldw;
+  int B, H, W, cg, OH, OW, og, KH, KW, pad, relu, mode, split_k;
+} GeepsConvTcParams;
+int geeps_conv_tc(const GeepsConvTcParams* p, void* stream);
+int geeps_conv_tc_supported(const GeepsConvTcParams* p);
+
 // ---------------- parameter pull fused with the consuming GEMM ----------------
 // Y[M,N] = X[M,K] * W[N,K]^T + bias (+ReLU), M <= 256, K a multiple of 64.  W's rows live on the server
 // shards: shard s holds rows [n_start[s], n_start[s+1]) (n_start[n_shards] = N) as bf16 at w_shard[s]

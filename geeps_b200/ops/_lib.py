@@ -26,6 +26,16 @@ class GemmParams(C.Structure):
     ]
 
 
+class ConvTcParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("y", C.c_void_p), ("w", C.c_void_p), ("bias", C.c_void_p), ("status", C.c_void_p),
+        ("x_pitch", C.c_longlong), ("y_pitch", C.c_longlong), ("ldw", C.c_longlong),
+        ("B", C.c_int), ("H", C.c_int), ("W", C.c_int), ("cg", C.c_int), ("OH", C.c_int), ("OW", C.c_int),
+        ("og", C.c_int), ("KH", C.c_int), ("KW", C.c_int), ("pad", C.c_int), ("relu", C.c_int),
+        ("mode", C.c_int), ("split_k", C.c_int),
+    ]
+
+
 class PushApplyParams(C.Structure):
     _fields_ = [
         ("upd", C.c_void_p * MAX_RANKS), ("cache", C.c_void_p * MAX_RANKS),

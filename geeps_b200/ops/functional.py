@@ -11,7 +11,7 @@ import ctypes as C
 import torch
 
 from . import _lib as L
-from ._lib import ConvGeom, GemmParams, PoolGeom, check, launch, lib, ptr, stream_ptr
+from ._lib import ConvGeom, ConvTcParams, GemmParams, PoolGeom, check, launch, lib, ptr, stream_ptr
 
 bf16 = torch.bfloat16
 
@@ -60,6 +60,45 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
             p.split_k = 1
         launch(lib().geeps_gemm_bf16_simt, "gemm_bf16(simt)", C.byref(p), stream_ptr())
     return out
+
+
+CONV_FWD, CONV_DGRAD, CONV_WGRAD = 0, 1, 2
+
+
+def conv_tc_params(mode: int, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, k: int, pad: int, *,
+                   bias: torch.Tensor | None = None, relu: bool = False, split_k: int = 0,
+                   status: torch.Tensor | None = None) -> ConvTcParams:
+    """Arguments of the implicit-GEMM convolution (stride 1).  x: [B, H, W, cg] and y: [B, OH, OW, og] are NHWC
+    bf16 tensors or channel slices of wider ones (last-dim stride 1, dense pixels); w: [og, ldw] with column
+    (kh * k + kw) * cg + ci, bf16 for forward / data gradient, fp32 (the gradient) for the weight gradient."""
+    B, H, W, cg = x.shape
+    _, OH, OW, og = y.shape
+    assert x.stride(3) == 1 and y.stride(3) == 1 and w.stride(1) == 1
+    xp, yp = x.stride(2), y.stride(2)
+    assert x.stride(1) == W * xp and x.stride(0) == H * W * xp, "x pixels must be dense"
+    assert y.stride(1) == OW * yp and y.stride(0) == OH * OW * yp, "y pixels must be dense"
+    p = ConvTcParams()
+    p.x, p.y, p.w = x.data_ptr(), y.data_ptr(), w.data_ptr()
+    p.bias = bias.data_ptr() if bias is not None else None
+    p.status = status.data_ptr() if status is not None else None
+    p.x_pitch, p.y_pitch, p.ldw = xp, yp, w.stride(0)
+    p.B, p.H, p.W, p.cg, p.OH, p.OW, p.og = B, H, W, cg, OH, OW, og
+    p.KH, p.KW, p.pad, p.relu, p.mode, p.split_k = k, k, pad, int(relu), mode, split_k
+    return p
+
+
+def conv_tc_supported(p: ConvTcParams) -> bool:
+    return bool(lib().geeps_conv_tc_supported(C.byref(p)))
+
+
+def conv_tc(mode: int, x, y, w, k: int, pad: int, **kw) -> None:
+    """Stride-1 convolution without a patch matrix (tcgen05 + 4-D TMA): forward writes y, CONV_DGRAD writes x
+    (y holds dY), CONV_WGRAD writes w (fp32, y holds dY)."""
+    L.require_cuda()
+    assert x.dtype == bf16 and y.dtype == bf16
+    assert w.dtype == (torch.float32 if mode == CONV_WGRAD else bf16)
+    p = conv_tc_params(mode, x, y, w, k, pad, **kw)
+    launch(lib().geeps_conv_tc, "conv_tc", C.byref(p), stream_ptr())
 
 
 def nchw_to_nhwc_bf16(x: torch.Tensor, cpad: int | None = None) -> torch.Tensor:

@@ -1,0 +1,75 @@
+"""Implicit-GEMM convolution (tcgen05 + 4-D TMA, stride 1) against torch's fp32 convolution."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BF = torch.bfloat16
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+CASES = [
+    # B, H, W, C_total, c_off, cg, O_total, o_off, og, k, pad
+    (8, 13, 13, 64, 0, 64, 96, 0, 96, 3, 1),            # one channel chunk, one N tile
+    (4, 27, 27, 96, 48, 48, 256, 128, 128, 5, 2),       # a 48-channel group slice (zero-filled to 64), 5x5
+    (16, 13, 13, 192, 0, 192, 384, 0, 384, 3, 1),       # three chunks, two N tiles
+    (5, 10, 12, 16, 0, 16, 40, 0, 40, 3, 0),            # no padding: output smaller than input
+    (3, 9, 9, 32, 0, 32, 64, 0, 64, 1, 0),              # 1x1
+    (2, 32, 32, 96, 0, 96, 32, 0, 32, 3, 1),            # wide image: boxes split the width
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_conv_tc_forward_dgrad_wgrad_match_torch(case):
+    from geeps_b200.ops import functional as F
+    B, H, W, Ct, c_off, cg, Ot, o_off, og, k, pad = case
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(hash(case) % 1000)
+    OH, OW = H + 2 * pad - k + 1, W + 2 * pad - k + 1
+    kd = k * k * cg
+    ld = (kd + 7) // 8 * 8
+    x_full = torch.randn(B, H, W, Ct, device=dev, generator=gen).to(BF)
+    w = torch.zeros(og, ld, device=dev, dtype=BF)
+    w[:, :kd] = (torch.randn(og, kd, device=dev, generator=gen) / kd ** 0.5).to(BF)
+    bias = torch.randn(og, device=dev, generator=gen)
+    dy_full = torch.randn(B, OH, OW, Ot, device=dev, generator=gen).to(BF)
+    x = x_full[..., c_off:c_off + cg]
+    dy = dy_full[..., o_off:o_off + og]
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    # fp32 reference on the bf16-rounded operands
+    xr = x.float().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    wr = w[:, :kd].float().view(og, k, k, cg).permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    yr = torch.nn.functional.conv2d(xr, wr, bias, padding=pad)
+    yr.backward(dy.float().permute(0, 3, 1, 2))
+    y_ref = torch.relu(yr.detach()).permute(0, 2, 3, 1)
+    dx_ref = xr.grad.permute(0, 2, 3, 1)
+    dw_ref = wr.grad.permute(0, 2, 3, 1).reshape(og, kd)
+
+    y_full = torch.full((B, OH, OW, Ot), 7.0, device=dev, dtype=BF)
+    y = y_full[..., o_off:o_off + og]
+    assert F.conv_tc_supported(F.conv_tc_params(F.CONV_FWD, x, y, w, k, pad))
+    F.conv_tc(F.CONV_FWD, x, y, w, k, pad, bias=bias, relu=True, status=status)
+    assert _rel(y, y_ref) < 1e-2
+    if Ot != og:      # channels outside the slice are untouched
+        rest = torch.cat([y_full[..., :o_off], y_full[..., o_off + og:]], dim=-1)
+        assert bool((rest == 7.0).all())
+
+    dx_full = torch.full((B, H, W, Ct), 3.0, device=dev, dtype=BF)
+    dx = dx_full[..., c_off:c_off + cg]
+    F.conv_tc(F.CONV_DGRAD, dx, dy, w, k, pad, status=status)
+    assert _rel(dx, dx_ref) < 1e-2
+    if Ct != cg:
+        rest = torch.cat([dx_full[..., :c_off], dx_full[..., c_off + cg:]], dim=-1)
+        assert bool((rest == 3.0).all())
+
+    for split in (0, 1):
+        dw = torch.full((og, ld), 5.0, device=dev)
+        F.conv_tc(F.CONV_WGRAD, x, dy, dw, k, pad, split_k=split, status=status)
+        assert _rel(dw[:, :kd], dw_ref) < 1e-2, split
+        assert bool((dw[:, kd:] == 0).all())
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
