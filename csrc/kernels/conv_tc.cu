@@ -121,7 +121,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       tc05::tma_prefetch_desc(&tmA);
       tc05::tma_prefetch_desc(&tmB);
-      uint32_t it = 0;
+      // every index below advances incrementally: this one thread's latency is the producer's throughput,
+      // and an integer division costs more than the TMA issue itself
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       const uint32_t tx_bytes = MODE == MODE_WGRAD ? (uint32_t)((2 + BN / 64) * d.rows * 128)
                                                    : (uint32_t)(d.rows * 128 + BN * 128);
@@ -131,39 +134,53 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int kt_begin = z * kt_per, kt_end = min(d.kt_total, kt_begin + kt_per);
         Box mb = {0, 0, 0};
         if (MODE != MODE_WGRAD) mb = decode_box(d, mi);
-        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
+        // fwd / dgrad: k-tile = (kh, kw, channel chunk), starting at 0 (no split)
+        int kh = 0, kw = 0, cc = 0, tap = 0;
+        // wgrad: k-tile = pixel box; the N panels of this tile are fixed
+        Box kb = {0, 0, 0};
+        int pc[4] = {0, 0, 0, 0}, pdw[4] = {0, 0, 0, 0}, pdh[4] = {0, 0, 0, 0};
+        if (MODE == MODE_WGRAD) {
+          kb = decode_box(d, kt_begin);
+          for (int j = 0; j < BN / 64; ++j) {
+            const int panel = ni * (BN / 64) + j;
+            const bool valid = panel * 64 < d.n_valid;
+            const int ptap = valid ? panel / d.cchunks : 0;
+            const int pkh = ptap / d.KW;
+            pc[j] = valid ? (panel - ptap * d.cchunks) * 64 : d.zero_fill_c;
+            pdw[j] = ptap - pkh * d.KW - d.pad;
+            pdh[j] = pkh - d.pad;
+          }
+        }
+        for (int kt = kt_begin; kt < kt_end; ++kt) {
           if (!tc05::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           uint8_t* sa = tiles + (size_t)s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           uint64_t* bar = &ctl->full[s];
           tc05::mbar_expect_tx(bar, tx_bytes);
           if (MODE == MODE_FWD) {
-            const int tap = kt / d.cchunks, cc = kt - tap * d.cchunks;
-            const int kh = tap / d.KW, kw = tap - kh * d.KW;
             tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 + kw - d.pad, mb.h0 + kh - d.pad, mb.b0);
             tc05::tma_load_3d(sb, &tmB, bar, cc * 64, tap, ni * BN);
           } else if (MODE == MODE_DGRAD) {
-            const int tap = kt / d.cchunks, cc = kt - tap * d.cchunks;
-            const int kh = tap / d.KW, kw = tap - kh * d.KW;
             tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 + d.pad - kw, mb.h0 + d.pad - kh, mb.b0);
             for (int h = 0; h < BN / 64; ++h)
               tc05::tma_load_3d(sb + h * PANEL_BYTES, &tmB, bar, ni * BN + 64 * h, tap, cc * 64);
           } else {
-            const Box kb = decode_box(d, kt);
             for (int h = 0; h < 2; ++h)
               tc05::tma_load_4d(sa + h * PANEL_BYTES, &tmA, bar, mi * BM + 64 * h, kb.w0, kb.h0, kb.b0);
-            for (int j = 0; j < BN / 64; ++j) {
-              const int panel = ni * (BN / 64) + j;
-              const bool valid = panel * 64 < d.n_valid;
-              const int tap = valid ? panel / d.cchunks : 0;
-              const int cc = panel - tap * d.cchunks;
-              const int kh = tap / d.KW, kw = tap - kh * d.KW;
-              tc05::tma_load_4d(sb + j * PANEL_BYTES, &tmB, bar, valid ? cc * 64 : d.zero_fill_c,
-                                kb.w0 + kw - d.pad, kb.h0 + kh - d.pad, kb.b0);
-            }
+            for (int j = 0; j < BN / 64; ++j)
+              tc05::tma_load_4d(sb + j * PANEL_BYTES, &tmB, bar, pc[j], kb.w0 + pdw[j], kb.h0 + pdh[j], kb.b0);
           }
+          if (MODE == MODE_WGRAD) {
+            kb.w0 += d.bw;
+            if (kb.w0 >= d.wt * d.bw) {
+              kb.w0 = 0; kb.h0 += d.bh;
+              if (kb.h0 >= d.ht * d.bh) { kb.h0 = 0; kb.b0 += d.bnb; }
+            }
+          } else if (++cc == d.cchunks) {
+            cc = 0; ++tap;
+            if (++kw == d.KW) { kw = 0; ++kh; }
+          }
+          if (++s == S) { s = 0; ph ^= 1u; }
         }
       }
     }
@@ -171,7 +188,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = tc05::make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
-      uint32_t it = 0, tile_i = 0;
+      uint32_t tile_i = 0, ph = 0;
+      int s = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
         const int z = t / tiles_mn;
@@ -180,9 +198,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!tc05::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
         tc05::fence_after_sync();
         const uint32_t tacc = tmem + acc * (uint32_t)acc_stride;
-        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
+        for (int kt = kt_begin; kt < kt_end; ++kt) {
           if (!tc05::mbar_wait(&ctl->full[s], ph, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           tc05::fence_after_sync();
           const uint32_t sa = tc05::smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -196,6 +212,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc05::mma_bf16_ss(tacc, da, db, idesc, (kt > kt_begin || k > 0) ? 1u : 0u);
           }
           tc05::mma_commit(&ctl->empty[s]);
+          if (++s == S) { s = 0; ph ^= 1u; }
         }
         if (ok) tc05::mma_commit(&ctl->tmem_full[acc]);
       }
@@ -453,7 +470,7 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
     if (split <= 0) {
       split = 1;
       if (tiles < kSMs && d.kt_total >= 8) {
-        long long want = (2 * kSMs + tiles - 1) / tiles;
+        long long want = (2 * kSMs) / tiles;   // at most two full waves: one work item more would add a third round
         long long cap = d.kt_total / 4;
         split = (int)(want < cap ? want : cap);
         if (split < 1) split = 1;

@@ -97,15 +97,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       tc05::tma_prefetch_desc(&tmA);
       tc05::tma_prefetch_desc(&tmB);
-      uint32_t it = 0;   // running k-tile counter across all tiles of this CTA
+      // ring slot and phase advance incrementally: a division per k-tile in this single thread would cost
+      // more than issuing the loads
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int mn = t % tiles_mn, z = t / tiles_mn;
         const int m0 = (mn % d.m_tiles) * BM, n0 = (mn / d.m_tiles) * BN;
         const int kt_begin = z * kt_per, kt_end = min(d.kt_total, kt_begin + kt_per);
-        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
+        for (int kt = kt_begin; kt < kt_end; ++kt) {
           if (!tc05::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           uint8_t* sa = tiles + (size_t)s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
@@ -124,6 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           } else {
             tc05::tma_load_2d(sb, &tmB, &ctl->full[s], k0, n0);
           }
+          if (++s == S) { s = 0; ph ^= 1u; }
         }
       }
     }
@@ -131,7 +133,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       const uint32_t idesc = tc05::make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
-      uint32_t it = 0, tile_i = 0;
+      uint32_t tile_i = 0, ph = 0;
+      int s = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
         const int z = t / tiles_mn;
@@ -141,9 +144,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!tc05::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
         tc05::fence_after_sync();
         const uint32_t tacc = tmem + acc * (uint32_t)acc_stride;
-        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
+        for (int kt = kt_begin; kt < kt_end; ++kt) {
           if (!tc05::mbar_wait(&ctl->full[s], ph, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           tc05::fence_after_sync();
           const uint32_t sa = tc05::smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -159,6 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc05::mma_bf16_ss(tacc, da, db, idesc, (kt > kt_begin || k > 0) ? 1u : 0u);
           }
           tc05::mma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
+          if (++s == S) { s = 0; ph ^= 1u; }
         }
         if (ok) tc05::mma_commit(&ctl->tmem_full[acc]);
       }
@@ -457,7 +459,7 @@ int geeps_gemm_bf16(const GeepsGemmParams* p, void* stream) {
     split = 1;
     const long long tiles = (long long)m_tiles * n_tiles;
     if (p->out_fp32 && !p->relu && tiles < kSMs && d.kt_total >= 8) {
-      long long want = (2 * kSMs + tiles - 1) / tiles;
+      long long want = (2 * kSMs) / tiles;   // at most two full waves: one work item more would add a third round
       long long cap = d.kt_total / 4;
       split = (int)(want < cap ? want : cap);
       if (split < 1) split = 1;

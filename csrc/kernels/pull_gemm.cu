@@ -97,14 +97,17 @@ pull_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const PullGemmDev d) {
     // ---------------- X tiles: TMA from local memory ----------------
     if (lane == 0) {
       tc05::tma_prefetch_desc(&tmA);
+      // ring slots and phases advance incrementally everywhere in this kernel: a division per k-tile in a
+      // single-thread role costs more than the work it schedules
+      int s = 0;
+      uint32_t ph = 0;
       for (int kt = 0; kt < KT; ++kt) {
-        const int s = kt % SA;
-        const uint32_t ph = (uint32_t)(kt / SA) & 1u;
         if (!tc05::mbar_wait(&ctl->empty_a[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) break;
         uint8_t* sa = tiles_a + (size_t)s * A_STAGE;
         tc05::mbar_expect_tx(&ctl->full_a[s], (uint32_t)A_STAGE);
         for (int mt = 0; mt < d.m_tiles; ++mt)
           tc05::tma_load_2d(sa + mt * A_TILE_BYTES, &tmA, &ctl->full_a[s], kt * BK, mt * BM);
+        if (++s == SA) { s = 0; ph ^= 1u; }
       }
     }
   } else if (warp == 1) {
@@ -112,10 +115,11 @@ pull_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const PullGemmDev d) {
     if (lane == 0) {
       const uint32_t idesc = tc05::make_idesc_bf16(BM, BN, 0, 0);
       bool ok = true;
+      int s = 0, t = 0;
+      uint32_t pha = 0, phb = 0;
       for (int kt = 0; kt < KT && ok; ++kt) {
-        const int s = kt % SA, t = kt % SB;
-        if (!tc05::mbar_wait(&ctl->full_a[s], (uint32_t)(kt / SA) & 1u, abort_flag, WAIT_BUDGET_NS) ||
-            !tc05::mbar_wait(&ctl->full_b[t], (uint32_t)(kt / SB) & 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+        if (!tc05::mbar_wait(&ctl->full_a[s], pha, abort_flag, WAIT_BUDGET_NS) ||
+            !tc05::mbar_wait(&ctl->full_b[t], phb, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
         tc05::fence_after_sync();
         const uint32_t sa = tc05::smem_u32(tiles_a + (size_t)s * A_STAGE);
         const uint32_t sb = tc05::smem_u32(tiles_b + (size_t)t * B_STAGE);
@@ -129,6 +133,8 @@ pull_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const PullGemmDev d) {
         }
         tc05::mma_commit(&ctl->empty_a[s]);
         tc05::mma_commit(&ctl->empty_b[t]);
+        if (++s == SA) { s = 0; pha ^= 1u; }
+        if (++t == SB) { t = 0; phb ^= 1u; }
       }
       if (ok) tc05::mma_commit(&ctl->tmem_full);
     }
@@ -171,8 +177,8 @@ pull_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const PullGemmDev d) {
       const __nv_bfloat16* any_valid = (const __nv_bfloat16*)p.X;   // address for zero-size (zero-fill) copies
       // copy this thread's own chunks of k-tile `kt_old` from its SMEM stage into the local parameter cache;
       // the thread's later cp.async into the same SMEM addresses follows in program order
-      auto mirror = [&](int kt_old) {
-        const uint8_t* st = tiles_b + (size_t)(kt_old % SB) * B_STAGE;
+      auto mirror = [&](int kt_old, int slot) {
+        const uint8_t* st = tiles_b + (size_t)slot * B_STAGE;
 #pragma unroll
         for (int i = 0; i < NS; ++i) {
           if (i >= nslots || !src_row[i]) continue;
@@ -182,12 +188,12 @@ pull_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const PullGemmDev d) {
           *reinterpret_cast<uint4*>((__nv_bfloat16*)p.w_local + n * p.ldw + (long long)kt_old * BK + (idx & 7) * 8) = v;
         }
       };
+      int s = 0;
+      uint32_t ph = 0;
       for (int kt = 0; kt < KT; ++kt) {
-        const int s = kt % SB;
-        const uint32_t ph = (uint32_t)(kt / SB) & 1u;
         if (!tc05::mbar_wait(&ctl->empty_b[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) break;
         const uint32_t sb = tc05::smem_u32(tiles_b + (size_t)s * B_STAGE);
-        if (p.w_local != nullptr && kt >= SB) mirror(kt - SB);   // the tile this stage held has been consumed
+        if (p.w_local != nullptr && kt >= SB) mirror(kt - SB, s);   // the tile this stage held has been consumed
 #pragma unroll
         for (int i = 0; i < NS; ++i) {
           if (i >= nslots) continue;
@@ -197,28 +203,36 @@ pull_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const PullGemmDev d) {
         }
         // arrives on `staged` once this thread's copies above have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(tc05::smem_u32(&ctl->staged[s])) : "memory");
+        if (++s == SB) { s = 0; ph ^= 1u; }
       }
       asm volatile("cp.async.wait_all;" ::: "memory");
       if (p.w_local != nullptr) {
         // the last SB tiles: wait until the MMAs have consumed everything, then mirror them
         if (tc05::mbar_wait(&ctl->tmem_full, 0, abort_flag, WAIT_BUDGET_NS))
-          for (int kt = (KT > SB ? KT - SB : 0); kt < KT; ++kt) mirror(kt);
+          for (int kt = (KT > SB ? KT - SB : 0); kt < KT; ++kt) mirror(kt, kt % SB);
       }
     } else {
       // committer warp.  The cross-proxy fence is expensive while copies are in flight (it waits for
       // them), so one fence publishes a group of G landed tiles.
       const int G = SB >= 12 ? 4 : (SB >= 6 ? 2 : 1);
       if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 0;
         for (int kt0 = 0; kt0 < KT; kt0 += G) {
           const int ng = min(G, KT - kt0);
           bool okc = true;
+          int sw = s;
+          uint32_t phw = ph;
           for (int g = 0; g < ng && okc; ++g) {
-            const int kt = kt0 + g;
-            okc = tc05::mbar_wait(&ctl->staged[kt % SB], (uint32_t)(kt / SB) & 1u, abort_flag, WAIT_BUDGET_NS);
+            okc = tc05::mbar_wait(&ctl->staged[sw], phw, abort_flag, WAIT_BUDGET_NS);
+            if (++sw == SB) { sw = 0; phw ^= 1u; }
           }
           if (!okc) break;
           tc05::fence_proxy_async_smem();
-          for (int g = 0; g < ng; ++g) tc05::mbar_arrive(&ctl->full_b[(kt0 + g) % SB]);
+          for (int g = 0; g < ng; ++g) {
+            tc05::mbar_arrive(&ctl->full_b[s]);
+            if (++s == SB) { s = 0; ph ^= 1u; }
+          }
         }
       }
     }

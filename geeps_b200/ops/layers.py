@@ -12,6 +12,7 @@ max pooling, BatchNorm + scale, inner product, softmax loss.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -19,6 +20,8 @@ import torch
 from . import functional as F
 
 BF = torch.bfloat16
+# stride-1 convolutions as implicit GEMM (GEEPS_IMPLICIT_CONV=0 keeps the im2col + GEMM + col2im formulation)
+IMPLICIT_CONV = os.environ.get("GEEPS_IMPLICIT_CONV", "1") != "0"
 
 
 def _pad8(n: int) -> int:
@@ -117,6 +120,7 @@ class Conv2d(Layer):
     def setup(self, in_shape, device):
         B, H, W, C = in_shape
         self.in_shape = in_shape
+        self.device = device
         G = self.groups
         self.cg, self.og = C // G, self.cout // G
         self.kd = self.k * self.k * self.cg
@@ -126,14 +130,30 @@ class Conv2d(Layer):
         self.OH, self.OW = self.geoms[0].OH, self.geoms[0].OW
         self.M = B * self.OH * self.OW
         self.pointwise = self.k == 1 and self.stride == 1 and self.pad == 0 and G == 1 and C % 8 == 0
-        if not self.pointwise:
-            self.cols = [torch.empty(self.M, self.ld, dtype=BF, device=device) for _ in range(G)]
-            self.dcol = torch.empty(self.M, self.ld, dtype=BF, device=device) if self.need_dx else None
+        # stride-1 layers run as an implicit GEMM (no patch matrix); the final say comes from the kernel's own
+        # alignment check on the first forward, when the output binding is known
+        self.implicit = (IMPLICIT_CONV and not self.pointwise and self.stride == 1 and self.cg % 8 == 0
+                         and self.og % 8 == 0 and C % 8 == 0)
+        self.cols = self.dcol = None
+        if not self.pointwise and not self.implicit:
+            self._alloc_patch_buffers()
         self.y = None
         self.dx = torch.empty(in_shape, dtype=BF, device=device) if self.need_dx else None
         self.out_shape = (B, self.OH, self.OW, self.cout)
         self.device = device
         return self.out_shape
+
+    def _alloc_patch_buffers(self):
+        self.cols = [torch.empty(self.M, self.ld, dtype=BF, device=self.device) for _ in range(self.groups)]
+        self.dcol = torch.empty(self.M, self.ld, dtype=BF, device=self.device) if self.need_dx else None
+
+    def _x4(self, x, g):
+        B, H, W, C = self.in_shape
+        return x.view(B, H, W, C)[..., g * self.cg:(g + 1) * self.cg]
+
+    def _y4(self, y2d, g):
+        B = self.in_shape[0]
+        return y2d.unflatten(0, (B, self.OH, self.OW))[..., g * self.og:(g + 1) * self.og]
 
     def param_specs(self):
         fan_in = self.kd
@@ -153,7 +173,20 @@ class Conv2d(Layer):
             self.y = torch.empty(self.M, self.cout, dtype=BF, device=self.device)
         w16 = self.p16["weight"]
         bias = self.p32.get("bias")
+        if self.implicit and self.cols is None and not getattr(self, "_implicit_checked", False):
+            self._implicit_checked = True
+            ok = all(F.conv_tc_supported(F.conv_tc_params(F.CONV_FWD, self._x4(x, g), self._y4(self.y, g),
+                                                          w16[g * self.og:(g + 1) * self.og], self.k, self.pad))
+                     for g in range(self.groups))
+            if not ok:
+                self.implicit = False
+                self._alloc_patch_buffers()
         for g in range(self.groups):
+            if self.implicit:
+                F.conv_tc(F.CONV_FWD, self._x4(x, g), self._y4(self.y, g), w16[g * self.og:(g + 1) * self.og],
+                          self.k, self.pad, bias=None if bias is None else bias[g * self.og:(g + 1) * self.og],
+                          relu=self.relu)
+                continue
             if self.pointwise:
                 a = x.view(self.M, -1)
             else:
@@ -174,6 +207,13 @@ class Conv2d(Layer):
             F.colsum(dy, self.g32["bias"])
         w16 = self.p16["weight"]
         for g in range(self.groups):
+            if self.implicit:
+                xg, dy4 = self._x4(self.x, g), self._y4(dy, g)
+                F.conv_tc(F.CONV_WGRAD, xg, dy4, gw[g * self.og:(g + 1) * self.og], self.k, self.pad)
+                if self.need_dx:
+                    F.conv_tc(F.CONV_DGRAD, self._x4(self.dx, g), dy4, w16[g * self.og:(g + 1) * self.og],
+                              self.k, self.pad)
+                continue
             dyg = dy[:, g * self.og:(g + 1) * self.og]
             a = self.x.view(self.M, -1) if self.pointwise else self.cols[g]
             # dW_g[og, ld] = dy_g^T @ col_g      (both operands stored K-outermost)

@@ -7,6 +7,7 @@ once and launches the kernel of interest three times.
   push_apply  fused reduce + momentum-SGD apply + publish over a 256 MB table (1 rank)
   lrn         LRN forward + backward on a conv1-sized activation
   pull_gemm   fused pull + GEMM on an fc6-shaped layer (4 local shards)
+  conv_fwd / conv_dgrad / conv_wgrad   implicit-GEMM convolution, conv3 shape (256 x 13 x 13, 256 -> 384, 3x3)
 """
 from __future__ import annotations
 
@@ -66,6 +67,19 @@ def main():
         out = torch.zeros(M, N, dtype=torch.float32, device=dev)
         for _ in range(4):
             F.pull_gemm(x, [t.data_ptr() for t in parts], [s * (N // shards) for s in range(shards)], out, ldw=K)
+    elif case in ("conv_fwd", "conv_dgrad", "conv_wgrad"):
+        B, H, cin, cout, k, pad = 256, 13, 256, 384, 3, 1
+        x = (torch.randn(B, H, H, cin, device=dev) * 0.5).to(BF)
+        y = (torch.randn(B, H, H, cout, device=dev) * 0.5).to(BF)
+        w = (torch.randn(cout, k * k * cin, device=dev) * 0.02).to(BF)
+        dw = torch.empty(cout, k * k * cin, device=dev)
+        for _ in range(4):
+            if case == "conv_fwd":
+                F.conv_tc(F.CONV_FWD, x, y, w, k, pad, relu=True)
+            elif case == "conv_dgrad":
+                F.conv_tc(F.CONV_DGRAD, x, y, w, k, pad)
+            else:
+                F.conv_tc(F.CONV_WGRAD, x, y, dw, k, pad)
     else:
         raise SystemExit(f"unknown case {case}")
     torch.cuda.synchronize()
