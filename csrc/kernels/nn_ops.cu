@@ -493,6 +493,77 @@ nchw_to_nhwc_pix_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B
   }
 }
 
+// NCHW fp32 -> space-to-depth NHWC bf16: y[b][hs][ws][(dy*S + dx)*C + c] = x[b][c][hs*S + dy][ws*S + dx]
+// (zero past the image edge and in the channel padding).  A stride-S convolution over x is then a
+// stride-1 convolution with ceil(k/S) taps per dimension over y.  One thread per output pixel; the
+// 4 x 3-channel case keeps the pixel's 48 values in registers and reads 16 contiguous bytes per (c, dy).
+template <int S, int C>
+__global__ void __launch_bounds__(256)
+nchw_to_s2d_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int H, int W, int Hs, int Ws, int Cpad) {
+  constexpr int N = S * S * C;
+  const long long total = (long long)B * Hs * Ws;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int ws = (int)(i % Ws);
+    const long long t = i / Ws;
+    const int hs = (int)(t % Hs);
+    const long long b = t / Hs;
+    float v[N];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+#pragma unroll
+      for (int dy = 0; dy < S; ++dy) {
+        const int h = hs * S + dy;
+        const float* row = x + ((b * C + c) * H + h) * (long long)W;
+#pragma unroll
+        for (int dx = 0; dx < S; ++dx) {
+          const int w = ws * S + dx;
+          v[(dy * S + dx) * C + c] = (h < H && w < W) ? __ldg(row + w) : 0.f;
+        }
+      }
+    }
+    bf16* dst = y + i * Cpad;
+#pragma unroll
+    for (int j = 0; j + 8 <= N; j += 8)
+      *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                      pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+    for (int j = N & ~7; j < Cpad; ++j) dst[j] = __float2bfloat16(j < N ? v[j] : 0.f);
+  }
+}
+
+// any S, C: one thread per output element
+__global__ void __launch_bounds__(256)
+nchw_to_s2d_generic_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int C, int H, int W, int S,
+                           int Hs, int Ws, int Cpad) {
+  const long long total = (long long)B * Hs * Ws * Cpad;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int j = (int)(i % Cpad);
+    long long t = i / Cpad;
+    const int ws = (int)(t % Ws); t /= Ws;
+    const int hs = (int)(t % Hs);
+    const long long b = t / Hs;
+    float v = 0.f;
+    if (j < S * S * C) {
+      const int c = j % C, q = j / C, dx = q % S, dy = q / S;
+      const int h = hs * S + dy, w = ws * S + dx;
+      if (h < H && w < W) v = x[((b * C + c) * H + h) * (long long)W + w];
+    }
+    y[i] = __float2bfloat16(v);
+  }
+}
+
+// g[r][c] = 0 where mask[c] == 0
+__global__ void __launch_bounds__(256)
+col_mask_kernel(float* __restrict__ g, const uint8_t* __restrict__ mask, long long rows, int cols, long long ld) {
+  const long long total = rows * cols;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cols);
+    if (!mask[c]) g[(i / cols) * ld + c] = 0.f;
+  }
+}
+
 // ---------------- pooling (NHWC, 8 channels per thread) ----------------
 // Output may be a channel slice of a wider tensor (pitch ldy, offset applied by the caller).
 __global__ void __launch_bounds__(256)
@@ -720,6 +791,23 @@ int geeps_nchw_f32_to_nhwc_bf16(const float* x, void* y, int B, int C, int H, in
     nchw_to_nhwc_pix_kernel<<<grid_1d((long long)B * H * W), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H * W, Cpad);
   else
     nchw_f32_to_nhwc_bf16_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H, W, Cpad);
+  return CK();
+}
+
+int geeps_nchw_f32_to_s2d_bf16(const float* x, void* y, int B, int C, int H, int W, int S, int Hs, int Ws, int Cpad,
+                               void* stream) {
+  if (S <= 0 || Cpad < S * S * C || (Cpad & 7)) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (S == 4 && C == 3)
+    nchw_to_s2d_kernel<4, 3><<<grid_1d((long long)B * Hs * Ws), 256, 0, st>>>(x, (bf16*)y, B, H, W, Hs, Ws, Cpad);
+  else
+    nchw_to_s2d_generic_kernel<<<grid_1d((long long)B * Hs * Ws * Cpad), 256, 0, st>>>(x, (bf16*)y, B, C, H, W, S, Hs,
+                                                                                      Ws, Cpad);
+  return CK();
+}
+
+int geeps_col_mask_f32(float* g, const unsigned char* mask, long long rows, int cols, long long ld, void* stream) {
+  col_mask_kernel<<<grid_1d(rows * cols), 256, 0, (cudaStream_t)stream>>>(g, mask, rows, cols, ld);
   return CK();
 }
 

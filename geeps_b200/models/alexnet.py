@@ -8,8 +8,9 @@ from .net import Net
 
 def alexnet(num_classes: int = 1000, dropout: float = 0.5) -> Net:
     layers = [
-        # the 3 input channels are zero-padded to 4 so the patch matrix is built with 8-byte vectors
-        Conv2d("conv1", 96, 11, stride=4, relu=True, std=0.01, need_dx=False),
+        # the input layer emits a space-to-depth(4) layout [B, 57, 57, 48]: the 11 x 11 stride-4 convolution
+        # becomes a 3 x 3 stride-1 implicit GEMM (taps past 11 are zero columns), so no patch matrix is built
+        Conv2d("conv1", 96, 11, stride=4, relu=True, std=0.01, need_dx=False, s2d=4),
         LRN(5, 1e-4, 0.75, 1.0),
         Pool("max", 3, 2),
         Conv2d("conv2", 256, 5, pad=2, groups=2, relu=True, std=0.01, bias_value=0.1),
@@ -25,4 +26,4 @@ def alexnet(num_classes: int = 1000, dropout: float = 0.5) -> Net:
         Dropout(dropout, seed=71),
         Linear("fc8", num_classes, std=0.01, fp32_out=True),
     ]
-    return Net("alexnet", Input(cpad=4), layers)
+    return Net("alexnet", Input(s2d=4, s2d_k=11), layers)

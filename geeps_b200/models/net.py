@@ -125,10 +125,7 @@ class Net:
         n = 0
         for l in self.param_layers():
             for sp in l.param_specs():
-                if valid_only and sp.valid_cols and len(sp.shape) == 2:
-                    n += sp.shape[0] * sp.valid_cols
-                else:
-                    n += sp.numel
+                n += sp.num_valid() if valid_only else sp.numel
         return n
 
     def train(self, mode=True):

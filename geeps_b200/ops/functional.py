@@ -110,6 +110,23 @@ def nchw_to_nhwc_bf16(x: torch.Tensor, cpad: int | None = None) -> torch.Tensor:
     return y
 
 
+def nchw_to_s2d_bf16(x: torch.Tensor, y: torch.Tensor, S: int) -> torch.Tensor:
+    """fp32 NCHW -> space-to-depth NHWC bf16: y[b, hs, ws, (dy*S + dx)*C + c] = x[b, c, hs*S + dy, ws*S + dx]."""
+    L.require_cuda()
+    B, Cc, H, W = x.shape
+    _, Hs, Ws, cpad = y.shape
+    assert x.dtype == torch.float32 and y.dtype == bf16 and x.is_contiguous() and y.is_contiguous()
+    launch(lib().geeps_nchw_f32_to_s2d_bf16, "nchw_to_s2d", ptr(x), ptr(y), B, Cc, H, W, S, Hs, Ws, cpad, stream_ptr())
+    return y
+
+
+def col_mask(g: torch.Tensor, mask: torch.Tensor) -> None:
+    """Zero the columns of the fp32 matrix g whose mask byte is 0."""
+    assert g.dtype == torch.float32 and mask.dtype == torch.uint8 and g.stride(1) == 1
+    launch(lib().geeps_col_mask_f32, "col_mask", ptr(g), ptr(mask), C.c_longlong(g.shape[0]), int(mask.numel()),
+           C.c_longlong(g.stride(0)), stream_ptr())
+
+
 def conv_geom(x_shape, c0: int, cg: int, kh: int, kw: int, stride: int, pad: int, ldcol: int) -> ConvGeom:
     B, H, W, Cc = x_shape
     g = ConvGeom()

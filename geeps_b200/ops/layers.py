@@ -35,6 +35,7 @@ class ParamSpec:
     init: str             # "gaussian:<std>", "msra:<fan_in>", "const:<v>"
     valid_cols: int = 0   # for 2-D weights: columns [valid_cols, shape[1]) are padding and stay zero
     decay: bool = True
+    col_mask: object = None   # optional bool tensor [shape[1]]: columns that are real parameters (others stay zero)
 
     @property
     def numel(self) -> int:
@@ -51,7 +52,17 @@ class ParamSpec:
         t = torch.randn(self.shape, generator=gen) * std
         if self.valid_cols and len(self.shape) == 2:
             t[:, self.valid_cols:] = 0
+        if self.col_mask is not None:
+            t[:, ~self.col_mask] = 0
         return t
+
+    def num_valid(self) -> int:
+        """Number of real parameters (padding and masked columns excluded)."""
+        if len(self.shape) != 2:
+            return self.numel
+        if self.col_mask is not None:
+            return self.shape[0] * int(self.col_mask.sum())
+        return self.shape[0] * (self.valid_cols or self.shape[1])
 
 
 class Layer:
@@ -93,16 +104,27 @@ class Layer:
 class Input(Layer):
     """fp32 NCHW batch -> NHWC bf16 (optionally zero-padding the channel count)."""
 
-    def __init__(self, cpad: int | None = None):
+    def __init__(self, cpad: int | None = None, s2d: int = 0, s2d_k: int = 0):
+        """s2d = S > 0: emit the space-to-depth layout [B, Hs, Ws, S*S*C] that turns the following k x k
+        stride-S convolution (k = s2d_k, no padding) into a stride-1 convolution with ceil(k/S) taps."""
         super().__init__()
-        self.cpad = cpad
+        self.cpad, self.s2d, self.s2d_k = cpad, s2d, s2d_k
 
     def setup(self, in_shape, device):
         B, C, H, W = in_shape
-        self.out_shape = (B, H, W, self.cpad or C)
+        if self.s2d:
+            S, k = self.s2d, self.s2d_k
+            taps = -(-k // S)
+            Hs, Ws = (H - k) // S + taps, (W - k) // S + taps
+            self.out_shape = (B, Hs, Ws, _pad8(S * S * C))
+            self.y = torch.empty(self.out_shape, dtype=BF, device=device)
+        else:
+            self.out_shape = (B, H, W, self.cpad or C)
         return self.out_shape
 
     def forward(self, x):
+        if self.s2d:
+            return F.nchw_to_s2d_bf16(x, self.y, self.s2d)
         return F.nchw_to_nhwc_bf16(x, self.cpad)
 
     def backward(self, dy):
@@ -111,8 +133,14 @@ class Input(Layer):
 
 class Conv2d(Layer):
     def __init__(self, name, cout, k, stride=1, pad=0, groups=1, relu=False, bias=True, std=0.01, bias_value=0.0,
-                 need_dx=True, cin_valid=None):
+                 need_dx=True, cin_valid=None, s2d=0):
+        """s2d = S: the input arrives in space-to-depth layout (Input(s2d=S, s2d_k=k)); the k x k stride-S
+        convolution runs as a ceil(k/S)-tap stride-1 convolution whose weight columns for taps past k stay zero."""
         super().__init__()
+        self.s2d, self.orig_k = s2d, k
+        if s2d:
+            assert stride == s2d and pad == 0 and groups == 1
+            k, stride = -(-k // s2d), 1
         self.name, self.cout, self.k, self.stride, self.pad, self.groups = name, cout, k, stride, pad, groups
         self.relu, self.has_bias, self.std, self.bias_value, self.need_dx = relu, bias, std, bias_value, need_dx
         self.cin_valid = cin_valid
@@ -129,6 +157,17 @@ class Conv2d(Layer):
                       for g in range(G)]
         self.OH, self.OW = self.geoms[0].OH, self.geoms[0].OW
         self.M = B * self.OH * self.OW
+        self.col_mask = self.col_mask_dev = None
+        if self.s2d:
+            # column (a*T + b)*Cs + (dy*S + dx)*C0 + c is filter tap (a*S + dy, b*S + dx) of input channel c
+            S, T = self.s2d, self.k
+            c0 = C // (S * S)
+            col = torch.arange(self.ld)
+            tap, j = col // C, col % C
+            kh = (tap // T) * S + (j // c0) // S
+            kw = (tap % T) * S + (j // c0) % S
+            self.col_mask = (col < self.kd) & (j < S * S * c0) & (kh < self.orig_k) & (kw < self.orig_k)
+            self.col_mask_dev = self.col_mask.to(torch.uint8).to(device)
         self.pointwise = self.k == 1 and self.stride == 1 and self.pad == 0 and G == 1 and C % 8 == 0
         # stride-1 layers run as an implicit GEMM (no patch matrix); the final say comes from the kernel's own
         # alignment check on the first forward, when the output binding is known
@@ -156,9 +195,9 @@ class Conv2d(Layer):
         return y2d.unflatten(0, (B, self.OH, self.OW))[..., g * self.og:(g + 1) * self.og]
 
     def param_specs(self):
-        fan_in = self.kd
+        fan_in = int(self.col_mask.sum()) if self.col_mask is not None else self.kd
         specs = [ParamSpec("weight", (self.cout, self.ld), f"gaussian:{self.std}" if self.std > 0 else f"msra:{fan_in}",
-                           valid_cols=self.kd)]
+                           valid_cols=self.kd, col_mask=self.col_mask)]
         if self.has_bias:
             specs.append(ParamSpec("bias", (self.cout,), f"const:{self.bias_value}", decay=False))
         return specs
@@ -225,6 +264,8 @@ class Conv2d(Layer):
                 else:
                     F.gemm(dyg, wg, self.dcol, b_mn=True)
                     F.col2im(self.dcol, self.dx, self.geoms[g])
+        if self.col_mask_dev is not None:
+            F.col_mask(gw, self.col_mask_dev)
         return self.dx
 
     def _relu_mask(self, dy):

@@ -73,3 +73,40 @@ def test_conv_tc_forward_dgrad_wgrad_match_torch(case):
         assert bool((dw[:, kd:] == 0).all())
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0
+
+
+def test_space_to_depth_conv_matches_strided_torch_conv():
+    """Input(s2d) + Conv2d(s2d): an 11x11 stride-4 convolution run as a 3-tap stride-1 implicit GEMM."""
+    from geeps_b200.ops.layers import Conv2d, Input
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(3)
+    B, C, H, k, S, cout = 4, 3, 67, 11, 4, 32
+    x = torch.randn(B, C, H, H, device=dev, generator=gen)
+    inp, conv = Input(s2d=S, s2d_k=k), Conv2d("c1", cout, k, stride=S, relu=True, need_dx=False, s2d=S)
+    shape = conv.setup(inp.setup((B, C, H, H), dev), dev)
+    OH = (H - k) // S + 1
+    assert shape == (B, OH, OH, cout)
+    spec = conv.param_specs()[0]
+    assert spec.num_valid() == cout * k * k * C
+    w32 = spec.initial(torch.Generator().manual_seed(1)).to(dev) * 5
+    bias = torch.randn(cout, device=dev, generator=gen)
+    conv.p32, conv.p16 = {"weight": w32, "bias": bias}, {"weight": w32.to(BF)}
+    conv.g32 = {"weight": torch.full_like(w32, 9.0), "bias": torch.zeros(cout, device=dev)}
+    y = conv.forward(inp.forward(x)).view(B, OH, OH, cout)
+
+    # the same weights as a [cout, C, k, k] filter: column (a*T + b)*48 + (dy*S + dx)*C + c -> tap (a*S+dy, b*S+dx)
+    T, Cs = conv.k, S * S * C
+    wt = w32.to(BF).float()[:, :T * T * Cs].view(cout, T, T, S, S, C)       # [o, a, b, dy, dx, c]
+    wfull = wt.permute(0, 5, 1, 3, 2, 4).reshape(cout, C, T * S, T * S)[:, :, :k, :k].contiguous().requires_grad_(True)
+    xr = x.to(BF).float()
+    yr = torch.nn.functional.conv2d(xr, wfull, bias, stride=S)
+    assert _rel(y, torch.relu(yr).permute(0, 2, 3, 1)) < 1e-2
+
+    dy = torch.randn(B, OH, OH, cout, device=dev, generator=gen).to(BF)
+    conv.backward(dy.view(-1, cout))
+    mask = (yr > 0).float()
+    yr.backward(dy.float().permute(0, 3, 1, 2) * mask)
+    gw = conv.g32["weight"][:, :T * T * Cs].view(cout, T, T, S, S, C).permute(0, 5, 1, 3, 2, 4).reshape(cout, C, T * S, T * S)
+    assert _rel(gw[:, :, :k, :k], wfull.grad) < 1e-2
+    # taps past the 11 x 11 filter receive no gradient, so they stay zero under SGD
+    assert float(gw[:, :, k:, :].abs().max()) == 0 and float(gw[:, :, :, k:].abs().max()) == 0
