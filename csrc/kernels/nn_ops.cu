@@ -27,6 +27,13 @@ __device__ __forceinline__ bool div_exact(int t, int stride, int& q) {
   return q * stride == t;
 }
 
+// 256 threads as (8-channel vectors of a pixel) x (pixels of a row)
+inline dim3 pool_block(int cv) {
+  int bx = cv < 1 ? 1 : (cv > 256 ? 256 : cv);
+  int by = 256 / bx;
+  return dim3(bx, by < 1 ? 1 : by, 1);
+}
+
 inline int grid_1d(long long n, int block = 256, int cap = 148 * 16) {
   long long b = (n + block - 1) / block;
   if (b > cap) b = cap;
@@ -370,7 +377,7 @@ lrn_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __re
 __global__ void __launch_bounds__(256)
 lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ scale,
                     const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
-                    float beta) {
+                    float beta, int relu_mask) {
   const long long total = P * C;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const int half = size / 2;
@@ -381,7 +388,9 @@ lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, cons
     float acc = 0.f;
     const int lo = max(0, c - half), hi = min(C - 1, c + half);
     for (int j = lo; j <= hi; ++j) acc += bf(dy[base + j]) * bf(y[base + j]) / scale[base + j];
-    dx[i] = __float2bfloat16(bf(dy[i]) * __powf(scale[i], -beta) - coef * bf(x[i]) * acc);
+    const float xi = bf(x[i]);
+    const float d = bf(dy[i]) * __powf(scale[i], -beta) - coef * xi * acc;
+    dx[i] = __float2bfloat16((relu_mask && xi <= 0.f) ? 0.f : d);
   }
 }
 
@@ -435,7 +444,7 @@ template <int HALF>
 __global__ void __launch_bounds__(256)
 lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ scale,
                        const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
-                       float beta) {
+                       float beta, int relu_mask) {
   const int cv = C >> 3;
   const long long total = P * cv;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -468,7 +477,9 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
     for (int j = 8 - HALF; j <= 8 + HALF; ++j) acc += ratio[j];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      o.v[e] = __float2bfloat16(dyc[e] * __powf(scc[e], -beta) - coef * bf(xv.v[e]) * acc);
+      const float xe = bf(xv.v[e]);
+      // relu_mask: x is the output of a ReLU whose backward is folded in here (no gradient where it clipped)
+      o.v[e] = __float2bfloat16((relu_mask && xe <= 0.f) ? 0.f : dyc[e] * __powf(scc[e], -beta) - coef * xe * acc);
       if (e < 7) acc += ratio[8 + e + HALF + 1] - ratio[8 + e - HALF];
     }
     st8(dx + base + c, o);
@@ -566,84 +577,88 @@ col_mask_kernel(float* __restrict__ g, const uint8_t* __restrict__ mask, long lo
 
 // ---------------- pooling (NHWC, 8 channels per thread) ----------------
 // Output may be a channel slice of a wider tensor (pitch ldy, offset applied by the caller).
+// One block per output row (b, oh): threadIdx.x walks the 8-channel vectors of a pixel, threadIdx.y the
+// pixels of the row, so no thread ever divides to find its coordinates and a warp reads contiguous pixels.
 __global__ void __launch_bounds__(256)
 maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ argmax,
                        const GeepsPoolGeom g) {
   const int cv = g.C >> 3;
-  const long long total = (long long)g.B * g.OH * g.OW * cv;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int c = (int)(i % cv) * 8;
-    long long p = i / cv;
-    const int ow = (int)(p % g.OW); p /= g.OW;
-    const int oh = (int)(p % g.OH);
-    const int b = (int)(p / g.OH);
-    float best[8]; int arg[8];
+  const int oh = blockIdx.x % g.OH, b = blockIdx.x / g.OH;
+  const int ih0 = oh * g.stride - g.pad;
+  const int kh_lo = max(0, -ih0), kh_hi = min(g.K, g.H - ih0);
+  const bf16* xb = x + (long long)b * g.H * g.W * g.ldx;
+  const long long orow = ((long long)b * g.OH + oh) * g.OW;
+  for (int ow = threadIdx.y; ow < g.OW; ow += blockDim.y) {
+    const int iw0 = ow * g.stride - g.pad;
+    const int kw_lo = max(0, -iw0), kw_hi = min(g.K, g.W - iw0);
+    for (int cvi = threadIdx.x; cvi < cv; cvi += blockDim.x) {
+      const int c = cvi * 8;
+      float best[8]; int arg[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { best[e] = -3.0e38f; arg[e] = 255; }
-    for (int kh = 0; kh < g.K; ++kh) {
-      const int ih = oh * g.stride - g.pad + kh;
-      if (ih < 0 || ih >= g.H) continue;
-      for (int kw = 0; kw < g.K; ++kw) {
-        const int iw = ow * g.stride - g.pad + kw;
-        if (iw < 0 || iw >= g.W) continue;
-        Bf8 v = ld8(x + (((long long)b * g.H + ih) * g.W + iw) * g.ldx + c);
+      for (int e = 0; e < 8; ++e) { best[e] = -3.0e38f; arg[e] = 255; }
+      for (int kh = kh_lo; kh < kh_hi; ++kh) {
+        const bf16* xr = xb + ((long long)(ih0 + kh) * g.W + iw0) * g.ldx + c;
+        for (int kw = kw_lo; kw < kw_hi; ++kw) {
+          Bf8 v = ld8(xr + (long long)kw * g.ldx);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { float f = bf(v.v[e]); if (f > best[e]) { best[e] = f; arg[e] = kh * g.K + kw; } }
+          for (int e = 0; e < 8; ++e) { float f = bf(v.v[e]); if (f > best[e]) { best[e] = f; arg[e] = kh * g.K + kw; } }
+        }
       }
-    }
-    const long long opix = ((long long)b * g.OH + oh) * g.OW + ow;
-    Bf8 o;
+      const long long opix = orow + ow;
+      Bf8 o;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(best[e]);
-    st8(y + opix * g.ldy + c, o);
-    uint2 pk;
-    pk.x = (uint32_t)arg[0] | ((uint32_t)arg[1] << 8) | ((uint32_t)arg[2] << 16) | ((uint32_t)arg[3] << 24);
-    pk.y = (uint32_t)arg[4] | ((uint32_t)arg[5] << 8) | ((uint32_t)arg[6] << 16) | ((uint32_t)arg[7] << 24);
-    *reinterpret_cast<uint2*>(argmax + opix * g.C + c) = pk;
+      for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(best[e]);
+      st8(y + opix * g.ldy + c, o);
+      uint2 pk;
+      pk.x = (uint32_t)arg[0] | ((uint32_t)arg[1] << 8) | ((uint32_t)arg[2] << 16) | ((uint32_t)arg[3] << 24);
+      pk.y = (uint32_t)arg[4] | ((uint32_t)arg[5] << 8) | ((uint32_t)arg[6] << 16) | ((uint32_t)arg[7] << 24);
+      *reinterpret_cast<uint2*>(argmax + opix * g.C + c) = pk;
+    }
   }
 }
+// One block per input row (b, ih).  The output rows whose window covers ih are the same for the whole
+// block, the output columns covering iw are a short range: only those windows are visited.
 __global__ void __launch_bounds__(256)
 maxpool_backward_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ argmax, bf16* __restrict__ dx,
                         const GeepsPoolGeom g, int accumulate) {
   const int cv = g.C >> 3;
-  const long long total = (long long)g.B * g.H * g.W * cv;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int c = (int)(i % cv) * 8;
-    long long p = i / cv;
-    const int iw = (int)(p % g.W); p /= g.W;
-    const int ih = (int)(p % g.H);
-    const int b = (int)(p / g.H);
-    float acc[8];
+  const int ih = blockIdx.x % g.H, b = blockIdx.x / g.H;
+  const int th = ih + g.pad;
+  // oh * stride <= th <= oh * stride + K - 1
+  const int oh_lo = max(0, (th - g.K + g.stride) / g.stride), oh_hi = min(g.OH - 1, th / g.stride);
+  const long long obase = (long long)b * g.OH * g.OW;
+  bf16* drow = dx + ((long long)b * g.H + ih) * g.W * g.ldx;
+  for (int iw = threadIdx.y; iw < g.W; iw += blockDim.y) {
+    const int tw = iw + g.pad;
+    const int ow_lo = max(0, (tw - g.K + g.stride) / g.stride), ow_hi = min(g.OW - 1, tw / g.stride);
+    for (int cvi = threadIdx.x; cvi < cv; cvi += blockDim.x) {
+      const int c = cvi * 8;
+      float acc[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-    for (int kh = 0; kh < g.K; ++kh) {
-      const int th = ih + g.pad - kh;
-      int oh, ow;
-      if (th < 0 || !div_exact(th, g.stride, oh) || oh >= g.OH) continue;
-      for (int kw = 0; kw < g.K; ++kw) {
-        const int tw = iw + g.pad - kw;
-        if (tw < 0 || !div_exact(tw, g.stride, ow) || ow >= g.OW) continue;
-        const long long opix = ((long long)b * g.OH + oh) * g.OW + ow;
-        const uint2 pk = *reinterpret_cast<const uint2*>(argmax + opix * g.C + c);
-        Bf8 d = ld8(dy + opix * g.ldy + c);
-        const int code = kh * g.K + kw;
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+        const int kh = th - oh * g.stride;
+        for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+          const int code = kh * g.K + (tw - ow * g.stride);
+          const long long opix = obase + (long long)oh * g.OW + ow;
+          const uint2 pk = *reinterpret_cast<const uint2*>(argmax + opix * g.C + c);
+          Bf8 d = ld8(dy + opix * g.ldy + c);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int a = (int)(((e < 4 ? pk.x : pk.y) >> ((e & 3) * 8)) & 0xff);
-          if (a == code) acc[e] += bf(d.v[e]);
+          for (int e = 0; e < 8; ++e) {
+            const int a = (int)(((e < 4 ? pk.x : pk.y) >> ((e & 3) * 8)) & 0xff);
+            if (a == code) acc[e] += bf(d.v[e]);
+          }
         }
       }
+      bf16* dst = drow + (long long)iw * g.ldx + c;
+      Bf8 o;
+      if (accumulate) { Bf8 old = ld8(dst);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
+      st8(dst, o);
     }
-    bf16* dst = dx + (((long long)b * g.H + ih) * g.W + iw) * g.ldx + c;
-    Bf8 o;
-    if (accumulate) { Bf8 old = ld8(dst);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
-    st8(dst, o);
   }
 }
 
@@ -925,34 +940,33 @@ int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, 
   return CK();
 }
 int geeps_lrn_backward(const void* x, const void* y, const float* scale, const void* dy, void* dx, long long P,
-                       int C, int size, float alpha, float beta, void* stream) {
+                       int C, int size, float alpha, float beta, int relu_mask, void* stream) {
   const int g8 = grid_1d(P * (C / 8));
   cudaStream_t st8 = (cudaStream_t)stream;
   if (C % 8 == 0 && size == 5)
-    lrn_backward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
+    lrn_backward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
   else if (C % 8 == 0 && size == 3)
-    lrn_backward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
+    lrn_backward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
   else if (C % 8 == 0 && size == 7)
-    lrn_backward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta);
+    lrn_backward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
   else
     lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, scale,
                                                                          (const bf16*)dy, (bf16*)dx, P, C, size, alpha,
-                                                                         beta);
+                                                                         beta, relu_mask);
   return CK();
 }
 
 int geeps_maxpool_forward(const void* x, void* y, void* argmax, const GeepsPoolGeom* g, void* stream) {
   if (g->C % 8 || g->ldx % 8 || g->ldy % 8 || g->K * g->K > 255) return (int)cudaErrorInvalidValue;
-  const long long n = (long long)g->B * g->OH * g->OW * (g->C / 8);
-  maxpool_forward_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, (uint8_t*)argmax, *g);
+  maxpool_forward_kernel<<<g->B * g->OH, pool_block(g->C / 8), 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y,
+                                                                                        (uint8_t*)argmax, *g);
   return CK();
 }
 int geeps_maxpool_backward(const void* dy, const void* argmax, void* dx, const GeepsPoolGeom* g, int accumulate,
                            void* stream) {
   if (g->C % 8 || g->ldx % 8 || g->ldy % 8) return (int)cudaErrorInvalidValue;
-  const long long n = (long long)g->B * g->H * g->W * (g->C / 8);
-  maxpool_backward_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const uint8_t*)argmax,
-                                                                       (bf16*)dx, *g, accumulate);
+  maxpool_backward_kernel<<<g->B * g->H, pool_block(g->C / 8), 0, (cudaStream_t)stream>>>(
+      (const bf16*)dy, (const uint8_t*)argmax, (bf16*)dx, *g, accumulate);
   return CK();
 }
 int geeps_avgpool_forward(const void* x, void* y, const GeepsPoolGeom* g, void* stream) {

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import functional as F
-from ..ops.layers import BF, BatchNorm, Conv2d, Layer, Pool, SoftmaxLoss
+from ..ops.layers import BF, LRN, BatchNorm, Conv2d, Layer, Pool, SoftmaxLoss
 
 
 class Concat(Layer):
@@ -119,6 +119,11 @@ class Net:
             s = l.setup(s, device)
         self.loss_layer.setup(s, device)
         self.device = device
+        # conv + ReLU followed by LRN: the LRN backward already reads the ReLU output, so it applies the ReLU
+        # mask to the gradient it hands down and the convolution skips its own masking pass
+        for a, b in zip(self.layers, self.layers[1:]):
+            if isinstance(a, Conv2d) and a.relu and isinstance(b, LRN):
+                a.dy_is_masked, b.mask_relu_input = True, True
         return s
 
     def num_params(self, valid_only=True):

@@ -199,10 +199,11 @@ def lrn_forward(x2d, y2d, scale, size=5, alpha=1e-4, beta=0.75, k=1.0) -> None:
                                   C.c_float(beta), C.c_float(k), stream_ptr())
 
 
-def lrn_backward(x2d, y2d, scale, dy2d, dx2d, size=5, alpha=1e-4, beta=0.75) -> None:
+def lrn_backward(x2d, y2d, scale, dy2d, dx2d, size=5, alpha=1e-4, beta=0.75, relu_mask=False) -> None:
+    """relu_mask: x2d is a ReLU output whose backward is folded in (dx = 0 where x <= 0)."""
     P, Cc = x2d.shape
     launch(lib().geeps_lrn_backward, "lrn_backward", ptr(x2d), ptr(y2d), ptr(scale), ptr(dy2d), ptr(dx2d), C.c_longlong(P), Cc, size,
-                                   C.c_float(alpha), C.c_float(beta), stream_ptr())
+           C.c_float(alpha), C.c_float(beta), int(relu_mask), stream_ptr())
 
 
 def pool_geom(x_shape, k: int, stride: int, pad: int, ldx: int, ldy: int, ceil_mode: bool = True) -> PoolGeom:

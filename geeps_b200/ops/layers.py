@@ -138,6 +138,7 @@ class Conv2d(Layer):
         convolution runs as a ceil(k/S)-tap stride-1 convolution whose weight columns for taps past k stay zero."""
         super().__init__()
         self.s2d, self.orig_k = s2d, k
+        self.dy_is_masked = False       # set by Net when the consumer of the output applies this layer's ReLU mask
         if s2d:
             assert stride == s2d and pad == 0 and groups == 1
             k, stride = -(-k // s2d), 1
@@ -239,7 +240,7 @@ class Conv2d(Layer):
         # dy: [M, cout] bf16 (possibly a slice view of a wider tensor)
         if dy.dim() != 2:
             dy = dy.view(self.M, self.cout)
-        if self.relu:
+        if self.relu and not self.dy_is_masked:
             dy = self._relu_mask(dy)
         gw = self.g32["weight"]
         if self.has_bias:
@@ -367,6 +368,7 @@ class LRN(Layer):
     def __init__(self, size=5, alpha=1e-4, beta=0.75, k=1.0):
         super().__init__()
         self.size, self.alpha, self.beta, self.k = size, alpha, beta, k
+        self.mask_relu_input = False    # set by Net when the producer's ReLU backward is folded into this layer's
 
     def setup(self, in_shape, device):
         self.C = in_shape[-1]
@@ -385,7 +387,8 @@ class LRN(Layer):
         return self.y
 
     def backward(self, dy):
-        F.lrn_backward(self.x, self.y, self.scale, dy.reshape(self.P, self.C), self.dx, self.size, self.alpha, self.beta)
+        F.lrn_backward(self.x, self.y, self.scale, dy.reshape(self.P, self.C), self.dx, self.size, self.alpha, self.beta,
+                       relu_mask=self.mask_relu_input)
         return self.dx
 
 

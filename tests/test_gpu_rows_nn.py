@@ -157,6 +157,10 @@ def test_lrn_forward_backward():
     F.lrn_backward(x, y, scale, dy, dx, size=5, alpha=1e-2, beta=0.75)
     yr.backward(dy.float())
     assert torch.allclose(dx.float(), xr.grad, atol=3e-2, rtol=3e-2)
+    # with the producer's ReLU backward folded in: no gradient where the input is not positive
+    dxm = torch.empty_like(x)
+    F.lrn_backward(x, y, scale, dy, dxm, size=5, alpha=1e-2, beta=0.75, relu_mask=True)
+    assert torch.equal(dxm, torch.where(x > 0, dx, torch.zeros_like(dx)))
 
 
 @pytest.mark.parametrize("k,s,p,H", [(3, 2, 0, 13), (3, 2, 0, 16), (3, 1, 1, 9), (2, 2, 0, 8)])
