@@ -413,6 +413,10 @@ int geeps_gemm_tc_supported(const GeepsGemmParams* p) {
 int geeps_gemm_bf16(const GeepsGemmParams* p, void* stream) {
   if (!geeps_gemm_tc_supported(p)) return (int)cudaErrorInvalidValue;
   const int kSMs = 148;
+  // large K-major products go to CTA pairs (half the B traffic per SM) when 256-row tiles can fill the machine
+  if (p->block_n == 0 && p->split_k <= 1 && geeps_gemm_pair_supported(p) &&
+      ((p->M + 255) / 256) * ((p->N + 255) / 256) >= kSMs / 2)
+    return geeps_gemm_bf16_pair(p, stream);
   const int m_tiles = (int)((p->M + BM - 1) / BM);
   const int unit = p->b_mn_major ? 64 : 32;
   const int kt_total = (int)((p->K + BK - 1) / BK);

@@ -87,6 +87,9 @@ typedef struct GeepsGemmParams {
 int geeps_gemm_bf16(const GeepsGemmParams* p, void* stream);       // tcgen05 + TMA + TMEM
 int geeps_gemm_bf16_simt(const GeepsGemmParams* p, void* stream);  // plain SIMT fallback / cross-check
 int geeps_gemm_tc_supported(const GeepsGemmParams* p);             // 1 if the tcgen05 path accepts p
+// CTA-pair variant (tcgen05 cta_group::2, 256-row tiles): K-major A and B, no split-K, beta == 0, M >= 256
+int geeps_gemm_bf16_pair(const GeepsGemmParams* p, void* stream);
+int geeps_gemm_pair_supported(const GeepsGemmParams* p);
 // C[m][n] = beta * C[m][n] (exactly 0 when beta == 0) over an M x N view with pitch ldc
 int geeps_scale_matrix_f32(float* c, long long M, long long N, long long ldc, float beta, void* stream);
 

@@ -42,8 +42,13 @@ inline int grid_1d(long long n, int block = 256, int cap = 148 * 16) {
 }
 
 // ---------------- layout conversion ----------------
+// The NCHW input batch is fp32 or bf16 (a host pipeline that ships bf16 halves the host-to-device bytes).
+__device__ __forceinline__ float in_val(const float* p) { return __ldg(p); }
+__device__ __forceinline__ float in_val(const bf16* p) { return __bfloat162float(*p); }
+
+template <typename T>
 __global__ void __launch_bounds__(256)
-nchw_f32_to_nhwc_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int C, int H, int W, int Cpad) {
+nchw_f32_to_nhwc_bf16_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int C, int H, int W, int Cpad) {
   const long long total = (long long)B * H * W * Cpad;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -52,7 +57,7 @@ nchw_f32_to_nhwc_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, 
     const int w = (int)(p % W); p /= W;
     const int h = (int)(p % H);
     const int b = (int)(p / H);
-    y[i] = c < C ? __float2bfloat16(x[(((long long)b * C + c) * H + h) * W + w]) : __float2bfloat16(0.f);
+    y[i] = __float2bfloat16(c < C ? in_val(x + (((long long)b * C + c) * H + h) * W + w) : 0.f);
   }
 }
 
@@ -487,18 +492,19 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
 }
 
 // NCHW fp32 -> NHWC bf16, one thread per pixel: reads are coalesced along W in every channel plane
+template <typename T>
 __global__ void __launch_bounds__(256)
-nchw_to_nhwc_pix_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int C, int HW, int Cpad) {
+nchw_to_nhwc_pix_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int C, int HW, int Cpad) {
   const long long total = (long long)B * HW;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const long long b = i / HW, p = i % HW;
-    const float* src = x + b * C * HW + p;
+    const T* src = x + b * C * HW + p;
     bf16* dst = y + i * Cpad;
     for (int c0 = 0; c0 < Cpad; c0 += 4) {
       float v[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = (c0 + e < C) ? src[(long long)(c0 + e) * HW] : 0.f;
+      for (int e = 0; e < 4; ++e) v[e] = (c0 + e < C) ? in_val(src + (long long)(c0 + e) * HW) : 0.f;
       *reinterpret_cast<uint2*>(dst + c0) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
     }
   }
@@ -508,9 +514,9 @@ nchw_to_nhwc_pix_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B
 // (zero past the image edge and in the channel padding).  A stride-S convolution over x is then a
 // stride-1 convolution with ceil(k/S) taps per dimension over y.  One thread per output pixel; the
 // 4 x 3-channel case keeps the pixel's 48 values in registers and reads 16 contiguous bytes per (c, dy).
-template <int S, int C>
+template <int S, int C, typename T>
 __global__ void __launch_bounds__(256)
-nchw_to_s2d_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int H, int W, int Hs, int Ws, int Cpad) {
+nchw_to_s2d_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int H, int W, int Hs, int Ws, int Cpad) {
   constexpr int N = S * S * C;
   const long long total = (long long)B * Hs * Ws;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -525,11 +531,11 @@ nchw_to_s2d_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int
 #pragma unroll
       for (int dy = 0; dy < S; ++dy) {
         const int h = hs * S + dy;
-        const float* row = x + ((b * C + c) * H + h) * (long long)W;
+        const T* row = x + ((b * C + c) * H + h) * (long long)W;
 #pragma unroll
         for (int dx = 0; dx < S; ++dx) {
           const int w = ws * S + dx;
-          v[(dy * S + dx) * C + c] = (h < H && w < W) ? __ldg(row + w) : 0.f;
+          v[(dy * S + dx) * C + c] = (h < H && w < W) ? in_val(row + w) : 0.f;
         }
       }
     }
@@ -543,8 +549,9 @@ nchw_to_s2d_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int
 }
 
 // any S, C: one thread per output element
+template <typename T>
 __global__ void __launch_bounds__(256)
-nchw_to_s2d_generic_kernel(const float* __restrict__ x, bf16* __restrict__ y, int B, int C, int H, int W, int S,
+nchw_to_s2d_generic_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int C, int H, int W, int S,
                            int Hs, int Ws, int Cpad) {
   const long long total = (long long)B * Hs * Ws * Cpad;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -558,7 +565,7 @@ nchw_to_s2d_generic_kernel(const float* __restrict__ x, bf16* __restrict__ y, in
     if (j < S * S * C) {
       const int c = j % C, q = j / C, dx = q % S, dy = q / S;
       const int h = hs * S + dy, w = ws * S + dx;
-      if (h < H && w < W) v = x[((b * C + c) * H + h) * (long long)W + w];
+      if (h < H && w < W) v = in_val(x + ((b * C + c) * H + h) * (long long)W + w);
     }
     y[i] = __float2bfloat16(v);
   }
@@ -798,27 +805,44 @@ softmax_ce_kernel(const float* __restrict__ logits, const long long* __restrict_
 
 #define CK() ((int)cudaGetLastError())
 
-extern "C" {
-
-int geeps_nchw_f32_to_nhwc_bf16(const float* x, void* y, int B, int C, int H, int W, int Cpad, void* stream) {
+template <typename T>
+static int nchw_to_nhwc_launch(const T* x, void* y, int B, int C, int H, int W, int Cpad, cudaStream_t st) {
   const long long n = (long long)B * H * W * Cpad;
   if (Cpad % 4 == 0)
-    nchw_to_nhwc_pix_kernel<<<grid_1d((long long)B * H * W), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H * W, Cpad);
+    nchw_to_nhwc_pix_kernel<T><<<grid_1d((long long)B * H * W), 256, 0, st>>>(x, (bf16*)y, B, C, H * W, Cpad);
   else
-    nchw_f32_to_nhwc_bf16_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>(x, (bf16*)y, B, C, H, W, Cpad);
+    nchw_f32_to_nhwc_bf16_kernel<T><<<grid_1d(n), 256, 0, st>>>(x, (bf16*)y, B, C, H, W, Cpad);
   return CK();
 }
 
-int geeps_nchw_f32_to_s2d_bf16(const float* x, void* y, int B, int C, int H, int W, int S, int Hs, int Ws, int Cpad,
-                               void* stream) {
+template <typename T>
+static int nchw_to_s2d_launch(const T* x, void* y, int B, int C, int H, int W, int S, int Hs, int Ws, int Cpad,
+                              cudaStream_t st) {
+  if (S == 4 && C == 3)
+    nchw_to_s2d_kernel<4, 3, T><<<grid_1d((long long)B * Hs * Ws), 256, 0, st>>>(x, (bf16*)y, B, H, W, Hs, Ws, Cpad);
+  else
+    nchw_to_s2d_generic_kernel<T><<<grid_1d((long long)B * Hs * Ws * Cpad), 256, 0, st>>>(x, (bf16*)y, B, C, H, W, S,
+                                                                                         Hs, Ws, Cpad);
+  return CK();
+}
+
+extern "C" {
+
+int geeps_nchw_to_nhwc_bf16(const void* x, int x_is_bf16, void* y, int B, int C, int H, int W, int Cpad, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  return x_is_bf16 ? nchw_to_nhwc_launch((const bf16*)x, y, B, C, H, W, Cpad, st)
+                   : nchw_to_nhwc_launch((const float*)x, y, B, C, H, W, Cpad, st);
+}
+int geeps_nchw_f32_to_nhwc_bf16(const float* x, void* y, int B, int C, int H, int W, int Cpad, void* stream) {
+  return geeps_nchw_to_nhwc_bf16(x, 0, y, B, C, H, W, Cpad, stream);
+}
+
+int geeps_nchw_to_s2d_bf16(const void* x, int x_is_bf16, void* y, int B, int C, int H, int W, int S, int Hs, int Ws,
+                           int Cpad, void* stream) {
   if (S <= 0 || Cpad < S * S * C || (Cpad & 7)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
-  if (S == 4 && C == 3)
-    nchw_to_s2d_kernel<4, 3><<<grid_1d((long long)B * Hs * Ws), 256, 0, st>>>(x, (bf16*)y, B, H, W, Hs, Ws, Cpad);
-  else
-    nchw_to_s2d_generic_kernel<<<grid_1d((long long)B * Hs * Ws * Cpad), 256, 0, st>>>(x, (bf16*)y, B, C, H, W, S, Hs,
-                                                                                      Ws, Cpad);
-  return CK();
+  return x_is_bf16 ? nchw_to_s2d_launch((const bf16*)x, y, B, C, H, W, S, Hs, Ws, Cpad, st)
+                   : nchw_to_s2d_launch((const float*)x, y, B, C, H, W, S, Hs, Ws, Cpad, st);
 }
 
 int geeps_col_mask_f32(float* g, const unsigned char* mask, long long rows, int cols, long long ld, void* stream) {

@@ -20,9 +20,11 @@ typedef struct GeepsPoolGeom {
 } GeepsPoolGeom;
 
 int geeps_nchw_f32_to_nhwc_bf16(const float* x, void* y, int B, int C, int H, int W, int Cpad, void* stream);
-// NCHW fp32 -> space-to-depth NHWC bf16 [B][Hs][Ws][Cpad], channel (dy*S + dx)*C + c, zero-padded
-int geeps_nchw_f32_to_s2d_bf16(const float* x, void* y, int B, int C, int H, int W, int S, int Hs, int Ws, int Cpad,
-                               void* stream);
+// NCHW (fp32, or bf16 when x_is_bf16) -> NHWC bf16 with the channels zero-padded to Cpad
+int geeps_nchw_to_nhwc_bf16(const void* x, int x_is_bf16, void* y, int B, int C, int H, int W, int Cpad, void* stream);
+// NCHW (fp32 or bf16) -> space-to-depth NHWC bf16 [B][Hs][Ws][Cpad], channel (dy*S + dx)*C + c, zero-padded
+int geeps_nchw_to_s2d_bf16(const void* x, int x_is_bf16, void* y, int B, int C, int H, int W, int S, int Hs, int Ws,
+                           int Cpad, void* stream);
 // g[r][c] = 0 where mask[c] == 0 (fp32 matrix, pitch ld)
 int geeps_col_mask_f32(float* g, const unsigned char* mask, long long rows, int cols, long long ld, void* stream);
 int geeps_im2col(const void* x, void* col, const GeepsConvGeom* g, void* stream);

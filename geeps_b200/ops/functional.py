@@ -30,7 +30,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
 
     a_mn / b_mn: the operand is stored transposed ([K, M] / [K, N] row-major).
     out is bf16 or fp32 and may be a column slice of a wider matrix.
-    impl: "auto" (tcgen05 when the layout allows, else SIMT), "tc", or "simt".
+    impl: "auto" (tcgen05 when the layout allows, else SIMT), "tc", "pair" (CTA pairs, 256-row tiles) or "simt".
     """
     L.require_cuda()
     assert a.dtype == bf16 and b.dtype == bf16 and out.dtype in (bf16, torch.float32)
@@ -52,6 +52,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn: bool = Fa
     p.status = status.data_ptr() if status is not None else None
     if bias is not None:
         assert bias.dtype == torch.float32
+    if impl == "pair":
+        launch(lib().geeps_gemm_bf16_pair, "gemm_bf16(tcgen05 pair)", C.byref(p), stream_ptr())
+        return out
     use_tc = impl == "tc" or (impl == "auto" and lib().geeps_gemm_tc_supported(C.byref(p)))
     if use_tc:
         launch(lib().geeps_gemm_bf16, "gemm_bf16(tcgen05)", C.byref(p), stream_ptr())
@@ -105,18 +108,21 @@ def nchw_to_nhwc_bf16(x: torch.Tensor, cpad: int | None = None) -> torch.Tensor:
     L.require_cuda()
     B, Cc, H, W = x.shape
     cpad = cpad or Cc
+    assert x.dtype in (torch.float32, bf16) and x.is_contiguous()
     y = torch.empty((B, H, W, cpad), dtype=bf16, device=x.device)
-    launch(lib().geeps_nchw_f32_to_nhwc_bf16, "nchw_to_nhwc", ptr(x), ptr(y), B, Cc, H, W, cpad, stream_ptr())
+    launch(lib().geeps_nchw_to_nhwc_bf16, "nchw_to_nhwc", ptr(x), int(x.dtype == bf16), ptr(y), B, Cc, H, W, cpad,
+           stream_ptr())
     return y
 
 
 def nchw_to_s2d_bf16(x: torch.Tensor, y: torch.Tensor, S: int) -> torch.Tensor:
-    """fp32 NCHW -> space-to-depth NHWC bf16: y[b, hs, ws, (dy*S + dx)*C + c] = x[b, c, hs*S + dy, ws*S + dx]."""
+    """NCHW (fp32 or bf16) -> space-to-depth NHWC bf16: y[b, hs, ws, (dy*S + dx)*C + c] = x[b, c, hs*S + dy, ws*S + dx]."""
     L.require_cuda()
     B, Cc, H, W = x.shape
     _, Hs, Ws, cpad = y.shape
-    assert x.dtype == torch.float32 and y.dtype == bf16 and x.is_contiguous() and y.is_contiguous()
-    launch(lib().geeps_nchw_f32_to_s2d_bf16, "nchw_to_s2d", ptr(x), ptr(y), B, Cc, H, W, S, Hs, Ws, cpad, stream_ptr())
+    assert x.dtype in (torch.float32, bf16) and y.dtype == bf16 and x.is_contiguous() and y.is_contiguous()
+    launch(lib().geeps_nchw_to_s2d_bf16, "nchw_to_s2d", ptr(x), int(x.dtype == bf16), ptr(y), B, Cc, H, W, S, Hs, Ws,
+           cpad, stream_ptr())
     return y
 
 

@@ -7,15 +7,17 @@ import torch
 
 
 class HostFeeder:
-    def __init__(self, x_shape, y_shape, device, depth: int = 2):
+    def __init__(self, x_shape, y_shape, device, depth: int = 2, x_dtype=torch.float32):
+        """x_dtype: dtype of the batches on the host and in the device slots (fp32, or bf16 to halve the
+        host-to-device bytes; the input layer converts either to bf16 NHWC)."""
         self.device = torch.device(device)
         self.copy_stream = torch.cuda.Stream(device=self.device)
-        self.x = [torch.empty(x_shape, device=self.device) for _ in range(depth)]
+        self.x = [torch.empty(x_shape, dtype=x_dtype, device=self.device) for _ in range(depth)]
         self.y = [torch.empty(y_shape, dtype=torch.int64, device=self.device) for _ in range(depth)]
         self.ready = [torch.cuda.Event() for _ in range(depth)]
         self.free = [torch.cuda.Event() for _ in range(depth)]
         self.depth, self.put_i, self.get_i = depth, 0, 0
-        self.bytes_per_batch = self.x[0].numel() * 4 + self.y[0].numel() * 8
+        self.bytes_per_batch = self.x[0].numel() * self.x[0].element_size() + self.y[0].numel() * 8
         for e in self.free:
             e.record(torch.cuda.current_stream(self.device))
 

@@ -94,3 +94,32 @@ def test_gemm_simt_matches_tc():
     F.gemm(a, b, out, impl="auto")  # K=90 is not a multiple of 8: takes the SIMT path
     torch.cuda.synchronize()
     assert torch.allclose(out, a.float() @ b.float().t(), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("M,N,K,bn,fp32", [(512, 64, 256, 64, False), (512, 256, 256, 256, False),
+                                           (1000, 384, 520, 0, False), (4096, 1000, 1024, 0, True)])
+def test_gemm_cta_pair_matches_fp32(M, N, K, bn, fp32):
+    """CTA-pair kernel (tcgen05 cta_group::2, 256-row tiles): bias + ReLU epilogue, ragged M / N / K edges."""
+    dev = torch.device("cuda:0")
+    torch.manual_seed(M + N + K)
+    a = _mk(M, K, False, dev, pad=8)
+    b = _mk(N, K, False, dev, pad=16)
+    bias = torch.randn(N, device=dev)
+    out = torch.full((M, N + 8), 7.0, dtype=torch.float32 if fp32 else torch.bfloat16, device=dev)[:, :N]
+    st = L.new_status(dev)
+    F.gemm(a, b, out, bias=bias, relu=True, block_n=bn, status=st, impl="pair")
+    torch.cuda.synchronize()
+    assert L.read_status(st)["code"] == 0, L.read_status(st)
+    ref = torch.relu(_ref(a, b, False, False) + bias)
+    assert ((out.float() - ref).norm() / ref.norm()).item() < (1e-5 if fp32 else 5e-3)
+
+
+def test_gemm_auto_dispatch_uses_pairs_for_large_products():
+    dev = torch.device("cuda:0")
+    torch.manual_seed(5)
+    M, N, K = 20000, 512, 192
+    a, b = _mk(M, K, False, dev), _mk(N, K, False, dev)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    F.gemm(a, b, out)
+    ref = _ref(a, b, False, False)
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 5e-3
