@@ -157,7 +157,7 @@ def main() -> None:
                       transport=TRANSPORT_NVLINK if args.transport == "nvlink" else TRANSPORT_TCP,
                       table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.01, momentum=0.9, weight_decay=5e-4,
                       grad_scale=1.0 / world, bf16_compute_cache=1)
-    stream = torch.cuda.Stream(device=dev)
+    stream = torch.cuda.Stream(device=dev, priority=-1)     # ahead of the runtime's comm stream
     with torch.cuda.stream(stream):
         mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=args.slack, seed=1,
                        manage_activations=args.cache_frac is not None, cache_fraction=args.cache_frac,

@@ -101,6 +101,7 @@ struct TableArena {
   size_t cache_off = 0, cache16_off = 0, ring_off = 0, master_off = 0, momentum_off = 0, flags_off = 0;
   size_t rows = 0, max_owned = 0;
   int ring_slots = 1;
+  int comm_lane = 0;                      // which comm stream carries this table's pushes
 };
 struct Fabric {
   bool active = false;
@@ -109,7 +110,10 @@ struct Fabric {
   std::vector<char*> peer_base;           // per rank (own rank: base)
   std::vector<TableArena> tables;         // by table id
   size_t status_off = 0;
-  void* comm_stream = nullptr;
+  void* comm_stream = nullptr;            // lane 0 (also used for the status mirror)
+  // comm streams by lane; a table's pushes always use the same lane (one lane today)
+  std::vector<void*> comm_lanes;
+  int push_ctas = 0;                      // CTA cap of the push kernel (0 = its default of 4 per SM)
   void* push_done_event = nullptr;
   std::vector<void*> table_events;
   int* host_status = nullptr;             // pinned mirror of the device status block

@@ -10,6 +10,7 @@
 // flag words; no TMA and no multicast object is involved.
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <unistd.h>
 
@@ -120,9 +121,19 @@ bool ClientLib::fabric_setup(std::string* err) {
     }
     if (!host_barrier(120000) || error_code_.load()) { *err = "barrier after arena mapping failed"; return false; }
   }
-  cudaStream_t cs;
-  cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
-  fabric_.comm_stream = cs;
+  {
+    // One comm stream at the lowest priority: the application's stream (created with a higher priority by
+    // the caller, if it wants) gets its CTAs dispatched first, the pushes fill in behind.  Several lanes
+    // (small tables ahead of the large fully-connected ones) were measured and were not faster.
+    int prio_lo = 0, prio_hi = 0;     // numerically lowest = greatest priority
+    cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+    cudaStream_t cs;
+    cudaStreamCreateWithPriority(&cs, cudaStreamNonBlocking, prio_lo);
+    fabric_.comm_lanes.assign(1, cs);
+    fabric_.comm_stream = cs;
+    for (TableArena& ta : fabric_.tables) ta.comm_lane = 0;
+    if (const char* e = getenv("GEEPS_PUSH_CTAS")) fabric_.push_ctas = atoi(e);
+  }
   cudaHostAlloc(reinterpret_cast<void**>(&fabric_.host_status), 4 * sizeof(int), cudaHostAllocDefault);
   memset(fabric_.host_status, 0, 4 * sizeof(int));
   fabric_.active = true;
@@ -146,7 +157,9 @@ void ClientLib::fabric_teardown() {
     }
     if (!same_process) cudaIpcCloseMemHandle(fabric_.peer_base[r]);
   }
-  if (fabric_.comm_stream) cudaStreamDestroy((cudaStream_t)fabric_.comm_stream);
+  for (void* cs : fabric_.comm_lanes) cudaStreamDestroy((cudaStream_t)cs);
+  fabric_.comm_lanes.clear();
+  fabric_.comm_stream = nullptr;
   if (fabric_.host_status) cudaFreeHost(fabric_.host_status);
   cudaFree(fabric_.base);
   fabric_.base = nullptr;
@@ -180,7 +193,7 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
       list.ptr[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kPushReadyOff);
     geeps_flag_signal(&list, (int)process_id_, stamp, stream);
   }
-  void* cs = fabric_.comm_stream;
+  void* cs = fabric_.comm_lanes[ta.comm_lane];
   const unsigned long long budget = (unsigned long long)config_.device_wait_budget_us * 1000ull;
   geeps_flag_wait(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_, stamp,
                   budget, status, cs);
@@ -213,7 +226,7 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
   p.momentum_coef = config_.momentum;
   p.weight_decay = config_.weight_decay;
   p.grad_scale = config_.grad_scale;
-  geeps_ps_push_apply(&p, 0, cs);
+  geeps_ps_push_apply(&p, fabric_.push_ctas, cs);
   bg_stats_.nr_push++;
   bg_stats_.bytes_pushed += ta.rows * kRowBytes;
 }

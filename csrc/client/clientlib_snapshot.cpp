@@ -63,7 +63,7 @@ bool ClientLib::save_snapshot(const std::string& dir) {
       if (!ok || error_code_.load()) { lk.unlock(); set_error(ERR_SNAPSHOT, "snapshot: updates did not settle"); return false; }
     }
   }
-  if (gpu_) { cudaStreamSynchronize((cudaStream_t)default_stream_); if (nvlink_) cudaStreamSynchronize((cudaStream_t)fabric_.comm_stream); }
+  if (gpu_) { cudaStreamSynchronize((cudaStream_t)default_stream_); if (nvlink_) for (void* cs : fabric_.comm_lanes) cudaStreamSynchronize((cudaStream_t)cs); }
   if (num_processes_ > 1 && !host_barrier(120000)) { set_error(ERR_SNAPSHOT, "snapshot barrier timed out"); return false; }
   // 2. write this shard
   ::mkdir(dir.c_str(), 0777);

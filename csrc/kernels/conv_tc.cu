@@ -22,7 +22,6 @@
 #include <cuda.h>
 #include <mutex>
 #include <stdio.h>
-#include <stdlib.h>
 
 #include "kernels.h"
 #include "tc05.cuh"
@@ -501,7 +500,6 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   const int stage_bytes = A_STAGE_BYTES + d.bn * BK * 2;
   d.stages = (200 * 1024 - 2 * C_SLAB_BYTES) / stage_bytes;
   if (d.stages > MAX_STAGES) d.stages = MAX_STAGES;
-  if (const char* e = getenv("GEEPS_TC_STAGES")) { int v = atoi(e); if (v >= 2 && v < d.stages) d.stages = v; }
   if (d.stages < 2) d.stages = 2;
   const long long num_tiles = (long long)d.m_tiles * d.n_tiles * d.split_k;
   const int grid = (int)(num_tiles < kSMs ? num_tiles : kSMs);

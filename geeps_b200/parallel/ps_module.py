@@ -99,6 +99,8 @@ class PSModule:
         # later steps walk the tape instead of re-running the Python layer code
         self.use_tape = use_tape and not manage_activations
         self._tapes, self._tape_sigs, self._tape_tries = {}, {}, {}     # keyed by (input ptr, label ptr, clock phase)
+        # diagnostics: set to [] to collect CUDA events (step start, forward end, backward end, clock end) per step
+        self.phase_events = None
         self.initial_params = {} if keep_init else None
         self.captured = None
         self._declare()
@@ -186,6 +188,10 @@ class PSModule:
         if recording:
             L.start_recording()
         self.captured = {} if capture else None
+        ev = self.phase_events
+        if ev is not None:
+            ev.append([torch.cuda.Event(enable_timing=True) for _ in range(4)])
+            ev[-1][0].record()
         with tr.span("input", "fwd"):
             h = net.input_layer.forward(x)
         M, n = self.managed, len(self.groups)
@@ -212,6 +218,8 @@ class PSModule:
         with tr.span("loss", "fwd"):
             loss = net.loss_layer.forward(h, labels)
             g = net.loss_layer.backward()
+        if ev is not None:
+            ev[-1][1].record()
         for i, (l, tabs) in reversed(list(enumerate(self.groups))):
             name = getattr(l, "name", type(l).__name__)
             if i - 1 in M:
@@ -231,8 +239,12 @@ class PSModule:
                         self.ps.update(t.h_upd)
             if i in M:
                 self.ps.post_local_access(M[i]["pb"])
+        if ev is not None:
+            ev[-1][2].record()
         with tr.span("clock", "ps", clock=self.steps):
             self.ps.clock()
+        if ev is not None:
+            ev[-1][3].record()
         if recording:
             self._finish_recording(L.stop_recording(), key)
         self.steps += 1

@@ -8,6 +8,8 @@ once and launches the kernel of interest three times.
   lrn         LRN forward + backward on a conv1-sized activation
   pull_gemm   fused pull + GEMM on an fc6-shaped layer (4 local shards)
   conv_fwd / conv_dgrad / conv_wgrad   implicit-GEMM convolution, conv3 shape (256 x 13 x 13, 256 -> 384, 3x3)
+  conv1_fwd   AlexNet conv1 after space-to-depth (256 x 57 x 57 x 48 -> 96, 3x3, no padding)
+  conv2_fwd / conv2_dgrad   one group of AlexNet conv2 (256 x 27 x 27, 48 of 96 -> 128 of 256 channels, 5x5)
 """
 from __future__ import annotations
 
@@ -80,6 +82,17 @@ def main():
                 F.conv_tc(F.CONV_DGRAD, x, y, w, k, pad)
             else:
                 F.conv_tc(F.CONV_WGRAD, x, y, dw, k, pad)
+    elif case in ("conv1_fwd", "conv2_fwd", "conv2_dgrad"):
+        if case == "conv1_fwd":
+            B, H, ct, cg, ot, og, k, pad = 256, 57, 48, 48, 96, 96, 3, 0
+        else:
+            B, H, ct, cg, ot, og, k, pad = 256, 27, 96, 48, 256, 128, 5, 2
+        OH = H + 2 * pad - k + 1
+        x = (torch.randn(B, H, H, ct, device=dev) * 0.5).to(BF)[..., :cg]
+        y = (torch.randn(B, OH, OH, ot, device=dev) * 0.5).to(BF)[..., :og]
+        w = (torch.randn(og, k * k * cg, device=dev) * 0.02).to(BF)
+        for _ in range(4):
+            F.conv_tc(F.CONV_DGRAD if case == "conv2_dgrad" else F.CONV_FWD, x, y, w, k, pad)
     else:
         raise SystemExit(f"unknown case {case}")
     torch.cuda.synchronize()
