@@ -376,7 +376,7 @@ std::string ClientLib::json_stats() {
                     "\",\"client\":" + stats_.to_json() + ",\"bgthread\":" + bg_stats_.to_json() +
                     ",\"router\":" + (router_ ? router_->stats.to_json() : std::string("{}")) +
                     ",\"server_router\":" + (server_ ? server_->router()->stats.to_json() : std::string("{}")) +
-                    ",\"server\":" + server_json + "}";
+                    ",\"push_timeline\":" + fabric_timeline_json() + ",\"server\":" + server_json + "}";
   if (!config_.output_dir.empty()) {
     std::ofstream f(config_.output_dir + "/json_stats." + std::to_string(process_id_), std::ios::app);
     f << out << "\n";

@@ -114,6 +114,13 @@ struct Fabric {
   // comm streams by lane; a table's pushes always use the same lane (one lane today)
   std::vector<void*> comm_lanes;
   int push_ctas = 0;                      // CTA cap of the push kernel (0 = its default of 4 per SM)
+  // Device timeline of the pushes (GEEPS_TIMELINE=1): per (table, clock) an event on the application's
+  // stream when the update was handed over, and events on the comm stream when every worker's update had
+  // arrived and when the reduce + apply + publish kernel finished.  Reported in the stats JSON.
+  struct TimelineRec { unsigned table; int clock; void* handed; void* arrived; void* applied; };
+  bool timeline = false;
+  void* timeline_origin = nullptr;
+  std::vector<TimelineRec> timeline_recs;
   void* push_done_event = nullptr;
   std::vector<void*> table_events;
   int* host_status = nullptr;             // pinned mirror of the device status block
@@ -152,6 +159,7 @@ class ClientLib {
 
   void shutdown();
   std::string json_stats();
+  std::string fabric_timeline_json();
   bool save_snapshot(const std::string& dir);
   bool load_snapshot(const std::string& dir);
   std::string plan_json() const { return plan_.to_json(); }

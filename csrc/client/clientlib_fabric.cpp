@@ -133,6 +133,7 @@ bool ClientLib::fabric_setup(std::string* err) {
     fabric_.comm_stream = cs;
     for (TableArena& ta : fabric_.tables) ta.comm_lane = 0;
     if (const char* e = getenv("GEEPS_PUSH_CTAS")) fabric_.push_ctas = atoi(e);
+    if (const char* e = getenv("GEEPS_TIMELINE")) fabric_.timeline = atoi(e) != 0;
   }
   cudaHostAlloc(reinterpret_cast<void**>(&fabric_.host_status), 4 * sizeof(int), cudaHostAllocDefault);
   memset(fabric_.host_status, 0, 4 * sizeof(int));
@@ -157,6 +158,8 @@ void ClientLib::fabric_teardown() {
     }
     if (!same_process) cudaIpcCloseMemHandle(fabric_.peer_base[r]);
   }
+  for (void* e : fabric_.table_events) if (e) cudaEventDestroy((cudaEvent_t)e);
+  fabric_.table_events.clear();
   for (void* cs : fabric_.comm_lanes) cudaStreamDestroy((cudaStream_t)cs);
   fabric_.comm_lanes.clear();
   fabric_.comm_stream = nullptr;
@@ -193,7 +196,32 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
       list.ptr[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kPushReadyOff);
     geeps_flag_signal(&list, (int)process_id_, stamp, stream);
   }
+  // The comm stream does not even start waiting before this worker's own announcement has run: the host
+  // enqueues a whole step ahead of the GPU, and a wait kernel that started right away would sit spinning on
+  // an SM through the entire forward pass, next to the compute kernels.
+  if (fabric_.table_events.size() <= table_id) fabric_.table_events.resize(table_id + 1, nullptr);
+  if (!fabric_.table_events[table_id]) {
+    cudaEvent_t e;
+    cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+    fabric_.table_events[table_id] = e;
+  }
+  cudaEventRecord((cudaEvent_t)fabric_.table_events[table_id], (cudaStream_t)stream);
+  cudaStreamWaitEvent((cudaStream_t)fabric_.comm_lanes[ta.comm_lane], (cudaEvent_t)fabric_.table_events[table_id], 0);
   void* cs = fabric_.comm_lanes[ta.comm_lane];
+  Fabric::TimelineRec rec = {table_id, (int)clock, nullptr, nullptr, nullptr};
+  const bool timed = fabric_.timeline && !is_init && fabric_.timeline_recs.size() < 4096;
+  if (timed) {
+    cudaEvent_t e0, e1, e2;
+    cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
+    rec.handed = e0; rec.arrived = e1; rec.applied = e2;
+    if (!fabric_.timeline_origin) {
+      cudaEvent_t o;
+      cudaEventCreate(&o);
+      cudaEventRecord(o, (cudaStream_t)stream);
+      fabric_.timeline_origin = o;
+    }
+    cudaEventRecord(e0, (cudaStream_t)stream);
+  }
   const unsigned long long budget = (unsigned long long)config_.device_wait_budget_us * 1000ull;
   geeps_flag_wait(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_, stamp,
                   budget, status, cs);
@@ -226,7 +254,12 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
   p.momentum_coef = config_.momentum;
   p.weight_decay = config_.weight_decay;
   p.grad_scale = config_.grad_scale;
+  if (timed) cudaEventRecord((cudaEvent_t)rec.arrived, (cudaStream_t)cs);
   geeps_ps_push_apply(&p, fabric_.push_ctas, cs);
+  if (timed) {
+    cudaEventRecord((cudaEvent_t)rec.applied, (cudaStream_t)cs);
+    fabric_.timeline_recs.push_back(rec);
+  }
   bg_stats_.nr_push++;
   bg_stats_.bytes_pushed += ta.rows * kRowBytes;
 }
@@ -251,6 +284,28 @@ bool ClientLib::fabric_check_status(bool sync) {
   cudaMemcpyAsync(fabric_.host_status, fabric_.base + fabric_.status_off, 4 * sizeof(int), cudaMemcpyDeviceToHost,
                   (cudaStream_t)fabric_.comm_stream);
   return ok;
+}
+
+// Milliseconds since the first recorded push, per (table, clock): update handed over on the application's
+// stream / all workers' updates arrived / apply + publish finished.  Synchronises the device.
+std::string ClientLib::fabric_timeline_json() {
+  if (!fabric_.active || !fabric_.timeline || fabric_.timeline_recs.empty()) return "[]";
+  cudaDeviceSynchronize();
+  std::string out = "[";
+  bool first = true;
+  for (const Fabric::TimelineRec& r : fabric_.timeline_recs) {
+    float a = 0, b = 0, c = 0;
+    cudaEvent_t o = (cudaEvent_t)fabric_.timeline_origin;
+    if (cudaEventElapsedTime(&a, o, (cudaEvent_t)r.handed) != cudaSuccess ||
+        cudaEventElapsedTime(&b, o, (cudaEvent_t)r.arrived) != cudaSuccess ||
+        cudaEventElapsedTime(&c, o, (cudaEvent_t)r.applied) != cudaSuccess) { cudaGetLastError(); continue; }
+    char buf[160];
+    snprintf(buf, sizeof(buf), "%s{\"table\":%u,\"clock\":%d,\"handed\":%.4f,\"arrived\":%.4f,\"applied\":%.4f}",
+             first ? "" : ",", r.table, r.clock, a, b, c);
+    out += buf;
+    first = false;
+  }
+  return out + "]";
 }
 
 }  // namespace geeps_b200

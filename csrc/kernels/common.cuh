@@ -61,18 +61,26 @@ __device__ __forceinline__ int ld_relaxed_sys(const int* p) {
 }
 
 // Spin until *flag >= expected or budget_ns elapses.  Returns true on success.
+// The polls are relaxed loads spaced by a sleep that backs off to 4 us, and one acquire load orders the
+// data behind the flag once it has been seen: a waiting warp shares its SM with compute kernels (the
+// persistent tensor-core kernels assign tiles statically, so one slowed SM slows the whole kernel), and
+// system-scope acquires issued every microsecond were measurably slowing them.
 __device__ __forceinline__ bool geeps_wait_ge(const int* flag, int expected, uint64_t budget_ns,
                                               int* seen_out) {
   int v = ld_acquire_sys(flag);
   if (v >= expected) { if (seen_out) *seen_out = v; return true; }
   const uint64_t t0 = geeps_globaltimer();
-  unsigned backoff = 32;
+  unsigned backoff = 64;
   for (;;) {
-    v = ld_acquire_sys(flag);
-    if (v >= expected) { if (seen_out) *seen_out = v; return true; }
+    v = ld_relaxed_sys(flag);
+    if (v >= expected) {
+      v = ld_acquire_sys(flag);
+      if (seen_out) *seen_out = v;
+      return true;
+    }
     if (geeps_globaltimer() - t0 > budget_ns) { if (seen_out) *seen_out = v; return false; }
     __nanosleep(backoff);
-    if (backoff < 1024) backoff <<= 1;
+    if (backoff < 4096) backoff <<= 1;
   }
 }
 

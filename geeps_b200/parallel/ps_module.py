@@ -99,8 +99,12 @@ class PSModule:
         # later steps walk the tape instead of re-running the Python layer code
         self.use_tape = use_tape and not manage_activations
         self._tapes, self._tape_sigs, self._tape_tries = {}, {}, {}     # keyed by (input ptr, label ptr, clock phase)
+        self.tape_mismatch = None
         # diagnostics: set to [] to collect CUDA events (step start, forward end, backward end, clock end) per step
         self.phase_events = None
+        # diagnostics: set to [] to collect (tag, CUDA event) at every layer boundary; the markers are part of a
+        # recorded tape, so they also fire during tape replay
+        self.layer_marks = None
         self.initial_params = {} if keep_init else None
         self.captured = None
         self._declare()
@@ -192,8 +196,10 @@ class PSModule:
         if ev is not None:
             ev.append([torch.cuda.Event(enable_timing=True) for _ in range(4)])
             ev[-1][0].record()
+        self._mark("start")
         with tr.span("input", "fwd"):
             h = net.input_layer.forward(x)
+        self._mark("f:input")
         M, n = self.managed, len(self.groups)
 
         def local(handle):
@@ -209,6 +215,7 @@ class PSModule:
                 l.set_output(local(M[i]["f"]))
             with tr.span(f"fwd:{name}", "fwd"):
                 h = l.forward(h)
+            self._mark("f:" + name)
             if i - 1 in M:
                 self.ps.post_local_access(M[i - 1]["pf"])
         if n - 1 in M:
@@ -218,6 +225,7 @@ class PSModule:
         with tr.span("loss", "fwd"):
             loss = net.loss_layer.forward(h, labels)
             g = net.loss_layer.backward()
+        self._mark("loss")
         if ev is not None:
             ev[-1][1].record()
         for i, (l, tabs) in reversed(list(enumerate(self.groups))):
@@ -239,6 +247,7 @@ class PSModule:
                         self.ps.update(t.h_upd)
             if i in M:
                 self.ps.post_local_access(M[i]["pb"])
+            self._mark("b:" + name)
         if ev is not None:
             ev[-1][2].record()
         with tr.span("clock", "ps", clock=self.steps):
@@ -250,6 +259,17 @@ class PSModule:
         self.steps += 1
         return loss
 
+    def _mark(self, tag):
+        if self.layer_marks is None:
+            return
+
+        def fire():
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.layer_marks.append((tag, e))
+            return 0
+        L.record_call(fire, "mark:" + tag)
+
     def _finish_recording(self, tape, key):
         """Keep the tape for this (input, label) buffer pair once two recordings of it issued the same native
         calls with the same arguments (dropout seeds aside, which are re-derived from the step count)."""
@@ -259,8 +279,14 @@ class PSModule:
                          for a in args if isinstance(a, ctypes.c_ulonglong)]
         tape.stepped_layers = [l for l in self.net.all_layers() if hasattr(l, "seed") and hasattr(l, "step")]
         sig = [row for row in tape.signature() if row[0] != "dropout"]
-        if self._tape_sigs.get(key) == sig:
+        prev = self._tape_sigs.get(key)
+        if prev == sig:
             self._tapes[key] = tape
+        elif prev is not None:
+            # keep the first difference for diagnostics (why a step does not repeat)
+            i = next((i for i, (a, b) in enumerate(zip(prev, sig)) if a != b), min(len(prev), len(sig)))
+            self.tape_mismatch = (key[2], i, prev[i][0] if i < len(prev) else None, sig[i][0] if i < len(sig) else None,
+                                  len(prev), len(sig))
         self._tape_sigs[key] = sig
 
     def params_fp32(self) -> dict:
