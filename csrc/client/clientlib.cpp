@@ -285,6 +285,7 @@ void ClientLib::preupdate_batch(int handle, RowOpVal** buf, void* stream) {
   }
   *buf = staging_ptr(op);
   accessed_clock_[handle] = clock_;
+  swap_wait_region_free(handle, op_stream(stream));
   stats_.nr_preupdate++;
   stats_.preupdate_time += now_seconds() - t0;
 }
@@ -317,6 +318,8 @@ bool ClientLib::localaccess_batch(int handle, RowData** buf, void* stream) {
     *buf = staging_ptr(op);
     accessed_clock_[handle] = clock_;
     if (op.fetch) read_batch_local(op, *buf, op_stream(stream));
+    else swap_wait_region_free(handle, op_stream(stream));   // rows produced in place: the region's previous
+                                                             // contents may still be on their way to the host
   }
   stats_.nr_localaccess++;
   stats_.localaccess_time += now_seconds() - t0;

@@ -210,6 +210,7 @@ class ClientLib {
   // swapper (clientlib_bg.cpp)
   void swap_init();
   void swap_issue_fetch(int handle);
+  void swap_wait_region_free(int handle, void* stream);
   bool swap_can_prefetch(int current, int target) const;
   void swap_prefetch_after(int handle);
   void swap_release(int pre_handle, void* stream, bool after_swap_stream);

@@ -59,6 +59,19 @@ void ClientLib::swap_issue_fetch(int h) {
   stats_.swap_h2d_bytes += bytes;
 }
 
+// `stream` may write the staging region of access h once every earlier user of an overlapping region has
+// released it (an eviction copy to the host releases on the swap stream).
+void ClientLib::swap_wait_region_free(int h, void* stream) {
+  if (!gpu_) return;
+  const OpInfo& op = plan_.ops[h];
+  for (size_t j = 0; j < plan_.ops.size(); ++j) {
+    const OpInfo& o = plan_.ops[j];
+    if (!is_pre(o.type) || !o.needs_staging || !release_ev_[j] || released_clock_[j] < 0) continue;
+    if ((int)j != h && !overlaps(o, op)) continue;
+    cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)release_ev_[j], 0);
+  }
+}
+
 // A later fetch may start now if no access that is live now, or that comes between now and the
 // target, uses an overlapping staging region.
 bool ClientLib::swap_can_prefetch(int current, int target) const {

@@ -67,6 +67,44 @@ size_t colour(std::vector<OpInfo>& ops, const std::vector<char>& staged) {
   }
   return height;
 }
+
+// Second strategy: fit every staged access into a pool of exactly `height` rows, taking the lowest free gap
+// and the highest free gap in turn.  For a chain of accesses in which only neighbours overlap (a layer's
+// input and output) this reaches the peak demand, where first-fit from the bottom fragments.  Offsets are
+// committed only if every access fits.
+bool colour_two_ended(std::vector<OpInfo>& ops, const std::vector<char>& staged, size_t height) {
+  struct Live { size_t off, rows; int pre; };
+  std::vector<Live> live;
+  std::vector<std::pair<size_t, size_t>> assigned;   // (op index, offset)
+  bool low = true;
+  for (size_t i = 0; i < ops.size(); ++i) {
+    const OpInfo& op = ops[i];
+    if (is_pre(op.type) && staged[i]) {
+      const size_t need = op.rows.size();
+      std::sort(live.begin(), live.end(), [](const Live& a, const Live& b) { return a.off < b.off; });
+      bool found = false;
+      size_t off = 0, cursor = 0;
+      for (size_t k = 0; k <= live.size(); ++k) {
+        const size_t gap_end = k < live.size() ? live[k].off : height;
+        if (gap_end >= cursor && gap_end - cursor >= need) {
+          off = low ? cursor : gap_end - need;
+          found = true;
+          if (low) break;          // lowest gap wanted: stop at the first; highest gap: keep the last
+        }
+        if (k < live.size()) cursor = std::max(cursor, live[k].off + live[k].rows);
+      }
+      if (!found) return false;
+      assigned.emplace_back(i, off);
+      live.push_back({off, need, (int)i});
+      low = !low;
+    } else if (is_post(op.type) && op.prestep >= 0 && staged[op.prestep]) {
+      for (size_t k = 0; k < live.size(); ++k)
+        if (live[k].pre == op.prestep) { live.erase(live.begin() + k); break; }
+    }
+  }
+  for (const auto& a : assigned) { ops[a.first].staging_offset = a.second; ops[a.first].needs_staging = true; }
+  return true;
+}
 }  // namespace
 
 Plan PlanCompiler::compile() const {
@@ -328,6 +366,8 @@ Plan PlanCompiler::compile() const {
   }
   plan.peak_staging_rows = peak_of(ops, staged, &plan.max_access_rows);
   plan.staging_rows = colour(ops, staged);
+  if (plan.staging_rows > plan.peak_staging_rows && colour_two_ended(ops, staged, plan.peak_staging_rows))
+    plan.staging_rows = plan.peak_staging_rows;
   for (size_t i = 0; i < n; ++i)
     if (is_post(ops[i].type)) {
       ops[i].needs_staging = ops[ops[i].prestep].needs_staging;

@@ -195,3 +195,34 @@ def test_cpu_row_ops_and_sgd_oracle():
     l.geeps_cpu_sgd_momentum(C.c_longlong(1000), fp(p), fp(v), fp(g), C.c_float(0.1), C.c_float(0.9), C.c_float(0.01), C.c_float(0.5))
     v_ref = 0.1 * (g * 0.5 + 0.01 * p0)
     assert np.allclose(v, v_ref, atol=1e-6) and np.allclose(p, p0 - v_ref, atol=1e-6)
+
+
+def test_plan_staging_pool_reaches_peak_for_a_layer_chain():
+    """Activations of a layer chain (each access overlaps only its neighbours) are staged in a pool as large as
+    the biggest adjacent pair: lowest / highest gap in turn, where first-fit from the bottom would fragment."""
+    sizes = [100, 100, 25, 25, 25, 75, 75, 20, 25, 30]
+    p = Planner(capacity_rows=230, mm=0)       # nothing can stay resident next to a 200-row staging pool
+    handles, base = [], 0
+    prev = None
+    for i, n in enumerate(sizes):
+        h = p.rec(LOCAL, rows=list(range(1000 * (i + 1), 1000 * (i + 1) + n)), fetch=False)
+        if prev is not None:
+            p.rec(POST_LOCAL, prestep=prev, keep=True)
+        prev = h
+    p.rec(POST_LOCAL, prestep=prev, keep=True)
+    p.rec(CLOCK)
+    plan = p.compile()
+    assert plan["ok"], plan.get("error")
+    assert plan["peak_staging_rows"] == 200
+    assert plan["staging_rows"] == 200
+    # no two live accesses overlap in the pool
+    live, checked = {}, 0
+    for op in plan["ops"]:
+        if op["type"] == "local_access" and op["needs_staging"]:
+            for off, n in live.values():
+                assert op["staging_offset"] + op["num_rows"] <= off or off + n <= op["staging_offset"]
+                checked += 1
+            live[op["handle"]] = (op["staging_offset"], op["num_rows"])
+        elif op["type"] == "post_local_access":
+            live.pop(op["prestep"], None)
+    assert checked >= len(sizes) - 1

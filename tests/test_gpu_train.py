@@ -112,7 +112,7 @@ def test_alexnet_step_runs_and_learns():
         mod.close()
 
 
-@pytest.mark.parametrize("frac", [None, 0.55])
+@pytest.mark.parametrize("frac", [None, 0.55, 0.25])
 def test_managed_activations_match_unmanaged(frac):
     """Activations routed through LocalAccess (and swapped to pinned host memory under a budget of 55 % of the working set) give the
     same losses as ordinary buffers."""
