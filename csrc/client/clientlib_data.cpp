@@ -54,7 +54,7 @@ bool ClientLib::read_row_batch_param_cache(const OpInfo& op, RowData* dst, void*
   if (ct.data_age < kBigIter) {
     const int staleness = std::max(0, (int)(clock_ - 1 - ct.data_age));
     stats_.staleness_hist[std::min(staleness, 7)]++;
-    stats_.max_staleness = std::max(stats_.max_staleness, staleness);
+    stats_.max_staleness = std::max(stats_.max_staleness.get(), staleness);
   }
   const size_t op_idx = &op - &plan_.ops[0];
   if (op.location == LOC_GPU) {

@@ -4,29 +4,49 @@
 #pragma once
 #include <stdint.h>
 
+#include <atomic>
 #include <sstream>
 #include <string>
 
 namespace geeps_b200 {
 
+// A counter that one thread (application, push worker, decoder) updates while GetStats() reads it from another:
+// relaxed atomic load / store, single writer per field, so += needs no read-modify-write instruction.
+template <typename T>
+struct Relaxed {
+  std::atomic<T> v;
+  Relaxed(T x = T()) : v(x) {}
+  Relaxed(const Relaxed& o) : v(o.get()) {}
+  Relaxed& operator=(const Relaxed& o) { set(o.get()); return *this; }
+  T get() const { return v.load(std::memory_order_relaxed); }
+  void set(T x) { v.store(x, std::memory_order_relaxed); }
+  operator T() const { return get(); }
+  Relaxed& operator=(T x) { set(x); return *this; }
+  Relaxed& operator+=(T x) { set(get() + x); return *this; }
+  Relaxed& operator++() { set(get() + 1); return *this; }
+  T operator++(int) { T old = get(); set(old + 1); return old; }
+};
+template <typename T>
+std::ostream& operator<<(std::ostream& o, const Relaxed<T>& r) { return o << r.get(); }
+
 struct Stats {
   // plan
-  size_t gpu_memory_capacity_rows = 0, staging_rows = 0, gpu_local_rows = 0, cpu_local_rows = 0;
-  size_t gpu_param_rows = 0, cpu_param_rows = 0;
+  Relaxed<size_t> gpu_memory_capacity_rows = 0, staging_rows = 0, gpu_local_rows = 0, cpu_local_rows = 0;
+  Relaxed<size_t> gpu_param_rows = 0, cpu_param_rows = 0;
   // foreground (application thread)
-  uint64_t nr_read = 0, nr_postread = 0, nr_preupdate = 0, nr_update = 0, nr_localaccess = 0, nr_clock = 0;
-  uint64_t rows_read = 0, rows_updated = 0, rows_fetched = 0, rows_kept = 0;
-  double read_time = 0, read_wait_time = 0, postread_time = 0, preupdate_time = 0, update_time = 0;
-  double localaccess_time = 0, clock_time = 0, vi_time = 0;
-  uint64_t staleness_hist[8] = {0, 0, 0, 0, 0, 0, 0, 0};   // observed (clock-1 - data_age) per read
-  int max_staleness = 0;
-  uint64_t swap_h2d_bytes = 0, swap_d2h_bytes = 0;
-  uint64_t device_wait_timeouts = 0, host_wait_timeouts = 0;
-  double iterate_time = 0;
+  Relaxed<uint64_t> nr_read = 0, nr_postread = 0, nr_preupdate = 0, nr_update = 0, nr_localaccess = 0, nr_clock = 0;
+  Relaxed<uint64_t> rows_read = 0, rows_updated = 0, rows_fetched = 0, rows_kept = 0;
+  Relaxed<double> read_time = 0, read_wait_time = 0, postread_time = 0, preupdate_time = 0, update_time = 0;
+  Relaxed<double> localaccess_time = 0, clock_time = 0, vi_time = 0;
+  Relaxed<uint64_t> staleness_hist[8];   // observed (clock-1 - data_age) per read
+  Relaxed<int> max_staleness = 0;
+  Relaxed<uint64_t> swap_h2d_bytes = 0, swap_d2h_bytes = 0;
+  Relaxed<uint64_t> device_wait_timeouts = 0, host_wait_timeouts = 0;
+  Relaxed<double> iterate_time = 0;
 
   std::string to_json() const {
     std::ostringstream o;
-    o << "{\"gpu_memory_capacity_rows\":" << (long long)gpu_memory_capacity_rows << ",\"staging_rows\":" << staging_rows
+    o << "{\"gpu_memory_capacity_rows\":" << (long long)gpu_memory_capacity_rows.get() << ",\"staging_rows\":" << staging_rows
       << ",\"gpu_local_rows\":" << gpu_local_rows << ",\"cpu_local_rows\":" << cpu_local_rows
       << ",\"gpu_param_rows\":" << gpu_param_rows << ",\"cpu_param_rows\":" << cpu_param_rows
       << ",\"nr_read\":" << nr_read << ",\"nr_postread\":" << nr_postread << ",\"nr_preupdate\":" << nr_preupdate
@@ -45,10 +65,10 @@ struct Stats {
 };
 
 struct BgthreadStats {
-  uint64_t nr_push = 0, nr_clock_only = 0, nr_recv = 0, nr_rmw_replay = 0, nr_oplog_reclaimed = 0;
-  uint64_t bytes_pushed = 0, bytes_received = 0;
-  double push_time = 0, push_d2h_time = 0, push_send_time = 0, recv_time = 0, recv_h2d_time = 0, recv_wait_lock_time = 0;
-  double device_push_ms = 0, device_pull_ms = 0;
+  Relaxed<uint64_t> nr_push = 0, nr_clock_only = 0, nr_recv = 0, nr_rmw_replay = 0, nr_oplog_reclaimed = 0;
+  Relaxed<uint64_t> bytes_pushed = 0, bytes_received = 0;
+  Relaxed<double> push_time = 0, push_d2h_time = 0, push_send_time = 0, recv_time = 0, recv_h2d_time = 0, recv_wait_lock_time = 0;
+  Relaxed<double> device_push_ms = 0, device_pull_ms = 0;
   std::string to_json() const {
     std::ostringstream o;
     o << "{\"nr_push\":" << nr_push << ",\"nr_clock_only\":" << nr_clock_only << ",\"nr_recv\":" << nr_recv

@@ -243,6 +243,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (issuer) tc05::bulk_wait_read<1>();
         tc05::named_bar_sync(1, 128);
         for (int h = 0; h < cols_per_slab; h += 32) {
+          if (n0 + c + h >= d.n_valid) break;      // columns past the tensor's extent are clipped by the store anyway
           uint32_t r[32];
           tc05::tmem_ld_32x32(tacc + (uint32_t)(c + h), r);
           tc05::tmem_ld_wait();

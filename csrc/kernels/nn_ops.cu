@@ -669,6 +669,75 @@ maxpool_backward_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__
   }
 }
 
+// Same product, staged through shared memory: a block owns `stride` consecutive input rows of one image; the few
+// output rows whose windows cover them (dy and argmax) are copied into shared memory once and every input
+// pixel then gathers from there.  The direct kernel re-reads each dy / argmax element from L2 for every input
+// pixel of its window (K*K times); here it crosses L2 -> SM once per block.
+__global__ void __launch_bounds__(256)
+maxpool_backward_smem_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ argmax, bf16* __restrict__ dx,
+                             const GeepsPoolGeom g, int accumulate, int rows_per_block, int max_oh) {
+  extern __shared__ __align__(16) uint8_t pool_smem[];
+  const int cv = g.C >> 3;
+  const int row_blocks = (g.H + rows_per_block - 1) / rows_per_block;
+  const int rb = blockIdx.x % row_blocks, b = blockIdx.x / row_blocks;
+  const int ih_lo = rb * rows_per_block, ih_hi = min(g.H, ih_lo + rows_per_block);      // [lo, hi)
+  const int oh_lo = max(0, (ih_lo + g.pad - g.K + g.stride) / g.stride);
+  const int oh_hi = min(g.OH - 1, (ih_hi - 1 + g.pad) / g.stride);
+  const int n_oh = oh_hi - oh_lo + 1;
+  bf16* s_dy = reinterpret_cast<bf16*>(pool_smem);                                        // [max_oh][OW][C]
+  uint8_t* s_arg = pool_smem + (size_t)max_oh * g.OW * g.C * sizeof(bf16);                // [max_oh][OW][C]
+  const int tid = threadIdx.y * blockDim.x + threadIdx.x, nthreads = blockDim.x * blockDim.y;
+  if (n_oh > 0) {
+    const long long obase = ((long long)b * g.OH + oh_lo) * g.OW;
+    const int vecs = n_oh * g.OW * cv;
+    for (int v = tid; v < vecs; v += nthreads) {
+      const int pix = v / cv, c = (v - pix * cv) * 8;
+      *reinterpret_cast<uint4*>(s_dy + (size_t)pix * g.C + c) =
+          *reinterpret_cast<const uint4*>(dy + (obase + pix) * g.ldy + c);
+      *reinterpret_cast<uint2*>(s_arg + (size_t)pix * g.C + c) =
+          *reinterpret_cast<const uint2*>(argmax + (obase + pix) * g.C + c);
+    }
+  }
+  __syncthreads();
+  for (int ih = ih_lo; ih < ih_hi; ++ih) {
+    const int th = ih + g.pad;
+    const int r_lo = max(oh_lo, (th - g.K + g.stride) / g.stride), r_hi = min(oh_hi, th / g.stride);
+    bf16* drow = dx + ((long long)b * g.H + ih) * g.W * g.ldx;
+    for (int iw = threadIdx.y; iw < g.W; iw += blockDim.y) {
+      const int tw = iw + g.pad;
+      const int ow_lo = max(0, (tw - g.K + g.stride) / g.stride), ow_hi = min(g.OW - 1, tw / g.stride);
+      for (int cvi = threadIdx.x; cvi < cv; cvi += blockDim.x) {
+        const int c = cvi * 8;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int oh = r_lo; oh <= r_hi; ++oh) {
+          const int kh = th - oh * g.stride;
+          for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+            const int code = kh * g.K + (tw - ow * g.stride);
+            const size_t sp = ((size_t)(oh - oh_lo) * g.OW + ow) * g.C + c;
+            const uint2 pk = *reinterpret_cast<const uint2*>(s_arg + sp);
+            Bf8 d = ld8(s_dy + sp);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int a = (int)(((e < 4 ? pk.x : pk.y) >> ((e & 3) * 8)) & 0xff);
+              if (a == code) acc[e] += bf(d.v[e]);
+            }
+          }
+        }
+        bf16* dst = drow + (long long)iw * g.ldx + c;
+        Bf8 o;
+        if (accumulate) { Bf8 old = ld8(dst);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
+        st8(dst, o);
+      }
+    }
+  }
+}
+
 // Caffe average pooling: divisor is the window area clipped to the padded extent.
 __device__ __forceinline__ int avg_area(int o, int stride, int pad, int K, int size) {
   const int s = o * stride - pad;
@@ -989,6 +1058,21 @@ int geeps_maxpool_forward(const void* x, void* y, void* argmax, const GeepsPoolG
 int geeps_maxpool_backward(const void* dy, const void* argmax, void* dx, const GeepsPoolGeom* g, int accumulate,
                            void* stream) {
   if (g->C % 8 || g->ldx % 8 || g->ldy % 8) return (int)cudaErrorInvalidValue;
+  // overlapping windows: stage the covering output rows in shared memory when they fit
+  const int rows_per_block = g->stride > 1 ? 2 * g->stride : 2;
+  const int max_oh = (rows_per_block + g->K - 2) / g->stride + 1;
+  const size_t smem = (size_t)max_oh * g->OW * g->C * 3;
+  if (g->K > g->stride && smem <= 96 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(maxpool_backward_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      attr_set = true;
+    }
+    const int row_blocks = (g->H + rows_per_block - 1) / rows_per_block;
+    maxpool_backward_smem_kernel<<<g->B * row_blocks, pool_block(g->C / 8), smem, (cudaStream_t)stream>>>(
+        (const bf16*)dy, (const uint8_t*)argmax, (bf16*)dx, *g, accumulate, rows_per_block, max_oh);
+    return CK();
+  }
   maxpool_backward_kernel<<<g->B * g->H, pool_block(g->C / 8), 0, (cudaStream_t)stream>>>(
       (const bf16*)dy, (const uint8_t*)argmax, (bf16*)dx, *g, accumulate);
   return CK();

@@ -61,8 +61,10 @@ RouterHandler::RouterHandler(const std::string& identity) : identity_(identity) 
 RouterHandler::~RouterHandler() {
   stop_handler_thread();
   stopping_ = true;
-  if (listen_fd_ >= 0) { ::shutdown(listen_fd_, SHUT_RDWR); ::close(listen_fd_); listen_fd_ = -1; }
+  const int lfd = listen_fd_.load();
+  if (lfd >= 0) ::shutdown(lfd, SHUT_RDWR);         // wakes the accept thread
   if (accept_thread_.joinable()) accept_thread_.join();
+  if (lfd >= 0) { ::close(lfd); listen_fd_ = -1; }
   std::vector<std::shared_ptr<Conn>> cs;
   { std::lock_guard<std::mutex> lk(conns_mu_); cs = all_conns_; }
   for (auto& c : cs) { c->alive = false; if (c->fd >= 0) ::shutdown(c->fd, SHUT_RDWR); }
@@ -70,10 +72,11 @@ RouterHandler::~RouterHandler() {
 }
 
 bool RouterHandler::bind(const std::string& host, unsigned port, std::string* err) {
-  listen_fd_ = ::socket(AF_INET, SOCK_STREAM, 0);
-  if (listen_fd_ < 0) { if (err) *err = "socket() failed"; return false; }
+  const int lfd = ::socket(AF_INET, SOCK_STREAM, 0);
+  if (lfd < 0) { if (err) *err = "socket() failed"; return false; }
+  listen_fd_ = lfd;
   int one = 1;
-  setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+  setsockopt(lfd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
   sockaddr_in addr;
   memset(&addr, 0, sizeof(addr));
   addr.sin_family = AF_INET;
@@ -83,12 +86,12 @@ bool RouterHandler::bind(const std::string& host, unsigned port, std::string* er
     addr.sin_addr.s_addr = htonl(INADDR_ANY);
   int rc = -1;
   for (int attempt = 0; attempt < 30 && rc != 0; ++attempt) {   // a port in TIME_WAIT frees up within seconds
-    rc = ::bind(listen_fd_, (sockaddr*)&addr, sizeof(addr));
+    rc = ::bind(lfd, (sockaddr*)&addr, sizeof(addr));
     if (rc != 0) std::this_thread::sleep_for(std::chrono::milliseconds(100));
   }
-  if (rc != 0 || ::listen(listen_fd_, 64) != 0) {
+  if (rc != 0 || ::listen(lfd, 64) != 0) {
     if (err) *err = "bind/listen on port " + std::to_string(port) + " failed: " + strerror(errno);
-    ::close(listen_fd_);
+    ::close(lfd);
     listen_fd_ = -1;
     return false;
   }
@@ -97,8 +100,9 @@ bool RouterHandler::bind(const std::string& host, unsigned port, std::string* er
 }
 
 void RouterHandler::accept_loop() {
+  const int lfd = listen_fd_.load();
   while (!stopping_) {
-    int fd = ::accept(listen_fd_, nullptr, nullptr);
+    int fd = ::accept(lfd, nullptr, nullptr);
     if (fd < 0) { if (stopping_) return; if (errno == EINTR) continue; return; }
     tune_socket(fd);
     uint32_t len = 0;

@@ -73,7 +73,7 @@ class RouterHandler {
   bool write_message(Conn* c, const Message& msg);
 
   std::string identity_;
-  int listen_fd_ = -1;
+  std::atomic<int> listen_fd_{-1};   // read by the accept thread, closed by the destructor
   std::thread accept_thread_;
   std::atomic<bool> stopping_{false};
   RouterHandler* local_peer_ = nullptr;
