@@ -115,6 +115,8 @@ def main() -> None:
     ap.add_argument("--input-dtype", default="bf16", choices=["fp32", "bf16"],
                     help="dtype of the synthetic input batches on the host and on the device; the input layer rounds "
                          "either to bf16 NHWC, so the results are identical and bf16 halves the host-to-device bytes")
+    ap.add_argument("--fp32-weight-cache", action="store_true",
+                    help="also refresh the workers' fp32 copies of the weights every clock (the layers read bf16 only)")
     ap.add_argument("--no-tape", action="store_true",
                     help="re-run the Python layer code every step instead of replaying the recorded native calls")
     args = ap.parse_args()
@@ -161,7 +163,7 @@ def main() -> None:
     with torch.cuda.stream(stream):
         mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=args.slack, seed=1,
                        manage_activations=args.cache_frac is not None, cache_fraction=args.cache_frac,
-                       use_tape=not args.no_tape)
+                       use_tape=not args.no_tape, bf16_weights_only=not args.fp32_weight_cache)
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
         in_dtype = torch.bfloat16 if args.input_dtype == "bf16" else torch.float32
         x_dev = torch.randn((B,) + image, device=dev, generator=gen).to(in_dtype)
@@ -242,6 +244,7 @@ def main() -> None:
                 "dtype": "bf16", "data": "synthetic", "impl": "ours",
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
                            "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack, "input_dtype": args.input_dtype,
+                           "weight_publish": "bf16+fp32" if args.fp32_weight_cache else "bf16 (biases / BN fp32)",
                            "host_replay_tapes": len(mod._tapes),
                            "tables": "fp32 master rows, momentum SGD on the owning shard",
                            "l2": "inputs (158 MB/step) and activations exceed the 126 MB L2; no explicit flush"},

@@ -84,6 +84,11 @@ void geeps_config_set_table_mode(void* c, int table, int mode) {
   if ((int)cfg->table_modes.size() <= table) cfg->table_modes.resize((size_t)table + 1, cfg->table_mode);
   cfg->table_modes[(size_t)table] = mode;
 }
+void geeps_config_set_table_fp32_from_row(void* c, int table, long long row) {
+  GeePsConfig* cfg = static_cast<GeePsConfig*>(c);
+  if ((int)cfg->table_fp32_from_row.size() <= table) cfg->table_fp32_from_row.resize((size_t)table + 1, 0);
+  cfg->table_fp32_from_row[(size_t)table] = (size_t)row;
+}
 
 // ---------------- GeePs facade ----------------
 void* geeps_new(unsigned process_id, void* config) { return new GeePs(process_id, *static_cast<GeePsConfig*>(config)); }

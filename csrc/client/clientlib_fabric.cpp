@@ -254,6 +254,8 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
   p.momentum_coef = config_.momentum;
   p.weight_decay = config_.weight_decay;
   p.grad_scale = config_.grad_scale;
+  p.fp32_from_row = (!is_init && config_.bf16_compute_cache && table_id < config_.table_fp32_from_row.size())
+                        ? (long long)config_.table_fp32_from_row[table_id] : 0;
   if (timed) cudaEventRecord((cudaEvent_t)rec.arrived, (cudaStream_t)cs);
   geeps_ps_push_apply(&p, fabric_.push_ctas, cs);
   if (timed) {

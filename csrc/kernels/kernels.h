@@ -44,6 +44,7 @@ typedef struct GeepsPushApplyParams {
   unsigned long long wait_budget_ns;
   int n_ranks, rank, clock_stamp, mode, publish;
   float lr, momentum_coef, weight_decay, grad_scale;
+  long long fp32_from_row;             // rows below this id are published to the bf16 caches only (0: all in fp32 too)
 } GeepsPushApplyParams;
 int geeps_ps_push_apply(const GeepsPushApplyParams* p, int max_ctas, void* stream);
 

@@ -584,6 +584,28 @@ col_mask_kernel(float* __restrict__ g, const uint8_t* __restrict__ mask, long lo
 
 // ---------------- pooling (NHWC, 8 channels per thread) ----------------
 // Output may be a channel slice of a wider tensor (pitch ldy, offset applied by the caller).
+// ---- packed helpers for max pooling: 8 channels at a time, two per 32-bit register ----
+// Window code per 16-bit lane.
+__device__ __forceinline__ uint32_t dup16(uint32_t code) { return code | (code << 16); }
+// acc (4 x bf16x2) += d where argmax byte == code.  `pk` holds the 8 argmax bytes, `d` the 8 gradients.
+__device__ __forceinline__ void pool_bwd_accum(__nv_bfloat162 (&acc)[4], const uint2 pk, const uint4 d, uint32_t code) {
+  const uint32_t c4 = code * 0x01010101u;
+  const uint32_t m0 = __vcmpeq4(pk.x, c4), m1 = __vcmpeq4(pk.y, c4);     // 0xff per matching channel
+  if ((m0 | m1) == 0) return;
+  const uint32_t dv[4] = {d.x, d.y, d.z, d.w};
+  const uint32_t mk[4] = {__byte_perm(m0, 0, 0x1100), __byte_perm(m0, 0, 0x3322), __byte_perm(m1, 0, 0x1100),
+                          __byte_perm(m1, 0, 0x3322)};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t sel = dv[j] & mk[j];
+    acc[j] = __hadd2(acc[j], *reinterpret_cast<const __nv_bfloat162*>(&sel));
+  }
+}
+__device__ __forceinline__ uint4 pool_bwd_pack(const __nv_bfloat162 (&acc)[4]) {
+  return make_uint4(*reinterpret_cast<const uint32_t*>(&acc[0]), *reinterpret_cast<const uint32_t*>(&acc[1]),
+                    *reinterpret_cast<const uint32_t*>(&acc[2]), *reinterpret_cast<const uint32_t*>(&acc[3]));
+}
+
 // One block per output row (b, oh): threadIdx.x walks the 8-channel vectors of a pixel, threadIdx.y the
 // pixels of the row, so no thread ever divides to find its coordinates and a warp reads contiguous pixels.
 __global__ void __launch_bounds__(256)
@@ -600,25 +622,32 @@ maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t
     const int kw_lo = max(0, -iw0), kw_hi = min(g.K, g.W - iw0);
     for (int cvi = threadIdx.x; cvi < cv; cvi += blockDim.x) {
       const int c = cvi * 8;
-      float best[8]; int arg[8];
+      // packed: best value and window code per 16-bit lane; strict > keeps the first maximum
+      const uint32_t neg = 0xff7fff7fu;                 // two bf16 lowest finite values
+      __nv_bfloat162 best[4];
+      uint32_t arg[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) { best[e] = -3.0e38f; arg[e] = 255; }
+      for (int j = 0; j < 4; ++j) { best[j] = *reinterpret_cast<const __nv_bfloat162*>(&neg); arg[j] = 0x00ff00ffu; }
       for (int kh = kh_lo; kh < kh_hi; ++kh) {
         const bf16* xr = xb + ((long long)(ih0 + kh) * g.W + iw0) * g.ldx + c;
         for (int kw = kw_lo; kw < kw_hi; ++kw) {
-          Bf8 v = ld8(xr + (long long)kw * g.ldx);
+          const uint4 v = *reinterpret_cast<const uint4*>(xr + (long long)kw * g.ldx);
+          const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+          const uint32_t code = dup16((uint32_t)(kh * g.K + kw));
 #pragma unroll
-          for (int e = 0; e < 8; ++e) { float f = bf(v.v[e]); if (f > best[e]) { best[e] = f; arg[e] = kh * g.K + kw; } }
+          for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 x2 = *reinterpret_cast<const __nv_bfloat162*>(&vv[j]);
+            const uint32_t gt = __hgt2_mask(x2, best[j]);
+            best[j] = __hmax2(best[j], x2);
+            arg[j] = (arg[j] & ~gt) | (code & gt);
+          }
         }
       }
       const long long opix = orow + ow;
-      Bf8 o;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(best[e]);
-      st8(y + opix * g.ldy + c, o);
-      uint2 pk;
-      pk.x = (uint32_t)arg[0] | ((uint32_t)arg[1] << 8) | ((uint32_t)arg[2] << 16) | ((uint32_t)arg[3] << 24);
-      pk.y = (uint32_t)arg[4] | ((uint32_t)arg[5] << 8) | ((uint32_t)arg[6] << 16) | ((uint32_t)arg[7] << 24);
+      *reinterpret_cast<uint4*>(y + opix * g.ldy + c) = pool_bwd_pack(best);
+      uint2 pk;      // 16-bit lanes -> bytes
+      pk.x = __byte_perm(arg[0], arg[1], 0x6420);
+      pk.y = __byte_perm(arg[2], arg[3], 0x6420);
       *reinterpret_cast<uint2*>(argmax + opix * g.C + c) = pk;
     }
   }
@@ -640,31 +669,27 @@ maxpool_backward_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__
     const int ow_lo = max(0, (tw - g.K + g.stride) / g.stride), ow_hi = min(g.OW - 1, tw / g.stride);
     for (int cvi = threadIdx.x; cvi < cv; cvi += blockDim.x) {
       const int c = cvi * 8;
-      float acc[8];
+      __nv_bfloat162 acc[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int j = 0; j < 4; ++j) acc[j] = __floats2bfloat162_rn(0.f, 0.f);
       for (int oh = oh_lo; oh <= oh_hi; ++oh) {
         const int kh = th - oh * g.stride;
         for (int ow = ow_lo; ow <= ow_hi; ++ow) {
           const int code = kh * g.K + (tw - ow * g.stride);
           const long long opix = obase + (long long)oh * g.OW + ow;
           const uint2 pk = *reinterpret_cast<const uint2*>(argmax + opix * g.C + c);
-          Bf8 d = ld8(dy + opix * g.ldy + c);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int a = (int)(((e < 4 ? pk.x : pk.y) >> ((e & 3) * 8)) & 0xff);
-            if (a == code) acc[e] += bf(d.v[e]);
-          }
+          const uint4 d = *reinterpret_cast<const uint4*>(dy + opix * g.ldy + c);
+          pool_bwd_accum(acc, pk, d, (uint32_t)code);
         }
       }
       bf16* dst = drow + (long long)iw * g.ldx + c;
-      Bf8 o;
-      if (accumulate) { Bf8 old = ld8(dst);
+      if (accumulate) {
+        const uint4 old = *reinterpret_cast<const uint4*>(dst);
+        const uint32_t ov[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
-      st8(dst, o);
+        for (int j = 0; j < 4; ++j) acc[j] = __hadd2(acc[j], *reinterpret_cast<const __nv_bfloat162*>(&ov[j]));
+      }
+      *reinterpret_cast<uint4*>(dst) = pool_bwd_pack(acc);
     }
   }
 }
@@ -708,31 +733,26 @@ maxpool_backward_smem_kernel(const bf16* __restrict__ dy, const uint8_t* __restr
       const int ow_lo = max(0, (tw - g.K + g.stride) / g.stride), ow_hi = min(g.OW - 1, tw / g.stride);
       for (int cvi = threadIdx.x; cvi < cv; cvi += blockDim.x) {
         const int c = cvi * 8;
-        float acc[8];
+        __nv_bfloat162 acc[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int j = 0; j < 4; ++j) acc[j] = __floats2bfloat162_rn(0.f, 0.f);
         for (int oh = r_lo; oh <= r_hi; ++oh) {
           const int kh = th - oh * g.stride;
           for (int ow = ow_lo; ow <= ow_hi; ++ow) {
             const int code = kh * g.K + (tw - ow * g.stride);
             const size_t sp = ((size_t)(oh - oh_lo) * g.OW + ow) * g.C + c;
-            const uint2 pk = *reinterpret_cast<const uint2*>(s_arg + sp);
-            Bf8 d = ld8(s_dy + sp);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int a = (int)(((e < 4 ? pk.x : pk.y) >> ((e & 3) * 8)) & 0xff);
-              if (a == code) acc[e] += bf(d.v[e]);
-            }
+            pool_bwd_accum(acc, *reinterpret_cast<const uint2*>(s_arg + sp), *reinterpret_cast<const uint4*>(s_dy + sp),
+                           (uint32_t)code);
           }
         }
         bf16* dst = drow + (long long)iw * g.ldx + c;
-        Bf8 o;
-        if (accumulate) { Bf8 old = ld8(dst);
+        if (accumulate) {
+          const uint4 old = *reinterpret_cast<const uint4*>(dst);
+          const uint32_t ov[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] += bf(old.v[e]); }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) o.v[e] = __float2bfloat16(acc[e]);
-        st8(dst, o);
+          for (int j = 0; j < 4; ++j) acc[j] = __hadd2(acc[j], *reinterpret_cast<const __nv_bfloat162*>(&ov[j]));
+        }
+        *reinterpret_cast<uint4*>(dst) = pool_bwd_pack(acc);
       }
     }
   }

@@ -116,8 +116,9 @@ push_apply_kernel(const GeepsPushApplyParams p) {
       // ---- fused publish into every worker's parameter cache ----
       if (p.publish) {
         const uint2 h = make_uint2(pack_bf16x2(w.x, w.y), pack_bf16x2(w.z, w.w));
+        const bool fp32_too = grow >= p.fp32_from_row;   // weights consumed in bf16 only skip two thirds of the bytes
         for (int q = 0; q < p.n_ranks; ++q) {
-          if (p.cache[q] != nullptr) st_f4(p.cache[q] + goff, w);
+          if (fp32_too && p.cache[q] != nullptr) st_f4(p.cache[q] + goff, w);
           if (p.cache16[q] != nullptr) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.cache16[q]) + goff) = h;
         }
       }

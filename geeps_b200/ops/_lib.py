@@ -47,7 +47,7 @@ class PushApplyParams(C.Structure):
         ("n_ranks", C.c_int), ("rank", C.c_int), ("clock_stamp", C.c_int), ("mode", C.c_int),
         ("publish", C.c_int),
         ("lr", C.c_float), ("momentum_coef", C.c_float), ("weight_decay", C.c_float),
-        ("grad_scale", C.c_float),
+        ("grad_scale", C.c_float), ("fp32_from_row", C.c_longlong),
     ]
 
 

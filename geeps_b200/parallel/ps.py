@@ -72,6 +72,8 @@ class GeePs:
             self._l.geeps_config_set_str(cfg, k.encode(), getattr(config, k).encode())
         for t, m in config.table_modes.items():
             self._l.geeps_config_set_table_mode(cfg, int(t), int(m))
+        for t, r in config.table_fp32_from_row.items():
+            self._l.geeps_config_set_table_fp32_from_row(cfg, int(t), C.c_longlong(int(r)))
         self._g = C.c_void_p(self._l.geeps_new(process_id, cfg))
         self._l.geeps_config_delete(cfg)
         self._ops = {}      # handle -> (kind, num_rows)

@@ -49,7 +49,11 @@ class _Table:
 class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
                  slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None, manage_activations: bool = False,
-                 cache_fraction: float | None = None, use_tape: bool = False):
+                 cache_fraction: float | None = None, use_tape: bool = False, bf16_weights_only: bool = False):
+        """bf16_weights_only: with the NVLINK transport and the bf16 compute cache, weight rows are published to
+        the workers' bf16 caches only (the layers never read weights in fp32; biases, BatchNorm scale / shift and
+        the shard's master rows stay fp32).  The fp32 views of weights (`params_fp32`) then keep their initial
+        values."""
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
         self.trace = trace or NullTrace()
@@ -94,6 +98,10 @@ class PSModule:
             ps_config.gpu_memory_capacity = budget_rows * 512
             ps_config.mm_warning_level = 0
         self.direct16 = ps_config.transport == TRANSPORT_NVLINK and ps_config.bf16_compute_cache
+        if bf16_weights_only and self.direct16:
+            for t in self.tables:
+                if t.specs and t.specs[0].name == "weight":
+                    ps_config.table_fp32_from_row[t.table_id] = (t.offsets[1] // ROW_FLOATS) if len(t.specs) > 1 else t.rows
         self.ps = GeePs(rank, ps_config)
         # tape replay: record two consecutive steps; if they issued identical native calls (static pointers),
         # later steps walk the tape instead of re-running the Python layer code

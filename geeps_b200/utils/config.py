@@ -33,6 +33,8 @@ class GeePsConfig:
     partitioner: int = PARTITION_RANGE
     table_mode: int = TABLE_ADDITIVE
     table_modes: dict = field(default_factory=dict)   # table id -> mode
+    # table id -> first row that is also published in fp32 (rows below it reach the bf16 caches only)
+    table_fp32_from_row: dict = field(default_factory=dict)
     learning_rate: float = 0.01
     momentum: float = 0.9
     weight_decay: float = 0.0

@@ -50,6 +50,10 @@ struct GeePsConfig {
   int partitioner;
   int table_mode;             /* default mode of every table */
   std::vector<int> table_modes;  /* optional per-table override */
+  /* NVLINK transport with bf16_compute_cache: rows of table t below table_fp32_from_row[t] are published to the
+     workers' bf16 caches only - their fp32 cache rows (what Read returns) are not refreshed.  For tables whose
+     leading rows (weights) are consumed through ReadBf16 only; default: every row also in fp32. */
+  std::vector<size_t> table_fp32_from_row;
   float learning_rate, momentum, weight_decay;
   float grad_scale;           /* multiplies the reduced update before the optimizer (e.g. 1/workers) */
   int bf16_compute_cache;     /* also keep a bf16 copy of the parameter cache (NVLINK transport) */

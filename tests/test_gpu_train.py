@@ -160,3 +160,29 @@ def test_tape_replay_matches_python_path():
             mod.close()
     assert losses[True] == pytest.approx(losses[False], rel=2e-3), losses
     assert launches[True] == launches[False]
+
+
+def test_bf16_only_weight_publish_trains_identically():
+    """Weights published to the bf16 caches only: same losses (the layers never read fp32 weights), biases still
+    refreshed in fp32, fp32 weight views left at their initial values."""
+    dev = torch.device("cuda:0")
+    B = 64
+    losses, mods = {}, {}
+    for only16 in (False, True):
+        with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+            mod = PSModule(tiny_net(), (B, 3, 16, 16), cfg(TRANSPORT_NVLINK, learning_rate=0.05), device=dev, seed=3,
+                           keep_init=True, bf16_weights_only=only16)
+            gen = torch.Generator(device=dev).manual_seed(5)
+            x = torch.randn(B, 3, 16, 16, device=dev, generator=gen)
+            y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+            losses[only16] = [mod.step(x, y).item() for _ in range(6)]
+            torch.cuda.synchronize()
+            p = {k: v.clone() for k, v in mod.params_fp32().items()}
+            init = mod.initial_params
+            wname = next(k for k in p if k.endswith(".weight"))
+            bname = next(k for k in p if k.endswith(".bias"))
+            assert not torch.equal(p[bname].cpu(), init[bname].cpu())          # biases move in fp32 either way
+            assert torch.equal(p[wname].cpu(), init[wname].cpu()) == only16    # fp32 weights only when published
+            assert mod.ps.last_error() == 0
+            mod.close()
+    assert losses[True] == pytest.approx(losses[False], rel=1e-3), losses
