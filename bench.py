@@ -88,7 +88,9 @@ class ClockSampler:
 
 def reference_arm(args) -> None:
     """The reference is a C++ library (SCons + ZeroMQ/boost/tbb/glog/gflags/cblas) with no Python
-    package and its Caffe application is an empty submodule; see DESIGN.md for the install attempt."""
+    package, and its Caffe application (the only program in it that trains AlexNet) is an empty submodule: the
+    offline pip install answers "neither setup.py nor pyproject.toml found".  The last line of the install
+    attempt's record, when present, is reported as the reason."""
     marker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "INSTALL_RESULT.txt")
     why = "reference cannot be installed offline: no setup.py/pyproject, needs zmq.hpp, boost, tbb, glog, gflags, cblas, scons; its Caffe app (the only AlexNet trainer) is an empty submodule"
     if os.path.exists(marker):
@@ -139,6 +141,9 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
         args.gpus = world
+    # before any pinned allocation: keep this rank's host buffers and threads on the socket next to its GPU
+    from geeps_b200.utils.affinity import bind_to_gpu_cores
+    cores = bind_to_gpu_cores(local_rank)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -243,7 +248,7 @@ def main() -> None:
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic", "impl": "ours",
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
-                           "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack, "input_dtype": args.input_dtype,
+                           "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack, "input_dtype": args.input_dtype, "cpu_cores_bound": len(cores) if cores else 0,
                            "weight_publish": "bf16+fp32" if args.fp32_weight_cache else "bf16 (biases / BN fp32)",
                            "host_replay_tapes": len(mod._tapes),
                            "tables": "fp32 master rows, momentum SGD on the owning shard",

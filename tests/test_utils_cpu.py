@@ -55,3 +55,16 @@ def test_tape_records_and_replays_native_calls():
     tape.replay()
     assert seen == [(8, 3), ("ps", 5)]
     assert L.launch_count() - n0 == 1
+
+
+def test_bind_to_gpu_cores_is_harmless_without_a_gpu():
+    import os
+    from geeps_b200.utils.affinity import bind_to_gpu_cores
+    before = os.sched_getaffinity(0)
+    cores = bind_to_gpu_cores(0)
+    after = os.sched_getaffinity(0)
+    if cores is None:
+        assert after == before          # no NVML here: nothing changed
+    else:
+        assert set(cores) == after and after <= before
+        os.sched_setaffinity(0, before)
