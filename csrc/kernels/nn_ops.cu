@@ -362,8 +362,11 @@ dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, fl
 }
 
 // ---------------- LRN across channels ----------------
+// Forward keeps r = 1 / scale per element in bf16 for the backward pass (scale = k + alpha/n * window sum of x^2):
+// half the bytes of an fp32 scale buffer in both directions, and the backward needs 1/scale (for dy*y/scale) and
+// scale^-beta = r^beta only.
 __global__ void __launch_bounds__(256)
-lrn_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __restrict__ scale, long long P, int C,
+lrn_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, bf16* __restrict__ scale, long long P, int C,
                    int size, float alpha, float beta, float k) {
   const long long total = P * C;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -375,12 +378,12 @@ lrn_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __re
     const int lo = max(0, c - half), hi = min(C - 1, c + half);
     for (int j = lo; j <= hi; ++j) { float f = bf(row[j]); s += f * f; }
     const float sc = k + alpha / (float)size * s;
-    scale[i] = sc;
+    scale[i] = __float2bfloat16(__frcp_rn(sc));
     y[i] = __float2bfloat16(bf(row[c]) * __powf(sc, -beta));
   }
 }
 __global__ void __launch_bounds__(256)
-lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ scale,
+lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const bf16* __restrict__ scale,
                     const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
                     float beta, int relu_mask) {
   const long long total = P * C;
@@ -392,9 +395,9 @@ lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, cons
     const long long base = i - c;
     float acc = 0.f;
     const int lo = max(0, c - half), hi = min(C - 1, c + half);
-    for (int j = lo; j <= hi; ++j) acc += bf(dy[base + j]) * bf(y[base + j]) / scale[base + j];
+    for (int j = lo; j <= hi; ++j) acc += bf(dy[base + j]) * bf(y[base + j]) * bf(scale[base + j]);
     const float xi = bf(x[i]);
-    const float d = bf(dy[i]) * __powf(scale[i], -beta) - coef * xi * acc;
+    const float d = bf(dy[i]) * __powf(bf(scale[i]), beta) - coef * xi * acc;
     dx[i] = __float2bfloat16((relu_mask && xi <= 0.f) ? 0.f : d);
   }
 }
@@ -403,7 +406,7 @@ lrn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, cons
 // 24 channels around them (window half-width <= 8); each squared value / ratio is computed once.
 template <int HALF>
 __global__ void __launch_bounds__(256)
-lrn_forward_v8_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* __restrict__ scale, long long P, int C,
+lrn_forward_v8_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, bf16* __restrict__ scale, long long P, int C,
                       int size, float alpha, float beta, float k) {
   const int cv = C >> 3;
   const long long total = P * cv;
@@ -428,26 +431,24 @@ lrn_forward_v8_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* _
     float xv[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) { xv[e] = sq[8 + e]; sq[8 + e] = xv[e] * xv[e]; }
-    Bf8 o;
-    float sc[8];
-#pragma unroll
+    Bf8 o, r;
     float s = 0.f;       // sliding window over the 2*HALF+1 channels around output e
 #pragma unroll
     for (int j = 8 - HALF; j <= 8 + HALF; ++j) s += sq[j];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      sc[e] = k + a_n * s;
-      o.v[e] = __float2bfloat16(xv[e] * __powf(sc[e], -beta));
+      const float sc = k + a_n * s;
+      o.v[e] = __float2bfloat16(xv[e] * __powf(sc, -beta));
+      r.v[e] = __float2bfloat16(__frcp_rn(sc));
       if (e < 7) s += sq[8 + e + HALF + 1] - sq[8 + e - HALF];
     }
     st8(y + base + c, o);
-    st_f4(scale + base + c, make_float4(sc[0], sc[1], sc[2], sc[3]));
-    st_f4(scale + base + c + 4, make_float4(sc[4], sc[5], sc[6], sc[7]));
+    st8(scale + base + c, r);
   }
 }
 template <int HALF>
 __global__ void __launch_bounds__(256)
-lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const float* __restrict__ scale,
+lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const bf16* __restrict__ scale,
                        const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
                        float beta, int relu_mask) {
   const int cv = C >> 3;
@@ -462,13 +463,11 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
     for (int v = 0; v < 3; ++v) {
       const int cc = c + (v - 1) * 8;
       if (cc >= 0 && cc < C) {
-        Bf8 d = ld8(dy + base + cc), yy = ld8(y + base + cc);
-        const float4 s0 = ld_f4(scale + base + cc), s1 = ld_f4(scale + base + cc + 4);
-        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        Bf8 d = ld8(dy + base + cc), yy = ld8(y + base + cc), rr = ld8(scale + base + cc);   // rr = 1 / scale
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          ratio[v * 8 + e] = __fdividef(bf(d.v[e]) * bf(yy.v[e]), sv[e]);
-          if (v == 1) { dyc[e] = bf(d.v[e]); scc[e] = sv[e]; }
+          ratio[v * 8 + e] = bf(d.v[e]) * bf(yy.v[e]) * bf(rr.v[e]);
+          if (v == 1) { dyc[e] = bf(d.v[e]); scc[e] = bf(rr.v[e]); }
         }
       } else {
 #pragma unroll
@@ -484,7 +483,7 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
     for (int e = 0; e < 8; ++e) {
       const float xe = bf(xv.v[e]);
       // relu_mask: x is the output of a ReLU whose backward is folded in here (no gradient where it clipped)
-      o.v[e] = __float2bfloat16((relu_mask && xe <= 0.f) ? 0.f : dyc[e] * __powf(scc[e], -beta) - coef * xe * acc);
+      o.v[e] = __float2bfloat16((relu_mask && xe <= 0.f) ? 0.f : dyc[e] * __powf(scc[e], beta) - coef * xe * acc);
       if (e < 7) acc += ratio[8 + e + HALF + 1] - ratio[8 + e - HALF];
     }
     st8(dx + base + c, o);
@@ -1037,33 +1036,33 @@ int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long lo
   return CK();
 }
 
-int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, int size, float alpha, float beta,
+int geeps_lrn_forward(const void* x, void* y, void* rscale, long long P, int C, int size, float alpha, float beta,
                       float k, void* stream) {
   const int g8 = grid_1d(P * (C / 8));
   cudaStream_t st8 = (cudaStream_t)stream;
   if (C % 8 == 0 && size == 5)
-    lrn_forward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, scale, P, C, size, alpha, beta, k);
+    lrn_forward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, (bf16*)rscale, P, C, size, alpha, beta, k);
   else if (C % 8 == 0 && size == 3)
-    lrn_forward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, scale, P, C, size, alpha, beta, k);
+    lrn_forward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, (bf16*)rscale, P, C, size, alpha, beta, k);
   else if (C % 8 == 0 && size == 7)
-    lrn_forward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, scale, P, C, size, alpha, beta, k);
+    lrn_forward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (bf16*)y, (bf16*)rscale, P, C, size, alpha, beta, k);
   else
-    lrn_forward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, scale, P, C, size,
+    lrn_forward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, (bf16*)rscale, P, C, size,
                                                                         alpha, beta, k);
   return CK();
 }
-int geeps_lrn_backward(const void* x, const void* y, const float* scale, const void* dy, void* dx, long long P,
+int geeps_lrn_backward(const void* x, const void* y, const void* rscale, const void* dy, void* dx, long long P,
                        int C, int size, float alpha, float beta, int relu_mask, void* stream) {
   const int g8 = grid_1d(P * (C / 8));
   cudaStream_t st8 = (cudaStream_t)stream;
   if (C % 8 == 0 && size == 5)
-    lrn_backward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
+    lrn_backward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
   else if (C % 8 == 0 && size == 3)
-    lrn_backward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
+    lrn_backward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
   else if (C % 8 == 0 && size == 7)
-    lrn_backward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, scale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
+    lrn_backward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
   else
-    lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, scale,
+    lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale,
                                                                          (const bf16*)dy, (bf16*)dx, P, C, size, alpha,
                                                                          beta, relu_mask);
   return CK();

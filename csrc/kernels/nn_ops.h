@@ -45,10 +45,11 @@ int geeps_relu_backward_2d(const void* dy, const void* y, void* dx, long long P,
                            long long lddx, void* stream);
 int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long ldd, long long lds, void* stream);
 int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream);
-int geeps_lrn_forward(const void* x, void* y, float* scale, long long P, int C, int size, float alpha, float beta,
+// rscale: bf16 buffer [P][C] that receives 1 / scale for the backward pass
+int geeps_lrn_forward(const void* x, void* y, void* rscale, long long P, int C, int size, float alpha, float beta,
                       float k, void* stream);
 // relu_mask != 0: x is a ReLU output; its backward is folded in (dx = 0 where x <= 0)
-int geeps_lrn_backward(const void* x, const void* y, const float* scale, const void* dy, void* dx, long long P,
+int geeps_lrn_backward(const void* x, const void* y, const void* rscale, const void* dy, void* dx, long long P,
                        int C, int size, float alpha, float beta, int relu_mask, void* stream);
 int geeps_maxpool_forward(const void* x, void* y, void* argmax, const GeepsPoolGeom* g, void* stream);
 int geeps_maxpool_backward(const void* dy, const void* argmax, void* dx, const GeepsPoolGeom* g, int accumulate,

@@ -199,6 +199,8 @@ def dropout(x, y, p: float, seed: int) -> None:
 
 
 def lrn_forward(x2d, y2d, scale, size=5, alpha=1e-4, beta=0.75, k=1.0) -> None:
+    """scale: bf16 [P, C] buffer that receives 1 / (k + alpha/size * window sum of x^2) for lrn_backward."""
+    assert scale.dtype == bf16
     P, Cc = x2d.shape
     assert x2d.is_contiguous() and y2d.is_contiguous()
     launch(lib().geeps_lrn_forward, "lrn_forward", ptr(x2d), ptr(y2d), ptr(scale), C.c_longlong(P), Cc, size, C.c_float(alpha),
@@ -207,6 +209,7 @@ def lrn_forward(x2d, y2d, scale, size=5, alpha=1e-4, beta=0.75, k=1.0) -> None:
 
 def lrn_backward(x2d, y2d, scale, dy2d, dx2d, size=5, alpha=1e-4, beta=0.75, relu_mask=False) -> None:
     """relu_mask: x2d is a ReLU output whose backward is folded in (dx = 0 where x <= 0)."""
+    assert scale.dtype == bf16
     P, Cc = x2d.shape
     launch(lib().geeps_lrn_backward, "lrn_backward", ptr(x2d), ptr(y2d), ptr(scale), ptr(dy2d), ptr(dx2d), C.c_longlong(P), Cc, size,
            C.c_float(alpha), C.c_float(beta), int(relu_mask), stream_ptr())

@@ -376,7 +376,7 @@ class LRN(Layer):
         for s in in_shape[:-1]:
             self.P *= s
         self.y = torch.empty(self.P, self.C, dtype=BF, device=device)
-        self.scale = torch.empty(self.P, self.C, device=device)
+        self.scale = torch.empty(self.P, self.C, dtype=BF, device=device)    # 1 / scale, kept for backward
         self.dx = torch.empty(self.P, self.C, dtype=BF, device=device)
         self.out_shape = in_shape
         return in_shape

@@ -58,7 +58,7 @@ def main():
         P, Cc = 256 * 55 * 55, 96
         x = torch.randn(P, Cc, device=dev).to(BF)
         y = torch.empty_like(x); dx = torch.empty_like(x)
-        scale = torch.empty(P, Cc, device=dev)
+        scale = torch.empty(P, Cc, dtype=BF, device=dev)
         for _ in range(4):
             F.lrn_forward(x, y, scale)
             F.lrn_backward(x, y, scale, y, dx)

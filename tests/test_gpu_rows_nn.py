@@ -147,7 +147,7 @@ def test_lrn_forward_backward():
     P, Cc = 500, 96
     x = (torch.randn(P, Cc, device=DEV) * 3).to(BF)
     y = torch.empty_like(x)
-    scale = torch.empty(P, Cc, device=DEV)
+    scale = torch.empty(P, Cc, dtype=BF, device=DEV)      # receives 1 / scale in bf16
     F.lrn_forward(x, y, scale, size=5, alpha=1e-2, beta=0.75, k=1.0)
     xr = x.float().requires_grad_(True)
     yr = TF.local_response_norm(xr.view(P, Cc, 1, 1), 5, alpha=1e-2, beta=0.75, k=1.0).view(P, Cc)
