@@ -457,7 +457,14 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
     d.cchunks = (p->cg + 63) / 64;
     const int panels = d.taps * d.cchunks;
     d.n_valid = panels * 64;
-    int per = panels < 4 ? panels : 4;
+    // panels per tile: fewest panel loads per pixel box over the whole product (2 dY panels + `per` patch panels
+    // for each of ceil(panels / per) tiles); ties go to the wider tile
+    int per = 1;
+    long long best_cost = -1;
+    for (int c = 1; c <= 4 && c <= panels; ++c) {
+      const long long cost = (long long)((panels + c - 1) / c) * (2 + c);
+      if (best_cost < 0 || cost <= best_cost) { best_cost = cost; per = c; }
+    }
     d.bn = per * 64;
     d.n_tiles = (panels + per - 1) / per;
     d.zero_fill_c = d.cchunks * 64;
