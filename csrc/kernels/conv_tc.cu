@@ -48,6 +48,7 @@ struct ConvDev {
   int m_tiles, n_tiles, kt_total, split_k, stages, tmem_cols;
   int relu, zero_fill_c;          // wgrad: a channel coordinate outside X, for panels past the last one
   int ch_valid;                   // wgrad: channels per tap (cg)
+  int narrow;                     // fwd / dgrad: result leaves in 32-channel (64-byte) slabs, see the host code
 };
 
 struct SmemCtl {
@@ -221,10 +222,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ---------------- epilogue: TMEM -> registers -> swizzled slab -> TMA store ----------------
     const int q = warp & 3;
     uint32_t tile_i = 0, slab_i = 0;
-    constexpr int cols_per_slab = MODE == MODE_WGRAD ? 32 : 64;
+    const int cols_per_slab = (MODE == MODE_WGRAD || d.narrow) ? 32 : 64;
     const bool issuer = threadIdx.x == 64;
     const int rloc = q * 32 + lane;
-    const uint32_t row_off = (uint32_t)rloc * 128u, rsw = (uint32_t)(rloc & 7);
+    // wide slab: 128-byte rows, 128-byte swizzle (16-byte chunk ^ row % 8); narrow slab: 64-byte rows, 64-byte
+    // swizzle (chunk ^ (row / 2) % 4)
+    const bool narrow = MODE != MODE_WGRAD && d.narrow;
+    const uint32_t row_off = (uint32_t)rloc * (narrow ? 64u : 128u);
+    const uint32_t rsw = narrow ? (uint32_t)((rloc >> 1) & 3) : (uint32_t)(rloc & 7);
     const bool relu = d.relu != 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_i) {
       const int mn = t % tiles_mn;
@@ -330,9 +335,9 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// rank-N map, 128-byte swizzle; dims / box innermost first, strides (bytes) for dims 1..rank-1
+// rank-N map (128-byte swizzle unless told otherwise); dims / box innermost first, strides (bytes) for dims 1..rank-1
 bool make_map(CUtensorMap* map, const void* base, int rank, const long long* dims, const long long* strides_bytes,
-              const int* box, bool fp32) {
+              const int* box, bool fp32, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gd[4], gs[3];
@@ -340,17 +345,17 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const long long* dim
   for (int i = 0; i < rank; ++i) { gd[i] = (cuuint64_t)dims[i]; bx[i] = (cuuint32_t)box[i]; es[i] = 1; }
   for (int i = 0; i + 1 < rank; ++i) gs[i] = (cuuint64_t)strides_bytes[i];
   return fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
-            const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // NHWC activation tensor as (channels, W, H, B) with a pixel pitch of `pitch` channels
 bool make_act_map(CUtensorMap* map, const void* base, int ch, int W, int H, int B, long long pitch, int bw, int bh,
-                  int bnb) {
+                  int bnb, bool narrow = false) {
   const long long dims[4] = {ch, W, H, B};
   const long long st[3] = {pitch * 2, pitch * 2 * W, pitch * 2 * W * H};
-  const int box[4] = {64, bw, bh, bnb};
-  return make_map(map, base, 4, dims, st, box, false);
+  const int box[4] = {narrow ? 32 : 64, bw, bh, bnb};
+  return make_map(map, base, 4, dims, st, box, false, narrow ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 // Pick the pixel box (bw, bh, bnb) with at most `cap` pixels that covers the W x H x B grid with the fewest
@@ -370,6 +375,14 @@ void pick_box(int W, int H, int B, int cap, int* bw, int* bh, int* bnb) {
 }
 
 int round_up(long long v, int m) { return (int)((v + m - 1) / m * m); }
+
+// A result tensor whose pixel pitch is not a multiple of 128 bytes and whose channel count ends in a half
+// slab (96 channels: 192-byte pixels) stores badly in 128-byte rows - they straddle lines and the last slab is
+// clipped (the 96-channel conv1 output took 218 us where 64 / 128 channels took 144 / 182 us).  Such tensors
+// leave in 32-channel slabs: 64-byte rows that never straddle a 128-byte line and are never clipped.
+int narrow_store(int channels, long long pitch) {
+  return (channels % 64 == 32 && (pitch * 2) % 128 != 0) ? 1 : 0;
+}
 
 template <int MODE>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const ConvDev& d, int grid,
@@ -414,6 +427,7 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   d.split_k = 1;
   d.zero_fill_c = 0;
   d.ch_valid = p->cg;
+  d.narrow = 0;
   CUtensorMap ta, tb, tc;
   bool ok = true;
   const long long wdims[3] = {p->cg, d.taps, p->og};
@@ -440,12 +454,14 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
       ok = make_act_map(&ta, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb);
       const int wbox[3] = {64, 1, bn};
       ok = ok && make_map(&tb, p->w, 3, wdims, wst, wbox, false);
-      ok = ok && make_act_map(&tc, p->y, p->og, p->OW, p->OH, p->B, p->y_pitch, d.bw, d.bh, d.bnb);
+      d.narrow = narrow_store(p->og, p->y_pitch);
+      ok = ok && make_act_map(&tc, p->y, p->og, p->OW, p->OH, p->B, p->y_pitch, d.bw, d.bh, d.bnb, d.narrow != 0);
     } else {
       ok = make_act_map(&ta, p->y, p->og, p->OW, p->OH, p->B, p->y_pitch, d.bw, d.bh, d.bnb);
       const int wbox[3] = {64, 1, 64};
       ok = ok && make_map(&tb, p->w, 3, wdims, wst, wbox, false);
-      ok = ok && make_act_map(&tc, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb);
+      d.narrow = narrow_store(p->cg, p->x_pitch);
+      ok = ok && make_act_map(&tc, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb, d.narrow != 0);
     }
   } else {
     // reduction over output pixels in boxes of up to 64
