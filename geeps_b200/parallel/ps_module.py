@@ -267,6 +267,13 @@ class PSModule:
         self.steps += 1
         return loss
 
+    def invalidate_tapes(self) -> None:
+        """Forget the recorded steps (call after anything that changes what a step launches: switching layers
+        between training and inference mode, rebinding buffers, changing hyper-parameters baked into arguments)."""
+        self._tapes.clear()
+        self._tape_sigs.clear()
+        self._tape_tries.clear()
+
     def _mark(self, tag):
         if self.layer_marks is None:
             return
