@@ -450,11 +450,23 @@ template <int HALF>
 __global__ void __launch_bounds__(256)
 lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const bf16* __restrict__ scale,
                        const bf16* __restrict__ dy, bf16* __restrict__ dx, long long P, int C, int size, float alpha,
-                       float beta, int relu_mask) {
+                       float beta, int relu_mask, float* __restrict__ colsum) {
+  // colsum (optional): per-channel sums of dx over all pixels - the bias gradient of the convolution whose
+  // ReLU is folded in here.  The host sizes the grid so that gridDim * blockDim is a multiple of C/8: every
+  // thread then keeps one channel group for all its pixels and sums in registers.
+  extern __shared__ float lrn_cs[];
   const int cv = C >> 3;
   const long long total = P * cv;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const float coef = 2.f * alpha * beta / (float)size;
+  float cs[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) cs[e] = 0.f;
+  if (colsum != nullptr) {
+    for (int j = threadIdx.x; j < C; j += blockDim.x) lrn_cs[j] = 0.f;
+    __syncthreads();
+  }
+  const int c_fixed = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) % cv) * 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int c = (int)(i % cv) * 8;
     const long long base = (i / cv) * C;
@@ -484,9 +496,16 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
       const float xe = bf(xv.v[e]);
       // relu_mask: x is the output of a ReLU whose backward is folded in here (no gradient where it clipped)
       o.v[e] = __float2bfloat16((relu_mask && xe <= 0.f) ? 0.f : dyc[e] * __powf(scc[e], beta) - coef * xe * acc);
+      cs[e] += bf(o.v[e]);
       if (e < 7) acc += ratio[8 + e + HALF + 1] - ratio[8 + e - HALF];
     }
     st8(dx + base + c, o);
+  }
+  if (colsum != nullptr) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&lrn_cs[c_fixed + e], cs[e]);
+    __syncthreads();
+    for (int j = threadIdx.x; j < C; j += blockDim.x) atomicAdd(colsum + j, lrn_cs[j]);
   }
 }
 
@@ -1012,6 +1031,10 @@ int geeps_colsum(const void* x, float* out, long long P, int C, long long ldx, f
   return CK();
 }
 
+int geeps_copy_f32(float* dst, const float* src, long long n, void* stream) {
+  return (int)cudaMemcpyAsync(dst, src, sizeof(float) * (size_t)n, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+}
+
 int geeps_relu_backward(const void* dy, const void* y, void* dx, long long n, void* stream) {
   if (n % 8) return (int)cudaErrorInvalidValue;
   relu_backward_kernel<<<grid_1d(n / 8), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)y, (bf16*)dx, n / 8);
@@ -1052,15 +1075,26 @@ int geeps_lrn_forward(const void* x, void* y, void* rscale, long long P, int C, 
   return CK();
 }
 int geeps_lrn_backward(const void* x, const void* y, const void* rscale, const void* dy, void* dx, long long P,
-                       int C, int size, float alpha, float beta, int relu_mask, void* stream) {
-  const int g8 = grid_1d(P * (C / 8));
+                       int C, int size, float alpha, float beta, int relu_mask, float* colsum, void* stream) {
+  int g8 = grid_1d(P * (C / 8));
   cudaStream_t st8 = (cudaStream_t)stream;
+  size_t cs_smem = 0;
+  if (colsum != nullptr) {
+    if (C % 8 || (size != 3 && size != 5 && size != 7) || C > 8192) return (int)cudaErrorInvalidValue;
+    // gridDim * 256 must be a multiple of C/8 (one channel group per thread): round the grid down to a multiple of m
+    int cv = C / 8, a = cv, b = 256;
+    while (b) { int t = a % b; a = b; b = t; }
+    const int m = cv / a;
+    g8 = g8 >= m ? g8 / m * m : m;
+    cs_smem = sizeof(float) * C;
+    cudaMemsetAsync(colsum, 0, sizeof(float) * C, st8);
+  }
   if (C % 8 == 0 && size == 5)
-    lrn_backward_v8_kernel<2><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
+    lrn_backward_v8_kernel<2><<<g8, 256, cs_smem, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask, colsum);
   else if (C % 8 == 0 && size == 3)
-    lrn_backward_v8_kernel<1><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
+    lrn_backward_v8_kernel<1><<<g8, 256, cs_smem, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask, colsum);
   else if (C % 8 == 0 && size == 7)
-    lrn_backward_v8_kernel<3><<<g8, 256, 0, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask);
+    lrn_backward_v8_kernel<3><<<g8, 256, cs_smem, st8>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale, (const bf16*)dy, (bf16*)dx, P, C, size, alpha, beta, relu_mask, colsum);
   else
     lrn_backward_kernel<<<grid_1d(P * C), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (const bf16*)y, (const bf16*)rscale,
                                                                          (const bf16*)dy, (bf16*)dx, P, C, size, alpha,

@@ -50,7 +50,9 @@ int geeps_lrn_forward(const void* x, void* y, void* rscale, long long P, int C, 
                       float k, void* stream);
 // relu_mask != 0: x is a ReLU output; its backward is folded in (dx = 0 where x <= 0)
 int geeps_lrn_backward(const void* x, const void* y, const void* rscale, const void* dy, void* dx, long long P,
-                       int C, int size, float alpha, float beta, int relu_mask, void* stream);
+                       int C, int size, float alpha, float beta, int relu_mask, float* colsum, void* stream);
+// colsum (or NULL): C floats that receive the per-channel sums of dx (C % 8 == 0, window 3 / 5 / 7 only)
+int geeps_copy_f32(float* dst, const float* src, long long n, void* stream);
 int geeps_maxpool_forward(const void* x, void* y, void* argmax, const GeepsPoolGeom* g, void* stream);
 int geeps_maxpool_backward(const void* dy, const void* argmax, void* dx, const GeepsPoolGeom* g, int accumulate,
                            void* stream);

@@ -124,6 +124,10 @@ class Net:
         for a, b in zip(self.layers, self.layers[1:]):
             if isinstance(a, Conv2d) and a.relu and isinstance(b, LRN):
                 a.dy_is_masked, b.mask_relu_input = True, True
+                if a.has_bias and b.C % 8 == 0 and b.size in (3, 5, 7):
+                    # the same pass also sums the masked gradient per channel: the convolution's bias gradient
+                    b.bias_grad = torch.zeros(b.C, device=device)
+                    a.bias_grad_src = b.bias_grad
         return s
 
     def num_params(self, valid_only=True):

@@ -207,12 +207,22 @@ def lrn_forward(x2d, y2d, scale, size=5, alpha=1e-4, beta=0.75, k=1.0) -> None:
                                   C.c_float(beta), C.c_float(k), stream_ptr())
 
 
-def lrn_backward(x2d, y2d, scale, dy2d, dx2d, size=5, alpha=1e-4, beta=0.75, relu_mask=False) -> None:
-    """relu_mask: x2d is a ReLU output whose backward is folded in (dx = 0 where x <= 0)."""
+def lrn_backward(x2d, y2d, scale, dy2d, dx2d, size=5, alpha=1e-4, beta=0.75, relu_mask=False, colsum=None) -> None:
+    """relu_mask: x2d is a ReLU output whose backward is folded in (dx = 0 where x <= 0).
+    colsum: optional fp32 [C] tensor that receives the per-channel sums of dx (the bias gradient of the layer
+    that produced x2d)."""
     assert scale.dtype == bf16
+    assert colsum is None or (colsum.dtype == torch.float32 and colsum.numel() == x2d.shape[1])
     P, Cc = x2d.shape
     launch(lib().geeps_lrn_backward, "lrn_backward", ptr(x2d), ptr(y2d), ptr(scale), ptr(dy2d), ptr(dx2d), C.c_longlong(P), Cc, size,
-           C.c_float(alpha), C.c_float(beta), int(relu_mask), stream_ptr())
+           C.c_float(alpha), C.c_float(beta), int(relu_mask), ptr(colsum) if colsum is not None else None, stream_ptr())
+
+
+def copy_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """dst[:] = src for contiguous fp32 tensors of the same size (device-to-device, on the current stream)."""
+    assert dst.dtype == torch.float32 and src.dtype == torch.float32 and dst.numel() == src.numel()
+    assert dst.is_contiguous() and src.is_contiguous()
+    launch(lib().geeps_copy_f32, "copy_f32", ptr(dst), ptr(src), C.c_longlong(dst.numel()), stream_ptr())
 
 
 def pool_geom(x_shape, k: int, stride: int, pad: int, ldx: int, ldy: int, ceil_mode: bool = True) -> PoolGeom:

@@ -139,6 +139,7 @@ class Conv2d(Layer):
         super().__init__()
         self.s2d, self.orig_k = s2d, k
         self.dy_is_masked = False       # set by Net when the consumer of the output applies this layer's ReLU mask
+        self.bias_grad_src = None       # set by Net: the consumer's backward already summed dy per channel into this
         if s2d:
             assert stride == s2d and pad == 0 and groups == 1
             k, stride = -(-k // s2d), 1
@@ -244,7 +245,10 @@ class Conv2d(Layer):
             dy = self._relu_mask(dy)
         gw = self.g32["weight"]
         if self.has_bias:
-            F.colsum(dy, self.g32["bias"])
+            if self.bias_grad_src is not None:
+                F.copy_f32(self.g32["bias"], self.bias_grad_src)
+            else:
+                F.colsum(dy, self.g32["bias"])
         w16 = self.p16["weight"]
         for g in range(self.groups):
             if self.implicit:
@@ -369,6 +373,7 @@ class LRN(Layer):
         super().__init__()
         self.size, self.alpha, self.beta, self.k = size, alpha, beta, k
         self.mask_relu_input = False    # set by Net when the producer's ReLU backward is folded into this layer's
+        self.bias_grad = None           # set by Net: fp32 [C] that receives the producer's bias gradient (sum of dx)
 
     def setup(self, in_shape, device):
         self.C = in_shape[-1]
@@ -388,7 +393,7 @@ class LRN(Layer):
 
     def backward(self, dy):
         F.lrn_backward(self.x, self.y, self.scale, dy.reshape(self.P, self.C), self.dx, self.size, self.alpha, self.beta,
-                       relu_mask=self.mask_relu_input)
+                       relu_mask=self.mask_relu_input, colsum=self.bias_grad)
         return self.dx
 
 

@@ -161,6 +161,12 @@ def test_lrn_forward_backward():
     dxm = torch.empty_like(x)
     F.lrn_backward(x, y, scale, dy, dxm, size=5, alpha=1e-2, beta=0.75, relu_mask=True)
     assert torch.equal(dxm, torch.where(x > 0, dx, torch.zeros_like(dx)))
+    # ... and the per-channel sums of that gradient (the producer's bias gradient) from the same pass
+    cs = torch.full((Cc,), 5.0, device=DEV)
+    dxs = torch.empty_like(x)
+    F.lrn_backward(x, y, scale, dy, dxs, size=5, alpha=1e-2, beta=0.75, relu_mask=True, colsum=cs)
+    assert torch.equal(dxs, dxm)
+    assert torch.allclose(cs, dxm.float().sum(0), atol=1e-2, rtol=1e-4)
 
 
 @pytest.mark.parametrize("k,s,p,H", [(3, 2, 0, 13), (3, 2, 0, 16), (3, 1, 1, 9), (2, 2, 0, 8)])
