@@ -147,6 +147,13 @@ int geeps_save_snapshot(void* g, const char* dir) { return static_cast<GeePs*>(g
 int geeps_load_snapshot(void* g, const char* dir) { return static_cast<GeePs*>(g)->LoadSnapshot(dir) ? 1 : 0; }
 // host-side fault injection for tests: 0 = stop sending heartbeats, 1 = withhold the push-ready flag,
 // 2 = drop the next `value` inbound row batches at the client router
+int geeps_locate_row(void* g, long long table, long long row, int metadata_server, int timeout_ms) {
+  return static_cast<GeePs*>(g)->impl()->locate_row((uint64_t)table, (uint64_t)row, (uint)metadata_server, timeout_ms);
+}
+void geeps_report_access(void* g, int metadata_server, long long table, long long row, int nread, int nwrite) {
+  static_cast<GeePs*>(g)->impl()->report_access((uint)metadata_server, (uint64_t)table, (uint64_t)row, (uint32_t)nread,
+                                                (uint32_t)nwrite);
+}
 void geeps_inject(void* g, int what, int value) {
   ClientLib* lib = static_cast<GeePs*>(g)->impl();
   if (what == 0) lib->inject_skip_heartbeats(value != 0);

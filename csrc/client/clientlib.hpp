@@ -181,6 +181,12 @@ class ClientLib {
   void server_clock_cbk(uint server_id, uint table_id, iter_t clock);
   void get_stats_cbk(uint server_id, const std::string& stats);
   void find_row_cbk(uint64_t table, uint64_t row, uint server_id);
+  // Placement service of the shards (the reference's MetadataServer protocol: FIND_ROW / ADD_ACCESS_INFO,
+  // src/server/metadata-server.cpp:44-170): ask shard `metadata_server` which shard it places (table, row) on
+  // under the configured pp_policy; -1 if no answer arrives within timeout_ms.  The data path itself uses the
+  // static partitioner.
+  int locate_row(uint64_t table, uint64_t row, uint metadata_server, int timeout_ms);
+  void report_access(uint metadata_server, uint64_t table, uint64_t row, uint32_t nread, uint32_t nwrite);
   void peer_lost_cbk(const std::string& who);
   void heartbeat_cbk(uint id, uint64_t counter, iter_t clock);
   void barrier_cbk(uint id, uint epoch);
@@ -273,6 +279,7 @@ class ClientLib {
   std::vector<iter_t> peer_clock_;
   std::vector<char> peer_dead_;
   std::condition_variable global_cv_;
+  std::map<std::pair<uint64_t, uint64_t>, int> located_;   // answers to locate_row (guarded by global_mu_)
   std::mutex global_mu_;
   std::map<uint, uint> barrier_seen_;      // rank -> last epoch seen
   uint barrier_epoch_ = 0;

@@ -2,6 +2,8 @@
 // clock bookkeeping, stats replies and the membership / control messages
 // (role of the reference's src/client/clientlib-cbk.cpp:51-111).
 #include <stdio.h>
+
+#include <chrono>
 #include <string.h>
 
 #include "clientlib.hpp"
@@ -9,8 +11,33 @@
 namespace geeps_b200 {
 
 void ClientLib::find_row_cbk(uint64_t table, uint64_t row, uint server_id) {
-  // placement answers only feed statistics: the data path uses the static partitioner
-  (void)table; (void)row; (void)server_id;
+  // placement answers go to whoever asked (locate_row); the data path uses the static partitioner
+  {
+    std::lock_guard<std::mutex> lk(global_mu_);
+    located_[{table, row}] = (int)server_id;
+  }
+  global_cv_.notify_all();
+}
+
+int ClientLib::locate_row(uint64_t table, uint64_t row, uint metadata_server, int timeout_ms) {
+  if (!encoder_ || metadata_server >= num_processes_) return -1;
+  {
+    std::lock_guard<std::mutex> lk(global_mu_);
+    located_.erase({table, row});
+  }
+  encoder_->find_row(table, row, metadata_server);
+  std::unique_lock<std::mutex> lk(global_mu_);
+  const bool got = global_cv_.wait_for(lk, std::chrono::milliseconds(timeout_ms),
+                                       [&] { return located_.count({table, row}) > 0 || error_code_.load() != 0; });
+  if (!got || !located_.count({table, row})) return -1;
+  return located_[{table, row}];
+}
+
+void ClientLib::report_access(uint metadata_server, uint64_t table, uint64_t row, uint32_t nread, uint32_t nwrite) {
+  if (!encoder_ || metadata_server >= num_processes_) return;
+  std::vector<access_info_t> infos(1);
+  infos[0].table = table; infos[0].row = row; infos[0].nread = nread; infos[0].nwrite = nwrite;
+  encoder_->add_access_info(metadata_server, infos);
 }
 
 void ClientLib::recv_row_batch_cbk(uint server_id, uint table_id, iter_t data_age, iter_t self_clock, const RowKey*,

@@ -102,6 +102,19 @@ class GeePs:
     def get_stats(self) -> dict:
         return json.loads(self._string(self._l.geeps_get_stats))
 
+    def locate_row(self, table: int, row: int, metadata_server: int = 0, timeout_ms: int = 5000) -> int:
+        """Ask shard `metadata_server` where its placement policy (config pp_policy: 1 hash, 2 first toucher,
+        3 most frequent accessor with load balance) puts (table, row); -1 if no answer in time.  The data path
+        uses the static partitioner; this is the reference's MetadataServer service
+        (src/server/metadata-server.cpp:119-170)."""
+        return int(self._l.geeps_locate_row(self._g, C.c_longlong(table), C.c_longlong(row), int(metadata_server),
+                                            int(timeout_ms)))
+
+    def report_access(self, table: int, row: int, nread: int = 1, nwrite: int = 0, metadata_server: int = 0) -> None:
+        """Feed the placement service with this worker's access counts for (table, row)."""
+        self._l.geeps_report_access(self._g, int(metadata_server), C.c_longlong(table), C.c_longlong(row), int(nread),
+                                    int(nwrite))
+
     def plan(self) -> dict:
         return json.loads(self._string(self._l.geeps_plan_json))
 

@@ -52,6 +52,65 @@ def helloworld_worker(rank, world, base_port, slack, clocks, q, kw):
         q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
 
 
+def placement_worker(rank, world, base_port, policy, q, kw):
+    """Exercises the shards' placement service (FIND_ROW / ADD_ACCESS_INFO) under one of the three policies."""
+    try:
+        import time
+        from geeps_b200.parallel.ps import GeePs
+        cfg = make_cfg(world, base_port, pp_policy=policy, **kw)
+        g = GeePs(rank, cfg)
+        rows = list(range(16))
+        r = g.virtual_read(0, rows, 0)
+        u = g.virtual_pre_update(0, rows)
+        pr = g.virtual_post_read(r)
+        up = g.virtual_update(u)
+        g.virtual_clock()
+        g.finish_virtual_iteration()
+        b = g.pre_update(u)
+        b.zero_()
+        g.update(up)
+        g.clock()
+        g.start_iterations()
+        def tick():
+            g.read(r, asynchronous=False)
+            bb = g.pre_update(u)
+            g.post_read(pr)
+            bb.zero_()
+            g.update(up)
+            g.clock()
+
+        def barrier():
+            # the read of the second clock (slack 0) returns only after every shard applied every worker's update
+            # of the first, and a worker's earlier messages to a shard precede that update on the same connection
+            tick(); tick(); g.read(r, asynchronous=False); bb = g.pre_update(u); g.post_read(pr); bb.zero_(); g.update(up); g.clock()
+
+        out = {}
+        if policy == 1:
+            out["owners"] = [g.locate_row(0, row) for row in range(8)]
+        elif policy == 2:
+            # first toucher: rank 0 asks first for rows 0,1,4,5 and rank 1 for rows 2,3,6,7
+            mine = [row for row in range(8) if (row // 2) % world == rank]
+            out["first"] = {row: g.locate_row(0, row) for row in mine}
+            barrier()
+            out["owners"] = [g.locate_row(0, row) for row in range(8)]
+        else:
+            # most frequent accessor: rank 1 reports 10 accesses of every row, rank 0 one; the decision is taken
+            # when a statistics request reaches the shard, queries before that are held back
+            for row in range(4):
+                g.report_access(0, row, nread=10 if rank == 1 else 1)
+            barrier()
+            if rank == 0:
+                g.get_stats()
+            out["owners"] = [g.locate_row(0, row, timeout_ms=20000) for row in range(4)]
+        barrier()
+        md = g.get_stats()["server"]["metadata"]
+        g.shutdown()
+        g.close()
+        q.put((rank, "ok", out, md))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None))
+
+
 def nvlink_hello_worker(rank, world, base_port, slack, clocks, q, kw):
     """Same helloworld-shaped run on the NVLINK transport: one GPU per rank, device-side clocks."""
     try:

@@ -215,3 +215,31 @@ def test_snapshot_resharded_to_a_smaller_world(tmp_path):
     assert one[0] == two[0]
     expect = (torch.arange(37 * 128, dtype=torch.float32) + 4 * 2 * 1.0 + 2.0).tolist()
     assert two[0] == expect
+
+
+@pytest.mark.parametrize("policy", [1, 2, 3])
+def test_placement_service_policies(policy):
+    """The shards' placement service (the reference's MetadataServer: hash / first toucher / most frequent accessor
+    with load balance) answers FIND_ROW queries from both workers consistently."""
+    from ps_workers import placement_worker
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = next_port()
+    procs = [ctx.Process(target=placement_worker, args=(r, 2, port, policy, q, {"device": DEVICE_CPU})) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=240) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    for o in out:
+        assert o[1] == "ok", o[2]
+    a, b = out[0][2], out[1][2]
+    assert a["owners"] == b["owners"]
+    if policy == 1:
+        assert a["owners"] == [row % 2 for row in range(8)]
+    elif policy == 2:
+        assert a["owners"] == [(row // 2) % 2 for row in range(8)]
+        assert all(v == 0 for v in a["first"].values()) and all(v == 1 for v in b["first"].values())
+    else:
+        assert a["owners"] == [1, 1, 1, 0]            # rank 1 accesses most; its fair share is 3 of the 4 rows
+    assert out[0][3]["policy"] == policy and out[0][3]["nr_requests"] > 0
