@@ -243,3 +243,11 @@ def test_placement_service_policies(policy):
     else:
         assert a["owners"] == [1, 1, 1, 0]            # rank 1 accesses most; its fair share is 3 of the 4 rows
     assert out[0][3]["policy"] == policy and out[0][3]["nr_requests"] > 0
+
+
+def test_helloworld_with_two_comm_channels():
+    """num_comm_channels = 2: two push workers per process share the tables; same result as one channel."""
+    out = _run_hello(2, 1, 30, num_comm_channels=2)
+    for rank, _, final, seen, max_stale, stats in out:
+        assert final == (60.0, 60.0), final
+        assert max_stale <= 1
