@@ -5,15 +5,19 @@
   python bench.py --impl reference ...                      (the unmodified reference, if it could be built)
 
 Config (the AlexNet entry of the benchmark spec): 5 conv + 3 FC with LRN, ~61 M parameters,
-synthetic 3x227x227 fp32 input ~N(0,1), labels uniform over 1000 classes, batch 256 per GPU
+synthetic 3x227x227 input ~N(0,1), labels uniform over 1000 classes, batch 256 per GPU
 (weak scaling), fp32 parameter tables with momentum SGD applied by the owning server shard,
 bf16 tensor-core compute, SSP slack 0.  One step = one parameter-server clock: Read every table,
 forward, backward (gradients written into the PreUpdate buffers), Update, Clock.
 
-Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks) with inputs
-resident on the device (158 MB per step, larger than L2); `e2e` runs the same public API call with a
-host->device copy of the step's batch from pinned memory and a device->host read of the loss in
-every step.
+Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks; the median of
+--repeats blocks of exactly --steps steps, every block listed under `ms_per_step_blocks`) with inputs
+resident on the device; `e2e` runs the same public API call with a host->device copy of the step's batch
+from pinned memory and a device->host read of the loss in every step.  The synthetic batches are N(0,1)
+values stored as bf16 by default (79 MB per step; the input layer rounds to bf16 NHWC either way);
+`e2e_fp32_input` is the same end-to-end run with fp32 batches on the host (158 MB per step).  `diag`
+gives the host time to enqueue a step and the host-to-device copy bandwidth per GPU with all ranks
+copying at once.
 """
 from __future__ import annotations
 
@@ -111,6 +115,9 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU)
     ap.add_argument("--transport", default="nvlink", choices=["nvlink", "tcp"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--single-e2e", action="store_true", help="skip the second end-to-end run with the other input dtype")
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="timed blocks of --steps steps each; the median block is reported, all blocks are listed")
     ap.add_argument("--cache-frac", type=float, default=None,
                     help="manage activations through the PS memory plan and cap the GPU budget at this fraction of the working set")
     ap.add_argument("--slack", type=int, default=0)
@@ -143,7 +150,7 @@ def main() -> None:
         args.gpus = world
     # before any pinned allocation: keep this rank's host buffers and threads on the socket next to its GPU
     from geeps_b200.utils.affinity import bind_to_gpu_cores
-    cores = bind_to_gpu_cores(local_rank)
+    cores = bind_to_gpu_cores(local_rank, int(os.environ.get("LOCAL_WORLD_SIZE", world)))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -182,61 +189,116 @@ def main() -> None:
                 dist.barrier()
             torch.cuda.synchronize(dev)
 
-        def timed(step_fn, steps):
+        def max_over_ranks(v):
+            t = torch.tensor([v], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+
+        def timed(step_fn, steps, repeats):
+            """`repeats` blocks of exactly `steps` steps, each bracketed by barrier + synchronize and timed with
+            CUDA events (max over ranks per block).  Returns the per-block times, the clock record over all blocks,
+            the launches of one block and the last loss."""
             sampler = ClockSampler(local_rank)
             sampler.start()
             for _ in range(3):       # keeps the GPU under load while nvidia-smi starts sampling (untimed)
                 step_fn()
             barrier()
             sampler.mark_begin()
-            launches0 = L.launch_count()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            loss = None
-            for _ in range(steps):
-                loss = step_fn()
-            torch.cuda.synchronize(dev)      # the runtime's comm stream (push / apply kernels) included
-            e1.record(stream)
-            e1.synchronize()
-            ms = e0.elapsed_time(e1)
+            block_ms, launches, loss = [], 0, None
+            for _ in range(repeats):
+                barrier()
+                launches0 = L.launch_count()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(steps):
+                    loss = step_fn()
+                torch.cuda.synchronize(dev)      # the runtime's comm stream (push / apply kernels) included
+                e1.record(stream)
+                e1.synchronize()
+                launches = L.launch_count() - launches0
+                block_ms.append(max_over_ranks(e0.elapsed_time(e1)))
             sampler.mark_end()
             clocks = sampler.stop()
             barrier()
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return t.item(), clocks, L.launch_count() - launches0, float(loss.item()) if loss is not None else None
+            return block_ms, clocks, launches, float(loss.item()) if loss is not None else None
 
         def step_device():
             return mod.step(x_dev, y_dev)
 
-        feeder = HostFeeder((B,) + image, (B,), dev, x_dtype=in_dtype)
         mailbox = LossMailbox(dev)
-        feeder.submit(x_host, y_host)
 
-        def step_e2e():
-            # every step: this step's batch comes from pinned host memory (its copy was started one step
-            # earlier on the copy stream), the next batch's copy starts now, and the loss goes back to the
-            # host; the host reads each step's loss one step later, so the launch queue never drains
-            xb, yb, slot = feeder.next(stream)
-            feeder.submit(x_host, y_host)
-            loss = mod.step(xb, yb)
-            feeder.release(slot, stream)
-            mailbox.post(loss, stream)
-            mailbox.collect(lag=1)
-            return loss
+        def make_e2e(feeder, xh):
+            feeder.submit(xh, y_host)
+
+            def step_e2e():
+                # every step: this step's batch comes from pinned host memory (its copy was started one step
+                # earlier on the copy stream), the next batch's copy starts now, and the loss goes back to the
+                # host; the host reads each step's loss one step later, so the launch queue never drains
+                xb, yb, slot = feeder.next(stream)
+                feeder.submit(xh, y_host)
+                loss = mod.step(xb, yb)
+                feeder.release(slot, stream)
+                mailbox.post(loss, stream)
+                mailbox.collect(lag=1)
+                return loss
+            return step_e2e
+
+        def e2e_record(step_fn, feeder):
+            for _ in range(2):
+                step_fn()
+            feeder.copy_times_ms()
+            blocks, _, _, _ = timed(step_fn, args.steps, args.repeats)
+            med = statistics.median(blocks)
+            copies = feeder.copy_times_ms()
+            copy_ms = max_over_ranks(statistics.median(copies)) if copies else None
+            return {"value": B * world * args.steps / (med / 1e3), "unit": "images/s",
+                    "h2d_bytes_per_step": feeder.bytes_per_batch, "d2h_bytes_per_step": mailbox.bytes_per_step,
+                    "ms_per_step": med / args.steps,
+                    "ms_per_step_blocks": [round(b / args.steps, 4) for b in blocks],
+                    # device time of one batch copy on the copy stream while the steps run (median, slowest rank)
+                    "h2d_copy_ms": copy_ms,
+                    "h2d_copy_gb_per_s": feeder.bytes_per_batch / copy_ms / 1e6 if copy_ms else None}
 
         for _ in range(max(args.warmup, 3)):
             step_device()
-        ms, clocks, launches, last_loss = timed(step_device, args.steps)
-        e2e = None
+        blocks, clocks, launches, last_loss = timed(step_device, args.steps, args.repeats)
+        ms = statistics.median(blocks)
+        # host time to enqueue one step (tape replay + runtime calls) with an empty launch queue: when it
+        # approaches the step time the host, not the GPU, paces the run
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            step_device()
+        host_enqueue_ms = max_over_ranks((time.perf_counter() - t0) / 5 * 1e3)
+        barrier()
+        e2e = e2e_other = diag = None
         if not args.no_e2e:
-            for _ in range(2):
-                step_e2e()
-            ms_e, _, _, _ = timed(step_e2e, args.steps)
-            e2e = {"value": B * world * args.steps / (ms_e / 1e3), "unit": "images/s",
-                   "h2d_bytes_per_step": feeder.bytes_per_batch, "d2h_bytes_per_step": mailbox.bytes_per_step,
-                   "ms_per_step": ms_e / args.steps}
+            feeder = HostFeeder((B,) + image, (B,), dev, x_dtype=in_dtype, timed=True)
+            e2e = e2e_record(make_e2e(feeder, x_host), feeder)
+            # all ranks copy at once with nothing else running: what the host-to-device path gives each GPU
+            barrier()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(feeder.copy_stream):
+                c0.record(feeder.copy_stream)
+                for _ in range(8):
+                    feeder.x[0].copy_(x_host, non_blocking=True)
+                c1.record(feeder.copy_stream)
+            c1.synchronize()
+            alone_ms = max_over_ranks(c0.elapsed_time(c1) / 8)
+            barrier()
+            diag = {"host_enqueue_ms_per_step": host_enqueue_ms,
+                    "h2d_copy_alone_ms": alone_ms,
+                    "h2d_copy_alone_gb_per_s": x_host.numel() * x_host.element_size() / alone_ms / 1e6}
+            if not args.single_e2e and model_name == "alexnet":
+                # the same run with the other input dtype on the host (the spec names an fp32 N(0,1) input; the
+                # input layer rounds it to bf16 either way, so a host pipeline may as well ship bf16)
+                other = torch.float32 if in_dtype == torch.bfloat16 else torch.bfloat16
+                feeder2 = HostFeeder((B,) + image, (B,), dev, x_dtype=other, timed=True)
+                x_host2 = x_host.to(other).pin_memory()
+                e2e_other = e2e_record(make_e2e(feeder2, x_host2), feeder2)
+                e2e_other["input_dtype"] = "fp32" if other == torch.float32 else "bf16"
+            e2e["input_dtype"] = args.input_dtype
         stats = mod.ps.get_stats()
         # kernels launched inside the runtime (flag signal + flag wait + push/apply per table per clock,
         # one data-age wait per table per clock) are not seen by the Python-side counter
@@ -245,14 +307,17 @@ def main() -> None:
             out = {
                 "metric": "images/sec (device-timed, max over ranks)", "value": B * world * args.steps / (ms / 1e3),
                 "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "ms_per_step": ms / args.steps, "repeats": args.repeats,
+                "ms_per_step_blocks": [round(b / args.steps, 4) for b in blocks],
+                "timed_seconds_total": sum(blocks) / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic", "impl": "ours",
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
                            "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack, "input_dtype": args.input_dtype, "cpu_cores_bound": len(cores) if cores else 0,
                            "weight_publish": "bf16+fp32" if args.fp32_weight_cache else "bf16 (biases / BN fp32)",
                            "host_replay_tapes": len(mod._tapes),
                            "tables": "fp32 master rows, momentum SGD on the owning shard",
-                           "l2": "inputs (158 MB/step) and activations exceed the 126 MB L2; no explicit flush"},
+                           "l2": "no explicit flush: per step the input batch (79 MB bf16 / 158 MB fp32), the activations "
+                                 "(conv1 output alone 148 MB) and 122 MB of bf16 weights exceed the 126 MB L2"},
                 "memory_plan": ({"cache_fraction_of_activations": args.cache_frac, "budget_rows": mod.budget_rows,
                                  "working_set_rows": mod.working_set_rows, "managed_activation_rows": mod.managed_rows,
                                  "param_rows": mod.param_rows,
@@ -260,7 +325,13 @@ def main() -> None:
                                  "swap_d2h_gb_per_s": stats["client"]["swap_d2h_bytes"] / max(1, mod.steps) / (ms / args.steps) / 1e6,
                                  "cpu_local_rows": stats["client"]["cpu_local_rows"], "gpu_local_rows": stats["client"]["gpu_local_rows"]}
                                 if args.cache_frac is not None else None),
-                "clocks": clocks, "e2e": e2e, "gpu_launches": launches + runtime_launches, "final_loss": last_loss,
+                "clocks": clocks, "e2e": e2e,
+                ("e2e_fp32_input" if e2e_other and e2e_other.get("input_dtype") == "fp32" else "e2e_other_input"): e2e_other,
+                "diag": diag,
+                "ps": {"device_push_ms_per_step": stats["bgthread"]["device_push_ms"] / max(1, stats["bgthread"]["device_push_samples"]) * len(mod.tables),
+                       "device_push_gb_per_s": stats["bgthread"]["device_push_gb_per_s"],
+                       "device_push_samples": stats["bgthread"]["device_push_samples"]},
+                "gpu_launches": launches + runtime_launches, "final_loss": last_loss,
             }
             print(json.dumps(out))
         mod.close()

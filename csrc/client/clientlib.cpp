@@ -87,6 +87,8 @@ ClientLib::~ClientLib() {
   for (auto& kv : tables_)
     for (ShardRows& sr : kv.second->shards) if (sr.gpu_index_dev) cudaFree(sr.gpu_index_dev);
   fabric_teardown();
+  if (row_status_dev_) cudaFree(row_status_dev_);
+  if (row_status_host_) cudaFreeHost(row_status_host_);
   if (default_stream_) cudaStreamDestroy((cudaStream_t)default_stream_);
   if (swap_stream_) cudaStreamDestroy((cudaStream_t)swap_stream_);
 }
@@ -238,6 +240,7 @@ bool ClientLib::read_batch(int handle, RowData** buf, void* stream, bool async) 
   stats_.nr_read++;
   stats_.rows_read += op.rows.size();
   stats_.read_time += now_seconds() - t0;
+  op_account(handle, t0);
   return ok && error_code_.load() == 0;
 }
 
@@ -257,6 +260,7 @@ void ClientLib::postread_batch(int handle, void* stream) {
   swap_release(plan_.ops[handle].prestep, op_stream(stream), false);
   stats_.nr_postread++;
   stats_.postread_time += now_seconds() - t0;
+  op_account(handle, t0);
 }
 
 void ClientLib::preupdate_batch(int handle, RowOpVal** buf, void* stream) {
@@ -280,6 +284,7 @@ void ClientLib::preupdate_batch(int handle, RowOpVal** buf, void* stream) {
       *buf = reinterpret_cast<RowOpVal*>(fabric_ring_ptr((uint)op.table, (int)process_id_, clock_)) + op.store_offset;
       stats_.nr_preupdate++;
       stats_.preupdate_time += now_seconds() - t0;
+      op_account(handle, t0);
       return;
     }
   }
@@ -288,6 +293,7 @@ void ClientLib::preupdate_batch(int handle, RowOpVal** buf, void* stream) {
   swap_wait_region_free(handle, op_stream(stream));
   stats_.nr_preupdate++;
   stats_.preupdate_time += now_seconds() - t0;
+  op_account(handle, t0);
 }
 
 void ClientLib::update_batch(int handle, void* stream, bool async) {
@@ -303,8 +309,11 @@ void ClientLib::update_batch(int handle, void* stream, bool async) {
   // once, so its push overlaps the rest of the iteration; during bootstrap Clock() signals all
   if (!pre.local) tables_[(uint)op.table]->last_stream = st;
   if (started_ && op.table_last_write) clock_table(clock_, (uint)op.table, false, false, st);
-  (void)async;
+  // the blocking form returns once the update buffer may be reused by the host (the reference's Update returns
+  // after the buffer was folded into the oplog); the asynchronous form leaves that to stream order
+  if (!async && gpu_) cudaStreamSynchronize((cudaStream_t)st);
   stats_.update_time += now_seconds() - t0;
+  op_account(handle, t0);
 }
 
 bool ClientLib::localaccess_batch(int handle, RowData** buf, void* stream) {
@@ -323,6 +332,7 @@ bool ClientLib::localaccess_batch(int handle, RowData** buf, void* stream) {
   }
   stats_.nr_localaccess++;
   stats_.localaccess_time += now_seconds() - t0;
+  op_account(handle, t0);
   return true;
 }
 
@@ -336,6 +346,7 @@ void ClientLib::postlocalaccess_batch(int handle, void* stream) {
     else swap_release(op.prestep, op_stream(stream), false);
   }
   stats_.localaccess_time += now_seconds() - t0;
+  op_account(handle, t0);
 }
 
 void ClientLib::start_opseq() {
@@ -349,19 +360,62 @@ void ClientLib::iterate() {
   if (!vi_finished_) { set_error(ERR_ORDER, "Clock before FinishVirtualIteration"); return; }
   if (started_ && last_handle_ != plan_.clock_handle - 1)
     set_error(ERR_ORDER, "Clock called before all declared accesses of the iteration");
-  if (!started_) clock_all(clock_, clock_ == kInitialClock);   // bootstrap: signal every table now
+  if (!started_) {   // bootstrap: signal every table now
+    if (clock_ == kInitialClock) bootstrap_init_pushed_ = true;
+    clock_all(clock_, clock_ == kInitialClock);
+  }
   clock_++;
   last_handle_ = -1;
   stats_.nr_clock++;
   if (nvlink_) fabric_check_status();
+  else check_row_status();
   if (config_.snapshot_interval > 0 && !config_.snapshot_dir.empty() && clock_ % config_.snapshot_interval == 0)
     save_snapshot(config_.snapshot_dir);
-  if (config_.log_interval > 0 && clock_ % config_.log_interval == 0)
-    fprintf(stderr, "[geeps worker %u] clock %d stats %s\n", process_id_, clock_, stats_.to_json().c_str());
+  if (config_.log_interval > 0 && clock_ % config_.log_interval == 0) {
+    fabric_collect_push_timing();
+    fprintf(stderr, "[geeps worker %u] clock %d stats %s bgthread %s\n", process_id_, clock_, stats_.to_json().c_str(),
+            bg_stats_.to_json().c_str());
+    dump_op_times();
+  }
   stats_.clock_time += now_seconds() - t0;
 }
 
+void ClientLib::op_account(int handle, double t0) {
+  if (handle < 0 || (size_t)handle >= op_time_.size()) return;
+  op_time_[handle] += now_seconds() - t0;
+  op_calls_[handle]++;
+}
+
+// Host time spent inside each declared access since the last dump, one line per handle (what the reference prints
+// per operation every log_interval clocks: src/client/clientlib-bg-access.cpp:544-573).
+void ClientLib::dump_op_times() {
+  static const char* names[] = {"read", "post_read", "pre_update", "update", "local_access", "post_local_access", "clock"};
+  for (size_t h = 0; h < op_time_.size(); ++h) {
+    if (!op_calls_[h]) continue;
+    const OpInfo& op = plan_.ops[h];
+    const OpInfo& pre = (op.prestep >= 0 && (size_t)op.prestep < plan_.ops.size()) ? plan_.ops[op.prestep] : op;
+    fprintf(stderr, "[geeps worker %u] op %zu %s table %lld rows %zu %s: calls %llu, %.3f ms total, %.1f us per call\n",
+            process_id_, h, (int)op.type >= 0 && (int)op.type < 7 ? names[(int)op.type] : "?",
+            pre.local ? -1LL : (long long)pre.table, pre.rows.size(),
+            pre.direct ? "direct" : (pre.location == LOC_GPU ? "staged" : "staged from host"),
+            (unsigned long long)op_calls_[h], op_time_[h] * 1e3, op_time_[h] * 1e6 / (double)op_calls_[h]);
+    op_time_[h] = 0;
+    op_calls_[h] = 0;
+  }
+}
+
+// Row kernels of the host-staged GPU path report failed bounds checks into a device block; mirror it.
+bool ClientLib::check_row_status() {
+  if (!row_status_dev_) return true;
+  cudaMemcpy(row_status_host_, row_status_dev_, 4 * sizeof(int), cudaMemcpyDeviceToHost);
+  if (row_status_host_[0] == 0) return true;
+  set_error(ERR_CUDA, "row kernel check failed (kernel " + std::to_string(row_status_host_[1]) + ", detail " +
+                          std::to_string(row_status_host_[2]) + ", seen " + std::to_string(row_status_host_[3]) + ")");
+  return false;
+}
+
 std::string ClientLib::json_stats() {
+  fabric_collect_push_timing();
   // ask the co-located shard for its counters and wait (bounded) for the reply
   {
     std::lock_guard<std::mutex> lk(global_mu_);

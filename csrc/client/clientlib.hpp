@@ -46,6 +46,10 @@ struct FlatOps {
   DataStorage data;
   Flag flag = NONE;
   iter_t clock = -1;
+  // read-my-writes: what one unit of this logged update adds to the worker's own view of the rows until the
+  // shard's answer replaces it (1 for additive tables and initial values; -lr * grad_scale, the plain gradient
+  // step, for optimizer tables, whose real step only the shard can compute)
+  float rmw_alpha = 1.f;
 };
 
 // Fixed pool of pre-allocated oplog entries handed out in FIFO order; get() blocks (bounded) when
@@ -86,7 +90,11 @@ struct CachedTable {
   iter_t server_clock_min = kInitialDataAge;
   std::vector<ShardRows> shards;
   iter_t signalled_clock = -1;         // last clock this worker signalled for the table
-  iter_t waited_stamp = -1;            // NVLINK: last data_age stamp a device wait was enqueued for
+  // NVLINK: data_age stamps for which a device wait has already been enqueued, per application stream (a wait
+  // only orders the stream it runs on), and a floor that holds for every stream (set where the host itself
+  // synchronised the device, e.g. after LoadSnapshot)
+  std::vector<std::pair<void*, iter_t>> waited_by_stream;
+  iter_t waited_floor = -1;
   int mode = 0;
   bool has_indirect_updates = false;   // some PreUpdate of this table goes through staging
   iter_t ring_zeroed_clock = -1;       // NVLINK: clock whose ring slot has been zeroed
@@ -122,6 +130,11 @@ struct Fabric {
   void* timeline_origin = nullptr;
   std::vector<TimelineRec> timeline_recs;
   void* push_done_event = nullptr;
+  // Device time of the latest pushes: a ring of event pairs around the reduce + apply + publish kernel on the comm
+  // stream, summed by GetStats() over the pairs that have completed (device_push_ms / device_push_gb_per_s).
+  struct PushTiming { void* begin = nullptr; void* end = nullptr; size_t table_bytes = 0; bool armed = false; };
+  std::vector<PushTiming> push_timing;
+  size_t push_timing_next = 0;
   std::vector<void*> table_events;
   int* host_status = nullptr;             // pinned mirror of the device status block
 };
@@ -209,6 +222,9 @@ class ClientLib {
   FlatOps* create_oplog_entry(CachedTable& ct, ParamCache& pc, MemType type, iter_t clock, void* stream);
   void push_updates_param_cache(iter_t clock, uint table_id, bool is_init);
   void reclaim_oplog(CachedTable& ct, iter_t up_to_clock);
+  float rmw_alpha_for(const CachedTable& ct, iter_t clock) const;
+  int* row_status() const { return nvlink_ ? (fabric_.base ? reinterpret_cast<int*>(fabric_.base + fabric_.status_off) : nullptr)
+                                           : row_status_dev_; }
   void recv_row_batch_gpu(CachedTable& ct, uint server_id, const RowData* rows, iter_t self_clock);
   void recv_row_batch_cpu(CachedTable& ct, uint server_id, const RowData* rows, iter_t self_clock);
   void read_batch_local(const OpInfo& op, RowData* staging, void* stream);
@@ -232,6 +248,7 @@ class ClientLib {
   void fabric_wait_data_age(CachedTable& ct, uint table_id, iter_t needed_age, void* stream);
   void fabric_push(iter_t clock, uint table_id, bool is_init, void* stream);
   bool fabric_check_status(bool sync = false);
+  void fabric_read_rmw(const OpInfo& op, RowData* dst, void* stream);
   float* fabric_cache_ptr(uint table_id, int rank) const;
   float* fabric_ring_ptr(uint table_id, int rank, iter_t clock) const;
 
@@ -246,6 +263,7 @@ class ClientLib {
   std::unique_ptr<PlanCompiler> compiler_;
   Plan plan_;
   bool vi_finished_ = false, started_ = false, shut_down_ = false;
+  bool bootstrap_init_pushed_ = false;   // clock 0 was signalled before StartIterations: its updates are initial values
   iter_t clock_ = kInitialClock;
   int last_handle_ = -1;
 
@@ -292,6 +310,15 @@ class ClientLib {
 
   Stats stats_;
   BgthreadStats bg_stats_;
+  // host time and call count of every declared access (indexed by handle), printed every log_interval clocks
+  std::vector<double> op_time_;
+  std::vector<uint64_t> op_calls_;
+  void op_account(int handle, double t0);
+  void dump_op_times();
+  void fabric_collect_push_timing();
+  int* row_status_dev_ = nullptr;      // status block of the row kernels on the host-staged GPU path
+  int* row_status_host_ = nullptr;     // its pinned mirror
+  bool check_row_status();
 };
 
 }  // namespace geeps_b200

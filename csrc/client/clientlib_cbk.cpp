@@ -3,6 +3,7 @@
 // (role of the reference's src/client/clientlib-cbk.cpp:51-111).
 #include <stdio.h>
 
+#include <algorithm>
 #include <chrono>
 #include <string.h>
 
@@ -61,8 +62,12 @@ void ClientLib::recv_row_batch_cbk(uint server_id, uint table_id, iter_t data_ag
                                 std::to_string(data_age) + ")");
     return;
   }
-  recv_row_batch_cpu(ct, server_id, rows, self_clock);
-  recv_row_batch_gpu(ct, server_id, rows, self_clock);
+  // Own updates newer than this are not in the rows just received and are replayed (read-my-writes).  An additive
+  // shard applies an update on arrival, so everything up to self_clock is in; an optimizer shard steps once per
+  // global clock, so only clocks up to data_age are.
+  const iter_t replay_after = ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM ? std::min(data_age, self_clock) : self_clock;
+  recv_row_batch_cpu(ct, server_id, rows, replay_after);
+  recv_row_batch_gpu(ct, server_id, rows, replay_after);
   ct.per_server_data_age[server_id] = data_age;
   ct.data_age = clock_min(ct.per_server_data_age);
   bg_stats_.nr_recv++;

@@ -21,6 +21,10 @@ const long long kNoLimit = (long long)1 << 62;
 bool ClientLib::read_row_batch_param_cache(const OpInfo& op, RowData* dst, void* stream) {
   CachedTable& ct = *tables_[(uint)op.table];
   const size_t n = op.rows.size();
+  if (nvlink_ && config_.read_my_writes && ct.plan->slack > 0) {
+    fabric_read_rmw(op, dst, stream);
+    return true;
+  }
   if (nvlink_) {
     // device wait already enqueued by the caller; gather from the local arena cache
     const void* idx = op_index_dev_[&op - &plan_.ops[0]];
@@ -59,7 +63,7 @@ bool ClientLib::read_row_batch_param_cache(const OpInfo& op, RowData* dst, void*
   const size_t op_idx = &op - &plan_.ops[0];
   if (op.location == LOC_GPU) {
     geeps_row_gather(reinterpret_cast<float*>(dst), ct.gpu.data_cache.floats(), op_index_dev_[op_idx], (long long)n, 0, 0,
-                     (long long)op.num_vals_limit, (long long)n, (long long)ct.gpu.data_cache.size(), nullptr, stream);
+                     (long long)op.num_vals_limit, (long long)n, (long long)ct.gpu.data_cache.size(), row_status(), stream);
     cudaStreamSynchronize((cudaStream_t)stream);   // the receiver may overwrite the cache once the lock drops
   } else if (gpu_) {
     // host-cached rows on a GPU worker: gather on the host into pinned staging, then H2D
@@ -86,8 +90,21 @@ FlatOps* ClientLib::create_oplog_entry(CachedTable& ct, ParamCache& pc, MemType,
   if (e->data.type() == MEM_DEVICE) cudaStreamSynchronize((cudaStream_t)stream);
   e->flag = FlatOps::INC;
   e->clock = clock;
+  e->rmw_alpha = rmw_alpha_for(ct, clock);
   pc.oplog[clock] = e;
   return e;
+}
+
+// What a logged update of `clock` contributes to this worker's own view of the rows under read-my-writes.
+// Additive tables (and the initial values pushed during bootstrap, which every table adds): the update itself,
+// exactly what the shard will add (src/client/clientlib-data.cpp:389-394 of the reference).  Optimizer tables:
+// the shard's momentum step depends on the other workers' gradients, so the worker applies the plain gradient
+// step -lr * grad_scale * g as a provisional value; the shard's rows replace it when they arrive, and updates
+// the shard had not yet seen are re-applied the same way.
+float ClientLib::rmw_alpha_for(const CachedTable& ct, iter_t clock) const {
+  const bool is_init = !started_ && clock == kInitialClock;
+  if (ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM && !is_init) return -config_.learning_rate * config_.grad_scale;
+  return 1.f;
 }
 
 // Fold an application update buffer into this clock's update log (and, with read-my-writes, into
@@ -108,11 +125,11 @@ void ClientLib::update_batch_param_cache(const OpInfo& pre, const RowOpVal* src,
     FlatOps* e = create_oplog_entry(ct, ct.gpu, MEM_DEVICE, clock_, stream);
     if (!e) return;
     geeps_row_scatter_add(e->data.floats(), reinterpret_cast<const float*>(src), op_index_dev_[op_idx], (long long)n, 0, 0,
-                          (long long)pre.num_vals_limit, (long long)e->data.size(), (long long)n, nullptr, stream);
+                          (long long)pre.num_vals_limit, (long long)e->data.size(), (long long)n, row_status(), stream);
     if (config_.read_my_writes)
-      geeps_row_scatter_add(ct.gpu.data_cache.floats(), reinterpret_cast<const float*>(src), op_index_dev_[op_idx],
-                            (long long)n, 0, 0, (long long)pre.num_vals_limit, (long long)ct.gpu.data_cache.size(),
-                            (long long)n, nullptr, stream);
+      geeps_row_scatter_axpy(ct.gpu.data_cache.floats(), reinterpret_cast<const float*>(src), op_index_dev_[op_idx],
+                             (long long)n, 0, 0, (long long)pre.num_vals_limit, (long long)ct.gpu.data_cache.size(),
+                             (long long)n, e->rmw_alpha, row_status(), stream);
     cudaStreamSynchronize((cudaStream_t)stream);
   } else {
     const RowOpVal* host_src = src;
@@ -126,7 +143,8 @@ void ClientLib::update_batch_param_cache(const OpInfo& pre, const RowOpVal* src,
     if (!e) return;
     add_rows_from_double_index_cpu(e->data.data(), host_src, pre.index.data(), n, 0, 0, pre.num_vals_limit);
     if (config_.read_my_writes)
-      add_rows_from_double_index_cpu(ct.cpu.data_cache.data(), host_src, pre.index.data(), n, 0, 0, pre.num_vals_limit);
+      axpy_rows_from_double_index_cpu(ct.cpu.data_cache.data(), host_src, pre.index.data(), n, 0, 0, pre.num_vals_limit,
+                                      e->rmw_alpha);
   }
 }
 
@@ -212,7 +230,7 @@ void ClientLib::recv_row_batch_cpu(CachedTable& ct, uint server_id, const RowDat
   for (auto& kv : ct.cpu.oplog) {
     if (kv.first <= self_clock) continue;
     for (size_t slot : sr.cpu_slots)
-      cpu_axpy(ROW_DATA_SIZE, 1.f, kv.second->data.data()[slot].data, ct.cpu.data_cache.data()[slot].data);
+      cpu_axpy(ROW_DATA_SIZE, kv.second->rmw_alpha, kv.second->data.data()[slot].data, ct.cpu.data_cache.data()[slot].data);
     bg_stats_.nr_rmw_replay++;
   }
 }
@@ -238,7 +256,7 @@ void ClientLib::recv_row_batch_gpu(CachedTable& ct, uint server_id, const RowDat
       if (recv_dev_.size() < ng) recv_dev_.init(recv_buffer_.size(), MEM_DEVICE);
       Mem::copy(recv_dev_.data(), MEM_DEVICE, recv_buffer_.data(), MEM_PINNED, ng * sizeof(RowData), swap_stream_, false);
       geeps_row_scatter(ct.gpu.data_cache.floats(), recv_dev_.floats(), sr.gpu_index_dev, (long long)ng, 0, 0, kNoLimit,
-                        (long long)ct.gpu.data_cache.size(), (long long)ng, nullptr, swap_stream_);
+                        (long long)ct.gpu.data_cache.size(), (long long)ng, row_status(), swap_stream_);
       cudaStreamSynchronize((cudaStream_t)swap_stream_);
     }
   }
@@ -248,15 +266,15 @@ void ClientLib::recv_row_batch_gpu(CachedTable& ct, uint server_id, const RowDat
     if (kv.first <= self_clock) continue;
     if (!gpu_) {
       for (size_t slot : sr.gpu_slots)
-        cpu_axpy(ROW_DATA_SIZE, 1.f, kv.second->data.data()[slot].data, ct.gpu.data_cache.data()[slot].data);
+        cpu_axpy(ROW_DATA_SIZE, kv.second->rmw_alpha, kv.second->data.data()[slot].data, ct.gpu.data_cache.data()[slot].data);
     } else if (sr.gpu_contiguous) {
       geeps_axpy(ct.gpu.data_cache.floats() + sr.gpu_slots[0] * ROW_DATA_SIZE,
-                 kv.second->data.floats() + sr.gpu_slots[0] * ROW_DATA_SIZE, 1.f, (long long)(ng * ROW_DATA_SIZE),
+                 kv.second->data.floats() + sr.gpu_slots[0] * ROW_DATA_SIZE, kv.second->rmw_alpha, (long long)(ng * ROW_DATA_SIZE),
                  swap_stream_);
     } else {
       for (size_t slot : sr.gpu_slots)
         geeps_axpy(ct.gpu.data_cache.floats() + slot * ROW_DATA_SIZE, kv.second->data.floats() + slot * ROW_DATA_SIZE,
-                   1.f, ROW_DATA_SIZE, swap_stream_);
+                   kv.second->rmw_alpha, ROW_DATA_SIZE, swap_stream_);
     }
     bg_stats_.nr_rmw_replay++;
   }

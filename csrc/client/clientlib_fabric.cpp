@@ -29,7 +29,8 @@ struct IpcBlob {
 };
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kFlagBytes = 256;
-constexpr size_t kPushReadyOff = 0, kDataAgeOff = 32, kGlobalClockOff = 64, kCtaCounterOff = 68;
+constexpr size_t kPushReadyOff = 0, kDataAgeOff = 32, kGlobalClockOff = 64, kCtaCounterOff = 68, kPublishBeginOff = 96;
+constexpr size_t kPushTimingRing = 64;
 }  // namespace
 
 float* ClientLib::fabric_cache_ptr(uint table_id, int rank) const {
@@ -144,6 +145,13 @@ bool ClientLib::fabric_setup(std::string* err) {
 void ClientLib::fabric_teardown() {
   if (!fabric_.base) return;
   cudaDeviceSynchronize();
+  if (num_processes_ > 1 && error_code_.load() != 0) {
+    // This rank leaves on an error without the closing barrier: healthy peers may still have kernels in flight
+    // that store into this arena through their mappings, and freeing exported memory under them is undefined.
+    // The arena and the mappings stay until the process exits (the driver reclaims them then).
+    fabric_.active = false;
+    return;
+  }
   const uint32_t pid = (uint32_t)getpid();
   for (uint r = 0; r < num_processes_; ++r) {
     if (r == process_id_ || !fabric_.peer_base[r]) continue;
@@ -158,6 +166,11 @@ void ClientLib::fabric_teardown() {
     }
     if (!same_process) cudaIpcCloseMemHandle(fabric_.peer_base[r]);
   }
+  for (Fabric::PushTiming& pt : fabric_.push_timing) {
+    if (pt.begin) cudaEventDestroy((cudaEvent_t)pt.begin);
+    if (pt.end) cudaEventDestroy((cudaEvent_t)pt.end);
+  }
+  fabric_.push_timing.clear();
   for (void* e : fabric_.table_events) if (e) cudaEventDestroy((cudaEvent_t)e);
   fabric_.table_events.clear();
   for (void* cs : fabric_.comm_lanes) cudaStreamDestroy((cudaStream_t)cs);
@@ -172,12 +185,18 @@ void ClientLib::fabric_teardown() {
 // Device-side SSP wait: the stream stalls (bounded) until every shard stamped data_age >= needed+1.
 void ClientLib::fabric_wait_data_age(CachedTable& ct, uint table_id, iter_t needed_age, void* stream) {
   const iter_t stamp = needed_age + 1;
-  if (stamp <= 0 || stamp <= ct.waited_stamp) return;
+  if (stamp <= 0 || stamp <= ct.waited_floor) return;
+  // a wait kernel orders only the stream it was enqueued on: another stream that touches the table in the same
+  // clock needs its own
+  std::pair<void*, iter_t>* mine = nullptr;
+  for (auto& w : ct.waited_by_stream) if (w.first == stream) mine = &w;
+  if (mine && stamp <= mine->second) return;
   const TableArena& ta = fabric_.tables[table_id];
   const int* flags = reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kDataAgeOff);
   geeps_flag_wait(flags, (int)num_processes_, stamp, (unsigned long long)config_.device_wait_budget_us * 1000ull,
                   reinterpret_cast<int*>(fabric_.base + fabric_.status_off), stream);
-  ct.waited_stamp = stamp;
+  if (mine) mine->second = stamp; else ct.waited_by_stream.emplace_back(stream, stamp);
+  stats_.device_waits_enqueued++;
 }
 
 // Push of (clock, table): announce "my update is complete" to every shard on the application's
@@ -223,8 +242,34 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
     cudaEventRecord(e0, (cudaStream_t)stream);
   }
   const unsigned long long budget = (unsigned long long)config_.device_wait_budget_us * 1000ull;
-  geeps_flag_wait(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_, stamp,
-                  budget, status, cs);
+  if (config_.read_my_writes && ct.plan->slack > 0) {
+    // readers that merge their own pending updates need to know when a publish is in progress: mark its begin on
+    // every worker before the first row is stored (the data_age stamp after the last row marks its end)
+    GeepsFlagList begin;
+    memset(&begin, 0, sizeof(begin));
+    begin.n = (int)num_processes_;
+    for (uint r = 0; r < num_processes_; ++r)
+      begin.ptr[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kPublishBeginOff);
+    geeps_flag_wait_signal(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_,
+                           stamp, budget, status, &begin, (int)process_id_, cs);
+  } else {
+    geeps_flag_wait(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_, stamp,
+                    budget, status, cs);
+  }
+  // device time of the push kernel itself (the wait for the other workers is not part of it)
+  Fabric::PushTiming* pt = nullptr;
+  if (!is_init) {
+    if (fabric_.push_timing.empty()) fabric_.push_timing.resize(kPushTimingRing);
+    pt = &fabric_.push_timing[fabric_.push_timing_next++ % kPushTimingRing];
+    if (!pt->begin) {
+      cudaEvent_t a, b;
+      cudaEventCreate(&a); cudaEventCreate(&b);
+      pt->begin = a; pt->end = b;
+    }
+    pt->table_bytes = ta.rows * kRowBytes;
+    pt->armed = true;
+    cudaEventRecord((cudaEvent_t)pt->begin, (cudaStream_t)cs);
+  }
   GeepsPushApplyParams p;
   memset(&p, 0, sizeof(p));
   for (uint r = 0; r < num_processes_; ++r) {
@@ -258,12 +303,62 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
                         ? (long long)config_.table_fp32_from_row[table_id] : 0;
   if (timed) cudaEventRecord((cudaEvent_t)rec.arrived, (cudaStream_t)cs);
   geeps_ps_push_apply(&p, fabric_.push_ctas, cs);
+  if (pt) cudaEventRecord((cudaEvent_t)pt->end, (cudaStream_t)cs);
   if (timed) {
     cudaEventRecord((cudaEvent_t)rec.applied, (cudaStream_t)cs);
     fabric_.timeline_recs.push_back(rec);
   }
   bg_stats_.nr_push++;
   bg_stats_.bytes_pushed += ta.rows * kRowBytes;
+}
+
+// Sum the device time of the pushes in the timing ring that have completed since the last call.
+void ClientLib::fabric_collect_push_timing() {
+  if (!fabric_.active) return;
+  for (Fabric::PushTiming& pt : fabric_.push_timing) {
+    if (!pt.armed || cudaEventQuery((cudaEvent_t)pt.end) != cudaSuccess) { cudaGetLastError(); continue; }
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, (cudaEvent_t)pt.begin, (cudaEvent_t)pt.end) == cudaSuccess) {
+      bg_stats_.device_push_ms += ms;
+      bg_stats_.device_push_bytes += pt.table_bytes;
+      bg_stats_.device_push_samples++;
+    } else {
+      cudaGetLastError();
+    }
+    pt.armed = false;
+  }
+}
+
+// Staged Read with read-my-updates: the worker's private copy = cache rows + its own updates that the owning
+// shards have not published yet (additive tables: the updates themselves; optimizer tables: the plain gradient
+// step -lr * grad_scale * g as a provisional value).  Counterpart of the reference's replay of the oplog onto
+// freshly received rows (src/client/clientlib-data.cpp:132-150), done at read time because here the shards write
+// the cache in place.
+void ClientLib::fabric_read_rmw(const OpInfo& op, RowData* dst, void* stream) {
+  CachedTable& ct = *tables_[(uint)op.table];
+  const TableArena& ta = fabric_.tables[op.table];
+  GeepsRmwReadParams p;
+  memset(&p, 0, sizeof(p));
+  p.dst = reinterpret_cast<float*>(dst);
+  p.cache = fabric_cache_ptr((uint)op.table, (int)process_id_);
+  p.ring = reinterpret_cast<const float*>(fabric_.base + ta.ring_off);
+  p.index = op_index_dev_[&op - &plan_.ops[0]];
+  p.data_age = reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kDataAgeOff);
+  p.publish_begin = reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPublishBeginOff);
+  p.status = reinterpret_cast<int*>(fabric_.base + fabric_.status_off);
+  p.num_rows = (long long)op.rows.size();
+  p.num_vals_limit = (long long)op.num_vals_limit;
+  p.dst_rows = (long long)op.rows.size();
+  p.total_rows = (long long)ta.rows;
+  p.wait_budget_ns = (unsigned long long)config_.device_wait_budget_us * 1000ull;
+  p.n_ranks = (int)num_processes_;
+  p.partition_kind = config_.partitioner;
+  p.ring_slots = ta.ring_slots;
+  p.clock = (int)clock_;
+  p.additive_below_clock = bootstrap_init_pushed_ ? (int)kInitialClock + 1 : 0;
+  p.alpha = ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM ? -config_.learning_rate * config_.grad_scale : 1.f;
+  geeps_row_gather_rmw(&p, stream);
+  bg_stats_.nr_rmw_replay++;
 }
 
 // Errors recorded by kernels (expired waits, failed bounds checks) surface here.  The device block

@@ -183,8 +183,10 @@ bool ClientLib::load_snapshot(const std::string& dir) {
       std::vector<int> flags(kRowFloats / 2, 0);
       for (int i = 0; i < 8; ++i) { flags[i] = snap_clock; flags[8 + i] = snap_clock; }   // push_ready, data_age stamps
       flags[16] = snap_clock;                                                              // global clock stamp
-      cudaMemcpy(fabric_.base + ta.flags_off, flags.data(), 72, cudaMemcpyHostToDevice);
-      ct.waited_stamp = snap_clock;
+      for (int i = 0; i < 8; ++i) flags[24 + i] = snap_clock;                              // publish-begin stamps
+      cudaMemcpy(fabric_.base + ta.flags_off, flags.data(), 128, cudaMemcpyHostToDevice);
+      ct.waited_floor = snap_clock;
+      ct.waited_by_stream.clear();
       cudaStreamSynchronize((cudaStream_t)default_stream_);
     } else {
       TabletStorage::DataTable* dt = server_->storage()->mutable_table(t);

@@ -121,6 +121,14 @@ bool ClientLib::vi_create_storage() {
   for (const OpInfo& op : plan_.ops)
     if (op.type == OP_PRE_UPDATE && !op.local && !op.direct) tables_[(uint)op.table]->has_indirect_updates = true;
   swap_init();
+  op_time_.assign(plan_.ops.size(), 0.0);
+  op_calls_.assign(plan_.ops.size(), 0);
+  if (gpu_ && !nvlink_) {
+    // status block for the row kernels of the host-staged path (failed bounds checks land here)
+    cudaMalloc(reinterpret_cast<void**>(&row_status_dev_), 4 * sizeof(int));
+    cudaMemset(row_status_dev_, 0, 4 * sizeof(int));
+    cudaHostAlloc(reinterpret_cast<void**>(&row_status_host_), 4 * sizeof(int), cudaHostAllocDefault);
+  }
   if (nvlink_) {
     if (!fabric_setup(&err)) { set_error(ERR_TRANSPORT, "NVLINK fabric: " + err); return false; }
   }

@@ -42,6 +42,7 @@ struct Stats {
   Relaxed<int> max_staleness = 0;
   Relaxed<uint64_t> swap_h2d_bytes = 0, swap_d2h_bytes = 0;
   Relaxed<uint64_t> device_wait_timeouts = 0, host_wait_timeouts = 0;
+  Relaxed<uint64_t> device_waits_enqueued = 0;   // data_age wait kernels put on application streams
   Relaxed<double> iterate_time = 0;
 
   std::string to_json() const {
@@ -59,7 +60,8 @@ struct Stats {
       << ",\"max_staleness\":" << max_staleness << ",\"staleness_hist\":[";
     for (int i = 0; i < 8; ++i) o << (i ? "," : "") << staleness_hist[i];
     o << "],\"swap_h2d_bytes\":" << swap_h2d_bytes << ",\"swap_d2h_bytes\":" << swap_d2h_bytes
-      << ",\"device_wait_timeouts\":" << device_wait_timeouts << ",\"host_wait_timeouts\":" << host_wait_timeouts << "}";
+      << ",\"device_wait_timeouts\":" << device_wait_timeouts << ",\"host_wait_timeouts\":" << host_wait_timeouts
+      << ",\"device_waits_enqueued\":" << device_waits_enqueued << "}";
     return o.str();
   }
 };
@@ -68,7 +70,9 @@ struct BgthreadStats {
   Relaxed<uint64_t> nr_push = 0, nr_clock_only = 0, nr_recv = 0, nr_rmw_replay = 0, nr_oplog_reclaimed = 0;
   Relaxed<uint64_t> bytes_pushed = 0, bytes_received = 0;
   Relaxed<double> push_time = 0, push_d2h_time = 0, push_send_time = 0, recv_time = 0, recv_h2d_time = 0, recv_wait_lock_time = 0;
-  Relaxed<double> device_push_ms = 0, device_pull_ms = 0;
+  // device time and table bytes of completed push kernels (reduce + apply + publish), NVLINK transport
+  Relaxed<double> device_push_ms = 0;
+  Relaxed<uint64_t> device_push_bytes = 0, device_push_samples = 0;
   std::string to_json() const {
     std::ostringstream o;
     o << "{\"nr_push\":" << nr_push << ",\"nr_clock_only\":" << nr_clock_only << ",\"nr_recv\":" << nr_recv
@@ -76,7 +80,10 @@ struct BgthreadStats {
       << ",\"bytes_pushed\":" << bytes_pushed << ",\"bytes_received\":" << bytes_received
       << ",\"push_time\":" << push_time << ",\"push_d2h_time\":" << push_d2h_time << ",\"push_send_time\":" << push_send_time
       << ",\"recv_time\":" << recv_time << ",\"recv_h2d_time\":" << recv_h2d_time
-      << ",\"recv_wait_lock_time\":" << recv_wait_lock_time << "}";
+      << ",\"recv_wait_lock_time\":" << recv_wait_lock_time << ",\"device_push_ms\":" << device_push_ms
+      << ",\"device_push_bytes\":" << device_push_bytes << ",\"device_push_samples\":" << device_push_samples
+      << ",\"device_push_gb_per_s\":"
+      << (device_push_ms.get() > 0 ? (double)device_push_bytes.get() / (device_push_ms.get() * 1e6) : 0.0) << "}";
     return o.str();
   }
 };

@@ -189,6 +189,9 @@ Plan PlanCompiler::compile() const {
     if (op.type == OP_PRE_UPDATE)
       for (size_t r : op.rows) once = once && write_count[{op.table, r}] <= 1;
     direct_cand[i] = cfg_.allow_direct && gpu && run && once && !op.one_off;
+    // read-my-updates over the update ring: at slack > 0 a read merges the worker's own pending updates into a
+    // private copy, so it cannot alias the cache that the shards write in place
+    if (op.type == OP_READ && cfg_.read_my_writes && cfg_.update_ring && t.slack > 0) direct_cand[i] = 0;
   }
 
   // ---- 4. worker-local batches: resident in GPU memory, or host memory + staging ----

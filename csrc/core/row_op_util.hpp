@@ -61,6 +61,16 @@ inline void add_rows_from_double_index_cpu(RowData* y, const RowData* x, const D
   }
 }
 
+// y[id1 + off1] += alpha * x[id0 + off0]
+inline void axpy_rows_from_double_index_cpu(RowData* y, const RowData* x, const DoubleIndex* index, size_t n,
+                                            size_t off0, size_t off1, size_t num_vals_limit, val_t alpha) {
+  for (size_t i = 0; i < n; ++i) {
+    const size_t xr = index[i].id0 + off0, yr = index[i].id1 + off1;
+    for (size_t v = 0; v < ROW_DATA_SIZE; ++v)
+      if (xr * ROW_DATA_SIZE + v < num_vals_limit) y[yr].data[v] += alpha * x[xr].data[v];
+  }
+}
+
 struct OptimizerParams {
   float lr = 0.01f, momentum = 0.9f, weight_decay = 0.f, grad_scale = 1.f;
 };

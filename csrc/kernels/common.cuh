@@ -29,6 +29,20 @@ enum GeepsKernelId : int {
   KID_GEMM_TC = 20, KID_GEMM_SIMT = 21, KID_PULL_GEMM = 22, KID_CONV_TC = 23,
 };
 
+// Number of SMs of the current device (cudaDevAttrMultiProcessorCount), read once per device and cached:
+// grids are sized from it, never from a literal.
+inline int geeps_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); dev = 0; }
+  int n = cached[dev];
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 148; }
+    cached[dev] = n;
+  }
+  return n;
+}
+
 __device__ __forceinline__ void geeps_report(int* status, int code, int kid, int detail, int seen) {
   if (status == nullptr) return;
   if (atomicCAS(status, 0, code) == 0) {

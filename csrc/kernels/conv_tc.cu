@@ -417,7 +417,7 @@ int geeps_conv_tc_supported(const GeepsConvTcParams* p) {
 
 int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   if (!geeps_conv_tc_supported(p)) return (int)cudaErrorInvalidValue;
-  const int kSMs = 148;
+  const int kSMs = geeps_sm_count();
   cudaStream_t st = (cudaStream_t)stream;
   ConvDev d;
   d.bias = p->mode == MODE_FWD ? p->bias : nullptr;

@@ -89,7 +89,7 @@ int geeps_scale_matrix_f32(float* c, long long M, long long N, long long ldc, fl
   long long total = M * N;
   if (total <= 0) return 0;
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > geeps_sm_count() * 8) blocks = geeps_sm_count() * 8;
   scale_matrix_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(c, M, N, ldc, beta);
   return (int)cudaGetLastError();
 }

@@ -412,7 +412,7 @@ int geeps_gemm_tc_supported(const GeepsGemmParams* p) {
 
 int geeps_gemm_bf16(const GeepsGemmParams* p, void* stream) {
   if (!geeps_gemm_tc_supported(p)) return (int)cudaErrorInvalidValue;
-  const int kSMs = 148;
+  const int kSMs = geeps_sm_count();
   // large K-major products go to CTA pairs (half the B traffic per SM) when 256-row tiles can fill the machine
   if (p->block_n == 0 && p->split_k <= 1 && geeps_gemm_pair_supported(p) &&
       ((p->M + 255) / 256) * ((p->N + 255) / 256) >= kSMs / 2)

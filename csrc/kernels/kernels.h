@@ -26,6 +26,10 @@ int geeps_row_scatter(float* dst, const float* src, const void* index, long long
 int geeps_row_scatter_add(float* dst, const float* src, const void* index, long long num_rows,
                           long long dst_off, long long src_off, long long num_vals_limit,
                           long long dst_rows, long long src_rows, int* status, void* stream);
+// scatter-add with a scale: dst[id1 + dst_off] += alpha * src[id0 + src_off]
+int geeps_row_scatter_axpy(float* dst, const float* src, const void* index, long long num_rows,
+                           long long dst_off, long long src_off, long long num_vals_limit,
+                           long long dst_rows, long long src_rows, float alpha, int* status, void* stream);
 int geeps_axpy(float* y, const float* x, float alpha, long long n, void* stream);
 
 // ---------------- parameter-server fabric ----------------
@@ -67,7 +71,28 @@ typedef struct GeepsFlagList { int* ptr[GEEPS_MAX_RANKS]; int n; } GeepsFlagList
 int geeps_flag_signal(const GeepsFlagList* list, int index, int stamp, void* stream);
 int geeps_flag_wait(const int* flags, int n, int stamp, unsigned long long budget_ns, int* status,
                     void* stream);
+// wait as geeps_flag_wait, then write `stamp` into slot `index` of each array of `then` (skipped when the wait
+// expired): the shard's "publish of this clock begins" mark on every worker
+int geeps_flag_wait_signal(const int* flags, int n, int stamp, unsigned long long budget_ns, int* status,
+                           const GeepsFlagList* then, int index, void* stream);
 int geeps_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+
+// Read with read-my-updates on the NVLINK transport: dst[id0] = cache[id1] + alpha * (sum of this worker's own ring
+// slots whose clock the owning shard has not published yet).  Per row the owning shard's data_age stamp is read
+// before and its publish_begin stamp after the copy; if a publish started in between, the row is read again
+// (bounded; an exhausted budget reports GEEPS_ERR_TIMEOUT).  ring holds ring_slots copies of the table
+// ([slot][total_rows][128], slot of clock k = k % ring_slots); clock is the reader's clock.
+typedef struct GeepsRmwReadParams {
+  float* dst; const float* cache; const float* ring; const void* index;
+  const int* data_age; const int* publish_begin;   // local flag arrays [n_ranks]
+  int* status;
+  long long num_rows, num_vals_limit, dst_rows, total_rows;
+  unsigned long long wait_budget_ns;
+  int n_ranks, partition_kind, ring_slots, clock;
+  int additive_below_clock;   // own updates of clocks below this are added as they are (initial values), not scaled
+  float alpha;
+} GeepsRmwReadParams;
+int geeps_row_gather_rmw(const GeepsRmwReadParams* p, void* stream);
 
 // ---------------- GEMM (bf16 x bf16 -> fp32 accumulate) ----------------
 // C[M,N] = alpha * A[M,K] * B[N,K]^T + beta * C + bias, optional ReLU.

@@ -34,7 +34,8 @@ inline dim3 pool_block(int cv) {
   return dim3(bx, by < 1 ? 1 : by, 1);
 }
 
-inline int grid_1d(long long n, int block = 256, int cap = 148 * 16) {
+inline int grid_1d(long long n, int block = 256, int cap = 0) {
+  if (cap <= 0) cap = geeps_sm_count() * 16;
   long long b = (n + block - 1) / block;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
@@ -983,7 +984,7 @@ int geeps_col2im(const void* dcol, void* dx, const GeepsConvGeom* g, int accumul
 
 static int reduce_grid(long long P, int C) {
   long long want = (P * (C / 8) + 255) / 256;
-  if (want > 148 * 4) want = 148 * 4;
+  if (want > geeps_sm_count() * 4) want = geeps_sm_count() * 4;
   long long min_blocks = ((long long)(C / 8) + 255) / 256;
   if (want < min_blocks) want = min_blocks;
   return (int)(want < 1 ? 1 : want);

@@ -32,14 +32,19 @@ __device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
 
 // Grid-wide "last CTA" rendezvous: returns true in exactly one CTA (thread 0 of it),
 // after every CTA's prior global/peer stores are visible system-wide.
-__device__ __forceinline__ bool last_cta_arrive(int* counter) {
+// `failed` CTAs (an expired in-kernel wait: their rows were skipped) add a high bit to the counter, and
+// *any_failed tells the last CTA whether any CTA of the launch did, so that it never stamps a clock that
+// was not applied everywhere.
+constexpr int kCtaFailBit = 1 << 20;
+__device__ __forceinline__ bool last_cta_arrive(int* counter, bool failed = false, bool* any_failed = nullptr) {
   __syncthreads();
   bool last = false;
   if (threadIdx.x == 0) {
     __threadfence_system();
-    int prev = atomicAdd(counter, 1);
-    if (prev == (int)gridDim.x - 1) {
+    const int prev = atomicAdd(counter, 1 + (failed ? kCtaFailBit : 0));
+    if ((prev & (kCtaFailBit - 1)) == (int)gridDim.x - 1) {
       __threadfence_system();
+      if (any_failed) *any_failed = failed || prev >= kCtaFailBit;
       *counter = 0;  // ready for the next launch on this stream
       last = true;
     }
@@ -125,8 +130,9 @@ push_apply_kernel(const GeepsPushApplyParams p) {
     }
   }
   // ---- stamp: rows (or at least the master) are globally visible ----
-  if (last_cta_arrive(p.cta_counter)) {
-    if (ok) {
+  bool any_failed = false;
+  if (last_cta_arrive(p.cta_counter, !ok, &any_failed)) {
+    if (!any_failed) {
       if (p.global_clock != nullptr) st_release_sys(p.global_clock, p.clock_stamp);
       if (p.publish)
         for (int q = 0; q < p.n_ranks; ++q)
@@ -199,6 +205,89 @@ __global__ void flag_wait_kernel(const int* flags, int n, int stamp, unsigned lo
   }
 }
 
+// The same wait, followed (on success) by a stamp into slot `index` of each listed array.
+__global__ void flag_wait_signal_kernel(const int* flags, int n, int stamp, unsigned long long budget_ns,
+                                        int* status, GeepsFlagList then, int index) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if ((int)threadIdx.x < n) {
+    int seen = 0;
+    if (!geeps_wait_ge(flags + threadIdx.x, stamp, budget_ns, &seen)) {
+      geeps_report(status, GEEPS_ERR_TIMEOUT, KID_FLAG_WAIT, (int)threadIdx.x, seen);
+      s_fail = 1;
+    }
+  }
+  __syncthreads();
+  if (!s_fail && (int)threadIdx.x < then.n && then.ptr[threadIdx.x] != nullptr) {
+    st_release_sys(then.ptr[threadIdx.x] + index, stamp);
+    __threadfence_system();
+  }
+}
+
+// Gather with read-my-updates (see kernels.h).  One warp per row; the row's owning shard follows from the
+// partitioning (range: idx / ceil(rows / shards); round robin: idx % shards).
+__global__ void __launch_bounds__(256)
+row_gather_rmw_kernel(const GeepsRmwReadParams p) {
+  struct __align__(16) IndexPair { long long id0; long long id1; };
+  const IndexPair* index = static_cast<const IndexPair*>(p.index);
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const long long per = (p.total_rows + p.n_ranks - 1) / p.n_ranks;
+  for (long long i = warp0; i < p.num_rows; i += nwarps) {
+    IndexPair ip;
+    if (lane == 0) ip = index[i];
+    ip.id0 = __shfl_sync(0xffffffffu, ip.id0, 0);
+    ip.id1 = __shfl_sync(0xffffffffu, ip.id1, 0);
+    if (ip.id0 < 0 || ip.id0 >= p.dst_rows || ip.id1 < 0 || ip.id1 >= p.total_rows) {
+      if (lane == 0) geeps_report(p.status, GEEPS_ERR_BOUNDS, KID_ROW_GATHER, (int)i, (int)(ip.id1));
+      continue;
+    }
+    const long long app_val0 = ip.id0 * GEEPS_ROW_FLOATS + lane * 4;
+    const int shard = p.partition_kind == 1 ? (int)(ip.id1 % p.n_ranks) : (int)(per ? ip.id1 / per : 0);
+    const float* src = p.cache + ip.id1 * GEEPS_ROW_FLOATS + lane * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool done = false;
+    // the flag words are read by lane 0 and broadcast, so that the whole warp takes the same decisions
+    for (int attempt = 0; attempt < 16 && !done; ++attempt) {
+      // stamp = (latest clock the shard has published) + 1; own clocks stamp .. clock-1 are still missing
+      int age = 0;
+      if (lane == 0) age = ld_acquire_sys(p.data_age + shard);
+      age = __shfl_sync(0xffffffffu, age, 0);
+      v = ld_f4_peer(src);
+      int first = age > p.clock - (p.ring_slots - 1) ? age : p.clock - (p.ring_slots - 1);
+      if (first < 0) first = 0;
+      for (int k = first; k < p.clock; ++k) {
+        const float a = k < p.additive_below_clock ? 1.f : p.alpha;
+        const float4 u = ld_f4_cg(p.ring + ((long long)(k % p.ring_slots) * p.total_rows + ip.id1) * GEEPS_ROW_FLOATS + lane * 4);
+        v.x += a * u.x; v.y += a * u.y; v.z += a * u.z; v.w += a * u.w;
+      }
+      __threadfence_system();
+      int begun = 0, waited_ok = 1;
+      if (lane == 0) {
+        begun = ld_acquire_sys(p.publish_begin + shard);
+        // a publish started while the row was being read: wait for it to complete, then read again
+        if (begun > age) { int seen = 0; waited_ok = geeps_wait_ge(p.data_age + shard, begun, p.wait_budget_ns, &seen) ? 1 : 0; }
+      }
+      begun = __shfl_sync(0xffffffffu, begun, 0);
+      waited_ok = __shfl_sync(0xffffffffu, waited_ok, 0);
+      if (begun <= age) done = true;
+      else if (!waited_ok) break;
+    }
+    if (!done) {
+      if (lane == 0) geeps_report(p.status, GEEPS_ERR_TIMEOUT, KID_ROW_GATHER, shard, (int)i);
+      continue;
+    }
+    float* d = p.dst + app_val0;
+    if (app_val0 + 4 <= p.num_vals_limit) st_f4(d, v);
+    else {
+      const float e[4] = {v.x, v.y, v.z, v.w};
+      for (int j = 0; j < 4 && app_val0 + j < p.num_vals_limit; ++j) d[j] = e[j];
+    }
+  }
+}
+
 // fp32 rows -> bf16 compute copy (local refresh of the compute cache)
 __global__ void __launch_bounds__(256)
 f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
@@ -216,7 +305,7 @@ f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ ds
 
 int pick_grid(long long rows, int max_ctas) {
   long long blocks = (rows + 7) / 8;
-  if (max_ctas <= 0) max_ctas = 148 * 4;
+  if (max_ctas <= 0) max_ctas = geeps_sm_count() * 4;
   if (blocks > max_ctas) blocks = max_ctas;
   if (blocks < 1) blocks = 1;
   return (int)blocks;
@@ -229,7 +318,8 @@ extern "C" {
 int geeps_ps_push_apply(const GeepsPushApplyParams* params, int max_ctas, void* stream) {
   const GeepsPushApplyParams& p = *params;
   if (p.n_ranks < 1 || p.n_ranks > GEEPS_MAX_RANKS) return (int)cudaErrorInvalidValue;
-  const int grid = pick_grid(p.n_owned, max_ctas);
+  int grid = pick_grid(p.n_owned, max_ctas);
+  if (grid >= kCtaFailBit) grid = kCtaFailBit - 1;
   cudaStream_t st = (cudaStream_t)stream;
   switch (p.n_ranks) {
     case 1: push_apply_kernel<1><<<grid, 256, 0, st>>>(p); break;
@@ -262,10 +352,25 @@ int geeps_flag_wait(const int* flags, int n, int stamp, unsigned long long budge
   return (int)cudaGetLastError();
 }
 
+int geeps_flag_wait_signal(const int* flags, int n, int stamp, unsigned long long budget_ns, int* status,
+                           const GeepsFlagList* then, int index, void* stream) {
+  if (n > 32 || then->n > 32) return (int)cudaErrorInvalidValue;
+  flag_wait_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n, stamp, budget_ns, status, *then, index);
+  return (int)cudaGetLastError();
+}
+
+int geeps_row_gather_rmw(const GeepsRmwReadParams* params, void* stream) {
+  const GeepsRmwReadParams& p = *params;
+  if (p.num_rows <= 0) return 0;
+  if (p.n_ranks < 1 || p.n_ranks > GEEPS_MAX_RANKS || p.ring_slots < 1) return (int)cudaErrorInvalidValue;
+  row_gather_rmw_kernel<<<pick_grid(p.num_rows, geeps_sm_count() * 8), 256, 0, (cudaStream_t)stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
 int geeps_f32_to_bf16(const float* src, void* dst, long long n, void* stream) {
   if (n <= 0) return 0;
   long long blocks = ((n >> 2) + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > geeps_sm_count() * 8) blocks = geeps_sm_count() * 8;
   if (blocks < 1) blocks = 1;
   f32_to_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(src, (__nv_bfloat16*)dst, n);
   return (int)cudaGetLastError();

@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(256)
 row_op_kernel(float* __restrict__ dst, const float* __restrict__ src,
               const IndexPair* __restrict__ index, long long num_rows,
               long long dst_off, long long src_off, long long num_vals_limit,
-              long long dst_rows, long long src_rows, int* status) {
+              long long dst_rows, long long src_rows, int* status, float alpha) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
@@ -57,12 +57,12 @@ row_op_kernel(float* __restrict__ dst, const float* __restrict__ src,
       float4 v = ld_f4(s);
       if (KIND == ROW_SCATTER_ADD) {
         float4 o = ld_f4(d);
-        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+        v.x = o.x + alpha * v.x; v.y = o.y + alpha * v.y; v.z = o.z + alpha * v.z; v.w = o.w + alpha * v.w;
       }
       st_f4(d, v);
     } else {  // ragged tail of the limit
       for (int e = 0; e < 4 && app_val0 + e < num_vals_limit; ++e) {
-        if (KIND == ROW_SCATTER_ADD) d[e] += s[e]; else d[e] = s[e];
+        if (KIND == ROW_SCATTER_ADD) d[e] += alpha * s[e]; else d[e] = s[e];
       }
     }
   }
@@ -86,7 +86,7 @@ axpy_kernel(float* __restrict__ y, const float* __restrict__ x, float alpha, lon
 
 inline int grid_for_rows(long long rows, int warps_per_block) {
   long long blocks = (rows + warps_per_block - 1) / warps_per_block;
-  const long long cap = 148LL * 8;  // 8 resident 256-thread CTAs per SM on 148 SMs
+  const long long cap = (long long)geeps_sm_count() * 8;  // 8 resident 256-thread CTAs per SM
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return (int)blocks;
@@ -95,11 +95,11 @@ inline int grid_for_rows(long long rows, int warps_per_block) {
 template <int KIND>
 int launch_row_op(float* dst, const float* src, const void* index, long long num_rows,
                   long long dst_off, long long src_off, long long num_vals_limit,
-                  long long dst_rows, long long src_rows, int* status, cudaStream_t stream) {
+                  long long dst_rows, long long src_rows, int* status, cudaStream_t stream, float alpha = 1.f) {
   if (num_rows <= 0) return 0;
   row_op_kernel<KIND><<<grid_for_rows(num_rows, 8), 256, 0, stream>>>(
       dst, src, static_cast<const IndexPair*>(index), num_rows, dst_off, src_off, num_vals_limit,
-      dst_rows, src_rows, status);
+      dst_rows, src_rows, status, alpha);
   return (int)cudaGetLastError();
 }
 
@@ -126,10 +126,17 @@ int geeps_row_scatter_add(float* dst, const float* src, const void* index, long 
                                         num_vals_limit, dst_rows, src_rows, status,
                                         (cudaStream_t)stream);
 }
+int geeps_row_scatter_axpy(float* dst, const float* src, const void* index, long long num_rows,
+                           long long dst_off, long long src_off, long long num_vals_limit,
+                           long long dst_rows, long long src_rows, float alpha, int* status, void* stream) {
+  return launch_row_op<ROW_SCATTER_ADD>(dst, src, index, num_rows, dst_off, src_off,
+                                        num_vals_limit, dst_rows, src_rows, status,
+                                        (cudaStream_t)stream, alpha);
+}
 int geeps_axpy(float* y, const float* x, float alpha, long long n, void* stream) {
   if (n <= 0) return 0;
   long long blocks = ((n >> 2) + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > geeps_sm_count() * 8) blocks = geeps_sm_count() * 8;
   if (blocks < 1) blocks = 1;
   axpy_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(y, x, alpha, n);
   return (int)cudaGetLastError();

@@ -17,6 +17,9 @@
 
 namespace geeps_b200 {
 
+namespace { constexpr uint64_t kMaxFrameBytes = 1ull << 34; }   // 16 GiB: above any table shard
+
+
 namespace {
 
 bool write_all(int fd, const void* buf, size_t n) {
@@ -186,6 +189,9 @@ void RouterHandler::reader_loop(std::shared_ptr<Conn> c) {
     if (nframes && !read_all(c->fd, lens.data(), nframes * 8)) break;
     Message msg(nframes);
     bool ok = true;
+    // a length no sender of this protocol produces (the largest frame is one table shard) is treated as a
+    // corrupt or hostile stream: the peer is dropped instead of the allocation being attempted
+    for (size_t i = 0; i < nframes && ok; ++i) ok = lens[i] <= kMaxFrameBytes;
     for (size_t i = 0; i < nframes && ok; ++i) {
       msg[i].resize(lens[i]);
       ok = lens[i] == 0 || read_all(c->fd, msg[i].data(), lens[i]);

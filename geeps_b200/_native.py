@@ -8,6 +8,7 @@ not on a machine that received the prebuilt .so).
 from __future__ import annotations
 
 import ctypes
+import fcntl
 import hashlib
 import os
 import shutil
@@ -72,46 +73,68 @@ def is_built() -> bool:
 
 
 def build(verbose: bool = False, force: bool = False) -> Path:
-    """Compile every .cu/.cpp under csrc/ for sm_100a and link lib/libgeeps_b200.so."""
+    """Compile every .cu/.cpp under csrc/ for sm_100a and link lib/libgeeps_b200.so.
+
+    Several processes may get here at once (one rank per GPU, test workers): a file lock serialises them, the
+    check is repeated under the lock, and the library and its stamp are moved into place atomically, so no
+    process ever loads a half-written file."""
     with _lock:
         if is_built() and not force:
             return lib_path()
-        cuda = _cuda_home()
         BUILD_DIR.mkdir(parents=True, exist_ok=True)
         LIB_DIR.mkdir(parents=True, exist_ok=True)
-        inc = [f"-I{CSRC}", f"-I{ROOT / 'include'}", f"-I{cuda / 'include'}"]
-        lines = [
-            f"nvcc = {cuda / 'bin' / 'nvcc'}",
-            "cxx = g++",
-            f"nvflags = {' '.join(NVCC_FLAGS)} {' '.join(inc)}",
-            f"cxxflags = {' '.join(CXX_FLAGS)} {' '.join(inc)}",
-            "rule nvcc",
-            "  command = $nvcc $nvflags -MD -MF $out.d -c $in -o $out > $out.log 2>&1 || (cat $out.log; false)",
-            "  depfile = $out.d",
-            "  deps = gcc",
-            "rule cxx",
-            "  command = $cxx $cxxflags -MD -MF $out.d -c $in -o $out",
-            "  depfile = $out.d",
-            "  deps = gcc",
-            "rule link",
-            f"  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt",
-        ]
-        objs = []
-        for src in sources():
-            obj = BUILD_DIR / (str(src.relative_to(CSRC)).replace("/", "_") + ".o")
-            rule = "nvcc" if src.suffix == ".cu" else "cxx"
-            lines.append(f"build {obj}: {rule} {src}")
-            objs.append(str(obj))
-        lines.append(f"build {lib_path()}: link {' '.join(objs)}")
-        lines.append(f"default {lib_path()}")
-        (BUILD_DIR / "build.ninja").write_text("\n".join(lines) + "\n")
-        cmd = ["ninja", "-C", str(BUILD_DIR)] + (["-v"] if verbose else [])
-        proc = subprocess.run(cmd, capture_output=True, text=True)
-        if proc.returncode != 0:
-            sys.stderr.write(proc.stdout[-8000:] + proc.stderr[-4000:])
-            raise RuntimeError("native build failed")
-        (LIB_DIR / (LIB_NAME + ".hash")).write_text(source_hash())
-        return lib_path()
+        with open(BUILD_DIR / ".lock", "w") as lock_file:
+            fcntl.flock(lock_file, fcntl.LOCK_EX)
+            try:
+                if is_built() and not force:
+                    return lib_path()
+                return _build_locked(verbose)
+            finally:
+                fcntl.flock(lock_file, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
+    cuda = _cuda_home()
+    inc = [f"-I{CSRC}", f"-I{ROOT / 'include'}", f"-I{cuda / 'include'}"]
+    lines = [
+        f"nvcc = {cuda / 'bin' / 'nvcc'}",
+        "cxx = g++",
+        f"nvflags = {' '.join(NVCC_FLAGS)} {' '.join(inc)}",
+        f"cxxflags = {' '.join(CXX_FLAGS)} {' '.join(inc)}",
+        "rule nvcc",
+        "  command = $nvcc $nvflags -MD -MF $out.d -c $in -o $out > $out.log 2>&1 || (cat $out.log; false)",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule cxx",
+        "  command = $cxx $cxxflags -MD -MF $out.d -c $in -o $out",
+        "  depfile = $out.d",
+        "  deps = gcc",
+        "rule link",
+        f"  command = $nvcc -shared -o $out $in -cudart static -lpthread -ldl -lrt",
+    ]
+    staged = BUILD_DIR / (LIB_NAME + ".new")
+    objs = []
+    for src in sources():
+        obj = BUILD_DIR / (str(src.relative_to(CSRC)).replace("/", "_") + ".o")
+        rule = "nvcc" if src.suffix == ".cu" else "cxx"
+        lines.append(f"build {obj}: {rule} {src}")
+        objs.append(str(obj))
+    lines.append(f"build {staged}: link {' '.join(objs)}")
+    lines.append(f"default {staged}")
+    (BUILD_DIR / "build.ninja").write_text("\n".join(lines) + "\n")
+    cmd = ["ninja", "-C", str(BUILD_DIR)] + (["-v"] if verbose else [])
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout[-8000:] + proc.stderr[-4000:])
+        raise RuntimeError("native build failed")
+    # ninja considers `staged` up to date next time only if it still exists: install a copy
+    tmp_lib = LIB_DIR / (LIB_NAME + f".tmp{os.getpid()}")
+    shutil.copy2(staged, tmp_lib)
+    os.replace(tmp_lib, lib_path())
+    tmp_hash = LIB_DIR / (LIB_NAME + f".hash.tmp{os.getpid()}")
+    tmp_hash.write_text(source_hash())
+    os.replace(tmp_hash, LIB_DIR / (LIB_NAME + ".hash"))
+    return lib_path()
 
 
 def ptxas_report() -> str:

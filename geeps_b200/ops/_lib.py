@@ -77,6 +77,17 @@ class PullGemmParams(C.Structure):
     ]
 
 
+class RmwReadParams(C.Structure):
+    _fields_ = [
+        ("dst", C.c_void_p), ("cache", C.c_void_p), ("ring", C.c_void_p), ("index", C.c_void_p),
+        ("data_age", C.c_void_p), ("publish_begin", C.c_void_p), ("status", C.c_void_p),
+        ("num_rows", C.c_longlong), ("num_vals_limit", C.c_longlong), ("dst_rows", C.c_longlong),
+        ("total_rows", C.c_longlong), ("wait_budget_ns", C.c_ulonglong),
+        ("n_ranks", C.c_int), ("partition_kind", C.c_int), ("ring_slots", C.c_int), ("clock", C.c_int),
+        ("additive_below_clock", C.c_int), ("alpha", C.c_float),
+    ]
+
+
 class FlagList(C.Structure):
     _fields_ = [("ptr", C.c_void_p * MAX_RANKS), ("n", C.c_int)]
 

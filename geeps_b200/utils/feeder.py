@@ -7,11 +7,14 @@ import torch
 
 
 class HostFeeder:
-    def __init__(self, x_shape, y_shape, device, depth: int = 2, x_dtype=torch.float32):
+    def __init__(self, x_shape, y_shape, device, depth: int = 2, x_dtype=torch.float32, timed: bool = False):
         """x_dtype: dtype of the batches on the host and in the device slots (fp32, or bf16 to halve the
-        host-to-device bytes; the input layer converts either to bf16 NHWC)."""
+        host-to-device bytes; the input layer converts either to bf16 NHWC).  timed: bracket every copy with
+        timing events on the copy stream (copy_times_ms() returns their durations)."""
         self.device = torch.device(device)
         self.copy_stream = torch.cuda.Stream(device=self.device)
+        self.timed = timed
+        self._timing = []          # (begin, end) event pairs of submitted copies
         self.x = [torch.empty(x_shape, dtype=x_dtype, device=self.device) for _ in range(depth)]
         self.y = [torch.empty(y_shape, dtype=torch.int64, device=self.device) for _ in range(depth)]
         self.ready = [torch.cuda.Event() for _ in range(depth)]
@@ -26,10 +29,28 @@ class HostFeeder:
         s = self.put_i % self.depth
         self.copy_stream.wait_event(self.free[s])      # the step that used this slot has finished with it
         with torch.cuda.stream(self.copy_stream):
+            if self.timed:
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(self.copy_stream)
             self.x[s].copy_(x_host, non_blocking=True)
             self.y[s].copy_(y_host, non_blocking=True)
+            if self.timed:
+                t1.record(self.copy_stream)
+                self._timing.append((t0, t1))
             self.ready[s].record(self.copy_stream)
         self.put_i += 1
+
+    def copy_times_ms(self, clear: bool = True) -> list:
+        """Device time of every completed copy submitted since the last call (needs timed=True)."""
+        out, keep = [], []
+        for t0, t1 in self._timing:
+            if t1.query():
+                out.append(t0.elapsed_time(t1))
+            else:
+                keep.append((t0, t1))
+        if clear:
+            self._timing = keep
+        return out
 
     def next(self, stream=None):
         """Device tensors of the oldest submitted batch; `stream` waits for its copy."""

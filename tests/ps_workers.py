@@ -377,3 +377,51 @@ def nvlink_leave_worker(rank, world, base_port, q, kw):
             os._exit(0)
     except Exception as e:  # pragma: no cover
         q.put((rank, "exception", repr(e) + traceback.format_exc(), 0.0, False))
+
+
+def rmw_worker(rank, world, base_port, mode, rmw, q, kw):
+    """Read-my-updates at slack 1 with a lagging peer.  Rank 1 sleeps before its update of clock 1; rank 0 reads in
+    clock 2 (admitted on the bootstrap data alone) and reports what it sees of its own clock-1 update.  Afterwards
+    both ranks run to the end and return the fully applied table (a slack-0 read declared after the Clock)."""
+    try:
+        import time
+        import torch
+        from geeps_b200.parallel.ps import GeePs
+        from geeps_b200.utils.config import DEVICE_CPU, TABLE_SGD_MOMENTUM
+        kw = dict(kw)
+        kw.setdefault("device", DEVICE_CPU)
+        cfg = make_cfg(world, base_port, read_my_writes=rmw, table_mode=mode, learning_rate=0.1, momentum=0.9,
+                       weight_decay=0.0, grad_scale=1.0, **kw)
+        g = GeePs(rank, cfg)
+        rows = list(range(48))
+        r = g.virtual_read(0, rows, 1)
+        u = g.virtual_pre_update(0, rows)
+        pr = g.virtual_post_read(r)
+        up = g.virtual_update(u)
+        g.virtual_clock()
+        r0 = g.virtual_read(0, rows, 0)        # after the Clock: a one-off read with slack 0 (everything applied)
+        g.virtual_post_read(r0)
+        g.finish_virtual_iteration()
+        g.pre_update(u).fill_(0.5)             # initial value 0.5 per worker (bootstrap updates always add)
+        g.update(up)
+        g.clock()
+        g.start_iterations()
+        seen = []
+        for c in range(1, 6):                  # clocks 1..5, every worker contributes 1.0 per element per clock
+            if rank == 1 and c == 1:
+                time.sleep(2.5)
+            x = g.read(r, asynchronous=False)
+            seen.append((g.clock_value, float(x.min()), float(x.max())))
+            b = g.pre_update(u)
+            g.post_read(pr)
+            b.fill_(1.0)
+            g.update(up)
+            g.clock()
+        final = g.read(r0, asynchronous=False)
+        out = (float(final.min()), float(final.max()))
+        stats = g.get_stats()
+        g.shutdown()
+        g.close()
+        q.put((rank, "ok", out, seen, stats["bgthread"]["nr_rmw_replay"], None))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))

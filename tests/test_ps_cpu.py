@@ -11,7 +11,7 @@ import torch
 from geeps_b200.parallel.ps import GeePs, GeePsError
 from geeps_b200.utils.config import (DEVICE_CPU, PARTITION_ROUND_ROBIN, TABLE_SGD_MOMENTUM, GeePsConfig)
 
-from ps_workers import helloworld_worker
+from ps_workers import helloworld_worker, rmw_worker
 
 _port = [12000 + (os.getpid() % 300) * 40]   # below the ephemeral port range
 
@@ -66,7 +66,55 @@ def test_round_robin_partition_and_read_my_writes():
     out = _run_hello(2, 1, 20, partitioner=PARTITION_ROUND_ROBIN, read_my_writes=1)
     for rank, _, final, seen, max_stale, stats in out:
         assert final == (40.0, 40.0)
-        assert stats["bgthread"]["nr_rmw_replay"] >= 0
+
+
+def _run_rmw(mode, rmw):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = next_port()
+    procs = [ctx.Process(target=rmw_worker, args=(r, 2, port, mode, rmw, q, {})) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for o in out:
+        assert o[1] == "ok", o[2]
+    return sorted(out)
+
+
+@pytest.mark.parametrize("rmw", [0, 1])
+def test_read_my_updates_additive_with_lagging_peer(rmw):
+    """Slack 1, two workers, rank 1 lags before its clock-1 update.  Rank 0's read in clock 2 is admitted on the
+    bootstrap data; with read-my-writes it must already contain rank 0's own +1 of clock 1, without it must not
+    (the shards cannot have published clock 1 before the lagging worker signalled it)."""
+    out = _run_rmw(0, rmw)
+    rank0 = out[0]
+    by_clock = {c: (lo, hi) for c, lo, hi in rank0[3]}
+    assert by_clock[1] == (1.0, 1.0)                       # initial value only
+    if rmw:
+        assert by_clock[2] == (2.0, 2.0), by_clock         # initial value + own update of clock 1
+    else:
+        assert by_clock[2] == (1.0, 1.0), by_clock
+    for o in out:
+        assert o[2] == (11.0, 11.0)                        # 1.0 + 5 clocks x 2 workers, fully applied
+
+
+def test_read_my_updates_optimizer_table_is_provisional_and_converges():
+    """Momentum-SGD table with read-my-writes: the worker's view of its own pending gradient is the plain step
+    -lr * g on top of the last published rows; once the shard has stepped, the published rows replace it and the
+    final table equals the CPU oracle (the raw gradient is never added to the weights)."""
+    out = _run_rmw(TABLE_SGD_MOMENTUM, 1)
+    by_clock = {c: (lo, hi) for c, lo, hi in out[0][3]}
+    assert by_clock[1] == (1.0, 1.0)
+    lo, hi = by_clock[2]
+    assert abs(lo - 0.9) < 1e-6 and abs(hi - 0.9) < 1e-6, by_clock     # 1.0 - 0.1 * own gradient of 1.0
+    p, v = 1.0, 0.0
+    for _ in range(5):                                     # five clocks, summed gradient 2.0
+        v = 0.9 * v + 0.1 * 2.0
+        p -= v
+    for o in out:
+        assert abs(o[2][0] - p) < 1e-4 and abs(o[2][1] - p) < 1e-4, (o[2], p)
 
 
 def _single(cfg_kw, rows=(0, 1, 2, 3)):

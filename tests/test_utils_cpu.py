@@ -68,3 +68,45 @@ def test_bind_to_gpu_cores_is_harmless_without_a_gpu():
     else:
         assert set(cores) == after and after <= before
         os.sched_setaffinity(0, before)
+
+
+def test_affinity_splits_a_mask_shared_by_all_gpus():
+    """A fake NVML reports the same 32-core mask for eight GPUs (a one-node virtual machine): the eight ranks get
+    disjoint slices; distinct masks are left alone."""
+    import os
+    from geeps_b200.utils import affinity
+
+    class FakeNvml:
+        def __init__(self, masks):
+            self.masks = masks
+
+        def nvmlInit(self): pass
+        def nvmlShutdown(self): pass
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetCpuAffinity(self, h, words):
+            return [self.masks[h]] + [0] * (words - 1)
+
+    assert affinity.split_shared_mask(list(range(32)), 8, 3) == [12, 13, 14, 15]
+    assert affinity.split_shared_mask(list(range(3)), 8, 3) == [0, 1, 2]
+    slices = [affinity.split_shared_mask(list(range(30)), 8, k) for k in range(8)]
+    assert sorted(c for s in slices for c in s) == list(range(30))
+    allowed = sorted(os.sched_getaffinity(0))
+    before = os.sched_getaffinity(0)
+    try:
+        mask = sum(1 << c for c in allowed if c < 64)
+        n = len([c for c in allowed if c < 64])
+        world = 2 if n >= 2 else 1
+        got = []
+        for k in range(world):      # one process plays both ranks: undo the binding in between
+            got.append(affinity.bind_to_gpu_cores(k, world, nvml=FakeNvml([mask] * 8)))
+            os.sched_setaffinity(0, before)
+        if world == 2:
+            assert not set(got[0]) & set(got[1]) and sorted(got[0] + got[1]) == [c for c in allowed if c < 64]
+        os.sched_setaffinity(0, before)
+        # different masks per GPU: each rank keeps its own
+        if n >= 2:
+            a, b = allowed[0], allowed[1]
+            got = affinity.bind_to_gpu_cores(1, 2, nvml=FakeNvml([1 << a, 1 << b] + [0] * 6))
+            assert got == [b]
+    finally:
+        os.sched_setaffinity(0, before)
