@@ -86,10 +86,14 @@ class GeePs:
         return self._l.geeps_last_error(self._g)
 
     def _string(self, fn) -> str:
-        need = fn(self._g, None, 0)
-        buf = C.create_string_buffer(need + 16)
-        fn(self._g, buf, need + 16)
-        return buf.value.decode()
+        # the text may differ from one call to the next (counters grow): never size the buffer from an earlier call
+        cap = 1 << 16
+        while True:
+            buf = C.create_string_buffer(cap)
+            need = fn(self._g, buf, cap)
+            if need <= cap:
+                return buf.value.decode()
+            cap = need + 4096
 
     def last_error_string(self) -> str:
         return self._string(self._l.geeps_last_error_string)
