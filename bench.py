@@ -128,6 +128,8 @@ def main() -> None:
                     help="also refresh the workers' fp32 copies of the weights every clock (the layers read bf16 only)")
     ap.add_argument("--no-tape", action="store_true",
                     help="re-run the Python layer code every step instead of replaying the recorded native calls")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="replay the recorded native calls one launch at a time instead of one CUDA graph per step")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -175,7 +177,8 @@ def main() -> None:
     with torch.cuda.stream(stream):
         mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=args.slack, seed=1,
                        manage_activations=args.cache_frac is not None, cache_fraction=args.cache_frac,
-                       use_tape=not args.no_tape, bf16_weights_only=not args.fp32_weight_cache)
+                       use_tape=not args.no_tape, bf16_weights_only=not args.fp32_weight_cache,
+                       use_graph=not (args.no_graph or args.no_tape) and args.transport == "nvlink")
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
         in_dtype = torch.bfloat16 if args.input_dtype == "bf16" else torch.float32
         x_dev = torch.randn((B,) + image, device=dev, generator=gen).to(in_dtype)
@@ -244,9 +247,17 @@ def main() -> None:
                 return loss
             return step_e2e
 
-        def e2e_record(step_fn, feeder):
-            for _ in range(2):
+        def settle(step_fn, probe, limit=48):
+            """Untimed steps until the step is replayed from its recording / captured graph for every buffer."""
+            n = quiet = 0
+            while n < limit and quiet < 2:
+                quiet = quiet + 1 if probe() else 0
                 step_fn()
+                n += 1
+            return n
+
+        def e2e_record(step_fn, feeder):
+            settle(step_fn, lambda: mod.is_steady(feeder.x[feeder.get_i % feeder.depth], feeder.y[feeder.get_i % feeder.depth]))
             feeder.copy_times_ms()
             blocks, _, _, _ = timed(step_fn, args.steps, args.repeats)
             med = statistics.median(blocks)
@@ -262,6 +273,7 @@ def main() -> None:
 
         for _ in range(max(args.warmup, 3)):
             step_device()
+        settle(step_device, lambda: mod.is_steady(x_dev, y_dev))
         blocks, clocks, launches, last_loss = timed(step_device, args.steps, args.repeats)
         ms = statistics.median(blocks)
         # host time to enqueue one step (tape replay + runtime calls) with an empty launch queue: when it
@@ -314,7 +326,8 @@ def main() -> None:
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
                            "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack, "input_dtype": args.input_dtype, "cpu_cores_bound": len(cores) if cores else 0,
                            "weight_publish": "bf16+fp32" if args.fp32_weight_cache else "bf16 (biases / BN fp32)",
-                           "host_replay_tapes": len(mod._tapes),
+                           "host_replay_tapes": len(mod._tapes), "step_graphs": len(mod._graphs),
+                           "graph_nodes": max([g.nodes for g in mod._graphs.values()] + [0]),
                            "tables": "fp32 master rows, momentum SGD on the owning shard",
                            "l2": "no explicit flush: per step the input batch (79 MB bf16 / 158 MB fp32), the activations "
                                  "(conv1 output alone 148 MB) and 122 MB of bf16 weights exceed the 126 MB L2"},

@@ -1,5 +1,6 @@
 // Flat C API over the C++ runtime for the Python layer (ctypes) and for tests: the GeePs facade,
 // the stand-alone plan compiler, the partitioner, the allocators and the host row-op oracle.
+#include <cuda_runtime.h>
 #include <string.h>
 
 #include <string>
@@ -138,6 +139,33 @@ void geeps_post_local_access(void* g, int handle, void* stream) {
 }
 void geeps_clock(void* g) { static_cast<GeePs*>(g)->Clock(); }
 void* geeps_read_bf16(void* g, int handle) { return static_cast<GeePs*>(g)->ReadBf16(handle); }
+int geeps_enable_device_clock(void* g) { return static_cast<GeePs*>(g)->EnableDeviceClock() ? 1 : 0; }
+void geeps_advance_replayed_clock(void* g) { static_cast<GeePs*>(g)->AdvanceReplayedClock(); }
+const void* geeps_device_clock_ptr(void* g) { return static_cast<GeePs*>(g)->DeviceClockPtr(); }
+
+// ---- CUDA graph helpers: capture what is enqueued on `stream` (and on every stream that joins it through
+// events) between begin and end, instantiate it, replay it ----
+int geeps_graph_begin(void* stream) {
+  return (int)cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeRelaxed);
+}
+int geeps_graph_end(void* stream, void** exec_out, long long* num_nodes) {
+  *exec_out = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture((cudaStream_t)stream, &graph);
+  if (e != cudaSuccess || graph == nullptr) { cudaGetLastError(); return e != cudaSuccess ? (int)e : (int)cudaErrorUnknown; }
+  size_t n = 0;
+  cudaGraphGetNodes(graph, nullptr, &n);
+  if (num_nodes) *num_nodes = (long long)n;
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+  *exec_out = exec;
+  return 0;
+}
+int geeps_graph_launch(void* exec, void* stream) { return (int)cudaGraphLaunch((cudaGraphExec_t)exec, (cudaStream_t)stream); }
+void geeps_graph_destroy(void* exec) { if (exec) cudaGraphExecDestroy((cudaGraphExec_t)exec); }
+
 int geeps_current_clock(void* g) { return static_cast<GeePs*>(g)->CurrentClock(); }
 int geeps_last_error(void* g) { return static_cast<GeePs*>(g)->LastError(); }
 int geeps_last_error_string(void* g, char* buf, int cap) { return copy_out(static_cast<GeePs*>(g)->LastErrorString(), buf, cap); }

@@ -221,6 +221,7 @@ bool ClientLib::read_batch(int handle, RowData** buf, void* stream, bool async) 
   if (!check_order(handle, OP_READ)) return false;
   const OpInfo& op = plan_.ops[handle];
   void* st = op_stream(stream);
+  last_app_stream_ = st;
   bool ok = true;
   if (nvlink_) {
     CachedTable& ct = *tables_[(uint)op.table];
@@ -307,6 +308,7 @@ void ClientLib::update_batch(int handle, void* stream, bool async) {
   stats_.rows_updated += pre.rows.size();
   // after StartIterations the last write of a table in the clock signals that table's clock at
   // once, so its push overlaps the rest of the iteration; during bootstrap Clock() signals all
+  last_app_stream_ = st;
   if (!pre.local) tables_[(uint)op.table]->last_stream = st;
   if (started_ && op.table_last_write) clock_table(clock_, (uint)op.table, false, false, st);
   // the blocking form returns once the update buffer may be reused by the host (the reference's Update returns
@@ -369,6 +371,7 @@ void ClientLib::iterate() {
   stats_.nr_clock++;
   if (nvlink_) fabric_check_status();
   else check_row_status();
+  if (device_clock_) fabric_end_iteration_device_clock();
   if (config_.snapshot_interval > 0 && !config_.snapshot_dir.empty() && clock_ % config_.snapshot_interval == 0)
     save_snapshot(config_.snapshot_dir);
   if (config_.log_interval > 0 && clock_ % config_.log_interval == 0) {

@@ -136,6 +136,7 @@ struct Fabric {
   std::vector<PushTiming> push_timing;
   size_t push_timing_next = 0;
   std::vector<void*> table_events;
+  void* join_event = nullptr;             // device-clock mode: comm lanes -> application stream at the end of a clock
   int* host_status = nullptr;             // pinned mirror of the device status block
 };
 
@@ -169,6 +170,10 @@ class ClientLib {
   void iterate();
   void start_opseq();
   void* read_bf16(int handle);
+  // device-resident clock (NVLINK transport): see clientlib_fabric.cpp
+  bool enable_device_clock();
+  void advance_replayed_iteration();
+  int* device_clock_ptr() const { return device_clock_; }
 
   void shutdown();
   std::string json_stats();
@@ -248,6 +253,9 @@ class ClientLib {
   void fabric_wait_data_age(CachedTable& ct, uint table_id, iter_t needed_age, void* stream);
   void fabric_push(iter_t clock, uint table_id, bool is_init, void* stream);
   bool fabric_check_status(bool sync = false);
+  void fabric_end_iteration_device_clock();
+  int stamp_arg(iter_t stamp) const { return device_clock_ ? (int)(stamp - clock_) : (int)stamp; }
+  const int* clock_ref() const { return device_clock_; }
   void fabric_read_rmw(const OpInfo& op, RowData* dst, void* stream);
   float* fabric_cache_ptr(uint table_id, int rank) const;
   float* fabric_ring_ptr(uint table_id, int rank, iter_t clock) const;
@@ -263,6 +271,8 @@ class ClientLib {
   std::unique_ptr<PlanCompiler> compiler_;
   Plan plan_;
   bool vi_finished_ = false, started_ = false, shut_down_ = false;
+  int* device_clock_ = nullptr;          // device word holding clock_ (device-clock mode), else null
+  void* last_app_stream_ = nullptr;      // stream of the application's latest access call
   bool bootstrap_init_pushed_ = false;   // clock 0 was signalled before StartIterations: its updates are initial values
   iter_t clock_ = kInitialClock;
   int last_handle_ = -1;

@@ -31,6 +31,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kFlagBytes = 256;
 constexpr size_t kPushReadyOff = 0, kDataAgeOff = 32, kGlobalClockOff = 64, kCtaCounterOff = 68, kPublishBeginOff = 96;
 constexpr size_t kPushTimingRing = 64;
+constexpr size_t kDeviceClockOff = 64;    // inside the 256-byte status area, after the 4 status words
 }  // namespace
 
 float* ClientLib::fabric_cache_ptr(uint table_id, int rank) const {
@@ -173,6 +174,7 @@ void ClientLib::fabric_teardown() {
   fabric_.push_timing.clear();
   for (void* e : fabric_.table_events) if (e) cudaEventDestroy((cudaEvent_t)e);
   fabric_.table_events.clear();
+  if (fabric_.join_event) { cudaEventDestroy((cudaEvent_t)fabric_.join_event); fabric_.join_event = nullptr; }
   for (void* cs : fabric_.comm_lanes) cudaStreamDestroy((cudaStream_t)cs);
   fabric_.comm_lanes.clear();
   fabric_.comm_stream = nullptr;
@@ -193,8 +195,9 @@ void ClientLib::fabric_wait_data_age(CachedTable& ct, uint table_id, iter_t need
   if (mine && stamp <= mine->second) return;
   const TableArena& ta = fabric_.tables[table_id];
   const int* flags = reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kDataAgeOff);
-  geeps_flag_wait(flags, (int)num_processes_, stamp, (unsigned long long)config_.device_wait_budget_us * 1000ull,
-                  reinterpret_cast<int*>(fabric_.base + fabric_.status_off), stream);
+  geeps_flag_wait_rel(flags, (int)num_processes_, stamp_arg(stamp), clock_ref(),
+                      (unsigned long long)config_.device_wait_budget_us * 1000ull,
+                      reinterpret_cast<int*>(fabric_.base + fabric_.status_off), stream);
   if (mine) mine->second = stamp; else ct.waited_by_stream.emplace_back(stream, stamp);
   stats_.device_waits_enqueued++;
 }
@@ -213,7 +216,7 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
     list.n = (int)num_processes_;
     for (uint r = 0; r < num_processes_; ++r)
       list.ptr[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kPushReadyOff);
-    geeps_flag_signal(&list, (int)process_id_, stamp, stream);
+    geeps_flag_signal_rel(&list, (int)process_id_, stamp_arg(stamp), clock_ref(), stream);
   }
   // The comm stream does not even start waiting before this worker's own announcement has run: the host
   // enqueues a whole step ahead of the GPU, and a wait kernel that started right away would sit spinning on
@@ -250,15 +253,18 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
     begin.n = (int)num_processes_;
     for (uint r = 0; r < num_processes_; ++r)
       begin.ptr[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kPublishBeginOff);
-    geeps_flag_wait_signal(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_,
-                           stamp, budget, status, &begin, (int)process_id_, cs);
+    geeps_flag_wait_signal_rel(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff),
+                               (int)num_processes_, stamp_arg(stamp), clock_ref(), budget, status, &begin,
+                               (int)process_id_, cs);
   } else {
-    geeps_flag_wait(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_, stamp,
-                    budget, status, cs);
+    geeps_flag_wait_rel(reinterpret_cast<const int*>(fabric_.base + ta.flags_off + kPushReadyOff), (int)num_processes_,
+                        stamp_arg(stamp), clock_ref(), budget, status, cs);
   }
   // device time of the push kernel itself (the wait for the other workers is not part of it)
   Fabric::PushTiming* pt = nullptr;
-  if (!is_init) {
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing((cudaStream_t)cs, &capturing);
+  if (!is_init && capturing == cudaStreamCaptureStatusNone) {   // an event recorded under capture cannot be queried
     if (fabric_.push_timing.empty()) fabric_.push_timing.resize(kPushTimingRing);
     pt = &fabric_.push_timing[fabric_.push_timing_next++ % kPushTimingRing];
     if (!pt->begin) {
@@ -292,7 +298,8 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
   p.wait_budget_ns = budget;
   p.n_ranks = (int)num_processes_;
   p.rank = (int)process_id_;
-  p.clock_stamp = stamp;
+  p.clock_stamp = stamp_arg(stamp);
+  p.clock_ref = clock_ref();
   p.mode = is_init ? GEEPS_TABLE_ADDITIVE : ct.mode;
   p.publish = 1;
   p.lr = config_.learning_rate;
@@ -354,11 +361,77 @@ void ClientLib::fabric_read_rmw(const OpInfo& op, RowData* dst, void* stream) {
   p.n_ranks = (int)num_processes_;
   p.partition_kind = config_.partitioner;
   p.ring_slots = ta.ring_slots;
-  p.clock = (int)clock_;
+  p.clock = stamp_arg(clock_);
+  p.clock_ref = clock_ref();
   p.additive_below_clock = bootstrap_init_pushed_ ? (int)kInitialClock + 1 : 0;
   p.alpha = ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM ? -config_.learning_rate * config_.grad_scale : 1.f;
   geeps_row_gather_rmw(&p, stream);
   bg_stats_.nr_rmw_replay++;
+}
+
+// ---- device-resident clock and replayed iterations ----
+// With the device clock on, every stamp a launch carries is relative to a clock word in device memory that a
+// one-thread kernel advances at the end of each iteration, after the comm streams have joined the application's
+// stream.  An iteration's launches then contain nothing that changes from one clock to the next (for a fixed phase
+// of the update ring), so the application can capture them once in a CUDA graph and replay the graph;
+// advance_replayed_iteration() does the host-side bookkeeping of such a replay.
+bool ClientLib::enable_device_clock() {
+  if (!nvlink_ || !fabric_.active) { set_error(ERR_ORDER, "the device clock needs the NVLINK transport after FinishVirtualIteration"); return false; }
+  if (device_clock_) return true;
+  cudaDeviceSynchronize();
+  const int now = (int)clock_;
+  cudaMemcpy(fabric_.base + fabric_.status_off + kDeviceClockOff, &now, sizeof(int), cudaMemcpyHostToDevice);
+  device_clock_ = reinterpret_cast<int*>(fabric_.base + fabric_.status_off + kDeviceClockOff);
+  return true;
+}
+
+// End of an iteration in device-clock mode: everything the iteration put on the comm streams completes before
+// the clock word moves (a push kernel that ran after the advance would read the next clock's value).
+void ClientLib::fabric_end_iteration_device_clock() {
+  cudaStream_t app = (cudaStream_t)(last_app_stream_ ? last_app_stream_ : default_stream_);
+  if (!fabric_.join_event) {
+    cudaEvent_t e;
+    cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+    fabric_.join_event = e;
+  }
+  for (void* cs : fabric_.comm_lanes) {
+    cudaEventRecord((cudaEvent_t)fabric_.join_event, (cudaStream_t)cs);
+    cudaStreamWaitEvent(app, (cudaEvent_t)fabric_.join_event, 0);
+  }
+  geeps_clock_advance(device_clock_, app);
+}
+
+void ClientLib::advance_replayed_iteration() {
+  if (!device_clock_ || !started_) { set_error(ERR_ORDER, "advance_replayed_iteration without the device clock"); return; }
+  for (auto& kv : tables_) {
+    CachedTable& ct = *kv.second;
+    ct.signalled_clock = clock_;
+    for (auto& w : ct.waited_by_stream) w.second += 1;
+    if (ct.ring_zeroed_clock == clock_ - 1) ct.ring_zeroed_clock = clock_;
+    bg_stats_.nr_push++;
+    bg_stats_.bytes_pushed += ct.plan->rows.size() * kRowBytes;
+  }
+  for (int h = 0; h < plan_.clock_handle; ++h) {
+    const OpInfo& op = plan_.ops[h];
+    accessed_clock_[h] = clock_;
+    if (op.type == OP_READ) { stats_.nr_read++; stats_.rows_read += op.rows.size(); }
+    else if (op.type == OP_POST_READ) stats_.nr_postread++;
+    else if (op.type == OP_PRE_UPDATE) stats_.nr_preupdate++;
+    else if (op.type == OP_UPDATE) { stats_.nr_update++; stats_.rows_updated += plan_.ops[op.prestep].rows.size(); }
+  }
+  clock_++;
+  last_handle_ = -1;
+  stats_.nr_clock++;
+  stats_.nr_replayed_clocks++;
+  // the replayed graph refreshed the pinned mirror of the status block: look at it without enqueuing anything
+  if (fabric_.host_status[0] != 0) {
+    const int code = fabric_.host_status[0];
+    if (code == 1) stats_.device_wait_timeouts++;
+    set_error(code == 1 ? ERR_DEVICE_TIMEOUT : ERR_CUDA,
+              std::string(code == 1 ? "device-side wait expired" : "device-side check failed") + " (kernel " +
+                  std::to_string(fabric_.host_status[1]) + ", detail " + std::to_string(fabric_.host_status[2]) +
+                  ", seen " + std::to_string(fabric_.host_status[3]) + ")");
+  }
 }
 
 // Errors recorded by kernels (expired waits, failed bounds checks) surface here.  The device block

@@ -49,6 +49,8 @@ typedef struct GeepsPushApplyParams {
   int n_ranks, rank, clock_stamp, mode, publish;
   float lr, momentum_coef, weight_decay, grad_scale;
   long long fp32_from_row;             // rows below this id are published to the bf16 caches only (0: all in fp32 too)
+  const int* clock_ref;                // NULL, or a device word added to clock_stamp when the kernel runs (stamps
+                                       // relative to a device-resident clock: launches that a CUDA graph replays)
 } GeepsPushApplyParams;
 int geeps_ps_push_apply(const GeepsPushApplyParams* p, int max_ctas, void* stream);
 
@@ -76,6 +78,16 @@ int geeps_flag_wait(const int* flags, int n, int stamp, unsigned long long budge
 int geeps_flag_wait_signal(const int* flags, int n, int stamp, unsigned long long budget_ns, int* status,
                            const GeepsFlagList* then, int index, void* stream);
 int geeps_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+// Forms whose stamp is relative to a device-resident clock word: the kernel uses stamp_rel + *clock_ref.  With them
+// a step's launches carry no per-step immediate, so the step can be captured once in a CUDA graph and replayed.
+int geeps_flag_signal_rel(const GeepsFlagList* list, int index, int stamp_rel, const int* clock_ref, void* stream);
+int geeps_flag_wait_rel(const int* flags, int n, int stamp_rel, const int* clock_ref, unsigned long long budget_ns,
+                        int* status, void* stream);
+int geeps_flag_wait_signal_rel(const int* flags, int n, int stamp_rel, const int* clock_ref,
+                               unsigned long long budget_ns, int* status, const GeepsFlagList* then, int index,
+                               void* stream);
+// *clock += 1 (one thread), at the end of a step
+int geeps_clock_advance(int* clock, void* stream);
 
 // Read with read-my-updates on the NVLINK transport: dst[id0] = cache[id1] + alpha * (sum of this worker's own ring
 // slots whose clock the owning shard has not published yet).  Per row the owning shard's data_age stamp is read
@@ -91,6 +103,7 @@ typedef struct GeepsRmwReadParams {
   int n_ranks, partition_kind, ring_slots, clock;
   int additive_below_clock;   // own updates of clocks below this are added as they are (initial values), not scaled
   float alpha;
+  const int* clock_ref;       // NULL, or a device word added to `clock` when the kernel runs
 } GeepsRmwReadParams;
 int geeps_row_gather_rmw(const GeepsRmwReadParams* p, void* stream);
 

@@ -354,7 +354,9 @@ __device__ __forceinline__ uint32_t mix32(uint64_t z) {
 }
 // y = x * keep(seed, idx) / (1 - p); the same call with dy as input gives dx.
 __global__ void __launch_bounds__(256)
-dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, float p, unsigned long long seed) {
+dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long n, float p, unsigned long long seed,
+               const int* __restrict__ step_ref) {
+  if (step_ref != nullptr) seed += (unsigned long long)(long long)*step_ref;
   const float inv = 1.f / (1.f - p);
   const uint32_t thresh = (uint32_t)(p * 4294967296.0);
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -1056,7 +1058,12 @@ int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long 
 }
 
 int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream) {
-  dropout_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, p, seed);
+  dropout_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, p, seed, nullptr);
+  return CK();
+}
+int geeps_dropout_ref(const void* x, void* y, long long n, float p, unsigned long long seed, const int* step_ref,
+                      void* stream) {
+  dropout_kernel<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>((const bf16*)x, (bf16*)y, n, p, seed, step_ref);
   return CK();
 }
 

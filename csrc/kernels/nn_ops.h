@@ -45,6 +45,10 @@ int geeps_relu_backward_2d(const void* dy, const void* y, void* dx, long long P,
                            long long lddx, void* stream);
 int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long ldd, long long lds, void* stream);
 int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream);
+// the same with the seed taken as seed + *step_ref when the kernel runs (a device-resident step counter: the launch
+// arguments stay the same from step to step, so the launch can sit in a replayed CUDA graph)
+int geeps_dropout_ref(const void* x, void* y, long long n, float p, unsigned long long seed, const int* step_ref,
+                      void* stream);
 // rscale: bf16 buffer [P][C] that receives 1 / scale for the backward pass
 int geeps_lrn_forward(const void* x, void* y, void* rscale, long long P, int C, int size, float alpha, float beta,
                       float k, void* stream);

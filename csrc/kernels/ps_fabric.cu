@@ -84,9 +84,10 @@ push_apply_kernel(const GeepsPushApplyParams p) {
   // ---- bounded wait: every worker's update for this clock is complete ----
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
+  const int clock_stamp = p.clock_stamp + (p.clock_ref != nullptr ? *p.clock_ref : 0);
   if (p.push_ready != nullptr && (int)threadIdx.x < p.n_ranks) {
     int seen = 0;
-    if (!geeps_wait_ge(p.push_ready + threadIdx.x, p.clock_stamp, p.wait_budget_ns, &seen)) {
+    if (!geeps_wait_ge(p.push_ready + threadIdx.x, clock_stamp, p.wait_budget_ns, &seen)) {
       geeps_report(p.status, GEEPS_ERR_TIMEOUT, KID_PUSH_APPLY, (int)threadIdx.x, seen);
       s_ok = 0;
     }
@@ -133,10 +134,10 @@ push_apply_kernel(const GeepsPushApplyParams p) {
   bool any_failed = false;
   if (last_cta_arrive(p.cta_counter, !ok, &any_failed)) {
     if (!any_failed) {
-      if (p.global_clock != nullptr) st_release_sys(p.global_clock, p.clock_stamp);
+      if (p.global_clock != nullptr) st_release_sys(p.global_clock, clock_stamp);
       if (p.publish)
         for (int q = 0; q < p.n_ranks; ++q)
-          if (p.data_age[q] != nullptr) st_release_sys(p.data_age[q] + p.rank, p.clock_stamp);
+          if (p.data_age[q] != nullptr) st_release_sys(p.data_age[q] + p.rank, clock_stamp);
     }
   }
 }
@@ -188,7 +189,8 @@ pull_kernel(const GeepsPullParams p) {
 }
 
 // Write `stamp` into slot `index` of each listed flag array (peer pointers).
-__global__ void flag_signal_kernel(GeepsFlagList list, int index, int stamp) {
+__global__ void flag_signal_kernel(GeepsFlagList list, int index, int stamp, const int* clock_ref) {
+  if (clock_ref != nullptr) stamp += *clock_ref;
   if (threadIdx.x < list.n && list.ptr[threadIdx.x] != nullptr) {
     __threadfence_system();
     st_release_sys(list.ptr[threadIdx.x] + index, stamp);
@@ -197,7 +199,8 @@ __global__ void flag_signal_kernel(GeepsFlagList list, int index, int stamp) {
 
 // Wait until flags[i] >= stamp for all i < n; record TIMEOUT in status otherwise.
 __global__ void flag_wait_kernel(const int* flags, int n, int stamp, unsigned long long budget_ns,
-                                 int* status) {
+                                 int* status, const int* clock_ref) {
+  if (clock_ref != nullptr) stamp += *clock_ref;
   if ((int)threadIdx.x < n) {
     int seen = 0;
     if (!geeps_wait_ge(flags + threadIdx.x, stamp, budget_ns, &seen))
@@ -206,9 +209,14 @@ __global__ void flag_wait_kernel(const int* flags, int n, int stamp, unsigned lo
 }
 
 // The same wait, followed (on success) by a stamp into slot `index` of each listed array.
+__global__ void clock_advance_kernel(int* clock) {
+  if (threadIdx.x == 0) *clock += 1;
+}
+
 __global__ void flag_wait_signal_kernel(const int* flags, int n, int stamp, unsigned long long budget_ns,
-                                        int* status, GeepsFlagList then, int index) {
+                                        int* status, GeepsFlagList then, int index, const int* clock_ref) {
   __shared__ int s_fail;
+  if (clock_ref != nullptr) stamp += *clock_ref;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
   if ((int)threadIdx.x < n) {
@@ -235,6 +243,7 @@ row_gather_rmw_kernel(const GeepsRmwReadParams p) {
   const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
   const long long per = (p.total_rows + p.n_ranks - 1) / p.n_ranks;
+  const int clock = p.clock + (p.clock_ref != nullptr ? *p.clock_ref : 0);
   for (long long i = warp0; i < p.num_rows; i += nwarps) {
     IndexPair ip;
     if (lane == 0) ip = index[i];
@@ -256,9 +265,9 @@ row_gather_rmw_kernel(const GeepsRmwReadParams p) {
       if (lane == 0) age = ld_acquire_sys(p.data_age + shard);
       age = __shfl_sync(0xffffffffu, age, 0);
       v = ld_f4_peer(src);
-      int first = age > p.clock - (p.ring_slots - 1) ? age : p.clock - (p.ring_slots - 1);
+      int first = age > clock - (p.ring_slots - 1) ? age : clock - (p.ring_slots - 1);
       if (first < 0) first = 0;
-      for (int k = first; k < p.clock; ++k) {
+      for (int k = first; k < clock; ++k) {
         const float a = k < p.additive_below_clock ? 1.f : p.alpha;
         const float4 u = ld_f4_cg(p.ring + ((long long)(k % p.ring_slots) * p.total_rows + ip.id1) * GEEPS_ROW_FLOATS + lane * 4);
         v.x += a * u.x; v.y += a * u.y; v.z += a * u.z; v.w += a * u.w;
@@ -340,23 +349,41 @@ int geeps_ps_pull(const GeepsPullParams* params, int max_ctas, void* stream) {
   return (int)cudaGetLastError();
 }
 
-int geeps_flag_signal(const GeepsFlagList* list, int index, int stamp, void* stream) {
-  flag_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(*list, index, stamp);
+int geeps_flag_signal_rel(const GeepsFlagList* list, int index, int stamp_rel, const int* clock_ref, void* stream) {
+  flag_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(*list, index, stamp_rel, clock_ref);
   return (int)cudaGetLastError();
 }
+int geeps_flag_signal(const GeepsFlagList* list, int index, int stamp, void* stream) {
+  return geeps_flag_signal_rel(list, index, stamp, nullptr, stream);
+}
 
+int geeps_flag_wait_rel(const int* flags, int n, int stamp_rel, const int* clock_ref, unsigned long long budget_ns,
+                        int* status, void* stream) {
+  if (n > 32) return (int)cudaErrorInvalidValue;
+  flag_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n, stamp_rel, budget_ns, status, clock_ref);
+  return (int)cudaGetLastError();
+}
 int geeps_flag_wait(const int* flags, int n, int stamp, unsigned long long budget_ns, int* status,
                     void* stream) {
-  if (n > 32) return (int)cudaErrorInvalidValue;
-  flag_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n, stamp, budget_ns, status);
+  return geeps_flag_wait_rel(flags, n, stamp, nullptr, budget_ns, status, stream);
+}
+
+int geeps_clock_advance(int* clock, void* stream) {
+  clock_advance_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(clock);
   return (int)cudaGetLastError();
 }
 
+int geeps_flag_wait_signal_rel(const int* flags, int n, int stamp_rel, const int* clock_ref,
+                               unsigned long long budget_ns, int* status, const GeepsFlagList* then, int index,
+                               void* stream) {
+  if (n > 32 || then->n > 32) return (int)cudaErrorInvalidValue;
+  flag_wait_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n, stamp_rel, budget_ns, status, *then, index,
+                                                              clock_ref);
+  return (int)cudaGetLastError();
+}
 int geeps_flag_wait_signal(const int* flags, int n, int stamp, unsigned long long budget_ns, int* status,
                            const GeepsFlagList* then, int index, void* stream) {
-  if (n > 32 || then->n > 32) return (int)cudaErrorInvalidValue;
-  flag_wait_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, n, stamp, budget_ns, status, *then, index);
-  return (int)cudaGetLastError();
+  return geeps_flag_wait_signal_rel(flags, n, stamp, nullptr, budget_ns, status, then, index, stream);
 }
 
 int geeps_row_gather_rmw(const GeepsRmwReadParams* params, void* stream) {

@@ -47,7 +47,7 @@ class PushApplyParams(C.Structure):
         ("n_ranks", C.c_int), ("rank", C.c_int), ("clock_stamp", C.c_int), ("mode", C.c_int),
         ("publish", C.c_int),
         ("lr", C.c_float), ("momentum_coef", C.c_float), ("weight_decay", C.c_float),
-        ("grad_scale", C.c_float), ("fp32_from_row", C.c_longlong),
+        ("grad_scale", C.c_float), ("fp32_from_row", C.c_longlong), ("clock_ref", C.c_void_p),
     ]
 
 
@@ -84,7 +84,7 @@ class RmwReadParams(C.Structure):
         ("num_rows", C.c_longlong), ("num_vals_limit", C.c_longlong), ("dst_rows", C.c_longlong),
         ("total_rows", C.c_longlong), ("wait_budget_ns", C.c_ulonglong),
         ("n_ranks", C.c_int), ("partition_kind", C.c_int), ("ring_slots", C.c_int), ("clock", C.c_int),
-        ("additive_below_clock", C.c_int), ("alpha", C.c_float),
+        ("additive_below_clock", C.c_int), ("alpha", C.c_float), ("clock_ref", C.c_void_p),
     ]
 
 
@@ -169,6 +169,47 @@ class Tape:
     @property
     def kernel_launches(self) -> int:
         return sum(1 for _, _, label in self.ops if not label.startswith("ps:"))
+
+
+class StepGraph:
+    """A CUDA graph of one training step: everything a tape enqueues on `stream` (and on the streams that join it
+    through events) captured once, then replayed with a single launch."""
+
+    def __init__(self, tape: "Tape", stream):
+        self.stream = stream
+        self.kernel_launches = tape.kernel_launches
+        self.nodes = 0
+        self._exec = C.c_void_p()
+        l = lib()
+        err = l.geeps_graph_begin(C.c_void_p(stream.cuda_stream))
+        if err:
+            raise RuntimeError(f"cudaStreamBeginCapture failed with {err}")
+        try:
+            tape.replay()
+        finally:
+            n = C.c_longlong(0)
+            err = l.geeps_graph_end(C.c_void_p(stream.cuda_stream), C.byref(self._exec), C.byref(n))
+        if err or not self._exec.value:
+            raise RuntimeError(f"capturing the step failed with {err}")
+        self.nodes = n.value
+
+    def launch(self) -> None:
+        global _launches
+        err = lib().geeps_graph_launch(self._exec, C.c_void_p(self.stream.cuda_stream))
+        if err:
+            raise RuntimeError(f"cudaGraphLaunch failed with {err}")
+        _launches += self.kernel_launches
+
+    def close(self) -> None:
+        if self._exec.value:
+            lib().geeps_graph_destroy(self._exec)
+            self._exec = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 _tape = None

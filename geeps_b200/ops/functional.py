@@ -192,8 +192,14 @@ def add_2d(dst2d, src2d) -> None:
                                   C.c_longlong(_ld(src2d)), stream_ptr())
 
 
-def dropout(x, y, p: float, seed: int) -> None:
+def dropout(x, y, p: float, seed: int, step_ref: int | None = None) -> None:
+    """step_ref: address of a device int added to the seed when the kernel runs (the launch arguments then do not
+    change from step to step)."""
     assert x.is_contiguous() and y.is_contiguous()
+    if step_ref:
+        launch(lib().geeps_dropout_ref, "dropout_ref", ptr(x), ptr(y), C.c_longlong(x.numel()), C.c_float(p),
+               C.c_ulonglong(seed), C.c_void_p(step_ref), stream_ptr())
+        return
     launch(lib().geeps_dropout, "dropout", ptr(x), ptr(y), C.c_longlong(x.numel()), C.c_float(p), C.c_ulonglong(seed),
                               stream_ptr())
 

@@ -447,6 +447,7 @@ class Dropout(Layer):
     def __init__(self, p=0.5, seed=1234):
         super().__init__()
         self.p, self.seed, self.step = p, seed, 0
+        self.step_ref = None      # address of a device-resident step counter (set by the trainer in graph mode)
 
     def setup(self, in_shape, device):
         self.y = torch.empty(in_shape, dtype=BF, device=device)
@@ -458,13 +459,19 @@ class Dropout(Layer):
         self.step += 1
         if not self.training:
             return x
-        F.dropout(x.contiguous(), self.y, self.p, self.seed + self.step)
+        if self.step_ref:
+            F.dropout(x.contiguous(), self.y, self.p, self.seed, self.step_ref)
+        else:
+            F.dropout(x.contiguous(), self.y, self.p, self.seed + self.step)
         return self.y
 
     def backward(self, dy):
         if not self.training:
             return dy
-        F.dropout(dy.contiguous(), self.dx, self.p, self.seed + self.step)
+        if self.step_ref:
+            F.dropout(dy.contiguous(), self.dx, self.p, self.seed, self.step_ref)
+        else:
+            F.dropout(dy.contiguous(), self.dx, self.p, self.seed + self.step)
         return self.dx
 
 

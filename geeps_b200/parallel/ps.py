@@ -223,6 +223,20 @@ class GeePs:
         _L.record_call(self._l.geeps_clock, "clock", self._g)
         self.check()
 
+    # ---- device-resident clock: iterations replayed from a CUDA graph ----
+    def enable_device_clock(self) -> int:
+        """Keep the clock in a device word (NVLINK transport) so that one iteration's launches can be captured in a
+        CUDA graph; returns the address of the word."""
+        if not self._l.geeps_enable_device_clock(self._g):
+            self.check()
+            raise GeePsError(-1, "device clock not available")
+        self._l.geeps_device_clock_ptr.restype = C.c_void_p
+        return int(self._l.geeps_device_clock_ptr(self._g))
+
+    def advance_replayed_clock(self) -> None:
+        """Host-side bookkeeping of one iteration whose launches were replayed from a captured graph."""
+        self._l.geeps_advance_replayed_clock(self._g)
+
     # ---- snapshots / lifecycle / test hooks ----
     def save_snapshot(self, directory: str) -> bool:
         return bool(self._l.geeps_save_snapshot(self._g, directory.encode()))

@@ -49,11 +49,16 @@ class _Table:
 class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
                  slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None, manage_activations: bool = False,
-                 cache_fraction: float | None = None, use_tape: bool = False, bf16_weights_only: bool = False):
+                 cache_fraction: float | None = None, use_tape: bool = False, bf16_weights_only: bool = False,
+                 use_graph: bool = False):
         """bf16_weights_only: with the NVLINK transport and the bf16 compute cache, weight rows are published to
         the workers' bf16 caches only (the layers never read weights in fp32; biases, BatchNorm scale / shift and
         the shard's master rows stay fp32).  The fp32 views of weights (`params_fp32`) then keep their initial
-        values."""
+        values.
+        use_graph: (NVLINK transport, implies use_tape) once a step's native calls are known to repeat, capture
+        them in a CUDA graph per (input buffer, label buffer, update-ring phase) and replay the graph: one launch
+        per step instead of one per kernel.  The runtime then keeps its clock in a device word (stamps relative
+        to it, dropout seeds derived from it), so nothing in the captured launches changes from step to step."""
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
         self.trace = trace or NullTrace()
@@ -105,7 +110,11 @@ class PSModule:
         self.ps = GeePs(rank, ps_config)
         # tape replay: record two consecutive steps; if they issued identical native calls (static pointers),
         # later steps walk the tape instead of re-running the Python layer code
-        self.use_tape = use_tape and not manage_activations
+        self.use_graph = (use_graph and not manage_activations and ps_config.transport == TRANSPORT_NVLINK
+                          and torch.cuda.is_available())
+        self.use_tape = (use_tape or self.use_graph) and not manage_activations
+        self._graphs, self._graph_failed = {}, False
+        self._period = (slack + 1) if (slack + 1) % 2 == 0 else 2 * (slack + 1)
         self._tapes, self._tape_sigs, self._tape_tries = {}, {}, {}     # keyed by (input ptr, label ptr, clock phase)
         self.tape_mismatch = None
         # diagnostics: set to [] to collect CUDA events (step start, forward end, backward end, clock end) per step
@@ -119,6 +128,11 @@ class PSModule:
         self._bootstrap(seed)
         self.ps.start_iterations()
         self.steps = 0
+        if self.use_graph:
+            ref = self.ps.enable_device_clock()
+            for l in net.all_layers():
+                if hasattr(l, "step_ref"):
+                    l.step_ref = ref
 
     # one virtual iteration = the exact call sequence of step()
     def _declare(self):
@@ -183,9 +197,30 @@ class PSModule:
         """One clock: forward, backward, push.  Returns the mean loss as a 1-element device tensor.
         capture=True keeps clones of the parameters this clock read in `self.captured`."""
         net, tr = self.net, self.trace
-        # the update buffers a clock writes rotate through slack + 2 slots, so the calls repeat with that period
-        key = (x.data_ptr(), labels.data_ptr(), self.steps % (self.slack + 2))
+        # the update ring has slack + 1 slots and staged buffers alternate between two copies, so the pointers a
+        # step uses repeat with the least common multiple of the two
+        key = (x.data_ptr(), labels.data_ptr(), self.steps % self._period)
+        graph = self._graphs.get(key) if self.use_graph and not capture else None
+        if graph is not None:
+            graph.launch()
+            self.ps.advance_replayed_clock()
+            self.ps.check()
+            self.steps += 1
+            return net.loss_layer.loss
         tape = self._tapes.get(key) if self.use_tape and not capture else None
+        if tape is not None and self.use_graph and not self._graph_failed:
+            # capture this step (the host-side bookkeeping of the iteration happens now, during the capture),
+            # then run it by launching the graph once
+            try:
+                graph = L.StepGraph(tape, torch.cuda.current_stream(self.device))
+            except RuntimeError as e:
+                self._graph_failed = True
+                raise RuntimeError(f"step capture failed: {e}") from e
+            self._graphs[key] = graph
+            graph.launch()
+            self.ps.check()
+            self.steps += 1
+            return net.loss_layer.loss
         if tape is not None:
             for arg, offset in tape.dropouts:      # the only arguments that change from step to step
                 arg.value = offset + self.steps
@@ -196,7 +231,7 @@ class PSModule:
                 l.step += 1
             return net.loss_layer.loss
         recording = (self.use_tape and not capture and self.steps >= 2 and self._tape_tries.get(key, 0) < 4
-                     and (key in self._tape_tries or len(self._tape_tries) < 8))
+                     and (key in self._tape_tries or len(self._tape_tries) < 24))
         if recording:
             L.start_recording()
         self.captured = {} if capture else None
@@ -267,12 +302,23 @@ class PSModule:
         self.steps += 1
         return loss
 
+    def is_steady(self, x: torch.Tensor, labels: torch.Tensor) -> bool:
+        """True when the next step with these buffers replays a captured graph (or, without graphs, a recorded
+        tape): the Python layer code and the capture work are behind us."""
+        key = (x.data_ptr(), labels.data_ptr(), self.steps % self._period)
+        if self.use_graph and not self._graph_failed:
+            return key in self._graphs
+        return (not self.use_tape) or key in self._tapes
+
     def invalidate_tapes(self) -> None:
         """Forget the recorded steps (call after anything that changes what a step launches: switching layers
         between training and inference mode, rebinding buffers, changing hyper-parameters baked into arguments)."""
         self._tapes.clear()
         self._tape_sigs.clear()
         self._tape_tries.clear()
+        for g in self._graphs.values():
+            g.close()
+        self._graphs.clear()
 
     def _mark(self, tag):
         if self.layer_marks is None:
@@ -313,5 +359,9 @@ class PSModule:
         return out
 
     def close(self):
+        torch.cuda.synchronize(self.device) if self.use_graph else None
+        for g in self._graphs.values():
+            g.close()
+        self._graphs.clear()
         self.ps.shutdown()
         self.ps.close()

@@ -127,6 +127,15 @@ class GeePs {
   /* The compiled plan as JSON (placement, offsets, indices, per-shard ranges) */
   std::string PlanJson() const;
   iter_t CurrentClock() const;
+  /* NVLINK transport: keep the clock in a device word, so that the launches of one iteration carry no value that
+   * changes from clock to clock and can be captured in a CUDA graph (one graph per phase of the update ring, i.e.
+   * per clock modulo slack + 1).  From then on Clock() joins the runtime's streams into the stream of the latest
+   * access call and advances the device word there.  After replaying a captured iteration, call
+   * AdvanceReplayedClock() instead of repeating the access calls.  DeviceClockPtr() is the device word (an int that
+   * kernels of the application may read, e.g. to derive per-step random seeds). */
+  bool EnableDeviceClock();
+  void AdvanceReplayedClock();
+  const int* DeviceClockPtr() const;
   geeps_b200::ClientLib* impl() { return impl_; }
 
  private:

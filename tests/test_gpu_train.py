@@ -163,6 +163,63 @@ def test_tape_replay_matches_python_path():
     assert launches[True] == launches[False]
 
 
+@pytest.mark.parametrize("slack", [0, 1])
+def test_graph_replay_matches_python_path(slack):
+    """One CUDA graph per (buffers, ring phase) replayed with a single launch gives the same losses as running the
+    layer code: the runtime's clock lives in a device word, the host bookkeeping advances per replay, errors still
+    surface, and the launch counter keeps counting the kernels inside the graph."""
+    from geeps_b200.ops import _lib as L
+    dev = torch.device("cuda:0")
+    B = 64
+    losses, launches = {}, {}
+    for graph in (False, True):
+        with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+            mod = PSModule(inception_bn_small(), (B, 3, 32, 32), cfg(TRANSPORT_NVLINK, learning_rate=0.01), device=dev,
+                           seed=9, slack=slack, use_graph=graph)
+            gen = torch.Generator(device=dev).manual_seed(5)
+            x = torch.randn(B, 3, 32, 32, device=dev, generator=gen)
+            y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+            n0 = L.launch_count()
+            losses[graph] = [mod.step(x, y).item() for _ in range(16)]
+            launches[graph] = L.launch_count() - n0
+            stats = mod.ps.get_stats()
+            assert (len(mod._graphs) == 2) == graph, len(mod._graphs)
+            assert (stats["client"]["nr_replayed_clocks"] > 0) == graph
+            assert stats["client"]["nr_clock"] == 17          # bootstrap + 16 steps, replayed or not
+            assert mod.ps.last_error() == 0
+            mod.close()
+    assert losses[True] == pytest.approx(losses[False], rel=2e-3), losses
+    assert launches[True] == launches[False]
+
+
+def test_graph_replay_alexnet_with_dropout_trains():
+    """AlexNet in graph mode: dropout masks follow the device-resident step counter (they change every step and
+    are the same in a step's forward and backward), and the loss on a fixed batch goes down."""
+    from geeps_b200.models.alexnet import alexnet
+    dev = torch.device("cuda:0")
+    B = 16
+    with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+        mod = PSModule(alexnet(), (B, 3, 227, 227), cfg(TRANSPORT_NVLINK, learning_rate=0.01, bf16_compute_cache=1),
+                       device=dev, seed=2, use_graph=True, bf16_weights_only=True)
+        gen = torch.Generator(device=dev).manual_seed(5)
+        x = torch.randn(B, 3, 227, 227, device=dev, generator=gen)
+        y = torch.randint(0, 1000, (B,), device=dev, generator=gen)
+        drop = next(l for l in mod.net.all_layers() if type(l).__name__ == "Dropout")
+        losses, masks = [], []
+        for i in range(30):
+            losses.append(mod.step(x, y).item())
+            masks.append((drop.y != 0).float().mean().item())
+        assert len(mod._graphs) == 2
+        assert mod.ps.last_error() == 0
+        assert all(0.3 < m < 0.7 for m in masks), masks
+        zs = [(drop.y == 0).clone()]
+        mod.step(x, y)
+        zs.append((drop.y == 0).clone())
+        assert not torch.equal(zs[0], zs[1])                  # a new mask every step, also under replay
+        assert sum(losses[-5:]) / 5 < sum(losses[:5]) / 5, losses
+        mod.close()
+
+
 def test_bf16_only_weight_publish_trains_identically():
     """Weights published to the bf16 caches only: same losses (the layers never read fp32 weights), biases still
     refreshed in fp32, fp32 weight views left at their initial values."""
