@@ -184,9 +184,12 @@ class StepGraph:
         err = l.geeps_graph_begin(C.c_void_p(stream.cuda_stream))
         if err:
             raise RuntimeError(f"cudaStreamBeginCapture failed with {err}")
+        global _launches
+        counted = _launches
         try:
-            tape.replay()
+            tape.replay()            # enqueues into the capture: nothing runs yet
         finally:
+            _launches = counted      # the kernels are counted when the graph is launched
             n = C.c_longlong(0)
             err = l.geeps_graph_end(C.c_void_p(stream.cuda_stream), C.byref(self._exec), C.byref(n))
         if err or not self._exec.value:
