@@ -110,10 +110,35 @@ std::string ClientLib::last_error_string() {
   return error_text_;
 }
 
+// One comm channel: a server shard bound to port_for(process, c), a client router connected to every other
+// process's shard of the same channel, codec objects and the handler thread.
+bool ClientLib::open_channel(uint c, std::unique_ptr<ServerThreadEntry>* server, std::shared_ptr<RouterHandler>* router,
+                             std::unique_ptr<ClientServerEncode>* encoder, std::unique_ptr<ServerClientDecode>* decoder,
+                             std::string* err) {
+  const uint nch = config_.num_comm_channels ? config_.num_comm_channels : 1;
+  server->reset(new ServerThreadEntry(c, nch, process_id_, num_processes_, config_));
+  if (!(*server)->start(err)) return false;
+  router->reset(new RouterHandler("client-" + std::to_string(process_id_)));
+  if (config_.local_opt) {
+    (*router)->set_local_peer((*server)->router().get());
+    (*server)->router()->set_local_peer(router->get());
+  }
+  for (uint s = 0; s < num_processes_; ++s) {
+    if (config_.local_opt && s == process_id_) continue;
+    const std::string host = s < config_.host_list.size() ? config_.host_list[s] : "127.0.0.1";
+    const unsigned port = ServerThreadEntry::port_for(config_, s, c);
+    if (!(*router)->connect_to("tablet-" + std::to_string(s), host, port, 60000, err)) return false;
+  }
+  encoder->reset(new ClientServerEncode(*router, num_processes_, process_id_, config_));
+  decoder->reset(new ServerClientDecode(this));
+  ServerClientDecode* dec = decoder->get();
+  (*router)->start_handler_thread([dec](const std::string& src, Message& msg) { dec->router_callback(src, msg); });
+  return true;
+}
+
 bool ClientLib::init_comm(std::string* err) {
-  // every process hosts a server shard (channel 0 carries the control plane as well)
-  server_.reset(new ServerThreadEntry(0, config_.num_comm_channels, process_id_, num_processes_, config_));
-  if (!server_->start(err)) return false;
+  // every process hosts a server shard per channel (channel 0 carries the control plane as well)
+  if (!open_channel(0, &server_, &router_, &encoder_, &decoder_, err)) return false;
   ClientLib* self = this;
   server_->decoder()->control_hook = [self](const std::string& src, Message& msg) {
     switch (msg[0].cmd()) {
@@ -124,22 +149,16 @@ bool ClientLib::init_comm(std::string* err) {
       default: break;
     }
   };
-  router_.reset(new RouterHandler("client-" + std::to_string(process_id_)));
-  if (config_.local_opt) {
-    router_->set_local_peer(server_->router().get());
-    server_->router()->set_local_peer(router_.get());
-  }
-  for (uint s = 0; s < num_processes_; ++s) {
-    if (config_.local_opt && s == process_id_) continue;
-    const std::string host = s < config_.host_list.size() ? config_.host_list[s] : "127.0.0.1";
-    const unsigned port = ServerThreadEntry::port_for(config_, s, 0);
-    if (!router_->connect_to("tablet-" + std::to_string(s), host, port, 60000, err)) return false;
-  }
-  encoder_.reset(new ClientServerEncode(router_, num_processes_, process_id_, config_));
-  decoder_.reset(new ServerClientDecode(this));
-  ServerClientDecode* dec = decoder_.get();
-  router_->start_handler_thread([dec](const std::string& src, Message& msg) { dec->router_callback(src, msg); });
   const uint nch = config_.num_comm_channels ? config_.num_comm_channels : 1;
+  for (uint c = 1; c < nch; ++c) {
+    extra_channels_.emplace_back();
+    Channel& ch = extra_channels_.back();
+    if (!open_channel(c, &ch.server, &ch.router, &ch.encoder, &ch.decoder, err)) return false;
+    // a data channel that loses a peer reports it like the control channel does
+    ch.server->decoder()->control_hook = [self](const std::string& src, Message& msg) {
+      if (msg[0].cmd() == CMD_PEER_LOST) self->peer_lost_cbk(src);
+    };
+  }
   for (uint c = 0; c < nch; ++c) {
     bg_workers_.emplace_back(new BackgroundWorker());
     bg_workers_.back()->add_callback(kIterateCmd, [self](std::vector<char>& args) { self->cbk_iterate(args); });
@@ -160,6 +179,10 @@ void ClientLib::shutdown() {
   if (heartbeat_thread_.joinable()) heartbeat_thread_.join();
   if (router_) router_->stop_handler_thread();
   if (server_) server_->stop();
+  for (Channel& ch : extra_channels_) {
+    if (ch.router) ch.router->stop_handler_thread();
+    if (ch.server) ch.server->stop();
+  }
 }
 
 // ---------------- virtual iteration (recording) ----------------
@@ -432,11 +455,22 @@ std::string ClientLib::json_stats() {
     if (server_stats_.count(process_id_)) server_json = server_stats_[process_id_];
   }
   std::string out = "{\"process_id\":" + std::to_string(process_id_) + ",\"clock\":" + std::to_string(clock_) +
+                    ",\"comm_channels\":" + std::to_string(num_channels()) +
                     ",\"transport\":\"" + (nvlink_ ? "nvlink" : "tcp") + "\",\"device\":\"" + (gpu_ ? "cuda" : "cpu") +
                     "\",\"client\":" + stats_.to_json() + ",\"bgthread\":" + bg_stats_.to_json() +
                     ",\"router\":" + (router_ ? router_->stats.to_json() : std::string("{}")) +
                     ",\"server_router\":" + (server_ ? server_->router()->stats.to_json() : std::string("{}")) +
-                    ",\"push_timeline\":" + fabric_timeline_json() + ",\"server\":" + server_json + "}";
+                    ",\"channels\":[";
+  for (uint c = 0; c < num_channels(); ++c) {
+    RouterHandler* cr = c == 0 ? router_.get() : extra_channels_[c - 1].router.get();
+    ServerThreadEntry* sv = c == 0 ? server_.get() : extra_channels_[c - 1].server.get();
+    out += std::string(c ? "," : "") + "{\"channel\":" + std::to_string(c) + ",\"port\":" +
+           std::to_string(ServerThreadEntry::port_for(config_, process_id_, c)) + ",\"router\":" +
+           (cr ? cr->stats.to_json() : std::string("{}")) + ",\"server_router\":" +
+           (sv ? sv->router()->stats.to_json() : std::string("{}")) + ",\"storage\":" +
+           (sv ? sv->storage()->get_stats() : std::string("{}")) + "}";
+  }
+  out += "],\"push_timeline\":" + fabric_timeline_json() + ",\"server\":" + server_json + "}";
   if (!config_.output_dir.empty()) {
     std::ofstream f(config_.output_dir + "/json_stats." + std::to_string(process_id_), std::ios::app);
     f << out << "\n";

@@ -287,14 +287,38 @@ class ClientLib {
   // swapper state: per-op events and the clock in which the op's fetch was issued
   std::vector<void*> fetch_done_ev_, release_ev_;
   std::vector<iter_t> fetch_issued_clock_, accessed_clock_, released_clock_;
-  std::mutex send_mu_;
+  std::mutex send_mu_, recv_mu_;    // the pinned bounce buffers are shared by the channels' push / receive threads
   std::vector<void*> op_index_dev_;                   // per op: device copy of its gather index
 
   // communication
+  // Channel 0: the control plane (heartbeats, barriers, handle exchange, placement service) and the tables with
+  // id % channels == 0.  Every further channel is a full stack of its own - server shard on its own port, client
+  // router with its own connections and reader threads, codec, push worker - and carries the tables with
+  // id % channels == its index (the reference's comm channels: src/client/clientlib.cpp:72-158, :216-224).
   std::unique_ptr<ServerThreadEntry> server_;
   std::shared_ptr<RouterHandler> router_;
   std::unique_ptr<ClientServerEncode> encoder_;
   std::unique_ptr<ServerClientDecode> decoder_;
+  struct Channel {
+    std::unique_ptr<ServerThreadEntry> server;
+    std::shared_ptr<RouterHandler> router;
+    std::unique_ptr<ClientServerEncode> encoder;
+    std::unique_ptr<ServerClientDecode> decoder;
+  };
+  std::vector<Channel> extra_channels_;     // channels 1 .. K-1
+  uint num_channels() const { return (uint)extra_channels_.size() + 1; }
+  uint channel_of(uint table_id) const { return table_id % num_channels(); }
+  ClientServerEncode* enc(uint table_id) {
+    const uint c = channel_of(table_id);
+    return c == 0 ? encoder_.get() : extra_channels_[c - 1].encoder.get();
+  }
+  ServerThreadEntry* srv(uint table_id) {
+    const uint c = channel_of(table_id);
+    return c == 0 ? server_.get() : extra_channels_[c - 1].server.get();
+  }
+  bool open_channel(uint c, std::unique_ptr<ServerThreadEntry>* server, std::shared_ptr<RouterHandler>* router,
+                    std::unique_ptr<ClientServerEncode>* encoder, std::unique_ptr<ServerClientDecode>* decoder,
+                    std::string* err);
   std::vector<std::unique_ptr<BackgroundWorker>> bg_workers_;   // one per comm channel
   Fabric fabric_;
 

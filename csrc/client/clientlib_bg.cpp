@@ -119,7 +119,7 @@ void ClientLib::clock_table(iter_t signalled_clock, uint table_id, bool is_init,
   }
   if (synchronous) { push_updates_param_cache(signalled_clock, table_id, is_init); return; }
   IterateArgs a{signalled_clock, table_id, is_init ? 1 : 0};
-  bg_workers_[table_id % bg_workers_.size()]->pusher()->push_work(kIterateCmd, a);
+  bg_workers_[channel_of(table_id) % bg_workers_.size()]->pusher()->push_work(kIterateCmd, a);
 }
 
 void ClientLib::clock_all(iter_t signalled_clock, bool is_init) {

@@ -173,7 +173,7 @@ void ClientLib::push_updates_param_cache(iter_t clock, uint table_id, bool is_in
     if (c != ct.cpu.oplog.end()) ce = c->second;
   }
   if (!ge && !ce) {
-    encoder_->clock_broadcast(clock, table_id);
+    enc(table_id)->clock_broadcast(clock, table_id);
     bg_stats_.nr_clock_only++;
     return;
   }
@@ -194,7 +194,7 @@ void ClientLib::push_updates_param_cache(iter_t clock, uint table_id, bool is_in
   for (uint s = 0; s < num_processes_; ++s) {
     const ShardRows& sr = ct.shards[s];
     const size_t n = sr.is_gpu.size();
-    if (n == 0) { encoder_->clock_to(s, clock, table_id); continue; }
+    if (n == 0) { enc(table_id)->clock_to(s, clock, table_id); continue; }
     assembled.resize(n);
     size_t gi = 0, ci = 0;
     for (size_t k = 0; k < n; ++k) {
@@ -203,7 +203,7 @@ void ClientLib::push_updates_param_cache(iter_t clock, uint table_id, bool is_in
       else { if (ce) src = ce->data.data() + sr.cpu_slots[ci]; ++ci; }
       if (src) memcpy(&assembled[k], src, sizeof(RowOpVal)); else memset(&assembled[k], 0, sizeof(RowOpVal));
     }
-    if (!encoder_->clock_with_updates_batch(s, clock, table_id, sr.keys.data(), assembled.data(), n, is_init))
+    if (!enc(table_id)->clock_with_updates_batch(s, clock, table_id, sr.keys.data(), assembled.data(), n, is_init))
       set_error(ERR_TRANSPORT, "cannot reach tablet-" + std::to_string(s));
     bg_stats_.bytes_pushed += n * sizeof(RowOpVal);
   }
@@ -240,6 +240,8 @@ void ClientLib::recv_row_batch_gpu(CachedTable& ct, uint server_id, const RowDat
   const size_t ng = sr.gpu_slots.size();
   if (!ng) return;
   const double t0 = now_seconds();
+  std::unique_lock<std::mutex> bounce(recv_mu_, std::defer_lock);
+  if (gpu_) bounce.lock();      // one pinned receive buffer and one swap stream for all channels
   if (!gpu_) {
     size_t gi = 0;
     for (size_t k = 0; k < sr.is_gpu.size(); ++k)

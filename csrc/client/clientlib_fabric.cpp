@@ -133,7 +133,13 @@ bool ClientLib::fabric_setup(std::string* err) {
     cudaStreamCreateWithPriority(&cs, cudaStreamNonBlocking, prio_lo);
     fabric_.comm_lanes.assign(1, cs);
     fabric_.comm_stream = cs;
-    for (TableArena& ta : fabric_.tables) ta.comm_lane = 0;
+    // one comm lane (stream) per comm channel; a table's pushes always ride the lane of its channel
+    for (uint c = 1; c < num_channels(); ++c) {
+      cudaStream_t lane;
+      cudaStreamCreateWithPriority(&lane, cudaStreamNonBlocking, prio_lo);
+      fabric_.comm_lanes.push_back(lane);
+    }
+    for (size_t t = 0; t < fabric_.tables.size(); ++t) fabric_.tables[t].comm_lane = (int)channel_of((uint)t);
     if (const char* e = getenv("GEEPS_PUSH_CTAS")) fabric_.push_ctas = atoi(e);
     if (const char* e = getenv("GEEPS_TIMELINE")) fabric_.timeline = atoi(e) != 0;
   }

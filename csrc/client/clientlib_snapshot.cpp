@@ -96,7 +96,7 @@ bool ClientLib::save_snapshot(const std::string& dir) {
       clocks.push_back(cut);
       for (uint w = 0; w < num_processes_; ++w) clocks.push_back(cut);
     } else {
-      const TabletStorage::DataTable* dt = server_->storage()->table(t);
+      const TabletStorage::DataTable* dt = srv(t)->storage()->table(t);
       if (dt && dt->created && dt->row_count == n) {
         if (n) memcpy(rows.data(), dt->store.data(), n * sizeof(RowData));
         if (dt->mode == GeePsConfig::TABLE_SGD_MOMENTUM) { mom.resize(n); has_mom = true; if (n) memcpy(mom.data(), dt->momentum.data(), n * sizeof(RowData)); }
@@ -189,7 +189,7 @@ bool ClientLib::load_snapshot(const std::string& dir) {
       ct.waited_by_stream.clear();
       cudaStreamSynchronize((cudaStream_t)default_stream_);
     } else {
-      TabletStorage::DataTable* dt = server_->storage()->mutable_table(t);
+      TabletStorage::DataTable* dt = srv(t)->storage()->mutable_table(t);
       dt->store.init(own.count, MEM_HOST);
       if (own.count) memcpy(dt->store.data(), mine.data(), own.count * sizeof(RowData));
       dt->store.row_keys = ct.shards[process_id_].keys;

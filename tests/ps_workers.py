@@ -425,3 +425,45 @@ def rmw_worker(rank, world, base_port, mode, rmw, q, kw):
         q.put((rank, "ok", out, seen, stats["bgthread"]["nr_rmw_replay"], None))
     except Exception as e:  # pragma: no cover
         q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
+
+
+def multitable_worker(rank, world, base_port, clocks, q, kw):
+    """Three tables of different sizes, every clock +1 (table 0), +2 (table 1), +3 (table 2) per worker."""
+    try:
+        import torch
+        from geeps_b200.parallel.ps import GeePs
+        from geeps_b200.utils.config import DEVICE_CPU
+        kw = dict(kw)
+        kw.setdefault("device", DEVICE_CPU)
+        cfg = make_cfg(world, base_port, num_tables=3, **kw)
+        g = GeePs(rank, cfg)
+        sizes = [64, 200, 17]
+        hs = [[g.virtual_read(t, list(range(n)), 0)] for t, n in enumerate(sizes)]
+        for t, n in enumerate(sizes):
+            hs[t].append(g.virtual_pre_update(t, list(range(n))))
+        for h in hs:
+            h.append(g.virtual_post_read(h[0]))
+            h.append(g.virtual_update(h[1]))
+        g.virtual_clock()
+        g.finish_virtual_iteration()
+        for r, u, pr, up in hs:
+            g.pre_update(u).zero_()
+        for r, u, pr, up in hs:
+            g.update(up)
+        g.clock()
+        g.start_iterations()
+        for c in range(clocks + 1):
+            xs = [g.read(r, asynchronous=False) for r, u, pr, up in hs]
+            vals = [(float(x.min()), float(x.max())) for x in xs]
+            bufs = [g.pre_update(u) for r, u, pr, up in hs]
+            for t, (r, u, pr, up) in enumerate(hs):
+                g.post_read(pr)
+                bufs[t].fill_(float(t + 1) if c < clocks else 0.0)
+                g.update(up)
+            g.clock()
+        stats = g.get_stats()
+        g.shutdown()
+        g.close()
+        q.put((rank, "ok", vals, stats["channels"], stats["comm_channels"], None))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))

@@ -11,7 +11,7 @@ import torch
 from geeps_b200.parallel.ps import GeePs, GeePsError
 from geeps_b200.utils.config import (DEVICE_CPU, PARTITION_ROUND_ROBIN, TABLE_SGD_MOMENTUM, GeePsConfig)
 
-from ps_workers import helloworld_worker, rmw_worker
+from ps_workers import helloworld_worker, multitable_worker, rmw_worker
 
 _port = [12000 + (os.getpid() % 300) * 40]   # below the ephemeral port range
 
@@ -299,3 +299,30 @@ def test_helloworld_with_two_comm_channels():
     for rank, _, final, seen, max_stale, stats in out:
         assert final == (60.0, 60.0), final
         assert max_stale <= 1
+
+
+def test_tables_are_split_over_independent_channels():
+    """num_comm_channels = 2 with three tables: tables 0 and 2 travel over channel 0 (port p), table 1 over
+    channel 1 (port p + 1) - its own server shard, sockets and threads.  Both channels' shards hold rows and saw
+    updates, and every table ends at the right value."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = next_port()
+    clocks = 12
+    procs = [ctx.Process(target=multitable_worker, args=(r, 2, port, clocks, q, dict(num_comm_channels=2))) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for o in sorted(out):
+        assert o[1] == "ok", o[2]
+        rank, _, vals, channels, nch, _ = o
+        assert nch == 2 and len(channels) == 2
+        assert vals == [(2.0 * clocks * (t + 1),) * 2 for t in range(3)], vals
+        assert channels[0]["port"] + 1 == channels[1]["port"]
+        # shard rows: tables 0 and 2 on channel 0, table 1 on channel 1 (range partition over two shards)
+        assert channels[0]["storage"]["nr_rows"] in (32 + 9, 32 + 8) and channels[1]["storage"]["nr_rows"] == 100
+        for ch in channels:
+            assert ch["storage"]["nr_update"] > 0 and ch["storage"]["nr_errors"] == 0
+            assert ch["server_router"]["msgs_received"] > 0
