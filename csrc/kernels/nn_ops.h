@@ -57,6 +57,15 @@ int geeps_lrn_backward(const void* x, const void* y, const void* rscale, const v
                        int C, int size, float alpha, float beta, int relu_mask, float* colsum, void* stream);
 // colsum (or NULL): C floats that receive the per-channel sums of dx (C % 8 == 0, window 3 / 5 / 7 only)
 int geeps_copy_f32(float* dst, const float* src, long long n, void* stream);
+// LRN across channels fused with the max pooling after it (dense input: g->ldx == g->C; window 3 / 5 / 7).
+// Forward keeps only the pooled tensor and the window codes; backward recomputes the normalisation from x and
+// delivers dx (gradient w.r.t. the LRN input) with an optional ReLU mask (x <= 0 -> 0) and, in colsum (C floats
+// or NULL), the per-channel sums of dx.
+int geeps_lrn_maxpool_supported(const GeepsPoolGeom* g, int size);
+int geeps_lrn_maxpool_forward(const void* x, void* p, void* argmax, const GeepsPoolGeom* g, int size, float alpha,
+                              float beta, float k, void* stream);
+int geeps_lrn_maxpool_backward(const void* x, const void* dp, const void* argmax, void* dx, const GeepsPoolGeom* g,
+                               int size, float alpha, float beta, float k, int relu_mask, float* colsum, void* stream);
 int geeps_maxpool_forward(const void* x, void* y, void* argmax, const GeepsPoolGeom* g, void* stream);
 int geeps_maxpool_backward(const void* dy, const void* argmax, void* dx, const GeepsPoolGeom* g, int accumulate,
                            void* stream);

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import functional as F
-from ..ops.layers import BF, LRN, BatchNorm, Conv2d, Layer, Pool, SoftmaxLoss
+from ..ops.layers import BF, LRN, BatchNorm, Conv2d, Layer, LRNMaxPool, Pool, SoftmaxLoss
 
 
 class Concat(Layer):
@@ -115,14 +115,24 @@ class Net:
 
     def setup(self, in_shape, device):
         s = self.input_layer.setup(in_shape, device)
-        for l in self.layers:
+        # an LRN directly followed by a max pooling becomes one fused layer (GEEPS_FUSE_LRN_POOL=0 keeps the pair)
+        fused, i = [], 0
+        while i < len(self.layers):
+            l = self.layers[i]
+            nxt = self.layers[i + 1] if i + 1 < len(self.layers) else None
+            if isinstance(l, LRN) and isinstance(nxt, Pool) and LRNMaxPool.fusable(l, nxt, s):
+                l = LRNMaxPool(l, nxt)
+                i += 1
             s = l.setup(s, device)
+            fused.append(l)
+            i += 1
+        self.layers = fused
         self.loss_layer.setup(s, device)
         self.device = device
         # conv + ReLU followed by LRN: the LRN backward already reads the ReLU output, so it applies the ReLU
         # mask to the gradient it hands down and the convolution skips its own masking pass
         for a, b in zip(self.layers, self.layers[1:]):
-            if isinstance(a, Conv2d) and a.relu and isinstance(b, LRN):
+            if isinstance(a, Conv2d) and a.relu and isinstance(b, (LRN, LRNMaxPool)):
                 a.dy_is_masked, b.mask_relu_input = True, True
                 if a.has_bias and b.C % 8 == 0 and b.size in (3, 5, 7):
                     # the same pass also sums the masked gradient per channel: the convolution's bias gradient

@@ -256,6 +256,29 @@ def maxpool_backward(dy, argmax, dx, g: PoolGeom, accumulate=False) -> None:
     launch(lib().geeps_maxpool_backward, "maxpool_backward", ptr(dy), ptr(argmax), ptr(dx), C.byref(g), int(accumulate), stream_ptr())
 
 
+def lrn_maxpool_supported(g: PoolGeom, size: int) -> bool:
+    return bool(lib().geeps_lrn_maxpool_supported(C.byref(g), int(size)))
+
+
+def lrn_maxpool_forward(x, p, argmax, g: PoolGeom, size=5, alpha=1e-4, beta=0.75, k=1.0) -> None:
+    """p = maxpool(LRN(x)) in one kernel; argmax receives the window codes (the only thing the backward needs
+    besides x)."""
+    assert x.is_contiguous() and x.dtype == bf16
+    launch(lib().geeps_lrn_maxpool_forward, "lrn_maxpool_forward", ptr(x), ptr(p), ptr(argmax), C.byref(g), int(size),
+           C.c_float(alpha), C.c_float(beta), C.c_float(k), stream_ptr())
+
+
+def lrn_maxpool_backward(x, dp, argmax, dx, g: PoolGeom, size=5, alpha=1e-4, beta=0.75, k=1.0, relu_mask=False,
+                         colsum=None) -> None:
+    """dx = gradient w.r.t. x of maxpool(LRN(x)) given dp; relu_mask zeroes it where x <= 0; colsum (fp32 [C])
+    receives the per-channel sums of dx."""
+    assert x.is_contiguous() and dx.is_contiguous()
+    assert colsum is None or (colsum.dtype == torch.float32 and colsum.numel() == g.C)
+    launch(lib().geeps_lrn_maxpool_backward, "lrn_maxpool_backward", ptr(x), ptr(dp), ptr(argmax), ptr(dx), C.byref(g),
+           int(size), C.c_float(alpha), C.c_float(beta), C.c_float(k), int(relu_mask),
+           ptr(colsum) if colsum is not None else None, stream_ptr())
+
+
 def avgpool_forward(x, y, g: PoolGeom) -> None:
     launch(lib().geeps_avgpool_forward, "avgpool_forward", ptr(x), ptr(y), C.byref(g), stream_ptr())
 

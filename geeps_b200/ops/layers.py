@@ -397,6 +397,61 @@ class LRN(Layer):
         return self.dx
 
 
+class LRNMaxPool(Layer):
+    """LRN across channels followed by max pooling as one fused kernel per direction (the normalised tensor and
+    its gradient never reach global memory; the backward recomputes the normalisation from the input).  Built by
+    Net.setup from an adjacent (LRN, max Pool) pair; `lrn` and `pool` keep the pair's definition."""
+
+    def __init__(self, lrn: "LRN", pool: "Pool"):
+        super().__init__()
+        self.lrn, self.pool = lrn, pool
+        self.size, self.alpha, self.beta, self.k = lrn.size, lrn.alpha, lrn.beta, lrn.k
+        self.mask_relu_input = False
+        self.bias_grad = None
+
+    @staticmethod
+    def fusable(lrn, pool, in_shape) -> bool:
+        if not (isinstance(lrn, LRN) and isinstance(pool, Pool) and pool.kind == "max" and pool.k > 0):
+            return False
+        if os.environ.get("GEEPS_FUSE_LRN_POOL", "1") == "0" or not torch.cuda.is_available():
+            return False
+        C = in_shape[-1]
+        g = F.pool_geom(in_shape, pool.k, pool.stride, pool.pad, C, C, pool.ceil_mode)
+        return F.lrn_maxpool_supported(g, lrn.size)
+
+    def setup(self, in_shape, device):
+        B, H, W, C = in_shape
+        self.in_shape, self.C = in_shape, C
+        p = self.pool
+        self.g = F.pool_geom(in_shape, p.k, p.stride, p.pad, C, C, p.ceil_mode)
+        self.out_shape = (B, self.g.OH, self.g.OW, C)
+        self.y = None
+        self.argmax = torch.empty(self.out_shape, dtype=torch.uint8, device=device)
+        self.dx = torch.empty(in_shape, dtype=BF, device=device)
+        self.device = device
+        return self.out_shape
+
+    def bind_output(self, y2d, ldy):
+        self.y = y2d
+        self.g.ldy = ldy
+
+    def set_output(self, flat):
+        self.y = flat[:self.out_numel()].view(self.out_shape)
+        self.g.ldy = self.out_shape[-1]
+
+    def forward(self, x):
+        if self.y is None:
+            self.y = torch.empty(self.out_shape, dtype=BF, device=self.device)
+        self.x = x.reshape(self.in_shape)
+        F.lrn_maxpool_forward(self.x, self.y, self.argmax, self.g, self.size, self.alpha, self.beta, self.k)
+        return self.y
+
+    def backward(self, dy):
+        F.lrn_maxpool_backward(self.x, dy, self.argmax, self.dx, self.g, self.size, self.alpha, self.beta, self.k,
+                               relu_mask=self.mask_relu_input, colsum=self.bias_grad)
+        return self.dx
+
+
 class Pool(Layer):
     def __init__(self, kind, k, stride, pad=0, ceil_mode=True):
         super().__init__()

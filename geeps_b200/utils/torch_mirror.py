@@ -93,6 +93,9 @@ class TorchMirror(nn.Module):
             self.loaders.append((f"{l.name}.gamma", lambda t, bn=bn: bn.weight.data.copy_(t)))
             self.loaders.append((f"{l.name}.beta", lambda t, bn=bn: bn.bias.data.copy_(t)))
             return [bn] + ([nn.ReLU()] if l.relu else []), c_true
+        if isinstance(l, GL.LRNMaxPool):
+            return [nn.LocalResponseNorm(l.size, l.alpha, l.beta, l.k),
+                    nn.MaxPool2d(l.pool.k, l.pool.stride, l.pool.pad, ceil_mode=l.pool.ceil_mode)], c_true
         if isinstance(l, GL.LRN):
             return [nn.LocalResponseNorm(l.size, l.alpha, l.beta, l.k)], c_true
         if isinstance(l, GL.Pool):

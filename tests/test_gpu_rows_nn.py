@@ -169,6 +169,56 @@ def test_lrn_forward_backward():
     assert torch.allclose(cs, dxm.float().sum(0), atol=1e-2, rtol=1e-4)
 
 
+@pytest.mark.parametrize("H,Cc,k,s,p,size", [(13, 96, 3, 2, 0, 5), (27, 256, 3, 2, 0, 5), (16, 24, 3, 2, 0, 3),
+                                              (9, 40, 3, 1, 1, 5), (8, 8, 2, 2, 0, 7)])
+def test_fused_lrn_maxpool_matches_fp32_reference_and_the_unfused_kernels(H, Cc, k, s, p, size):
+    """maxpool(LRN(x)) in one kernel per direction against torch in fp32 (LRN + max_pool2d + autograd) and against
+    this library's separate LRN and pooling kernels; with the ReLU mask and the per-channel sums of dx."""
+    torch.manual_seed(11)
+    B = 3
+    alpha, beta, kk = 1e-2, 0.75, 1.0
+    x = torch.relu(torch.randn(B, H, H, Cc, device=DEV) * 3).to(BF)        # a ReLU output, as in the network
+    g = F.pool_geom(x.shape, k, s, p, Cc, Cc)
+    assert F.lrn_maxpool_supported(g, size)
+    pooled = torch.empty(B, g.OH, g.OW, Cc, dtype=BF, device=DEV)
+    arg = torch.empty(B, g.OH, g.OW, Cc, dtype=torch.uint8, device=DEV)
+    F.lrn_maxpool_forward(x, pooled, arg, g, size, alpha, beta, kk)
+    # unfused kernels of this library
+    y = torch.empty_like(x)
+    scale = torch.empty_like(x)
+    F.lrn_forward(x.view(-1, Cc), y.view(-1, Cc), scale.view(-1, Cc), size, alpha, beta, kk)
+    pooled_u = torch.empty_like(pooled)
+    arg_u = torch.empty_like(arg)
+    F.maxpool_forward(y, pooled_u, arg_u, g)
+    assert torch.equal(pooled, pooled_u) and torch.equal(arg, arg_u)
+    # fp32 reference
+    xr = x.float().permute(0, 3, 1, 2).requires_grad_(True)
+    yr = TF.max_pool2d(TF.local_response_norm(xr, size, alpha=alpha, beta=beta, k=kk), k, s, p, ceil_mode=True)
+    assert yr.shape[2] == g.OH
+    assert torch.allclose(pooled.float().permute(0, 3, 1, 2), yr, atol=3e-2, rtol=2e-2)
+    dp = torch.randn_like(pooled)
+    yr.backward(dp.float().permute(0, 3, 1, 2))
+    ref = xr.grad.permute(0, 2, 3, 1)
+    dx = torch.empty_like(x)
+    cs = torch.full((Cc,), 7.0, device=DEV)
+    F.lrn_maxpool_backward(x, dp, arg, dx, g, size, alpha, beta, kk, relu_mask=True, colsum=cs)
+    ref_masked = torch.where(x > 0, ref, torch.zeros_like(ref))
+    bad = ((dx.float() - ref_masked).abs() > 3e-2 + 3e-2 * ref_masked.abs()).float().mean().item()
+    assert bad < 5e-3, bad       # the window maximum is taken on bf16-rounded values: rare near-ties pick another element
+    assert torch.allclose(cs, dx.float().sum((0, 1, 2)), atol=2e-2, rtol=1e-3)
+    # unfused backward of this library (pool backward, then LRN backward with the mask)
+    dy_u = torch.empty_like(x)
+    F.maxpool_backward(dp, arg_u, dy_u, g)
+    dx_u = torch.empty_like(x)
+    F.lrn_backward(x.view(-1, Cc), y.view(-1, Cc), scale.view(-1, Cc), dy_u.view(-1, Cc), dx_u.view(-1, Cc), size, alpha,
+                   beta, relu_mask=True)
+    assert torch.allclose(dx.float(), dx_u.float(), atol=4e-2, rtol=4e-2)
+    # without the mask and the sums
+    dx2 = torch.empty_like(x)
+    F.lrn_maxpool_backward(x, dp, arg, dx2, g, size, alpha, beta, kk)
+    assert torch.equal(torch.where(x > 0, dx2, torch.zeros_like(dx2)), dx)
+
+
 @pytest.mark.parametrize("k,s,p,H", [(3, 2, 0, 13), (3, 2, 0, 16), (3, 1, 1, 9), (2, 2, 0, 8)])
 def test_maxpool_avgpool(k, s, p, H):
     torch.manual_seed(4)
