@@ -95,8 +95,45 @@ def bench_rows():
                           "frac_of_hbm": round(gbs / hbm, 3), "peak_source": src}), flush=True)
 
 
+def bench_lrn_pool():
+    """LRN + max pooling of AlexNet (after conv1: 55x55x96, after conv2: 27x27x256; batch 256): the fused kernels
+    against the separate LRN and pooling kernels, with the bytes each formulation has to move."""
+    dev = torch.device("cuda")
+    _, hbm, src = _peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    for name, H, Cc in (("lrn+pool after conv1", 55, 96), ("lrn+pool after conv2", 27, 256)):
+        B = 256
+        x = torch.relu(torch.randn(B, H, H, Cc, device=dev)).to(BF)
+        g = F.pool_geom(x.shape, 3, 2, 0, Cc, Cc)
+        pooled = torch.empty(B, g.OH, g.OW, Cc, dtype=BF, device=dev)
+        arg = torch.empty(B, g.OH, g.OW, Cc, dtype=torch.uint8, device=dev)
+        dp = torch.randn_like(pooled)
+        dx = torch.empty_like(x)
+        cs = torch.zeros(Cc, device=dev)
+        y, scale, dy = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        x2, y2, s2, dy2, dx2 = (t.view(-1, Cc) for t in (x, y, scale, dy, dx))
+        nx, npool = x.numel() * 2, pooled.numel() * 2
+        cases = [
+            ("fused forward", lambda: F.lrn_maxpool_forward(x, pooled, arg, g), nx + npool + npool // 2),
+            ("fused backward", lambda: F.lrn_maxpool_backward(x, dp, arg, dx, g, relu_mask=True, colsum=cs),
+             2 * nx + npool + npool // 2),
+            ("separate forward", lambda: (F.lrn_forward(x2, y2, s2), F.maxpool_forward(y, pooled, arg, g)),
+             4 * nx + npool + npool // 2),
+            ("separate backward", lambda: (F.maxpool_backward(dp, arg, dy, g),
+                                           F.lrn_backward(x2, y2, s2, dy2, dx2, relu_mask=True, colsum=cs)),
+             6 * nx + npool + npool // 2),
+        ]
+        for what, fn, nbytes in cases:
+            t = timeit(fn, flush=flush)
+            gbs = nbytes / t / 1e6
+            print(json.dumps({"kernel": f"{name}: {what}", "ms": round(t, 4), "algorithmic_mb": round(nbytes / 1e6, 1),
+                              "gb_s": round(gbs, 1), "frac_of_hbm": round(gbs / hbm, 3), "peak_source": src}), flush=True)
+
+
 def main():
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("lrn_pool", "all"):
+        bench_lrn_pool()
     if what in ("gemm", "all"):
         bench_gemm()
     if what in ("rows", "all"):

@@ -6,6 +6,7 @@ once and launches the kernel of interest three times.
   gemm_dgrad  conv3 data-gradient shape (small K, MN-major B, output-heavy)
   push_apply  fused reduce + momentum-SGD apply + publish over a 256 MB table (1 rank)
   lrn         LRN forward + backward on a conv1-sized activation
+  lrn_pool    LRN fused with the 3x3 stride-2 max pooling after it, forward + backward (256 x 55 x 55 x 96)
   pull_gemm   fused pull + GEMM on an fc6-shaped layer (4 local shards)
   conv_fwd / conv_dgrad / conv_wgrad   implicit-GEMM convolution, conv3 shape (256 x 13 x 13, 256 -> 384, 3x3)
   conv1_fwd   AlexNet conv1 after space-to-depth (256 x 57 x 57 x 48 -> 96, 3x3, no padding)
@@ -62,6 +63,18 @@ def main():
         for _ in range(4):
             F.lrn_forward(x, y, scale)
             F.lrn_backward(x, y, scale, y, dx)
+    elif case == "lrn_pool":
+        B, H, Cc = 256, 55, 96
+        x = torch.relu(torch.randn(B, H, H, Cc, device=dev)).to(BF)
+        g = F.pool_geom(x.shape, 3, 2, 0, Cc, Cc)
+        pooled = torch.empty(B, g.OH, g.OW, Cc, dtype=BF, device=dev)
+        arg = torch.empty(B, g.OH, g.OW, Cc, dtype=torch.uint8, device=dev)
+        dp = torch.randn_like(pooled)
+        dx = torch.empty_like(x)
+        cs = torch.zeros(Cc, device=dev)
+        for _ in range(3):
+            F.lrn_maxpool_forward(x, pooled, arg, g)
+            F.lrn_maxpool_backward(x, dp, arg, dx, g, relu_mask=True, colsum=cs)
     elif case == "pull_gemm":
         M, N, K, shards = 256, 4096, 9216, 4
         x = (torch.randn(M, K, device=dev) * 0.3).to(BF)
