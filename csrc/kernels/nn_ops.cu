@@ -330,6 +330,41 @@ relu_backward_2d_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
     st8(dx + p * lddx + c, o);
   }
 }
+// ReLU backward fused with the per-channel sums of its result (the bias gradient of the layer whose output y is):
+// dx = y > 0 ? dy : 0, out[c] += sum over pixels of dx.  Every thread keeps one 8-channel slot and strides over
+// the pixels, as in channel_reduce_kernel.
+__global__ void __launch_bounds__(256)
+relu_backward_colsum_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y, bf16* __restrict__ dx,
+                            float* __restrict__ out, long long P, int C, long long lddy, long long ldy, long long lddx) {
+  extern __shared__ float sacc[];  // [C]
+  for (int i = threadIdx.x; i < C; i += blockDim.x) sacc[i] = 0.f;
+  __syncthreads();
+  const int cv = C >> 3;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long groups = nthreads / cv;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (tid < groups * cv) {
+    const int c = (int)(tid % cv) * 8;
+    float a[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = 0.f;
+    for (long long p = tid / cv; p < P; p += groups) {
+      const Bf8 d = ld8(dy + p * lddy + c), v = ld8(y + p * ldy + c);
+      Bf8 o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const bool on = bf(v.v[e]) > 0.f;
+        o.v[e] = on ? d.v[e] : __float2bfloat16(0.f);
+        a[e] += on ? bf(d.v[e]) : 0.f;
+      }
+      st8(dx + p * lddx + c, o);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&sacc[c + e], a[e]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < C; i += blockDim.x) atomicAdd(out + i, sacc[i]);
+}
 // dst += src over 2-D views (sum of branch gradients)
 __global__ void __launch_bounds__(256)
 add_2d_kernel(bf16* __restrict__ dst, const bf16* __restrict__ src, long long P, int C, long long ldd, long long lds) {
@@ -1049,6 +1084,20 @@ int geeps_relu_backward_2d(const void* dy, const void* y, void* dx, long long P,
   if (C % 8 || lddy % 8 || ldy % 8 || lddx % 8) return (int)cudaErrorInvalidValue;
   relu_backward_2d_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>((const bf16*)dy, (const bf16*)y,
                                                                                  (bf16*)dx, P, C, lddy, ldy, lddx);
+  return CK();
+}
+int geeps_relu_backward_colsum(const void* dy, const void* y, void* dx, float* colsum, long long P, int C,
+                               long long lddy, long long ldy, long long lddx, void* stream) {
+  if (C % 8 || lddy % 8 || ldy % 8 || lddx % 8 || C > 8192) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(colsum, 0, sizeof(float) * C, st);
+  // enough CTAs that every pixel lane has work, a whole number of channel slots per grid
+  long long want = (P * (C / 8) + 255) / 256;
+  if (want > geeps_sm_count() * 8) want = geeps_sm_count() * 8;
+  const long long min_blocks = ((long long)(C / 8) + 255) / 256;
+  if (want < min_blocks) want = min_blocks;
+  relu_backward_colsum_kernel<<<(int)(want < 1 ? 1 : want), 256, C * sizeof(float), st>>>(
+      (const bf16*)dy, (const bf16*)y, (bf16*)dx, colsum, P, C, lddy, ldy, lddx);
   return CK();
 }
 int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long ldd, long long lds, void* stream) {

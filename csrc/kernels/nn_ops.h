@@ -38,6 +38,9 @@ int geeps_bn_backward(const void* x, const void* dy, const void* y, void* dx, co
                       const float* gamma, float* sums, float* dgamma, float* dbeta, long long P, int C,
                       long long ldx, long long lddy, long long lddx, int relu, float grad_scale, void* stream);
 // out[c] (+)= scale * sum_p x[p][c]
+// dx = y > 0 ? dy : 0 and colsum[c] = sum over the P pixels of dx (C % 8 == 0, C <= 8192), one pass
+int geeps_relu_backward_colsum(const void* dy, const void* y, void* dx, float* colsum, long long P, int C,
+                               long long lddy, long long ldy, long long lddx, void* stream);
 int geeps_colsum(const void* x, float* out, long long P, int C, long long ldx, float scale, int zero_first,
                  void* stream);
 int geeps_relu_backward(const void* dy, const void* y, void* dx, long long n, void* stream);

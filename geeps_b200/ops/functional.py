@@ -186,6 +186,14 @@ def relu_backward_2d(dy2d, y2d, dx2d) -> None:
                                        C.c_longlong(_ld(y2d)), C.c_longlong(_ld(dx2d)), stream_ptr())
 
 
+def relu_backward_colsum(dy2d, y2d, dx2d, colsum_out) -> None:
+    """dx = dy where y > 0 else 0, and colsum_out[c] = sum of dx over the rows, in one pass."""
+    P, Cc = dy2d.shape
+    assert colsum_out.dtype == torch.float32 and colsum_out.numel() == Cc and colsum_out.is_contiguous()
+    launch(lib().geeps_relu_backward_colsum, "relu_backward_colsum", ptr(dy2d), ptr(y2d), ptr(dx2d), ptr(colsum_out),
+           C.c_longlong(P), Cc, C.c_longlong(_ld(dy2d)), C.c_longlong(_ld(y2d)), C.c_longlong(_ld(dx2d)), stream_ptr())
+
+
 def add_2d(dst2d, src2d) -> None:
     P, Cc = dst2d.shape
     launch(lib().geeps_add_bf16_2d, "add_bf16_2d", ptr(dst2d), ptr(src2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dst2d)),

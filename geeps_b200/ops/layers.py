@@ -241,10 +241,15 @@ class Conv2d(Layer):
         # dy: [M, cout] bf16 (possibly a slice view of a wider tensor)
         if dy.dim() != 2:
             dy = dy.view(self.M, self.cout)
+        bias_done = False
         if self.relu and not self.dy_is_masked:
-            dy = self._relu_mask(dy)
+            if self.has_bias and self.bias_grad_src is None and self.cout % 8 == 0 and self.cout <= 8192:
+                dy = self._relu_mask(dy, colsum=self.g32["bias"])     # mask and bias gradient in one pass
+                bias_done = True
+            else:
+                dy = self._relu_mask(dy)
         gw = self.g32["weight"]
-        if self.has_bias:
+        if self.has_bias and not bias_done:
             if self.bias_grad_src is not None:
                 F.copy_f32(self.g32["bias"], self.bias_grad_src)
             else:
@@ -273,10 +278,13 @@ class Conv2d(Layer):
             F.col_mask(gw, self.col_mask_dev)
         return self.dx
 
-    def _relu_mask(self, dy):
+    def _relu_mask(self, dy, colsum=None):
         if not hasattr(self, "_dy_masked"):
             self._dy_masked = torch.empty(self.M, self.cout, dtype=BF, device=self.device)
-        F.relu_backward_2d(dy, self.y, self._dy_masked)
+        if colsum is not None:
+            F.relu_backward_colsum(dy, self.y, self._dy_masked, colsum)
+        else:
+            F.relu_backward_2d(dy, self.y, self._dy_masked)
         return self._dy_masked
 
 
@@ -316,9 +324,14 @@ class Linear(Layer):
         if self.relu:
             if not hasattr(self, "_dym"):
                 self._dym = torch.empty(self.B, self.out_ld, dtype=BF, device=self.device)[:, :self.out]
-            F.relu_backward_2d(dy, self.y, self._dym)
+            if self.out % 8 == 0 and self.out <= 8192:
+                F.relu_backward_colsum(dy, self.y, self._dym, self.g32["bias"])
+            else:
+                F.relu_backward_2d(dy, self.y, self._dym)
+                F.colsum(self._dym, self.g32["bias"])
             dy = self._dym
-        F.colsum(dy, self.g32["bias"])
+        else:
+            F.colsum(dy, self.g32["bias"])
         # dW[out, in] = dy^T @ x ; dx[B, in] = dy @ W
         F.gemm(dy, self.x, self.g32["weight"], a_mn=True, b_mn=True, split_k=0)
         if self.need_dx:

@@ -169,6 +169,20 @@ def test_lrn_forward_backward():
     assert torch.allclose(cs, dxm.float().sum(0), atol=1e-2, rtol=1e-4)
 
 
+def test_relu_backward_with_column_sums_in_one_pass():
+    torch.manual_seed(12)
+    P, Cc = 3000, 384
+    wide_dy = torch.randn(P, Cc + 16, device=DEV).to(BF)
+    dy = wide_dy[:, 8:8 + Cc]                                # a channel slice of a wider tensor
+    y = torch.relu(torch.randn(P, Cc, device=DEV)).to(BF)
+    dx = torch.empty(P, Cc, dtype=BF, device=DEV)
+    cs = torch.full((Cc,), 3.0, device=DEV)
+    F.relu_backward_colsum(dy, y, dx, cs)
+    ref = torch.where(y > 0, dy, torch.zeros_like(dy))
+    assert torch.equal(dx, ref)
+    assert torch.allclose(cs, ref.float().sum(0), atol=1e-2, rtol=1e-4)
+
+
 @pytest.mark.parametrize("H,Cc,k,s,p,size", [(13, 96, 3, 2, 0, 5), (27, 256, 3, 2, 0, 5), (16, 24, 3, 2, 0, 3),
                                               (9, 40, 3, 1, 1, 5), (8, 8, 2, 2, 0, 7)])
 def test_fused_lrn_maxpool_matches_fp32_reference_and_the_unfused_kernels(H, Cc, k, s, p, size):
