@@ -85,6 +85,16 @@ void geeps_config_set_table_mode(void* c, int table, int mode) {
   if ((int)cfg->table_modes.size() <= table) cfg->table_modes.resize((size_t)table + 1, cfg->table_mode);
   cfg->table_modes[(size_t)table] = mode;
 }
+void geeps_config_set_table_pull(void* c, int table, int pull) {
+  GeePsConfig* cfg = static_cast<GeePsConfig*>(c);
+  if ((int)cfg->table_pull.size() <= table) cfg->table_pull.resize((size_t)table + 1, 0);
+  cfg->table_pull[(size_t)table] = pull;
+}
+void geeps_config_set_table_partition_align(void* c, int table, long long rows) {
+  GeePsConfig* cfg = static_cast<GeePsConfig*>(c);
+  if ((int)cfg->table_partition_align.size() <= table) cfg->table_partition_align.resize((size_t)table + 1, 1);
+  cfg->table_partition_align[(size_t)table] = rows > 0 ? (size_t)rows : 1;
+}
 void geeps_config_set_table_fp32_from_row(void* c, int table, long long row) {
   GeePsConfig* cfg = static_cast<GeePsConfig*>(c);
   if ((int)cfg->table_fp32_from_row.size() <= table) cfg->table_fp32_from_row.resize((size_t)table + 1, 0);
@@ -138,6 +148,9 @@ void geeps_post_local_access(void* g, int handle, void* stream) {
   static_cast<GeePs*>(g)->impl()->postlocalaccess_batch(handle, stream);
 }
 void geeps_clock(void* g) { static_cast<GeePs*>(g)->Clock(); }
+int geeps_read_pull(void* g, int handle, void* info, void* stream) {
+  return static_cast<GeePs*>(g)->ReadPull(handle, static_cast<GeePs::PullInfo*>(info), stream) ? 1 : 0;
+}
 void* geeps_read_bf16(void* g, int handle) { return static_cast<GeePs*>(g)->ReadBf16(handle); }
 int geeps_enable_device_clock(void* g) { return static_cast<GeePs*>(g)->EnableDeviceClock() ? 1 : 0; }
 void geeps_advance_replayed_clock(void* g) { static_cast<GeePs*>(g)->AdvanceReplayedClock(); }
@@ -225,6 +238,11 @@ int geeps_planner_compile_json(void* p, char* buf, int cap) {
 // ---------------- partitioner ----------------
 void geeps_partition_range(int kind, long long num_rows, int num_shards, int shard, long long* out3) {
   ShardRange r = Partitioner(kind, (size_t)num_rows, (size_t)num_shards).range_of((size_t)shard);
+  out3[0] = (long long)r.start; out3[1] = (long long)r.stride; out3[2] = (long long)r.count;
+}
+void geeps_partition_range_aligned(int kind, long long num_rows, int num_shards, int shard, long long align,
+                                   long long* out3) {
+  ShardRange r = Partitioner(kind, (size_t)num_rows, (size_t)num_shards, (size_t)align).range_of((size_t)shard);
   out3[0] = (long long)r.start; out3[1] = (long long)r.stride; out3[2] = (long long)r.count;
 }
 int geeps_partition_shard_of(int kind, long long num_rows, int num_shards, long long i) {

@@ -5,6 +5,8 @@
 #include <stdio.h>
 #include <unistd.h>
 
+#include <string.h>
+
 #include <fstream>
 
 namespace geeps_b200 {
@@ -73,6 +75,8 @@ ClientLib::ClientLib(uint process_id, const GeePsConfig& config) : process_id_(p
   pc.device_is_gpu = gpu_;
   pc.allow_direct = nvlink_;
   pc.update_ring = nvlink_;
+  pc.partition_align = config.table_partition_align;
+  for (int v : config.table_pull) pc.pull_tables.push_back(nvlink_ && v ? 1 : 0);
   compiler_.reset(new PlanCompiler(pc));
   last_heartbeat_.assign(num_processes_, now_seconds());
   peer_clock_.assign(num_processes_, 0);
@@ -266,6 +270,43 @@ bool ClientLib::read_batch(int handle, RowData** buf, void* stream, bool async) 
   stats_.read_time += now_seconds() - t0;
   op_account(handle, t0);
   return ok && error_code_.load() == 0;
+}
+
+// ReadPull of an uncached table: the freshness wait and the fp32 tail (rows from table_fp32_from_row on) are
+// enqueued here; the leading rows are described, not copied - the caller's kernel reads them from the shards.
+bool ClientLib::read_pull(int handle, GeePs::PullInfo* info, void* stream) {
+  const double t0 = now_seconds();
+  memset(info, 0, sizeof(*info));
+  if (!check_order(handle, OP_READ)) return false;
+  const OpInfo& op = plan_.ops[handle];
+  if (!nvlink_ || !fabric_.active || op.table >= fabric_.tables.size() || !fabric_.tables[op.table].pull) {
+    set_error(ERR_ORDER, "ReadPull on a table that is not an uncached (pull) table of the NVLINK transport");
+    return false;
+  }
+  void* st = op_stream(stream);
+  last_app_stream_ = st;
+  CachedTable& ct = *tables_[(uint)op.table];
+  const TableArena& ta = fabric_.tables[op.table];
+  fabric_wait_data_age(ct, (uint)op.table, clock_ - op.slack - 1, st);
+  if (ta.tail_rows) fabric_pull_rows((uint)op.table, reinterpret_cast<RowData*>(fabric_.base + ta.tail_off), ta.tail_from, st);
+  info->num_shards = (int)num_processes_;
+  for (uint s = 0; s < num_processes_ && s < 8; ++s) {
+    const ShardRange& r = ct.plan->shard_ranges[s];
+    info->shard_bf16[s] = config_.bf16_compute_cache ? fabric_.peer_base[s] + ta.master16_off : nullptr;
+    info->shard_fp32[s] = reinterpret_cast<const float*>(fabric_.peer_base[s] + ta.master_off);
+    info->row_start[s] = (long long)r.start;
+    info->row_count[s] = (long long)r.count;
+  }
+  info->tail = ta.tail_rows ? reinterpret_cast<RowData*>(fabric_.base + ta.tail_off) : nullptr;
+  info->tail_from_row = (long long)ta.tail_from;
+  info->tail_rows = (long long)ta.tail_rows;
+  accessed_clock_[handle] = clock_;
+  stats_.nr_read++;
+  stats_.nr_read_pull++;
+  stats_.rows_read += op.rows.size();
+  stats_.read_time += now_seconds() - t0;
+  op_account(handle, t0);
+  return error_code_.load() == 0;
 }
 
 void* ClientLib::read_bf16(int handle) {

@@ -107,6 +107,9 @@ struct CachedTable {
 // buffer is peer_base + the same offset.
 struct TableArena {
   size_t cache_off = 0, cache16_off = 0, ring_off = 0, master_off = 0, momentum_off = 0, flags_off = 0;
+  size_t master16_off = 0, tail_off = 0;  // uncached tables: the shard's bf16 copy of its rows; this worker's fp32 tail
+  size_t tail_from = 0, tail_rows = 0;
+  bool pull = false;                      // uncached: no cache / cache16 regions
   size_t rows = 0, max_owned = 0;
   int ring_slots = 1;
   int comm_lane = 0;                      // which comm stream carries this table's pushes
@@ -170,6 +173,7 @@ class ClientLib {
   void iterate();
   void start_opseq();
   void* read_bf16(int handle);
+  bool read_pull(int handle, GeePs::PullInfo* info, void* stream);
   // device-resident clock (NVLINK transport): see clientlib_fabric.cpp
   bool enable_device_clock();
   void advance_replayed_iteration();
@@ -257,6 +261,7 @@ class ClientLib {
   int stamp_arg(iter_t stamp) const { return device_clock_ ? (int)(stamp - clock_) : (int)stamp; }
   const int* clock_ref() const { return device_clock_; }
   void fabric_read_rmw(const OpInfo& op, RowData* dst, void* stream);
+  void fabric_pull_rows(uint table_id, RowData* dst, size_t row_from, void* stream);
   float* fabric_cache_ptr(uint table_id, int rank) const;
   float* fabric_ring_ptr(uint table_id, int rank, iter_t clock) const;
 

@@ -21,6 +21,11 @@ const long long kNoLimit = (long long)1 << 62;
 bool ClientLib::read_row_batch_param_cache(const OpInfo& op, RowData* dst, void* stream) {
   CachedTable& ct = *tables_[(uint)op.table];
   const size_t n = op.rows.size();
+  if (nvlink_ && ct.plan->pull) {
+    // uncached table: fetch every row from the shard that owns it (the caller enqueued the freshness wait)
+    fabric_pull_rows((uint)op.table, dst, 0, stream);
+    return true;
+  }
   if (nvlink_ && config_.read_my_writes && ct.plan->slack > 0) {
     fabric_read_rmw(op, dst, stream);
     return true;

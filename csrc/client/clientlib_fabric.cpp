@@ -31,6 +31,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kFlagBytes = 256;
 constexpr size_t kPushReadyOff = 0, kDataAgeOff = 32, kGlobalClockOff = 64, kCtaCounterOff = 68, kPublishBeginOff = 96;
 constexpr size_t kPushTimingRing = 64;
+constexpr size_t kPullCounterOff = 72;    // per table: scratch counter of the pull kernel (beside the push kernel's)
 constexpr size_t kDeviceClockOff = 64;    // inside the 256-byte status area, after the 4 status words
 }  // namespace
 
@@ -54,8 +55,18 @@ bool ClientLib::fabric_setup(std::string* err) {
     ta.rows = tp.rows.size();
     ta.ring_slots = tp.num_oplog_entries;
     for (const ShardRange& r : tp.shard_ranges) ta.max_owned = std::max(ta.max_owned, r.count);
-    ta.cache_off = off; off = align_up(off + ta.rows * kRowBytes, 256);
-    if (config_.bf16_compute_cache) { ta.cache16_off = off; off = align_up(off + ta.rows * kRowBytes / 2, 256); }
+    ta.pull = tp.pull;
+    if (!ta.pull) {
+      ta.cache_off = off; off = align_up(off + ta.rows * kRowBytes, 256);
+      if (config_.bf16_compute_cache) { ta.cache16_off = off; off = align_up(off + ta.rows * kRowBytes / 2, 256); }
+    } else {
+      // uncached: the shard keeps a bf16 copy of the rows it owns; the worker only has room for the fp32 tail
+      if (config_.bf16_compute_cache) { ta.master16_off = off; off = align_up(off + ta.max_owned * kRowBytes / 2, 256); }
+      ta.tail_from = tp.table_id < config_.table_fp32_from_row.size() ? config_.table_fp32_from_row[tp.table_id] : 0;
+      if (ta.tail_from > ta.rows) ta.tail_from = ta.rows;
+      ta.tail_rows = ta.tail_from > 0 ? ta.rows - ta.tail_from : 0;     // 0: no split, a generic Read pulls everything
+      if (ta.tail_rows) { ta.tail_off = off; off = align_up(off + ta.tail_rows * kRowBytes, 256); }
+    }
     ta.ring_off = off; off = align_up(off + (size_t)ta.ring_slots * ta.rows * kRowBytes, 256);
     ta.master_off = off; off = align_up(off + ta.max_owned * kRowBytes, 256);
     ta.momentum_off = off; off = align_up(off + ta.max_owned * kRowBytes, 256);
@@ -286,10 +297,11 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
   memset(&p, 0, sizeof(p));
   for (uint r = 0; r < num_processes_; ++r) {
     p.upd[r] = fabric_ring_ptr(table_id, (int)r, clock);
-    p.cache[r] = fabric_cache_ptr(table_id, (int)r);
-    p.cache16[r] = config_.bf16_compute_cache ? (void*)(fabric_.peer_base[r] + ta.cache16_off) : nullptr;
+    p.cache[r] = ta.pull ? nullptr : fabric_cache_ptr(table_id, (int)r);
+    p.cache16[r] = (config_.bf16_compute_cache && !ta.pull) ? (void*)(fabric_.peer_base[r] + ta.cache16_off) : nullptr;
     p.data_age[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kDataAgeOff);
   }
+  p.master16 = (ta.pull && config_.bf16_compute_cache) ? (void*)(fabric_.base + ta.master16_off) : nullptr;
   const ShardRange& own = ct.plan->shard_ranges[process_id_];
   p.master = reinterpret_cast<float*>(fabric_.base + ta.master_off);
   p.momentum = reinterpret_cast<float*>(fabric_.base + ta.momentum_off);
@@ -366,6 +378,7 @@ void ClientLib::fabric_read_rmw(const OpInfo& op, RowData* dst, void* stream) {
   p.wait_budget_ns = (unsigned long long)config_.device_wait_budget_us * 1000ull;
   p.n_ranks = (int)num_processes_;
   p.partition_kind = config_.partitioner;
+  p.partition_per = (long long)ct.plan->partition_per;
   p.ring_slots = ta.ring_slots;
   p.clock = stamp_arg(clock_);
   p.clock_ref = clock_ref();
@@ -438,6 +451,38 @@ void ClientLib::advance_replayed_iteration() {
                   std::to_string(fabric_.host_status[1]) + ", detail " + std::to_string(fabric_.host_status[2]) +
                   ", seen " + std::to_string(fabric_.host_status[3]) + ")");
   }
+}
+
+// Rows [row_from, end) of an uncached table, fetched from the master rows of the shards that own them into `dst`
+// (row row_from lands at dst[0]).  The stream has already waited for the table's freshness condition, and a
+// shard stamps data_age only after its master rows are written, so the kernel needs no wait of its own.
+void ClientLib::fabric_pull_rows(uint table_id, RowData* dst, size_t row_from, void* stream) {
+  CachedTable& ct = *tables_[table_id];
+  const TableArena& ta = fabric_.tables[table_id];
+  GeepsPullParams p;
+  memset(&p, 0, sizeof(p));
+  for (uint s = 0; s < num_processes_; ++s) {
+    const ShardRange& r = ct.plan->shard_ranges[s];
+    p.master[s] = reinterpret_cast<const float*>(fabric_.peer_base[s] + ta.master_off);
+    p.global_clock[s] = nullptr;
+    p.n_owned[s] = (long long)r.count;
+    p.row_start[s] = (long long)r.start;
+    p.row_stride[s] = (long long)r.stride;
+  }
+  p.cache = reinterpret_cast<float*>(dst);
+  p.cache16 = nullptr;
+  p.data_age_local = nullptr;
+  p.cta_counter = reinterpret_cast<int*>(fabric_.base + ta.flags_off + kPullCounterOff);
+  p.status = reinterpret_cast<int*>(fabric_.base + fabric_.status_off);
+  p.total_rows = (long long)ta.rows;
+  p.wait_budget_ns = (unsigned long long)config_.device_wait_budget_us * 1000ull;
+  p.n_ranks = (int)num_processes_;
+  p.rank = (int)process_id_;
+  p.needed_stamp = 0;
+  p.row_from = (long long)row_from;
+  p.row_base = (long long)row_from;
+  geeps_ps_pull(&p, 0, stream);
+  stats_.rows_pulled += ta.rows - row_from;
 }
 
 // Errors recorded by kernels (expired waits, failed bounds checks) surface here.  The device block

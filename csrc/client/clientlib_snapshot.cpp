@@ -174,11 +174,16 @@ bool ClientLib::load_snapshot(const std::string& dir) {
     for (size_t k = 0; k < own.count; ++k) { mine[k] = full[own.start + k * own.stride]; mine_mom[k] = full_mom[own.start + k * own.stride]; }
     if (nvlink_) {
       const TableArena& ta = fabric_.tables[t];
-      cudaMemcpy(fabric_.base + ta.cache_off, full.data(), full.size() * sizeof(RowData), cudaMemcpyHostToDevice);
-      if (config_.bf16_compute_cache)
-        geeps_f32_to_bf16(reinterpret_cast<const float*>(fabric_.base + ta.cache_off), fabric_.base + ta.cache16_off,
-                          (long long)(full.size() * ROW_DATA_SIZE), default_stream_);
+      if (!ta.pull) {
+        cudaMemcpy(fabric_.base + ta.cache_off, full.data(), full.size() * sizeof(RowData), cudaMemcpyHostToDevice);
+        if (config_.bf16_compute_cache)
+          geeps_f32_to_bf16(reinterpret_cast<const float*>(fabric_.base + ta.cache_off), fabric_.base + ta.cache16_off,
+                            (long long)(full.size() * ROW_DATA_SIZE), default_stream_);
+      }
       if (own.count) cudaMemcpy(fabric_.base + ta.master_off, mine.data(), own.count * sizeof(RowData), cudaMemcpyHostToDevice);
+      if (ta.pull && config_.bf16_compute_cache && own.count)   // uncached table: the shard's bf16 copy of its rows
+        geeps_f32_to_bf16(reinterpret_cast<const float*>(fabric_.base + ta.master_off), fabric_.base + ta.master16_off,
+                          (long long)(own.count * ROW_DATA_SIZE), default_stream_);
       if (own.count && any_mom) cudaMemcpy(fabric_.base + ta.momentum_off, mine_mom.data(), own.count * sizeof(RowData), cudaMemcpyHostToDevice);
       std::vector<int> flags(kRowFloats / 2, 0);
       for (int i = 0; i < 8; ++i) { flags[i] = snap_clock; flags[8 + i] = snap_clock; }   // push_ready, data_age stamps

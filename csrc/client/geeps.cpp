@@ -47,6 +47,7 @@ std::string GeePs::LastErrorString() const { return impl_->last_error_string(); 
 bool GeePs::SaveSnapshot(const std::string& dir) { return impl_->save_snapshot(dir); }
 bool GeePs::LoadSnapshot(const std::string& dir) { return impl_->load_snapshot(dir); }
 std::string GeePs::PlanJson() const { return impl_->plan_json(); }
+bool GeePs::ReadPull(int handle, PullInfo* info, void* cuda_stream) { return impl_->read_pull(handle, info, cuda_stream); }
 bool GeePs::EnableDeviceClock() { return impl_->enable_device_clock(); }
 void GeePs::AdvanceReplayedClock() { impl_->advance_replayed_iteration(); }
 const int* GeePs::DeviceClockPtr() const { return impl_->device_clock_ptr(); }

@@ -44,6 +44,7 @@ struct Stats {
   Relaxed<uint64_t> device_wait_timeouts = 0, host_wait_timeouts = 0;
   Relaxed<uint64_t> device_waits_enqueued = 0;   // data_age wait kernels put on application streams
   Relaxed<uint64_t> nr_replayed_clocks = 0;      // iterations whose launches came from a replayed CUDA graph
+  Relaxed<uint64_t> nr_read_pull = 0, rows_pulled = 0;   // uncached tables: ReadPull calls; rows fetched from the shards
   Relaxed<double> iterate_time = 0;
 
   std::string to_json() const {
@@ -62,7 +63,8 @@ struct Stats {
     for (int i = 0; i < 8; ++i) o << (i ? "," : "") << staleness_hist[i];
     o << "],\"swap_h2d_bytes\":" << swap_h2d_bytes << ",\"swap_d2h_bytes\":" << swap_d2h_bytes
       << ",\"device_wait_timeouts\":" << device_wait_timeouts << ",\"host_wait_timeouts\":" << host_wait_timeouts
-      << ",\"device_waits_enqueued\":" << device_waits_enqueued << ",\"nr_replayed_clocks\":" << nr_replayed_clocks << "}";
+      << ",\"device_waits_enqueued\":" << device_waits_enqueued << ",\"nr_replayed_clocks\":" << nr_replayed_clocks
+      << ",\"nr_read_pull\":" << nr_read_pull << ",\"rows_pulled\":" << rows_pulled << "}";
     return o.str();
   }
 };

@@ -3,7 +3,9 @@
 // row's position inside that shard.
 //
 //   range        equal contiguous chunks, the reference's only live policy
-//                (src/client/clientlib-viter.cpp:674-682)
+//                (src/client/clientlib-viter.cpp:674-682); with `align` > 1 every chunk is a whole number of
+//                align-row groups (a weight matrix whose rows span several table rows then never straddles
+//                two shards)
 //   round_robin  i mod num_shards, the hash policy that only exists in the reference's dead
 //                metadata server (src/server/metadata-server.cpp:129-134)
 //
@@ -24,8 +26,13 @@ struct ShardRange {
 
 class Partitioner {
  public:
-  Partitioner(int kind = PARTITION_RANGE, size_t num_rows = 0, size_t num_shards = 1)
-      : kind_(kind), n_(num_rows), s_(num_shards ? num_shards : 1) {}
+  Partitioner(int kind = PARTITION_RANGE, size_t num_rows = 0, size_t num_shards = 1, size_t align = 1)
+      : kind_(kind), n_(num_rows), s_(num_shards ? num_shards : 1), align_(align ? align : 1) {}
+  // rows per shard of the range policy
+  size_t per() const {
+    const size_t p = (n_ + s_ - 1) / s_;
+    return (p + align_ - 1) / align_ * align_;
+  }
   size_t num_rows() const { return n_; }
   size_t num_shards() const { return s_; }
   int kind() const { return kind_; }
@@ -37,23 +44,23 @@ class Partitioner {
       r.stride = s_;
       r.count = n_ > shard ? (n_ - shard + s_ - 1) / s_ : 0;
     } else {
-      const size_t per = (n_ + s_ - 1) / s_;
-      r.start = shard * per < n_ ? shard * per : n_;
+      const size_t p = per();
+      r.start = shard * p < n_ ? shard * p : n_;
       r.stride = 1;
-      const size_t end = (shard + 1) * per < n_ ? (shard + 1) * per : n_;
+      const size_t end = (shard + 1) * p < n_ ? (shard + 1) * p : n_;
       r.count = end - r.start;
     }
     return r;
   }
   size_t shard_of(size_t i) const {
     if (kind_ == PARTITION_ROUND_ROBIN) return i % s_;
-    const size_t per = (n_ + s_ - 1) / s_;
-    return per ? i / per : 0;
+    const size_t p = per();
+    return p ? i / p : 0;
   }
   size_t local_index(size_t i) const {
     if (kind_ == PARTITION_ROUND_ROBIN) return i / s_;
-    const size_t per = (n_ + s_ - 1) / s_;
-    return per ? i % per : 0;
+    const size_t p = per();
+    return p ? i % p : 0;
   }
   size_t global_index(size_t shard, size_t local) const {
     ShardRange r = range_of(shard);
@@ -62,7 +69,7 @@ class Partitioner {
 
  private:
   int kind_;
-  size_t n_, s_;
+  size_t n_, s_, align_;
 };
 
 }  // namespace geeps_b200

@@ -47,7 +47,8 @@ std::string Plan::to_json() const {
     << ",\"peak_staging_rows\":" << peak_staging_rows << ",\"staging_rows\":" << staging_rows
     << ",\"staging_copies\":" << staging_copies << ",\"gpu_local_rows\":" << gpu_local_rows
     << ",\"cpu_local_rows\":" << cpu_local_rows << ",\"gpu_param_rows\":" << gpu_param_rows
-    << ",\"cpu_param_rows\":" << cpu_param_rows << ",\"max_access_rows\":" << max_access_rows
+    << ",\"cpu_param_rows\":" << cpu_param_rows << ",\"uncached_param_rows\":" << uncached_param_rows
+    << ",\"max_access_rows\":" << max_access_rows
     << ",\"gpu_rows_total\":" << gpu_rows_total() << ",\"pf_slack\":" << pf_slack << ",\"ops\":[";
   for (size_t i = 0; i < ops.size(); ++i) {
     const OpInfo& p = ops[i];
@@ -70,7 +71,8 @@ std::string Plan::to_json() const {
     if (!first) o << ',';
     first = false;
     o << "{\"table_id\":" << t.table_id << ",\"num_rows\":" << t.rows.size() << ",\"gpu_rows\":" << t.gpu_rows
-      << ",\"cpu_rows\":" << t.cpu_rows << ",\"slack\":" << t.slack << ",\"num_oplog_entries\":"
+      << ",\"cpu_rows\":" << t.cpu_rows << ",\"pull\":" << (t.pull ? 1 : 0) << ",\"partition_per\":" << t.partition_per
+      << ",\"slack\":" << t.slack << ",\"num_oplog_entries\":"
       << t.num_oplog_entries << ",\"shards\":[";
     for (size_t s = 0; s < t.shard_ranges.size(); ++s) {
       if (s) o << ',';

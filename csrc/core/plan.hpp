@@ -68,6 +68,8 @@ struct TablePlan {
   int slack = 0;
   int num_oplog_entries = 1;
   std::vector<ShardRange> shard_ranges;  // over the cache index space
+  size_t partition_per = 0;              // rows per shard of the range partition (alignment included)
+  bool pull = false;                     // uncached: reads are fetched from the owning shards
   bool written = false;
 };
 
@@ -81,6 +83,10 @@ struct PlanConfig {
   bool device_is_gpu = true;     // false: everything is host memory, the budget is not enforced
   bool allow_direct = false;     // zero-copy param access (NVLINK transport)
   bool update_ring = false;      // update staging is a ring of slack+1 slots (NVLINK transport)
+  // per table (by id; missing entries = default): rows per alignment group of the range partition, and whether the
+  // table is kept uncached ("pull" tables: no worker-side copy, a Read fetches the rows from the owning shards)
+  std::vector<size_t> partition_align;
+  std::vector<char> pull_tables;
 };
 
 struct Plan {
@@ -93,6 +99,7 @@ struct Plan {
   int staging_copies = 2;           // 2 = double buffered across clocks
   size_t gpu_local_rows = 0, cpu_local_rows = 0;
   size_t gpu_param_rows = 0, cpu_param_rows = 0;
+  size_t uncached_param_rows = 0;   // rows of pull tables: no worker-side cache, fetched from the shards per Read
   size_t max_access_rows = 0;
   int pf_slack = 0;
   std::vector<std::string> warnings;

@@ -160,8 +160,12 @@ Plan PlanCompiler::compile() const {
     for (auto& rk : t.row_to_idx) { rk.second = idx++; t.rows.push_back(rk.first); }
     if (!t.written) { plan.error = "table " + std::to_string(t.table_id) + " is never updated before the Clock"; return plan; }
     t.num_oplog_entries = cfg_.update_ring ? t.slack + 1 : (cfg_.read_my_writes ? t.slack + 1 : 1);
-    Partitioner part(cfg_.partitioner, t.rows.size(), (size_t)cfg_.num_shards);
+    const size_t align = t.table_id < cfg_.partition_align.size() ? cfg_.partition_align[t.table_id] : 1;
+    Partitioner part(cfg_.partitioner, t.rows.size(), (size_t)cfg_.num_shards, align);
     for (int s = 0; s < cfg_.num_shards; ++s) t.shard_ranges.push_back(part.range_of((size_t)s));
+    t.partition_per = part.per();
+    t.pull = cfg_.update_ring && t.table_id < cfg_.pull_tables.size() && cfg_.pull_tables[t.table_id];
+    if (t.pull) plan.uncached_param_rows += t.rows.size();
     t.location.assign(t.rows.size(), LOC_UNKNOWN);
     t.slot.assign(t.rows.size(), 0);
   }
@@ -192,6 +196,14 @@ Plan PlanCompiler::compile() const {
     // read-my-updates over the update ring: at slack > 0 a read merges the worker's own pending updates into a
     // private copy, so it cannot alias the cache that the shards write in place
     if (op.type == OP_READ && cfg_.read_my_writes && cfg_.update_ring && t.slack > 0) direct_cand[i] = 0;
+    // an uncached table has no worker-side copy to alias: its reads land in the staging pool
+    if (op.type == OP_READ && t.pull) {
+      direct_cand[i] = 0;
+      if (!op.one_off && !(run && first == 0 && op.rows.size() == t.rows.size())) {
+        plan.error = "read of uncached table " + std::to_string(t.table_id) + " must cover the whole table in ascending row order";
+        return plan;
+      }
+    }
   }
 
   // ---- 4. worker-local batches: resident in GPU memory, or host memory + staging ----
@@ -227,7 +239,8 @@ Plan PlanCompiler::compile() const {
   // host-staged transport local data comes first and the parameter cache may spill to host memory.
   size_t param_reserved = 0;
   if (cfg_.update_ring)
-    for (auto& kv : plan.tables) param_reserved += kv.second.rows.size() * (1 + (size_t)kv.second.num_oplog_entries);
+    for (auto& kv : plan.tables)   // uncached tables keep the update ring resident, but no copy of the rows
+      param_reserved += kv.second.rows.size() * ((kv.second.pull ? 0 : 1) + (size_t)kv.second.num_oplog_entries);
   size_t cap = plan.capacity_rows;
   if (gpu && cap != (size_t)-1 && param_reserved) {
     if (param_reserved > cap) {

@@ -51,6 +51,8 @@ typedef struct GeepsPushApplyParams {
   long long fp32_from_row;             // rows below this id are published to the bf16 caches only (0: all in fp32 too)
   const int* clock_ref;                // NULL, or a device word added to clock_stamp when the kernel runs (stamps
                                        // relative to a device-resident clock: launches that a CUDA graph replays)
+  void* master16;                      // NULL, or this shard's bf16 copy of its master rows, compact [n_owned][128]
+                                       // (uncached tables: consumers read it in place over NVLink)
 } GeepsPushApplyParams;
 int geeps_ps_push_apply(const GeepsPushApplyParams* p, int max_ctas, void* stream);
 
@@ -66,6 +68,9 @@ typedef struct GeepsPullParams {
   long long total_rows;
   unsigned long long wait_budget_ns;
   int n_ranks, rank, needed_stamp;
+  long long row_from;  // only rows with id >= row_from are copied (0: all); cache / cache16 are indexed by
+                       // (row id - row_base), so a buffer that holds just the tail of a table can be filled
+  long long row_base;
 } GeepsPullParams;
 int geeps_ps_pull(const GeepsPullParams* p, int max_ctas, void* stream);
 
@@ -104,6 +109,7 @@ typedef struct GeepsRmwReadParams {
   int additive_below_clock;   // own updates of clocks below this are added as they are (initial values), not scaled
   float alpha;
   const int* clock_ref;       // NULL, or a device word added to `clock` when the kernel runs
+  long long partition_per;    // rows per shard of the range partition (0: ceil(total_rows / n_ranks))
 } GeepsRmwReadParams;
 int geeps_row_gather_rmw(const GeepsRmwReadParams* p, void* stream);
 

@@ -119,9 +119,10 @@ push_apply_kernel(const GeepsPushApplyParams p) {
         w = f4_add(w, g);
       }
       st_f4(p.master + loff, w);
+      const uint2 h = make_uint2(pack_bf16x2(w.x, w.y), pack_bf16x2(w.z, w.w));
+      if (p.master16 != nullptr) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.master16) + loff) = h;
       // ---- fused publish into every worker's parameter cache ----
       if (p.publish) {
-        const uint2 h = make_uint2(pack_bf16x2(w.x, w.y), pack_bf16x2(w.z, w.w));
         const bool fp32_too = grow >= p.fp32_from_row;   // weights consumed in bf16 only skip two thirds of the bytes
         for (int q = 0; q < p.n_ranks; ++q) {
           if (fp32_too && p.cache[q] != nullptr) st_f4(p.cache[q] + goff, w);
@@ -174,8 +175,9 @@ pull_kernel(const GeepsPullParams p) {
         if (lane == 0) geeps_report(p.status, GEEPS_ERR_BOUNDS, KID_PULL, (int)i, (int)grow);
         continue;
       }
+      if (grow < p.row_from) continue;
       float4 w = ld_f4_peer(p.master[s] + i * GEEPS_ROW_FLOATS + lane * 4);
-      const long long goff = grow * GEEPS_ROW_FLOATS + lane * 4;
+      const long long goff = (grow - p.row_base) * GEEPS_ROW_FLOATS + lane * 4;
       if (p.cache != nullptr) st_f4(p.cache + goff, w);
       if (p.cache16 != nullptr)
         *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.cache16) + goff) =
@@ -242,7 +244,7 @@ row_gather_rmw_kernel(const GeepsRmwReadParams p) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-  const long long per = (p.total_rows + p.n_ranks - 1) / p.n_ranks;
+  const long long per = p.partition_per > 0 ? p.partition_per : (p.total_rows + p.n_ranks - 1) / p.n_ranks;
   const int clock = p.clock + (p.clock_ref != nullptr ? *p.clock_ref : 0);
   for (long long i = warp0; i < p.num_rows; i += nwarps) {
     IndexPair ip;

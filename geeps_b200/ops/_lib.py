@@ -48,6 +48,7 @@ class PushApplyParams(C.Structure):
         ("publish", C.c_int),
         ("lr", C.c_float), ("momentum_coef", C.c_float), ("weight_decay", C.c_float),
         ("grad_scale", C.c_float), ("fp32_from_row", C.c_longlong), ("clock_ref", C.c_void_p),
+        ("master16", C.c_void_p),
     ]
 
 
@@ -60,6 +61,7 @@ class PullParams(C.Structure):
         ("cta_counter", C.c_void_p), ("status", C.c_void_p),
         ("total_rows", C.c_longlong), ("wait_budget_ns", C.c_ulonglong),
         ("n_ranks", C.c_int), ("rank", C.c_int), ("needed_stamp", C.c_int),
+        ("row_from", C.c_longlong), ("row_base", C.c_longlong),
     ]
 
 
@@ -85,6 +87,7 @@ class RmwReadParams(C.Structure):
         ("total_rows", C.c_longlong), ("wait_budget_ns", C.c_ulonglong),
         ("n_ranks", C.c_int), ("partition_kind", C.c_int), ("ring_slots", C.c_int), ("clock", C.c_int),
         ("additive_below_clock", C.c_int), ("alpha", C.c_float), ("clock_ref", C.c_void_p),
+        ("partition_per", C.c_longlong),
     ]
 
 

@@ -317,7 +317,15 @@ class Linear(Layer):
 
     def forward(self, x):
         self.x = x.reshape(self.B, self.k_in)
-        F.gemm(self.x, self.p16["weight"], self.y, bias=self.p32["bias"], relu=self.relu)
+        pull = getattr(self, "pull", None)
+        if pull:
+            # uncached table: the weight rows are read from the owning shards while the GEMM runs; p16["weight"]
+            # receives the local bf16 copy that the backward pass uses
+            shards, n_start = pull
+            F.pull_gemm(self.x, shards, n_start, self.y, ldw=self.ld, bias=self.p32["bias"], relu=self.relu,
+                        w_local=self.p16["weight"])
+        else:
+            F.gemm(self.x, self.p16["weight"], self.y, bias=self.p32["bias"], relu=self.relu)
         return self.y
 
     def backward(self, dy):

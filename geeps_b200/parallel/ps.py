@@ -57,6 +57,13 @@ def _rows(rows):
     return arr, len(rows)
 
 
+class PullInfo(C.Structure):
+    """Mirror of GeePs::PullInfo (include/geeps.hpp)."""
+    _fields_ = [("shard_bf16", C.c_void_p * 8), ("shard_fp32", C.c_void_p * 8),
+                ("row_start", C.c_longlong * 8), ("row_count", C.c_longlong * 8), ("num_shards", C.c_int),
+                ("tail", C.c_void_p), ("tail_from_row", C.c_longlong), ("tail_rows", C.c_longlong)]
+
+
 class GeePs:
     def __init__(self, process_id: int, config: GeePsConfig):
         self._l = _lib()
@@ -74,6 +81,10 @@ class GeePs:
             self._l.geeps_config_set_table_mode(cfg, int(t), int(m))
         for t, r in config.table_fp32_from_row.items():
             self._l.geeps_config_set_table_fp32_from_row(cfg, int(t), C.c_longlong(int(r)))
+        for t, v in config.table_pull.items():
+            self._l.geeps_config_set_table_pull(cfg, int(t), int(v))
+        for t, v in config.table_partition_align.items():
+            self._l.geeps_config_set_table_partition_align(cfg, int(t), C.c_longlong(int(v)))
         self._g = C.c_void_p(self._l.geeps_new(process_id, cfg))
         self._l.geeps_config_delete(cfg)
         self._ops = {}      # handle -> (kind, num_rows)
@@ -195,6 +206,17 @@ class GeePs:
         if not ok:
             self.check()
         return self._wrap(p.value, self._ops[handle][1])
+
+    def read_pull(self, handle: int, stream=None) -> "PullInfo":
+        """Stands in for read() on an uncached (pull) table: orders the stream after the table's freshness
+        condition, fetches the fp32 tail (rows from table_fp32_from_row on) into a private buffer and returns where
+        the shards keep the leading rows, for a kernel that reads them in place (ops.functional.pull_gemm)."""
+        info = PullInfo()
+        ok = _L.record_call(self._l.geeps_read_pull, "read_pull", self._g, handle, C.byref(info), self._stream(stream))
+        if not ok:
+            self.check()
+        info.tail_tensor = self._wrap(info.tail, info.tail_rows) if info.tail else None
+        return info
 
     def read_bf16(self, handle: int):
         p = self._l.geeps_read_bf16(self._g, handle)

@@ -50,7 +50,7 @@ class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
                  slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None, manage_activations: bool = False,
                  cache_fraction: float | None = None, use_tape: bool = False, bf16_weights_only: bool = False,
-                 use_graph: bool = False):
+                 use_graph: bool = False, pull_fc: bool = False, uncached=()):
         """bf16_weights_only: with the NVLINK transport and the bf16 compute cache, weight rows are published to
         the workers' bf16 caches only (the layers never read weights in fp32; biases, BatchNorm scale / shift and
         the shard's master rows stay fp32).  The fp32 views of weights (`params_fp32`) then keep their initial
@@ -58,7 +58,14 @@ class PSModule:
         use_graph: (NVLINK transport, implies use_tape) once a step's native calls are known to repeat, capture
         them in a CUDA graph per (input buffer, label buffer, update-ring phase) and replay the graph: one launch
         per step instead of one per kernel.  The runtime then keeps its clock in a device word (stamps relative
-        to it, dropout seeds derived from it), so nothing in the captured launches changes from step to step."""
+        to it, dropout seeds derived from it), so nothing in the captured launches changes from step to step.
+        pull_fc: (NVLINK transport with the bf16 compute cache) the tables of the fully-connected layers become
+        uncached tables: the shards do not publish them, and each layer's forward GEMM pulls the weight rows from
+        the owning shards while it computes (ops.functional.pull_gemm), leaving a local bf16 copy for the backward
+        pass; the bias rows arrive through the table's fp32 tail.
+        uncached: names of further layers whose tables are kept uncached (no worker-side copy; every Read fetches
+        the whole table from the shards into the staging pool) - the device-side form of a parameter cache that
+        does not fit the GPU budget."""
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
         self.trace = trace or NullTrace()
@@ -107,6 +114,24 @@ class PSModule:
             for t in self.tables:
                 if t.specs and t.specs[0].name == "weight":
                     ps_config.table_fp32_from_row[t.table_id] = (t.offsets[1] // ROW_FLOATS) if len(t.specs) > 1 else t.rows
+        # uncached (pull) tables
+        nv = ps_config.transport == TRANSPORT_NVLINK and torch.cuda.is_available()
+        from ..ops.layers import Linear as _Linear
+        for t in self.tables:
+            t.pull = t.fused_pull = False
+            l = t.layer
+            if not nv:
+                continue
+            if (pull_fc and isinstance(l, _Linear) and self.direct16 and l.B <= 256 and l.ld % ROW_FLOATS == 0
+                    and len(t.specs) == 2):
+                t.pull = t.fused_pull = True
+                ps_config.table_partition_align[t.table_id] = l.ld // ROW_FLOATS    # whole weight rows per shard
+                ps_config.table_fp32_from_row[t.table_id] = t.offsets[1] // ROW_FLOATS  # the bias rows are the tail
+            elif getattr(l, "name", None) in uncached:
+                t.pull = True
+                ps_config.table_fp32_from_row.pop(t.table_id, None)
+            if t.pull:
+                ps_config.table_pull[t.table_id] = 1
         self.ps = GeePs(rank, ps_config)
         # tape replay: record two consecutive steps; if they issued identical native calls (static pointers),
         # later steps walk the tape instead of re-running the Python layer code
@@ -178,7 +203,31 @@ class PSModule:
             self.ps.update(t.h_upd)
         self.ps.clock()
 
+    def _bind_read_pull(self, t):
+        """Fully-connected layer on an uncached table: no copy of the weights is made here - the layer's forward
+        GEMM reads them from the shards (and leaves a bf16 copy in p16 for its backward)."""
+        info = self.ps.read_pull(t.h_read)
+        l = t.layer
+        rpw = l.ld // ROW_FLOATS                       # table rows per weight row
+        wrows = t.offsets[1] // ROW_FLOATS
+        shards, n_start = [], []
+        for s in range(info.num_shards):
+            if info.row_count[s] == 0 or info.row_start[s] >= wrows:
+                break
+            shards.append(int(info.shard_bf16[s]))
+            n_start.append(int(info.row_start[s]) // rpw)
+        l.pull = (shards, n_start)
+        if t.p16_buf is None:
+            t.p16_buf = torch.zeros(t.rows, ROW_FLOATS, dtype=BF, device=self.device)
+        l.p16 = t.views(t.p16_buf)
+        tail = info.tail_tensor.view(-1)
+        l.p32 = {"bias": tail[:t.specs[1].numel].view(t.specs[1].shape)}
+        if self.captured is not None:
+            self.captured[f"{l.name}.bias"] = l.p32["bias"].clone()
+
     def _bind_read(self, t):
+        if t.fused_pull:
+            return self._bind_read_pull(t)
         buf = self.ps.read(t.h_read)
         t.layer.p32 = t.views(buf)
         b16 = self.ps.read_bf16(t.h_read) if self.direct16 else None

@@ -35,6 +35,10 @@ class GeePsConfig:
     table_modes: dict = field(default_factory=dict)   # table id -> mode
     # table id -> first row that is also published in fp32 (rows below it reach the bf16 caches only)
     table_fp32_from_row: dict = field(default_factory=dict)
+    # table id -> 1: uncached ("pull") table of the NVLINK transport: workers keep no copy, reads fetch from the shards
+    table_pull: dict = field(default_factory=dict)
+    # table id -> the range partition hands out rows in groups of this many
+    table_partition_align: dict = field(default_factory=dict)
     learning_rate: float = 0.01
     momentum: float = 0.9
     weight_decay: float = 0.0

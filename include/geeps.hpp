@@ -54,6 +54,14 @@ struct GeePsConfig {
      workers' bf16 caches only - their fp32 cache rows (what Read returns) are not refreshed.  For tables whose
      leading rows (weights) are consumed through ReadBf16 only; default: every row also in fp32. */
   std::vector<size_t> table_fp32_from_row;
+  /* NVLINK transport, per table: 1 = the table is uncached ("pull" table).  Workers keep no copy of its rows: the
+     owning shards hold the fp32 master rows (and a bf16 copy with bf16_compute_cache) and a Read fetches the whole
+     table from them over NVLink into the staging pool - the device-side form of a parameter cache that does not
+     fit the GPU budget.  ReadPull gives a consumer (a GEMM that pulls while it computes) the shard pointers. */
+  std::vector<int> table_pull;
+  /* per table: the range partition hands out rows in groups of this many (0 / 1: single rows), so that a matrix
+     row spanning several 128-float table rows never straddles two shards */
+  std::vector<size_t> table_partition_align;
   float learning_rate, momentum, weight_decay;
   float grad_scale;           /* multiplies the reduced update before the optimizer (e.g. 1/workers) */
   int bf16_compute_cache;     /* also keep a bf16 copy of the parameter cache (NVLINK transport) */
@@ -136,6 +144,20 @@ class GeePs {
   bool EnableDeviceClock();
   void AdvanceReplayedClock();
   const int* DeviceClockPtr() const;
+  /* Uncached (pull) tables.  ReadPull stands in for Read in the declared sequence: it orders `cuda_stream` after
+   * the table's freshness condition, fetches the rows from `table_fp32_from_row` on (fp32, e.g. biases) into a
+   * private buffer, and describes where the leading rows live on the shards so that the caller's kernel can read
+   * them in place: shard s holds rows [row_start[s], row_start[s] + row_count[s]) as bf16 at shard_bf16[s] (a peer
+   * pointer, 128 values per row) and as fp32 at shard_fp32[s]. */
+  struct PullInfo {
+    const void* shard_bf16[8];
+    const float* shard_fp32[8];
+    long long row_start[8], row_count[8];
+    int num_shards;
+    RowData* tail;              /* rows [tail_from_row, end) in fp32, private to this worker */
+    long long tail_from_row, tail_rows;
+  };
+  bool ReadPull(int handle, PullInfo* info, void* cuda_stream);
   geeps_b200::ClientLib* impl() { return impl_; }
 
  private:

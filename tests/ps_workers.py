@@ -168,12 +168,25 @@ def nvlink_train_worker(rank, world, base_port, steps, q, kw):
         from geeps_b200.parallel.ps_module import PSModule
         from geeps_b200.utils.config import DEVICE_CUDA, TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK
         torch.cuda.set_device(rank)
+        kw = dict(kw)
+        mod_kw = kw.pop("_module", {})
         cfg = make_cfg(world, base_port, device=DEVICE_CUDA, cuda_device=rank, transport=TRANSPORT_NVLINK,
                        table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.02, momentum=0.9, grad_scale=1.0 / world,
                        bf16_compute_cache=1, **kw)
         dev = torch.device("cuda", rank)
         with torch.cuda.stream(torch.cuda.Stream(device=dev)):
-            mod = PSModule(inception_bn_small(), (50, 3, 32, 32), cfg, rank=rank, world=world, device=dev, seed=3)
+            net_name = mod_kw.pop("net", "inception_bn_small")
+            if net_name == "fc_net":
+                # two fully-connected layers whose input widths are whole table rows (eligible for pulled tables)
+                from geeps_b200.models.net import Net
+                from geeps_b200.ops.layers import Conv2d, Input, Linear, Pool
+                net = Net("fc_net", Input(cpad=8), [
+                    Conv2d("c1", 16, 3, pad=1, relu=True, std=0.1, need_dx=False), Pool("max", 2, 2),
+                    Conv2d("c2", 32, 3, pad=1, relu=True, std=0.1), Pool("max", 2, 2), Pool("max", 2, 2),
+                    Linear("f1", 256, relu=True, std=0.05), Linear("f2", 10, std=0.05, fp32_out=True)])
+            else:
+                net = inception_bn_small()
+            mod = PSModule(net, (50, 3, 32, 32), cfg, rank=rank, world=world, device=dev, seed=3, **mod_kw)
             gen = torch.Generator(device=dev).manual_seed(100 + rank)
             x = torch.randn(50, 3, 32, 32, device=dev, generator=gen)
             y = torch.randint(0, 10, (50,), device=dev, generator=gen)

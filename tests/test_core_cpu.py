@@ -226,3 +226,21 @@ def test_plan_staging_pool_reaches_peak_for_a_layer_chain():
         elif op["type"] == "post_local_access":
             live.pop(op["prestep"], None)
     assert checked >= len(sizes) - 1
+
+
+def test_partition_alignment_keeps_row_groups_on_one_shard():
+    """Range partition in groups of 72 rows (a 9216-wide weight row = 72 table rows): every shard starts on a
+    group boundary, shards cover the table exactly once, and a trailing bias block goes to the last used shard."""
+    import ctypes as C
+    from geeps_b200 import _native
+    lib = _native.load()
+    lib.geeps_partition_range_aligned.restype = None
+    rows, shards, align = 4096 * 72 + 32, 8, 72
+    seen = 0
+    for s in range(shards):
+        out = (C.c_longlong * 3)()
+        lib.geeps_partition_range_aligned(0, C.c_longlong(rows), shards, s, C.c_longlong(align), out)
+        start, stride, count = out[0], out[1], out[2]
+        assert stride == 1 and start == seen and (start % align == 0 or count == 0)
+        seen += count
+    assert seen == rows

@@ -11,11 +11,11 @@ from ps_workers import nvlink_hello_worker, nvlink_leave_worker, nvlink_pull_gem
 _port = [15000 + (os.getpid() % 100) * 100]
 
 
-def _spawn(target, world, args):
+def _spawn(target, world, args, kw=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     _port[0] += 100
-    procs = [ctx.Process(target=target, args=(r, world, _port[0]) + args + (q,) + ({},)) for r in range(world)]
+    procs = [ctx.Process(target=target, args=(r, world, _port[0]) + args + (q,) + (kw or {},)) for r in range(world)]
     for p in procs:
         p.start()
     out = [q.get(timeout=300) for _ in procs]
@@ -56,6 +56,23 @@ def test_nvlink_data_parallel_training_is_consistent():
         assert all(l == l for l in losses), losses
         if world <= 2:       # with more workers the random-label batches average out within 10 steps
             assert losses[-1] < losses[0], losses
+
+
+def test_nvlink_training_with_pulled_fc_tables_and_graph_replay_is_consistent():
+    """The tables of both fully-connected layers are uncached: every rank's forward GEMM pulls the weight rows from
+    all shards over NVLink.  With graph replay on top.  Every worker still reads bit-identical parameters and the run matches the
+    published-table run of the same seed."""
+    world = _world()
+    runs = {}
+    for name, mk in (("published", dict(net="fc_net")), ("pulled", dict(net="fc_net", pull_fc=True, use_graph=True))):
+        out = _spawn(nvlink_train_worker, world, (10,), dict(_module=mk))
+        digests = [o[3] for o in out]
+        for d in digests[1:]:
+            assert d == digests[0]
+        runs[name] = out[0][2]
+        for o in out:
+            assert all(l == l for l in o[2]), o[2]
+    assert runs["pulled"] == pytest.approx(runs["published"], rel=2e-3), runs
 
 
 def test_pull_gemm_over_peer_memory():

@@ -220,6 +220,41 @@ def test_graph_replay_alexnet_with_dropout_trains():
         mod.close()
 
 
+@pytest.mark.parametrize("mode", ["pull_fc", "uncached"])
+def test_uncached_tables_train_like_published_ones(mode):
+    """Tables the shards do not publish: (pull_fc) the fully-connected layers pull their weight rows from the shards
+    inside the forward GEMM, (uncached) a convolution's table is fetched from the shards by every Read.  Both give
+    the losses of the ordinary publish path, bit for bit in the first case (same bf16 rows, same GEMM order)."""
+    dev = torch.device("cuda:0")
+    B = 64
+    losses, stats = {}, {}
+    for on in (False, True):
+        with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+            kw = {}
+            if on:
+                kw = dict(pull_fc=True) if mode == "pull_fc" else dict(uncached=("c2",))
+            mod = PSModule(tiny_net(), (B, 3, 16, 16), cfg(TRANSPORT_NVLINK, learning_rate=0.05), device=dev, seed=3,
+                           use_graph=True, **kw)
+            gen = torch.Generator(device=dev).manual_seed(5)
+            x = torch.randn(B, 3, 16, 16, device=dev, generator=gen)
+            y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+            losses[on] = [mod.step(x, y).item() for _ in range(12)]
+            torch.cuda.synchronize()
+            assert mod.ps.last_error() == 0
+            stats[on] = mod.ps.get_stats()["client"]
+            plan = mod.ps.plan()
+            pulled = [t for t in plan["tables"] if t["pull"]]
+            assert (len(pulled) > 0) == on
+            if on:
+                assert plan["uncached_param_rows"] == sum(t["num_rows"] for t in pulled)
+            mod.close()
+    assert stats[True]["rows_pulled"] > 0 and stats[False]["rows_pulled"] == 0
+    if mode == "pull_fc":
+        assert stats[True]["nr_read_pull"] > 0
+    assert losses[True] == pytest.approx(losses[False], rel=1e-3), losses
+    assert losses[True][-1] < losses[True][0]
+
+
 def test_bf16_only_weight_publish_trains_identically():
     """Weights published to the bf16 caches only: same losses (the layers never read fp32 weights), biases still
     refreshed in fp32, fp32 weight views left at their initial values."""
