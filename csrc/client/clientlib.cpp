@@ -121,6 +121,23 @@ bool ClientLib::open_channel(uint c, std::unique_ptr<ServerThreadEntry>* server,
                              std::string* err) {
   const uint nch = config_.num_comm_channels ? config_.num_comm_channels : 1;
   server->reset(new ServerThreadEntry(c, nch, process_id_, num_processes_, config_));
+  ClientLib* self = this;
+  if (c == 0) {
+    (*server)->control_hook = [self](const std::string& src, Message& msg) {
+      switch (msg[0].cmd()) {
+        case CMD_HEARTBEAT: { heartbeat_msg_t h; if (msg[0].unpack(&h)) self->heartbeat_cbk(h.id, h.counter, h.clock); break; }
+        case CMD_BARRIER: { barrier_msg_t h; if (msg[0].unpack(&h)) self->barrier_cbk(h.id, h.epoch); break; }
+        case CMD_IPC_EXCHANGE: self->ipc_exchange_cbk(msg); break;
+        case CMD_PEER_LOST: self->peer_lost_cbk(src); break;
+        default: break;
+      }
+    };
+  } else {
+    // a data channel that loses a peer reports it like the control channel does
+    (*server)->control_hook = [self](const std::string& src, Message& msg) {
+      if (msg[0].cmd() == CMD_PEER_LOST) self->peer_lost_cbk(src);
+    };
+  }
   if (!(*server)->start(err)) return false;
   router->reset(new RouterHandler("client-" + std::to_string(process_id_)));
   if (config_.local_opt) {
@@ -144,24 +161,11 @@ bool ClientLib::init_comm(std::string* err) {
   // every process hosts a server shard per channel (channel 0 carries the control plane as well)
   if (!open_channel(0, &server_, &router_, &encoder_, &decoder_, err)) return false;
   ClientLib* self = this;
-  server_->decoder()->control_hook = [self](const std::string& src, Message& msg) {
-    switch (msg[0].cmd()) {
-      case CMD_HEARTBEAT: { heartbeat_msg_t h; if (msg[0].unpack(&h)) self->heartbeat_cbk(h.id, h.counter, h.clock); break; }
-      case CMD_BARRIER: { barrier_msg_t h; if (msg[0].unpack(&h)) self->barrier_cbk(h.id, h.epoch); break; }
-      case CMD_IPC_EXCHANGE: self->ipc_exchange_cbk(msg); break;
-      case CMD_PEER_LOST: self->peer_lost_cbk(src); break;
-      default: break;
-    }
-  };
   const uint nch = config_.num_comm_channels ? config_.num_comm_channels : 1;
   for (uint c = 1; c < nch; ++c) {
     extra_channels_.emplace_back();
     Channel& ch = extra_channels_.back();
     if (!open_channel(c, &ch.server, &ch.router, &ch.encoder, &ch.decoder, err)) return false;
-    // a data channel that loses a peer reports it like the control channel does
-    ch.server->decoder()->control_hook = [self](const std::string& src, Message& msg) {
-      if (msg[0].cmd() == CMD_PEER_LOST) self->peer_lost_cbk(src);
-    };
   }
   for (uint c = 0; c < nch; ++c) {
     bg_workers_.emplace_back(new BackgroundWorker());

@@ -22,6 +22,7 @@ bool ServerThreadEntry::start(std::string* err) {
   storage_.reset(new TabletStorage(channel_id_, num_channels_, process_id_, num_processes_, encoder_, config_));
   metadata_.reset(new MetadataServer(process_id_, num_processes_, encoder_, config_));
   decoder_.reset(new ClientServerDecode(storage_, metadata_));
+  decoder_->control_hook = control_hook;
   std::shared_ptr<ClientServerDecode> dec = decoder_;
   router_->start_handler_thread([dec](const std::string& src, Message& msg) { dec->router_callback(src, msg); });
   return true;

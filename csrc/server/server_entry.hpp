@@ -1,6 +1,7 @@
 // Brings up one server shard of a process: router bound to the shard's TCP port, codec,
 // tablet storage, metadata server (role of the reference's src/server/server-entry.cpp:51-88).
 #pragma once
+#include <functional>
 #include <memory>
 #include <string>
 
@@ -20,6 +21,9 @@ class ServerThreadEntry {
   // Binds, builds the components and starts the handler thread.  false + err on failure.
   bool start(std::string* err);
   void stop();
+  // Handler for the control-plane messages that reach this shard (heartbeats, barriers, handle exchange, lost
+  // peers).  Set it before start(): a peer may deliver such a message the moment the port is bound.
+  std::function<void(const std::string&, Message&)> control_hook;
   static unsigned port_for(const GeePsConfig& config, uint process_id, uint channel_id);
   std::shared_ptr<RouterHandler> router() { return router_; }
   std::shared_ptr<TabletStorage> storage() { return storage_; }
