@@ -128,6 +128,10 @@ def main() -> None:
                     help="also refresh the workers' fp32 copies of the weights every clock (the layers read bf16 only)")
     ap.add_argument("--no-tape", action="store_true",
                     help="re-run the Python layer code every step instead of replaying the recorded native calls")
+    ap.add_argument("--pull-fc", action="store_true",
+                    help="fully-connected tables uncached: the forward GEMMs pull their weight rows from the shards "
+                         "(fused all-gather + GEMM) instead of reading a copy the shards published")
+    ap.add_argument("--uncached", default="", help="comma-separated layer names whose tables are kept uncached")
     ap.add_argument("--no-graph", action="store_true",
                     help="replay the recorded native calls one launch at a time instead of one CUDA graph per step")
     args = ap.parse_args()
@@ -178,7 +182,8 @@ def main() -> None:
         mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=args.slack, seed=1,
                        manage_activations=args.cache_frac is not None, cache_fraction=args.cache_frac,
                        use_tape=not args.no_tape, bf16_weights_only=not args.fp32_weight_cache,
-                       use_graph=not (args.no_graph or args.no_tape) and args.transport == "nvlink")
+                       use_graph=not (args.no_graph or args.no_tape) and args.transport == "nvlink",
+                       pull_fc=args.pull_fc, uncached=tuple(n for n in args.uncached.split(",") if n))
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
         in_dtype = torch.bfloat16 if args.input_dtype == "bf16" else torch.float32
         x_dev = torch.randn((B,) + image, device=dev, generator=gen).to(in_dtype)
@@ -326,6 +331,8 @@ def main() -> None:
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
                            "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack, "input_dtype": args.input_dtype, "cpu_cores_bound": len(cores) if cores else 0,
                            "weight_publish": "bf16+fp32" if args.fp32_weight_cache else "bf16 (biases / BN fp32)",
+                           "pulled_fc_tables": sum(1 for t in mod.tables if t.fused_pull),
+                           "uncached_tables": sum(1 for t in mod.tables if t.pull),
                            "host_replay_tapes": len(mod._tapes), "step_graphs": len(mod._graphs),
                            "graph_nodes": max([g.nodes for g in mod._graphs.values()] + [0]),
                            "tables": "fp32 master rows, momentum SGD on the owning shard",
