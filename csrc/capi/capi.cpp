@@ -64,6 +64,7 @@ int geeps_config_set(void* c, const char* key, double v) {
   else if (k == "weight_decay") cfg->weight_decay = (float)v;
   else if (k == "grad_scale") cfg->grad_scale = (float)v;
   else if (k == "bf16_compute_cache") cfg->bf16_compute_cache = (int)v;
+  else if (k == "use_multicast") cfg->use_multicast = (int)v;
   else if (k == "device_wait_budget_us") cfg->device_wait_budget_us = (size_t)v;
   else if (k == "host_wait_budget_ms") cfg->host_wait_budget_ms = (size_t)v;
   else if (k == "heartbeat_timeout_ms") cfg->heartbeat_timeout_ms = (size_t)v;

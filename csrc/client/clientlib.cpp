@@ -501,6 +501,7 @@ std::string ClientLib::json_stats() {
   }
   std::string out = "{\"process_id\":" + std::to_string(process_id_) + ",\"clock\":" + std::to_string(clock_) +
                     ",\"comm_channels\":" + std::to_string(num_channels()) +
+                    ",\"multicast\":" + (fabric_.use_mc ? "true" : "false") +
                     ",\"transport\":\"" + (nvlink_ ? "nvlink" : "tcp") + "\",\"device\":\"" + (gpu_ ? "cuda" : "cpu") +
                     "\",\"client\":" + stats_.to_json() + ",\"bgthread\":" + bg_stats_.to_json() +
                     ",\"router\":" + (router_ ? router_->stats.to_json() : std::string("{}")) +

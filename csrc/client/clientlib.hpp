@@ -28,6 +28,7 @@
 #include "core/plan.hpp"
 #include "encoder_decoder.hpp"
 #include "geeps.hpp"
+#include "multicast_arena.hpp"
 #include "net/router_handler.hpp"
 #include "net/work_queue.hpp"
 #include "server/server_entry.hpp"
@@ -116,6 +117,9 @@ struct TableArena {
 };
 struct Fabric {
   bool active = false;
+  MulticastArena mc;                      // arena allocated through the VMM API and bound to a multicast object
+  bool use_mc = false;                    //   ... in use: base / peer_base / mc_base come from it
+  char* mc_base = nullptr;                // multicast view of the arena (same offsets), or null
   char* base = nullptr;                   // local arena
   size_t bytes = 0;
   std::vector<char*> peer_base;           // per rank (own rank: base)
@@ -340,6 +344,7 @@ class ClientLib {
   std::mutex global_mu_;
   std::map<uint, uint> barrier_seen_;      // rank -> last epoch seen
   uint barrier_epoch_ = 0;
+  static constexpr uint kIpcRoundStride = 1u << 16;      // key of ipc_blobs_: rank + kIpcRoundStride * round
   std::map<uint, std::vector<char>> ipc_blobs_;
   std::map<uint, std::string> server_stats_;
 

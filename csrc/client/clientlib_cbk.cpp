@@ -121,7 +121,7 @@ void ClientLib::ipc_exchange_cbk(const Message& msg) {
   if (msg.size() < 2 || !msg[0].unpack(&h)) return;
   {
     std::lock_guard<std::mutex> lk(global_mu_);
-    ipc_blobs_[h.id].assign(msg[1].data(), msg[1].data() + msg[1].size());
+    ipc_blobs_[h.id + kIpcRoundStride * h.table_id].assign(msg[1].data(), msg[1].data() + msg[1].size());
   }
   global_cv_.notify_all();
 }

@@ -26,6 +26,8 @@ struct IpcBlob {
   cudaIpcMemHandle_t handle;
   uint64_t raw_ptr;
   uint64_t bytes;
+  int32_t phase;        // 0: capability round (can this rank use the multicast arena?), 1: handle round
+  int32_t mc_capable;
 };
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kFlagBytes = 256;
@@ -75,43 +77,99 @@ bool ClientLib::fabric_setup(std::string* err) {
   fabric_.status_off = off;
   off += 256;
   fabric_.bytes = off;
-  void* base = nullptr;
-  cudaError_t e = cudaMalloc(&base, fabric_.bytes);
-  if (e != cudaSuccess) { *err = std::string("arena cudaMalloc: ") + cudaGetErrorString(e); cudaGetLastError(); return false; }
-  cudaMemset(base, 0, fabric_.bytes);
-  cudaDeviceSynchronize();
-  fabric_.base = static_cast<char*>(base);
-  fabric_.peer_base.assign(num_processes_, nullptr);
-  fabric_.peer_base[process_id_] = fabric_.base;
+  int my_device = 0;
+  cudaGetDevice(&my_device);
+  // every rank sends one blob per round; a round is complete when all blobs of that phase are in
+  auto exchange = [&](const IpcBlob& mine_blob, std::vector<IpcBlob>* all) -> bool {
+    std::vector<char> blob(sizeof(IpcBlob));
+    memcpy(blob.data(), &mine_blob, sizeof(IpcBlob));
+    const uint round = (uint)mine_blob.phase;
+    encoder_->ipc_exchange(blob, round);
+    std::unique_lock<std::mutex> lk(global_mu_);
+    const bool got = global_cv_.wait_for(lk, std::chrono::seconds(120), [&] {
+      if (error_code_.load() != 0) return true;
+      for (uint r = 0; r < num_processes_; ++r) {
+        auto it = ipc_blobs_.find(r + kIpcRoundStride * round);
+        if (it == ipc_blobs_.end() || it->second.size() != sizeof(IpcBlob)) return false;
+      }
+      return true;
+    });
+    if (!got || error_code_.load()) return false;
+    all->assign(num_processes_, IpcBlob());
+    for (uint r = 0; r < num_processes_; ++r)
+      memcpy(&(*all)[r], ipc_blobs_[r + kIpcRoundStride * round].data(), sizeof(IpcBlob));
+    return true;
+  };
+  // ---- multicast arena (optional): agree first, so that either every rank uses it or none does ----
+  bool use_mc = false;
+  if (config_.use_multicast && num_processes_ > 1) {
+    std::string mc_err;
+    IpcBlob cap;
+    memset(&cap, 0, sizeof(cap));
+    cap.pid = (uint32_t)getpid();
+    cap.device = my_device;
+    cap.bytes = fabric_.bytes;
+    cap.phase = 0;
+    cap.mc_capable = MulticastArena::device_supported(my_device) && fabric_.mc.allocate(fabric_.bytes, my_device, &mc_err);
+    if (!cap.mc_capable) fprintf(stderr, "[geeps worker %u] multicast arena not available: %s\n", process_id_, mc_err.c_str());
+    std::vector<IpcBlob> all;
+    if (!exchange(cap, &all)) { *err = "timed out agreeing on the multicast arena with the other ranks"; return false; }
+    use_mc = true;
+    for (uint r = 0; r < num_processes_; ++r) {
+      use_mc = use_mc && all[r].mc_capable != 0 && all[r].bytes == fabric_.bytes;
+      for (uint q = 0; q < r; ++q) use_mc = use_mc && all[q].pid != all[r].pid;     // one process per rank only
+    }
+    if (!use_mc) fabric_.mc.release();
+  }
+  if (use_mc) {
+    const std::string tag = std::to_string(ServerThreadEntry::port_for(config_, 0, 0));
+    std::string mc_err;
+    // Nothing is bound before every rank has come this far without an error: up to the bind a failing rank can
+    // still leave and the others fall into their timeouts with plain memory.
+    bool ok = fabric_.mc.listen(tag, (int)process_id_, &mc_err);
+    ok = host_barrier(120000) && ok && error_code_.load() == 0;
+    ok = ok && fabric_.mc.send_handles(tag, (int)process_id_, (int)num_processes_, &mc_err);
+    ok = ok && fabric_.mc.receive_and_map((int)process_id_, (int)num_processes_, &mc_err);
+    if (!ok) set_error(ERR_TRANSPORT, "multicast arena: " + mc_err);
+    if (!host_barrier(120000) || error_code_.load()) { *err = "multicast arena setup failed: " + mc_err; return false; }
+    if (!fabric_.mc.bind_and_map(&mc_err)) { *err = "multicast arena: " + mc_err; return false; }
+    fabric_.use_mc = true;
+    fabric_.base = fabric_.mc.base();
+    fabric_.mc_base = fabric_.mc.multicast_base();
+    fabric_.peer_base.assign(num_processes_, nullptr);
+    for (uint r = 0; r < num_processes_; ++r) fabric_.peer_base[r] = fabric_.mc.peer((int)r);
+    cudaMemset(fabric_.base, 0, fabric_.bytes);
+    cudaDeviceSynchronize();
+    if (!host_barrier(120000) || error_code_.load()) { *err = "barrier after multicast binding failed"; return false; }
+  }
+  void* base = fabric_.base;
+  cudaError_t e = cudaSuccess;
+  if (!use_mc) {
+    e = cudaMalloc(&base, fabric_.bytes);
+    if (e != cudaSuccess) { *err = std::string("arena cudaMalloc: ") + cudaGetErrorString(e); cudaGetLastError(); return false; }
+    cudaMemset(base, 0, fabric_.bytes);
+    cudaDeviceSynchronize();
+    fabric_.base = static_cast<char*>(base);
+    fabric_.peer_base.assign(num_processes_, nullptr);
+    fabric_.peer_base[process_id_] = fabric_.base;
+  }
 
   // ---- exchange arena handles over the control plane ----
-  if (num_processes_ > 1) {
+  if (num_processes_ > 1 && !use_mc) {
     IpcBlob mine;
     memset(&mine, 0, sizeof(mine));
     mine.pid = (uint32_t)getpid();
+    mine.phase = 1;
     cudaGetDevice(&mine.device);
     mine.raw_ptr = (uint64_t)(uintptr_t)base;
     mine.bytes = fabric_.bytes;
     e = cudaIpcGetMemHandle(&mine.handle, base);
     if (e != cudaSuccess) { *err = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e); cudaGetLastError(); return false; }
-    std::vector<char> blob(sizeof(mine));
-    memcpy(blob.data(), &mine, sizeof(mine));
-    encoder_->ipc_exchange(blob);
-    {
-      std::unique_lock<std::mutex> lk(global_mu_);
-      const bool got = global_cv_.wait_for(lk, std::chrono::seconds(120), [&] {
-        return ipc_blobs_.size() >= num_processes_ || error_code_.load() != 0;
-      });
-      if (!got || error_code_.load()) { *err = "timed out exchanging arena handles with the other ranks"; return false; }
-    }
+    std::vector<IpcBlob> all;
+    if (!exchange(mine, &all)) { *err = "timed out exchanging arena handles with the other ranks"; return false; }
     for (uint r = 0; r < num_processes_; ++r) {
       if (r == process_id_) continue;
-      IpcBlob theirs;
-      {
-        std::lock_guard<std::mutex> lk(global_mu_);
-        if (ipc_blobs_[r].size() != sizeof(IpcBlob)) { *err = "bad arena handle from rank " + std::to_string(r); return false; }
-        memcpy(&theirs, ipc_blobs_[r].data(), sizeof(theirs));
-      }
+      const IpcBlob theirs = all[r];
       if (theirs.bytes != fabric_.bytes) { *err = "rank " + std::to_string(r) + " compiled a different plan"; return false; }
       if (theirs.pid == mine.pid) {
         // ranks living in one process (threads): plain pointers, peer access enabled explicitly
@@ -171,14 +229,15 @@ void ClientLib::fabric_teardown() {
     return;
   }
   const uint32_t pid = (uint32_t)getpid();
-  for (uint r = 0; r < num_processes_; ++r) {
+  for (uint r = 0; r < num_processes_ && !fabric_.use_mc; ++r) {
     if (r == process_id_ || !fabric_.peer_base[r]) continue;
     bool same_process = false;
     {
       std::lock_guard<std::mutex> lk(global_mu_);
-      if (ipc_blobs_[r].size() == sizeof(IpcBlob)) {
+      std::vector<char>& blob = ipc_blobs_[r + kIpcRoundStride * 1];
+      if (blob.size() == sizeof(IpcBlob)) {
         IpcBlob b;
-        memcpy(&b, ipc_blobs_[r].data(), sizeof(b));
+        memcpy(&b, blob.data(), sizeof(b));
         same_process = b.pid == pid;
       }
     }
@@ -196,7 +255,11 @@ void ClientLib::fabric_teardown() {
   fabric_.comm_lanes.clear();
   fabric_.comm_stream = nullptr;
   if (fabric_.host_status) cudaFreeHost(fabric_.host_status);
-  cudaFree(fabric_.base);
+  // the ranks left their last clock together (closing barrier in shutdown()): nothing uses the mappings any more
+  if (fabric_.use_mc) fabric_.mc.release();
+  else cudaFree(fabric_.base);
+  fabric_.use_mc = false;
+  fabric_.mc_base = nullptr;
   fabric_.base = nullptr;
   fabric_.active = false;
 }
@@ -302,6 +365,16 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
     p.data_age[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kDataAgeOff);
   }
   p.master16 = (ta.pull && config_.bf16_compute_cache) ? (void*)(fabric_.base + ta.master16_off) : nullptr;
+  if (fabric_.use_mc && fabric_.mc_base != nullptr) {
+    // through the multicast view: one in-switch reduction per row instead of a load per worker, one store per
+    // row instead of a store per worker
+    const size_t slot = (size_t)(clock % ta.ring_slots);
+    p.upd_mc = reinterpret_cast<const float*>(fabric_.mc_base + ta.ring_off + slot * ta.rows * kRowBytes);
+    if (!ta.pull) {
+      p.cache_mc = reinterpret_cast<float*>(fabric_.mc_base + ta.cache_off);
+      p.cache16_mc = config_.bf16_compute_cache ? (void*)(fabric_.mc_base + ta.cache16_off) : nullptr;
+    }
+  }
   const ShardRange& own = ct.plan->shard_ranges[process_id_];
   p.master = reinterpret_cast<float*>(fabric_.base + ta.master_off);
   p.momentum = reinterpret_cast<float*>(fabric_.base + ta.momentum_off);

@@ -88,10 +88,10 @@ void ClientServerEncode::barrier(uint epoch) {
   }
 }
 
-void ClientServerEncode::ipc_exchange(const std::vector<char>& blob) {
+void ClientServerEncode::ipc_exchange(const std::vector<char>& blob, uint32_t round) {
   for (uint s = 0; s < num_servers_; ++s) {
     Message msg(2);
-    ipc_exchange_msg_t h{CMD_IPC_EXCHANGE, client_id_, 0, 1};
+    ipc_exchange_msg_t h{CMD_IPC_EXCHANGE, client_id_, round, 1};
     msg[0].pack(h);
     msg[1].pack_memory(blob.data(), blob.size());
     router_->send_to(server_name(s), std::move(msg));

@@ -32,7 +32,9 @@ class ClientServerEncode {
   void get_stats(uint server_id);
   void heartbeat(uint64_t counter, iter_t clock);
   void barrier(uint epoch);
-  void ipc_exchange(const std::vector<char>& blob);
+  // `round` distinguishes successive exchanges (a fast rank may start the next one before a slow rank has read
+  // the previous one): the receiver keeps one blob per (rank, round)
+  void ipc_exchange(const std::vector<char>& blob, uint32_t round = 0);
   void shutdown_notice();
  private:
   std::shared_ptr<RouterHandler> router_;

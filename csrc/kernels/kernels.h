@@ -53,6 +53,13 @@ typedef struct GeepsPushApplyParams {
                                        // relative to a device-resident clock: launches that a CUDA graph replays)
   void* master16;                      // NULL, or this shard's bf16 copy of its master rows, compact [n_owned][128]
                                        // (uncached tables: consumers read it in place over NVLink)
+  // NVSwitch multicast view (all NULL: peer loads / stores).  upd_mc: the update buffer as seen through the
+  // multicast mapping - one multimem.ld_reduce returns the sum over all workers, added inside the switch, instead
+  // of one load per worker; cache_mc / cache16_mc: the caches through the mapping - one multimem.st publishes to
+  // every worker instead of one store per worker.  Same table layout as upd / cache / cache16.
+  const float* upd_mc;
+  float* cache_mc;
+  void* cache16_mc;
 } GeepsPushApplyParams;
 int geeps_ps_push_apply(const GeepsPushApplyParams* p, int max_ctas, void* stream);
 

@@ -108,7 +108,9 @@ push_apply_kernel(const GeepsPushApplyParams p) {
       }
       const long long goff = grow * GEEPS_ROW_FLOATS + lane * 4;  // offset in full-table buffers
       const long long loff = i * GEEPS_ROW_FLOATS + lane * 4;     // offset in shard-local buffers
-      float4 g = (NR > 0) ? reduce_fixed_order<(NR > 0 ? NR : 1)>(p, goff, strong) : reduce_dyn(p, goff, strong);
+      float4 g;
+      if (p.upd_mc != nullptr) g = multimem_ld_reduce_f4(p.upd_mc + goff);     // reduced inside the switch
+      else g = (NR > 0) ? reduce_fixed_order<(NR > 0 ? NR : 1)>(p, goff, strong) : reduce_dyn(p, goff, strong);
       float4 w = ld_f4(p.master + loff);
       if (p.mode == GEEPS_TABLE_SGD_MOMENTUM) {
         float4 m = ld_f4(p.momentum + loff);
@@ -124,6 +126,11 @@ push_apply_kernel(const GeepsPushApplyParams p) {
       // ---- fused publish into every worker's parameter cache ----
       if (p.publish) {
         const bool fp32_too = grow >= p.fp32_from_row;   // weights consumed in bf16 only skip two thirds of the bytes
+        if (p.upd_mc != nullptr) {
+          // one store per row reaches every worker's cache through the switch
+          if (fp32_too && p.cache_mc != nullptr) multimem_st_f4(p.cache_mc + goff, w);
+          if (p.cache16_mc != nullptr) multimem_st_bf16x4(static_cast<__nv_bfloat16*>(p.cache16_mc) + goff, h);
+        } else
         for (int q = 0; q < p.n_ranks; ++q) {
           if (fp32_too && p.cache[q] != nullptr) st_f4(p.cache[q] + goff, w);
           if (p.cache16[q] != nullptr) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.cache16[q]) + goff) = h;

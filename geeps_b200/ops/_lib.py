@@ -48,7 +48,7 @@ class PushApplyParams(C.Structure):
         ("publish", C.c_int),
         ("lr", C.c_float), ("momentum_coef", C.c_float), ("weight_decay", C.c_float),
         ("grad_scale", C.c_float), ("fp32_from_row", C.c_longlong), ("clock_ref", C.c_void_p),
-        ("master16", C.c_void_p),
+        ("master16", C.c_void_p), ("upd_mc", C.c_void_p), ("cache_mc", C.c_void_p), ("cache16_mc", C.c_void_p),
     ]
 
 

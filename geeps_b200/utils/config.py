@@ -44,6 +44,7 @@ class GeePsConfig:
     weight_decay: float = 0.0
     grad_scale: float = 1.0
     bf16_compute_cache: int = 0
+    use_multicast: int = 0     # NVLINK transport: reduce / publish through an NVSwitch multicast mapping (multimem)
     device_wait_budget_us: int = 30_000_000
     host_wait_budget_ms: int = 0
     heartbeat_timeout_ms: int = 30000
@@ -54,6 +55,6 @@ class GeePsConfig:
     _NUMERIC = ("num_tables", "tcp_base_port", "num_comm_channels", "log_interval", "pp_policy", "local_opt",
                 "gpu_memory_capacity", "mm_warning_level", "pinned_cpu_memory", "read_my_writes", "device",
                 "cuda_device", "transport", "partitioner", "table_mode", "learning_rate", "momentum",
-                "weight_decay", "grad_scale", "bf16_compute_cache", "device_wait_budget_us",
+                "weight_decay", "grad_scale", "bf16_compute_cache", "use_multicast", "device_wait_budget_us",
                 "host_wait_budget_ms", "heartbeat_timeout_ms", "snapshot_interval", "num_workers_override")
     _STRING = ("output_dir", "snapshot_dir")

@@ -62,6 +62,11 @@ struct GeePsConfig {
   /* per table: the range partition hands out rows in groups of this many (0 / 1: single rows), so that a matrix
      row spanning several 128-float table rows never straddles two shards */
   std::vector<size_t> table_partition_align;
+  /* NVLINK transport: allocate the arena through the virtual-memory API, bind it to an NVSwitch multicast object and
+     let the push kernel reduce (multimem.ld_reduce) and publish (multimem.st) through it.  Falls back to peer loads
+     and stores when a device lacks multicast support.  Sums are then added inside the switch, in an order the
+     switch chooses; the peer-load kernel adds in rank order. */
+  int use_multicast;
   float learning_rate, momentum, weight_decay;
   float grad_scale;           /* multiplies the reduced update before the optimizer (e.g. 1/workers) */
   int bf16_compute_cache;     /* also keep a bf16 copy of the parameter cache (NVLINK transport) */
@@ -83,7 +88,7 @@ struct GeePsConfig {
     pinned_cpu_memory(1),
     read_my_writes(0),
     device(DEVICE_CUDA), cuda_device(-1), transport(TRANSPORT_TCP),
-    partitioner(PARTITION_RANGE), table_mode(TABLE_ADDITIVE),
+    partitioner(PARTITION_RANGE), table_mode(TABLE_ADDITIVE), use_multicast(0),
     learning_rate(0.01f), momentum(0.9f), weight_decay(0.f), grad_scale(1.f),
     bf16_compute_cache(0),
     device_wait_budget_us(30u * 1000u * 1000u), host_wait_budget_ms(0), heartbeat_timeout_ms(30000),

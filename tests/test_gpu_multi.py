@@ -45,6 +45,37 @@ def test_nvlink_helloworld(slack):
             assert hi <= most + 1e-6, (clock, hi, most)
 
 
+@pytest.mark.parametrize("slack", [0, 1])
+def test_nvlink_helloworld_through_the_multicast_view(slack):
+    """Same run with the arena bound to an NVSwitch multicast object: the push kernel reduces with
+    multimem.ld_reduce and publishes with multimem.st.  Integer-valued updates, so the in-switch sum is exact."""
+    world, clocks = _world(), 40
+    out = _spawn(nvlink_hello_worker, world, (slack, clocks), dict(use_multicast=1, _rows=3000))
+    for rank, _, final, seen, _, stats in out:
+        assert stats["multicast"] is True, "the multicast arena was not used"
+        assert final == (float(world * clocks),) * 2, final
+        for clock, lo, hi in seen:
+            need = world * max(0, min(clock - slack - 1, clocks))
+            most = min(clock - 1, clocks) + (world - 1) * min(clock + slack, clocks)
+            assert lo >= need - 1e-6, (clock, lo, need)
+            assert hi <= most + 1e-6, (clock, hi, most)
+
+
+def test_nvlink_training_through_the_multicast_view_matches_peer_loads():
+    """Data-parallel training with the reduce and the publish going through the switch: every worker reads
+    bit-identical parameters, and the losses follow the peer-load run (the sums differ only in the order of the
+    additions)."""
+    world = _world()
+    runs = {}
+    for name, kw in (("p2p", {}), ("multicast", dict(use_multicast=1))):
+        out = _spawn(nvlink_train_worker, world, (10,), kw)
+        digests = [o[3] for o in out]
+        for d in digests[1:]:
+            assert d == digests[0]
+        runs[name] = out[0][2]
+    assert runs["multicast"] == pytest.approx(runs["p2p"], rel=5e-3), runs
+
+
 def test_nvlink_data_parallel_training_is_consistent():
     world = _world()
     out = _spawn(nvlink_train_worker, world, (10,))
