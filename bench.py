@@ -132,6 +132,9 @@ def main() -> None:
                     help="fully-connected tables uncached: the forward GEMMs pull their weight rows from the shards "
                          "(fused all-gather + GEMM) instead of reading a copy the shards published")
     ap.add_argument("--uncached", default="", help="comma-separated layer names whose tables are kept uncached")
+    ap.add_argument("--multicast", type=int, default=0, choices=[0, 1],
+                    help="1: the parameter-server arena is bound to an NVSwitch multicast object and large tables are "
+                         "reduced / published through it (multimem) from 4 GPUs on")
     ap.add_argument("--no-graph", action="store_true",
                     help="replay the recorded native calls one launch at a time instead of one CUDA graph per step")
     args = ap.parse_args()
@@ -176,7 +179,7 @@ def main() -> None:
                       device=DEVICE_CUDA, cuda_device=local_rank,
                       transport=TRANSPORT_NVLINK if args.transport == "nvlink" else TRANSPORT_TCP,
                       table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.01, momentum=0.9, weight_decay=5e-4,
-                      grad_scale=1.0 / world, bf16_compute_cache=1)
+                      grad_scale=1.0 / world, bf16_compute_cache=1, use_multicast=args.multicast if world > 1 else 0)
     stream = torch.cuda.Stream(device=dev, priority=-1)     # ahead of the runtime's comm stream
     with torch.cuda.stream(stream):
         mod = PSModule(net, (B,) + image, cfg, rank=rank, world=world, device=dev, slack=args.slack, seed=1,
@@ -331,6 +334,7 @@ def main() -> None:
                 "config": {"model": model_name, "global_batch": B * world, "batch_per_gpu": B, "image": list(image),
                            "parallelism": f"dp{world}+ps{world}", "transport": args.transport, "slack": args.slack, "input_dtype": args.input_dtype, "cpu_cores_bound": len(cores) if cores else 0,
                            "weight_publish": "bf16+fp32" if args.fp32_weight_cache else "bf16 (biases / BN fp32)",
+                           "multicast": bool(stats.get("multicast", False)),
                            "pulled_fc_tables": sum(1 for t in mod.tables if t.fused_pull),
                            "uncached_tables": sum(1 for t in mod.tables if t.pull),
                            "host_replay_tapes": len(mod._tapes), "step_graphs": len(mod._graphs),

@@ -365,7 +365,13 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
     p.data_age[r] = reinterpret_cast<int*>(fabric_.peer_base[r] + ta.flags_off + kDataAgeOff);
   }
   p.master16 = (ta.pull && config_.bf16_compute_cache) ? (void*)(fabric_.base + ta.master16_off) : nullptr;
-  if (fabric_.use_mc && fabric_.mc_base != nullptr) {
+  // The switch path moves fewer bytes per link once there are several peers (each row crosses a link once instead
+  // of once per peer) but a row's round trip is longer: measured, it wins from 4 ranks on for tables of tens of MB,
+  // and loses for small tables and for 2 ranks (GEEPS_MC_MIN_MB / GEEPS_MC_MIN_RANKS move the thresholds).
+  static const long long mc_min_bytes = (getenv("GEEPS_MC_MIN_MB") ? atoll(getenv("GEEPS_MC_MIN_MB")) : 32) << 20;
+  static const int mc_min_ranks = getenv("GEEPS_MC_MIN_RANKS") ? atoi(getenv("GEEPS_MC_MIN_RANKS")) : 4;
+  if (fabric_.use_mc && fabric_.mc_base != nullptr && (long long)(ta.rows * kRowBytes) >= mc_min_bytes &&
+      (int)num_processes_ >= mc_min_ranks) {
     // through the multicast view: one in-switch reduction per row instead of a load per worker, one store per
     // row instead of a store per worker
     const size_t slot = (size_t)(clock % ta.ring_slots);

@@ -100,17 +100,10 @@ push_apply_kernel(const GeepsPushApplyParams p) {
     const int lane = threadIdx.x & 31;
     const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-    for (long long i = warp0; i < p.n_owned; i += nwarps) {
-      const long long grow = p.row_start + i * p.row_stride;  // row id inside the table
-      if (grow < 0 || grow >= p.total_rows) {
-        if (lane == 0) geeps_report(p.status, GEEPS_ERR_BOUNDS, KID_PUSH_APPLY, (int)i, (int)grow);
-        continue;
-      }
+    // apply + publish of one owned row, given the reduced update of this lane's four values
+    auto finish_row = [&](long long i, long long grow, float4 g) {
       const long long goff = grow * GEEPS_ROW_FLOATS + lane * 4;  // offset in full-table buffers
       const long long loff = i * GEEPS_ROW_FLOATS + lane * 4;     // offset in shard-local buffers
-      float4 g;
-      if (p.upd_mc != nullptr) g = multimem_ld_reduce_f4(p.upd_mc + goff);     // reduced inside the switch
-      else g = (NR > 0) ? reduce_fixed_order<(NR > 0 ? NR : 1)>(p, goff, strong) : reduce_dyn(p, goff, strong);
       float4 w = ld_f4(p.master + loff);
       if (p.mode == GEEPS_TABLE_SGD_MOMENTUM) {
         float4 m = ld_f4(p.momentum + loff);
@@ -130,11 +123,47 @@ push_apply_kernel(const GeepsPushApplyParams p) {
           // one store per row reaches every worker's cache through the switch
           if (fp32_too && p.cache_mc != nullptr) multimem_st_f4(p.cache_mc + goff, w);
           if (p.cache16_mc != nullptr) multimem_st_bf16x4(static_cast<__nv_bfloat16*>(p.cache16_mc) + goff, h);
-        } else
-        for (int q = 0; q < p.n_ranks; ++q) {
-          if (fp32_too && p.cache[q] != nullptr) st_f4(p.cache[q] + goff, w);
-          if (p.cache16[q] != nullptr) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.cache16[q]) + goff) = h;
+        } else {
+          for (int q = 0; q < p.n_ranks; ++q) {
+            if (fp32_too && p.cache[q] != nullptr) st_f4(p.cache[q] + goff, w);
+            if (p.cache16[q] != nullptr) *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.cache16[q]) + goff) = h;
+          }
         }
+      }
+    };
+    auto row_of = [&](long long i, long long* grow) -> bool {
+      *grow = p.row_start + i * p.row_stride;  // row id inside the table
+      if (*grow < 0 || *grow >= p.total_rows) {
+        if (lane == 0) geeps_report(p.status, GEEPS_ERR_BOUNDS, KID_PUSH_APPLY, (int)i, (int)*grow);
+        return false;
+      }
+      return true;
+    };
+    if (p.upd_mc != nullptr) {
+      // Through the switch one load per row returns the sum over all workers, so a warp has a single request in
+      // flight per row where the peer-load path has one per worker: four rows are requested before the first is
+      // applied, to cover the round trip through the switch.
+      constexpr int U = 4;
+      for (long long i0 = warp0; i0 < p.n_owned; i0 += nwarps * U) {
+        float4 g[U];
+        long long grow[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * nwarps;
+          valid[u] = i < p.n_owned && row_of(i, &grow[u]);
+          if (valid[u]) g[u] = multimem_ld_reduce_f4(p.upd_mc + grow[u] * GEEPS_ROW_FLOATS + lane * 4);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (valid[u]) finish_row(i0 + u * nwarps, grow[u], g[u]);
+      }
+    } else {
+      for (long long i = warp0; i < p.n_owned; i += nwarps) {
+        long long grow;
+        if (!row_of(i, &grow)) continue;
+        const long long goff = grow * GEEPS_ROW_FLOATS + lane * 4;
+        finish_row(i, grow, (NR > 0) ? reduce_fixed_order<(NR > 0 ? NR : 1)>(p, goff, strong) : reduce_dyn(p, goff, strong));
       }
     }
   }

@@ -25,6 +25,8 @@ def main():
     ap.add_argument("--slack", type=int, nargs="+", default=[0, 1, 4])
     ap.add_argument("--clocks", type=int, default=10)
     ap.add_argument("--transport", default="nvlink")
+    ap.add_argument("--multicast", type=int, default=0,
+                    help="1: reduce and publish through the NVSwitch multicast view (multimem) instead of peer loads / stores")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -44,7 +46,8 @@ def main():
                               port_list=[port + (run % 19) * 100 + 10 * r for r in range(world)],
                               device=DEVICE_CUDA, cuda_device=local,
                               transport=TRANSPORT_NVLINK if a.transport == "nvlink" else TRANSPORT_TCP,
-                              partitioner=PARTITION_ROUND_ROBIN, table_mode=TABLE_SGD_MOMENTUM, grad_scale=1.0 / world)
+                              partitioner=PARTITION_ROUND_ROBIN, table_mode=TABLE_SGD_MOMENTUM, grad_scale=1.0 / world,
+                              use_multicast=a.multicast)
             with torch.cuda.stream(torch.cuda.Stream(device=dev)):
                 g = GeePs(rank, cfg)
                 ids = range(rows)
@@ -78,11 +81,13 @@ def main():
                 t = torch.tensor([e0.elapsed_time(e1) / a.clocks], device=dev, dtype=torch.float64)
                 if dist: dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 err = g.last_error()
+                multicast = bool(g.get_stats().get("multicast", False))
                 g.shutdown(); g.close()
             if rank == 0:
                 nbytes = rows * 512
                 out = {"bench": "ps_pushpull", "transport": a.transport, "world": world, "table_mb": nbytes / 2**20,
-                       "slack": slack, "ms_per_clock": t.item(), "gb_s_per_gpu": nbytes / t.item() / 1e6, "error": err}
+                       "slack": slack, "ms_per_clock": t.item(), "gb_s_per_gpu": nbytes / t.item() / 1e6, "error": err,
+                       "multicast": multicast}
                 if world > 1:
                     link_ms = 2 * (world - 1) / world * nbytes / 770e9 * 1e3
                     out["nvlink_roofline_ms"] = link_ms

@@ -119,6 +119,8 @@ def nvlink_hello_worker(rank, world, base_port, slack, clocks, q, kw):
         from geeps_b200.utils.config import DEVICE_CUDA, TRANSPORT_NVLINK
         torch.cuda.set_device(rank)
         kw = dict(kw)
+        if kw.get("use_multicast"):     # small tables and two ranks would otherwise stay on the peer-load path
+            os.environ["GEEPS_MC_MIN_MB"], os.environ["GEEPS_MC_MIN_RANKS"] = "0", "2"
         nrows = kw.pop("_rows", 1000)
         cfg = make_cfg(world, base_port, device=DEVICE_CUDA, cuda_device=rank, transport=TRANSPORT_NVLINK, **kw)
         stream = torch.cuda.Stream(device=rank)
@@ -169,6 +171,8 @@ def nvlink_train_worker(rank, world, base_port, steps, q, kw):
         from geeps_b200.utils.config import DEVICE_CUDA, TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK
         torch.cuda.set_device(rank)
         kw = dict(kw)
+        if kw.get("use_multicast"):
+            os.environ["GEEPS_MC_MIN_MB"], os.environ["GEEPS_MC_MIN_RANKS"] = "0", "2"
         mod_kw = kw.pop("_module", {})
         cfg = make_cfg(world, base_port, device=DEVICE_CUDA, cuda_device=rank, transport=TRANSPORT_NVLINK,
                        table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.02, momentum=0.9, grad_scale=1.0 / world,
