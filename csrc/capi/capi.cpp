@@ -157,6 +157,20 @@ int geeps_enable_device_clock(void* g) { return static_cast<GeePs*>(g)->EnableDe
 void geeps_advance_replayed_clock(void* g) { static_cast<GeePs*>(g)->AdvanceReplayedClock(); }
 const void* geeps_device_clock_ptr(void* g) { return static_cast<GeePs*>(g)->DeviceClockPtr(); }
 
+// ---- stream fork / join for independent branches of a network (Inception modules) ----
+void* geeps_event_new() {
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  return e;
+}
+void geeps_event_delete(void* e) { if (e) cudaEventDestroy((cudaEvent_t)e); }
+// work enqueued on `to` after this call starts only when everything enqueued on `from` so far has finished
+int geeps_stream_order(void* from, void* to, void* event) {
+  cudaError_t e = cudaEventRecord((cudaEvent_t)event, (cudaStream_t)from);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent((cudaStream_t)to, (cudaEvent_t)event, 0);
+  return (int)e;
+}
+
 // ---- CUDA graph helpers: capture what is enqueued on `stream` (and on every stream that joins it through
 // events) between begin and end, instantiate it, replay it ----
 int geeps_graph_begin(void* stream) {

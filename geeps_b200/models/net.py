@@ -7,15 +7,34 @@ from ..ops import functional as F
 from ..ops.layers import BF, LRN, BatchNorm, Conv2d, Layer, LRNMaxPool, Pool, SoftmaxLoss
 
 
+_side_streams = {}
+
+
+def side_streams(device, n: int) -> list:
+    """n CUDA streams of `device` shared by all Concat modules (branch i of every module runs on stream i)."""
+    pool = _side_streams.setdefault(str(device), [])
+    while len(pool) < n:
+        pool.append(torch.cuda.Stream(device=device))
+    return pool[:n]
+
+
 class Concat(Layer):
     """Parallel branches whose outputs are concatenated along channels.  The last layer of each
     branch writes straight into its channel slice of the joint output (no copy); in backward
-    each branch reads its slice of the joint gradient and the branch input-gradients are summed."""
+    each branch reads its slice of the joint gradient and the branch input-gradients are summed.
 
-    def __init__(self, name, branches):
+    The branches are independent, and at the image sizes where these modules sit a single kernel rarely fills
+    the GPU: with concurrent=True (default on a GPU; GEEPS_CONCAT_STREAMS=0 turns it off) branch i > 0 runs on a
+    side stream, forked from and joined back into the caller's stream, so the branches overlap - also inside a
+    captured step graph, where the fork / join become graph edges."""
+
+    def __init__(self, name, branches, concurrent=None):
         super().__init__()
         self.name = name
         self.branches = branches       # list of lists of layers
+        import os
+        self.concurrent = (os.environ.get("GEEPS_CONCAT_STREAMS", "1") != "0") if concurrent is None else concurrent
+        self._events = None
 
     def sublayers(self):
         for br in self.branches:
@@ -68,29 +87,53 @@ class Concat(Layer):
         for br in self.branches:
             br[0].set_input(x)
 
+    def _run_branches(self, fn):
+        """fn(i, branch) for every branch; branches 1.. on side streams between a fork and a join when concurrent."""
+        n = len(self.branches)
+        if not (self.concurrent and n > 1 and self.y.is_cuda):
+            for i, br in enumerate(self.branches):
+                fn(i, br)
+            return
+        main = torch.cuda.current_stream(self.y.device)
+        sides = side_streams(self.y.device, n - 1)
+        if self._events is None:
+            self._events = [F.new_event() for _ in range(2 * (n - 1))]
+        for i in range(1, n):
+            F.stream_order(main, sides[i - 1], self._events[i - 1])                 # fork
+        fn(0, self.branches[0])
+        for i in range(1, n):
+            with torch.cuda.stream(sides[i - 1]):
+                fn(i, self.branches[i])
+            F.stream_order(sides[i - 1], main, self._events[n - 1 + i - 1])         # join
+
     def forward(self, x):
         x4 = x if x.dim() == 4 else x.view(self.in_shape)
-        for br in self.branches:
+
+        def run(i, br):
             h = x4
             for l in br:
                 h = l.forward(h)
+        self._run_branches(run)
         return self.y
 
     def backward(self, dy):
         if dy.dim() != 2:
             dy = dy.view(self.P, -1)
-        off = 0
-        total = None
-        for br, w in zip(self.branches, self.widths):
-            g = dy[:, off:off + w]
+        offs, off = [], 0
+        for w in self.widths:
+            offs.append(off)
+            off += w
+        grads = [None] * len(self.branches)
+
+        def run(i, br):
+            g = dy[:, offs[i]:offs[i] + self.widths[i]]
             for l in reversed(br):
                 g = l.backward(g)
-            g2 = g.view(-1, self.in_shape[-1])
-            if total is None:
-                total = g2
-            else:
-                F.add_2d(total, g2)
-            off += w
+            grads[i] = g.view(-1, self.in_shape[-1])
+        self._run_branches(run)
+        total = grads[0]
+        for g2 in grads[1:]:
+            F.add_2d(total, g2)
         return total
 
 

@@ -194,6 +194,18 @@ def relu_backward_colsum(dy2d, y2d, dx2d, colsum_out) -> None:
            C.c_longlong(P), Cc, C.c_longlong(_ld(dy2d)), C.c_longlong(_ld(y2d)), C.c_longlong(_ld(dx2d)), stream_ptr())
 
 
+def stream_order(src_stream, dst_stream, event) -> None:
+    """Everything enqueued on dst_stream from now on waits for what src_stream holds now (`event`: a handle from
+    new_event()).  Recorded like a launch, so forks and joins of network branches replay and capture with the step."""
+    L.record_call(lib().geeps_stream_order, "stream_order", C.c_void_p(src_stream.cuda_stream),
+                  C.c_void_p(dst_stream.cuda_stream), C.c_void_p(event))
+
+
+def new_event() -> int:
+    lib().geeps_event_new.restype = C.c_void_p
+    return int(lib().geeps_event_new())
+
+
 def add_2d(dst2d, src2d) -> None:
     P, Cc = dst2d.shape
     launch(lib().geeps_add_bf16_2d, "add_bf16_2d", ptr(dst2d), ptr(src2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dst2d)),
