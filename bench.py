@@ -345,6 +345,7 @@ def main() -> None:
                 "memory_plan": ({"cache_fraction_of_activations": args.cache_frac, "budget_rows": mod.budget_rows,
                                  "working_set_rows": mod.working_set_rows, "managed_activation_rows": mod.managed_rows,
                                  "param_rows": mod.param_rows,
+                                 "uncached_param_rows": sum(t.rows for t in mod.tables if t.pull),
                                  "swap_h2d_gb_per_s": stats["client"]["swap_h2d_bytes"] / max(1, mod.steps) / (ms / args.steps) / 1e6,
                                  "swap_d2h_gb_per_s": stats["client"]["swap_d2h_bytes"] / max(1, mod.steps) / (ms / args.steps) / 1e6,
                                  "cpu_local_rows": stats["client"]["cpu_local_rows"], "gpu_local_rows": stats["client"]["gpu_local_rows"]}

@@ -91,11 +91,32 @@ class PSModule:
                     continue
                 nrows = (nbytes + 511) // 512
                 self.managed[i] = {"rows": range(1_000_000 * (i + 1), 1_000_000 * (i + 1) + nrows), "nrows": nrows}
+        direct16 = ps_config.transport == TRANSPORT_NVLINK and ps_config.bf16_compute_cache
+        # uncached (pull) tables
+        nv = ps_config.transport == TRANSPORT_NVLINK and torch.cuda.is_available()
+        from ..ops.layers import Linear as _Linear
+        for t in self.tables:
+            t.pull = t.fused_pull = False
+            l = t.layer
+            if not nv:
+                continue
+            if (pull_fc and isinstance(l, _Linear) and direct16 and l.B <= 256 and l.ld % ROW_FLOATS == 0
+                    and len(t.specs) == 2):
+                t.pull = t.fused_pull = True
+                ps_config.table_partition_align[t.table_id] = l.ld // ROW_FLOATS    # whole weight rows per shard
+                ps_config.table_fp32_from_row[t.table_id] = t.offsets[1] // ROW_FLOATS  # the bias rows are the tail
+            elif getattr(l, "name", None) in uncached:
+                t.pull = True
+                ps_config.table_fp32_from_row.pop(t.table_id, None)
+            if t.pull:
+                ps_config.table_pull[t.table_id] = 1
         self.param_rows = sum(t.rows for t in self.tables)
         self.managed_rows = sum(m["nrows"] for m in self.managed.values())
         if cache_fraction is not None:
             ring = slack + 1 if ps_config.transport == TRANSPORT_NVLINK else 1 + int(bool(ps_config.read_my_writes))
-            param_state = self.param_rows * (1 + ring)
+            # rows of parameter state that stay in GPU memory: the update ring of every table, plus the worker's copy
+            # of every table that is not uncached
+            param_state = sum(t.rows * (ring + (0 if t.pull else 1)) for t in self.tables)
             if ps_config.transport == TRANSPORT_NVLINK:
                 # peers read and write the parameter cache and the update ring in place, so that state stays
                 # device resident; the cap applies to the activation working set, but never goes below what
@@ -109,29 +130,11 @@ class PSModule:
             self.working_set_rows = param_state + self.managed_rows
             ps_config.gpu_memory_capacity = budget_rows * 512
             ps_config.mm_warning_level = 0
-        self.direct16 = ps_config.transport == TRANSPORT_NVLINK and ps_config.bf16_compute_cache
+        self.direct16 = direct16
         if bf16_weights_only and self.direct16:
             for t in self.tables:
-                if t.specs and t.specs[0].name == "weight":
+                if t.specs and t.specs[0].name == "weight" and not t.pull:
                     ps_config.table_fp32_from_row[t.table_id] = (t.offsets[1] // ROW_FLOATS) if len(t.specs) > 1 else t.rows
-        # uncached (pull) tables
-        nv = ps_config.transport == TRANSPORT_NVLINK and torch.cuda.is_available()
-        from ..ops.layers import Linear as _Linear
-        for t in self.tables:
-            t.pull = t.fused_pull = False
-            l = t.layer
-            if not nv:
-                continue
-            if (pull_fc and isinstance(l, _Linear) and self.direct16 and l.B <= 256 and l.ld % ROW_FLOATS == 0
-                    and len(t.specs) == 2):
-                t.pull = t.fused_pull = True
-                ps_config.table_partition_align[t.table_id] = l.ld // ROW_FLOATS    # whole weight rows per shard
-                ps_config.table_fp32_from_row[t.table_id] = t.offsets[1] // ROW_FLOATS  # the bias rows are the tail
-            elif getattr(l, "name", None) in uncached:
-                t.pull = True
-                ps_config.table_fp32_from_row.pop(t.table_id, None)
-            if t.pull:
-                ps_config.table_pull[t.table_id] = 1
         self.ps = GeePs(rank, ps_config)
         # tape replay: record two consecutive steps; if they issued identical native calls (static pointers),
         # later steps walk the tape instead of re-running the Python layer code

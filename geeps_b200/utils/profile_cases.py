@@ -4,6 +4,9 @@ Each case allocates well under 1 GB (but more than the 126 MB L2 where DRAM figu
 once and launches the kernel of interest three times.
   gemm        conv3-forward-shaped bf16 GEMM (M=43264, N=384, K=2304), tcgen05 kernel
   gemm_dgrad  conv3 data-gradient shape (small K, MN-major B, output-heavy)
+  gemm_fc6    fully-connected forward at batch 256 (M=256, N=4096, K=9216): weight-streaming bound
+  gemm_pair   8192^3 on the CTA-pair kernel (tcgen05 cta_group::2)
+  maxpool     3x3 stride-2 max pooling forward + backward on a conv1-sized activation (256 x 55 x 55 x 96)
   push_apply  fused reduce + momentum-SGD apply + publish over a 256 MB table (1 rank)
   lrn         LRN forward + backward on a conv1-sized activation
   lrn_pool    LRN fused with the 3x3 stride-2 max pooling after it, forward + backward (256 x 55 x 55 x 96)
@@ -35,6 +38,31 @@ def main():
         out = torch.empty(M, N, dtype=BF, device=dev)
         for _ in range(4):
             F.gemm(a, b, out, b_mn=b_mn)
+    elif case == "gemm_fc6":
+        M, N, K = 256, 4096, 9216
+        a = (torch.randn(M, K, device=dev) * 0.1).to(BF)
+        b = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+        bias = torch.zeros(N, device=dev)
+        out = torch.empty(M, N, dtype=BF, device=dev)
+        for _ in range(4):
+            F.gemm(a, b, out, bias=bias, relu=True)
+    elif case == "gemm_pair":
+        M = N = K = 8192
+        a = (torch.randn(M, K, device=dev) * 0.1).to(BF)
+        b = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+        out = torch.empty(M, N, dtype=BF, device=dev)
+        for _ in range(3):
+            F.gemm(a, b, out)
+    elif case == "maxpool":
+        B, H, Cc = 256, 55, 96
+        x = torch.randn(B, H, H, Cc, device=dev).to(BF)
+        g = F.pool_geom(x.shape, 3, 2, 0, Cc, Cc)
+        y = torch.empty(B, g.OH, g.OW, Cc, dtype=BF, device=dev)
+        arg = torch.empty(B, g.OH, g.OW, Cc, dtype=torch.uint8, device=dev)
+        dx = torch.empty_like(x)
+        for _ in range(3):
+            F.maxpool_forward(x, y, arg, g)
+            F.maxpool_backward(y, arg, dx, g)
     elif case == "push_apply":
         rows = 512 * 1024          # 256 MB table
         upd = torch.randn(rows, 128, device=dev) * 0.01
