@@ -204,14 +204,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc05::fence_after_sync();
           const uint32_t sa = tc05::smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
+          // descriptors as 32-bit halves: per MMA this one thread spends an add per operand, not a rebuild
+          const uint32_t a_lo = tc05::desc_lo(sa, A_MN ? PANEL_BYTES : 16), b_lo = tc05::desc_lo(sb, B_MN ? PANEL_BYTES : 16);
+          constexpr uint32_t d_hi = tc05::desc_hi(1024);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = A_MN ? tc05::make_smem_desc(sa + k * 2048, PANEL_BYTES, 1024)
-                                     : tc05::make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t db = B_MN ? tc05::make_smem_desc(sb + k * 2048, PANEL_BYTES, 1024)
-                                     : tc05::make_smem_desc(sb + k * 32, 16, 1024);
-            tc05::mma_bf16_ss(tacc, da, db, idesc, (kt > kt_begin || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc05::mma_bf16_ss_lohi(tacc, a_lo + (A_MN ? 128 : 2) * k, d_hi, b_lo + (B_MN ? 128 : 2) * k, d_hi, idesc,
+                                   (kt > kt_begin || k > 0) ? 1u : 0u);
           tc05::mma_commit(&ctl->empty[s]);
           if (++s == S) { s = 0; ph ^= 1u; }
         }
@@ -417,6 +416,7 @@ int geeps_conv_tc_supported(const GeepsConvTcParams* p) {
 
 int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   if (!geeps_conv_tc_supported(p)) return (int)cudaErrorInvalidValue;
+  if (p->mode != MODE_WGRAD && p->split_k >= 0 && geeps_conv_halo_applicable(p)) return geeps_conv_halo(p, stream);
   const int kSMs = geeps_sm_count();
   cudaStream_t st = (cudaStream_t)stream;
   ConvDev d;

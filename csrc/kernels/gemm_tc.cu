@@ -149,16 +149,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc05::fence_after_sync();
           const uint32_t sa = tc05::smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
+          // descriptors as 32-bit halves: per MMA this one thread spends an add per operand, not a rebuild.
+          // K-major: 16 k-elements = 32 bytes inside the 128-byte swizzle row (2 units of 16 bytes);
+          // MN-major: 16 k-rows of 128 bytes = two 8-row groups of 1024 bytes (128 units).
+          const uint32_t a_lo = tc05::desc_lo(sa, A_MN ? 64 * BK * 2 : 16), b_lo = tc05::desc_lo(sb, B_MN ? 64 * BK * 2 : 16);
+          constexpr uint32_t d_hi = tc05::desc_hi(1024);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major: 16 k-elements = 32 bytes inside the 128-byte swizzle row.
-            // MN-major: 16 k-rows of 128 bytes = two 8-row groups of 1024 bytes.
-            const uint64_t da = A_MN ? tc05::make_smem_desc(sa + k * 2048, 64 * BK * 2, 1024)
-                                     : tc05::make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t db = B_MN ? tc05::make_smem_desc(sb + k * 2048, 64 * BK * 2, 1024)
-                                     : tc05::make_smem_desc(sb + k * 32, 16, 1024);
-            tc05::mma_bf16_ss(tacc, da, db, idesc, (kt > kt_begin || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc05::mma_bf16_ss_lohi(tacc, a_lo + (A_MN ? 128 : 2) * k, d_hi, b_lo + (B_MN ? 128 : 2) * k, d_hi, idesc,
+                                   (kt > kt_begin || k > 0) ? 1u : 0u);
           tc05::mma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
           if (++s == S) { s = 0; ph ^= 1u; }
         }

@@ -160,6 +160,11 @@ typedef struct GeepsConvTcParams {
 } GeepsConvTcParams;
 int geeps_conv_tc(const GeepsConvTcParams* p, void* stream);
 int geeps_conv_tc_supported(const GeepsConvTcParams* p);
+// Halo-tile variant for forward / data gradient (conv_halo.cu): every activation is fetched once per 64-channel
+// chunk and the filter taps are shifted MMA-descriptor starts.  geeps_conv_tc() routes to it when applicable
+// (a negative split_k on a forward / data-gradient call keeps the call on the box kernel).
+int geeps_conv_halo_applicable(const GeepsConvTcParams* p);
+int geeps_conv_halo(const GeepsConvTcParams* p, void* stream);
 
 // ---------------- parameter pull fused with the consuming GEMM ----------------
 // Y[M,N] = X[M,K] * W[N,K]^T + bias (+ReLU), M <= 256, K a multiple of 64.  W's rows live on the server

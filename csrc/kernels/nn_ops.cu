@@ -600,7 +600,10 @@ nchw_to_s2d_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int H, 
     for (int j = 0; j + 8 <= N; j += 8)
       *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
                                                       pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-    for (int j = N & ~7; j < Cpad; ++j) dst[j] = __float2bfloat16(j < N ? v[j] : 0.f);
+    int j = N & ~7;
+    if ((N & 7) == 0)
+      for (; j + 8 <= Cpad; j += 8) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0, 0, 0, 0);
+    for (; j < Cpad; ++j) dst[j] = __float2bfloat16(j < N ? v[j] : 0.f);
   }
 }
 

@@ -50,6 +50,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// One lane of a converged warp.  The single-thread roles run their loops with the whole warp (so every value in
+// them is warp-uniform and no lane sits in a divergent branch for the life of the kernel) and give only the
+// TMA / MMA / commit instructions to the elected lane.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+// mbar_wait() by all lanes of a converged warp with one verdict for the warp
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               uint64_t budget_ns) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, budget_ns)) != 0;
+}
+
 // ---------------- TMA (tiled 2D load, no multicast) ----------------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y) {
   asm volatile(
@@ -97,6 +115,19 @@ __device__ __forceinline__ void tma_reduce_add_3d(const void* tmap, const void* 
 __device__ __forceinline__ void tma_store_4d(const void* tmap, const void* smem_src, int x, int y, int z, int w) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// the same store with the source given as a shared-window address
+__device__ __forceinline__ void tma_store_4d_addr(const void* tmap, uint32_t smem_src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(tmap), "r"(smem_src), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// one bf16 (rounded to nearest even) to a shared-window address
+__device__ __forceinline__ void st_shared_bf16(uint32_t addr, float v) {
+  asm volatile(
+      "{\n\t.reg .b16 h;\n\t"
+      "cvt.rn.bf16.f32 h, %1;\n\t"
+      "st.shared.b16 [%0], h;\n\t}"
+      ::"r"(addr), "f"(v) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // wait until at most N of this thread's bulk groups still READ their shared-memory source
@@ -182,6 +213,27 @@ __device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, ui
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The same descriptor as two 32-bit halves.  A single thread issues every MMA, so the instructions it spends per
+// MMA are the kernel's issue rate: the high half is a constant of the layout, and moving the start address by
+// `bytes` adds bytes >> 4 to the low half (the 14-bit address field cannot carry: shared memory ends below 256 KB).
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ void mma_bf16_ss_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 

@@ -8,9 +8,10 @@ from .net import Net
 
 def alexnet(num_classes: int = 1000, dropout: float = 0.5) -> Net:
     layers = [
-        # the input layer emits a space-to-depth(4) layout [B, 57, 57, 48]: the 11 x 11 stride-4 convolution
-        # becomes a 3 x 3 stride-1 implicit GEMM (taps past 11 are zero columns), so no patch matrix is built
-        Conv2d("conv1", 96, 11, stride=4, relu=True, std=0.01, need_dx=False, s2d=4),
+        # the input layer emits a space-to-depth(4) layout [B, 57, 57, 48 + 16 zero channels]: the 11 x 11 stride-4
+        # convolution becomes a 3 x 3 stride-1 implicit GEMM (taps past 11 and the padding channels are zero
+        # columns), so no patch matrix is built and every pixel is one aligned 128-byte line
+        Conv2d("conv1", 96, 11, stride=4, relu=True, std=0.01, need_dx=False, s2d=4, cin_valid=3),
         LRN(5, 1e-4, 0.75, 1.0),
         Pool("max", 3, 2),
         Conv2d("conv2", 256, 5, pad=2, groups=2, relu=True, std=0.01, bias_value=0.1),
@@ -26,4 +27,4 @@ def alexnet(num_classes: int = 1000, dropout: float = 0.5) -> Net:
         Dropout(dropout, seed=71),
         Linear("fc8", num_classes, std=0.01, fp32_out=True),
     ]
-    return Net("alexnet", Input(s2d=4, s2d_k=11), layers)
+    return Net("alexnet", Input(s2d=4, s2d_k=11, cpad=64), layers)

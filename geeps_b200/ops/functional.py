@@ -104,6 +104,19 @@ def conv_tc(mode: int, x, y, w, k: int, pad: int, **kw) -> None:
     launch(lib().geeps_conv_tc, "conv_tc", C.byref(p), stream_ptr())
 
 
+def conv_halo_applicable(p: ConvTcParams) -> bool:
+    """Does conv_tc() route this call to the halo-tile kernel (activations fetched once per channel chunk)?"""
+    return bool(lib().geeps_conv_halo_applicable(C.byref(p)))
+
+
+def conv_halo(mode: int, x, y, w, k: int, pad: int, **kw) -> None:
+    """The halo-tile kernel called directly (forward / data gradient), whatever conv_tc() would have chosen."""
+    L.require_cuda()
+    assert mode in (CONV_FWD, CONV_DGRAD) and x.dtype == bf16 and y.dtype == bf16 and w.dtype == bf16
+    p = conv_tc_params(mode, x, y, w, k, pad, **kw)
+    launch(lib().geeps_conv_halo, "conv_halo", C.byref(p), stream_ptr())
+
+
 def nchw_to_nhwc_bf16(x: torch.Tensor, cpad: int | None = None) -> torch.Tensor:
     L.require_cuda()
     B, Cc, H, W = x.shape

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m geeps_b200.utils.microbench [gemm|ps|rows|all]
+"""Kernel micro-benchmarks: python -m geeps_b200.utils.microbench [gemm|conv|lrn_pool|rows|all]
 
 Every number is a CUDA-event time on the launching stream after warm-up, with a buffer larger than
 L2 written between timed launches.  GEMM lines also give cuBLAS (torch.matmul) on the same shape and
@@ -130,8 +130,45 @@ def bench_lrn_pool():
                               "gb_s": round(gbs, 1), "frac_of_hbm": round(gbs / hbm, 3), "peak_source": src}), flush=True)
 
 
+def bench_conv():
+    """Stride-1 convolutions of AlexNet (batch 256) and Inception (batch 128): the box kernel (one activation load
+    per filter tap) against the halo-tile kernel (one load per channel chunk), forward and data gradient."""
+    dev = torch.device("cuda")
+    peak, _, src = _peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    shapes = [
+        # name, B, H, cg, og, k, pad, groups sharing the tensors
+        ("alexnet conv1 (space-to-depth, pixel padded to 64 channels)", 256, 57, 64, 96, 3, 0, 1),
+        ("alexnet conv2 (one of 2 groups)", 256, 27, 48, 128, 5, 2, 2),
+        ("inception 3x3 56x56 64->192", 128, 56, 64, 192, 3, 1, 1),
+        ("inception 3x3 28x28 128->192", 128, 28, 128, 192, 3, 1, 1),
+        ("inception 5x5 28x28 32->96", 128, 28, 32, 96, 5, 2, 1),
+        ("inception 3x3 14x14 112->224", 128, 14, 112, 224, 3, 1, 1),
+    ]
+    for name, B, H, cg, og, k, pad, groups in shapes:
+        OH = H + 2 * pad - k + 1
+        xf = torch.randn(B, H, H, cg * groups, device=dev).to(BF)
+        yf = torch.empty(B, OH, OH, og * groups, device=dev, dtype=BF)
+        x, y = xf[..., :cg], yf[..., :og]
+        kd = k * k * cg
+        w = (torch.randn(og, kd, device=dev) / kd ** 0.5).to(BF)
+        bias = torch.zeros(og, device=dev)
+        flops = 2.0 * B * OH * OH * og * kd
+        for mode, mname in ((F.CONV_FWD, "fwd"), (F.CONV_DGRAD, "dgrad")):
+            kw = dict(bias=bias, relu=True) if mode == F.CONV_FWD else {}
+            t_box = timeit(lambda: F.conv_tc(mode, x, y, w, k, pad, split_k=-1, **kw), flush=flush)
+            t_halo = timeit(lambda: F.conv_halo(mode, x, y, w, k, pad, **kw), flush=flush)
+            print(json.dumps({"kernel": f"{name} {mname}", "box_ms": round(t_box, 4), "halo_ms": round(t_halo, 4),
+                              "halo_tflops": round(flops / t_halo / 1e9, 1),
+                              "halo_frac_of_peak": round(flops / t_halo / 1e9 / peak, 3), "peak_source": src,
+                              "routed_to_halo": bool(F.conv_halo_applicable(F.conv_tc_params(mode, x, y, w, k, pad)))}),
+                  flush=True)
+
+
 def main():
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("conv", "all"):
+        bench_conv()
     if what in ("lrn_pool", "all"):
         bench_lrn_pool()
     if what in ("gemm", "all"):

@@ -12,7 +12,8 @@ once and launches the kernel of interest three times.
   lrn_pool    LRN fused with the 3x3 stride-2 max pooling after it, forward + backward (256 x 55 x 55 x 96)
   pull_gemm   fused pull + GEMM on an fc6-shaped layer (4 local shards)
   conv_fwd / conv_dgrad / conv_wgrad   implicit-GEMM convolution, conv3 shape (256 x 13 x 13, 256 -> 384, 3x3)
-  conv1_fwd   AlexNet conv1 after space-to-depth (256 x 57 x 57 x 48 -> 96, 3x3, no padding)
+  conv1_fwd   AlexNet conv1 after space-to-depth (256 x 57 x 57 x 64 (48 + 16 zero) -> 96, 3x3, no padding);
+              routed to the halo-tile kernel, like conv2_fwd / conv2_dgrad (GEEPS_HALO_CONV=0: the box kernel)
   conv2_fwd / conv2_dgrad   one group of AlexNet conv2 (256 x 27 x 27, 48 of 96 -> 128 of 256 channels, 5x5)
 """
 from __future__ import annotations
@@ -125,7 +126,7 @@ def main():
                 F.conv_tc(F.CONV_WGRAD, x, y, dw, k, pad)
     elif case in ("conv1_fwd", "conv2_fwd", "conv2_dgrad"):
         if case == "conv1_fwd":
-            B, H, ct, cg, ot, og, k, pad = 256, 57, 48, 48, 96, 96, 3, 0
+            B, H, ct, cg, ot, og, k, pad = 256, 57, 64, 64, 96, 96, 3, 0
         else:
             B, H, ct, cg, ot, og, k, pad = 256, 27, 96, 48, 256, 128, 5, 2
         OH = H + 2 * pad - k + 1

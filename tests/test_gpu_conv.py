@@ -75,14 +75,72 @@ def test_conv_tc_forward_dgrad_wgrad_match_torch(case):
     assert status.tolist()[0] == 0
 
 
-def test_space_to_depth_conv_matches_strided_torch_conv():
-    """Input(s2d) + Conv2d(s2d): an 11x11 stride-4 convolution run as a 3-tap stride-1 implicit GEMM."""
+HALO_CASES = CASES + [
+    (3, 57, 57, 48, 0, 48, 96, 0, 96, 3, 0),            # AlexNet conv1 after space-to-depth: 96 channels leave in 32-wide slabs
+    (3, 28, 28, 192, 0, 192, 96, 0, 96, 3, 1),          # three chunks, rows split 4 + 4 per tile, last tile short
+    (2, 14, 14, 96, 32, 32, 64, 0, 48, 5, 2),           # 5x5 on a small map, channel slices on both sides
+    (2, 56, 56, 64, 0, 64, 192, 0, 192, 3, 1),          # two rows per block, two N tiles
+]
+
+
+@pytest.mark.parametrize("case", HALO_CASES)
+def test_conv_halo_forward_dgrad_match_torch(case):
+    """The halo-tile kernel called directly on every shape it accepts (conv_tc() picks it only where it pays)."""
+    from geeps_b200.ops import functional as F
+    B, H, W, Ct, c_off, cg, Ot, o_off, og, k, pad = case
+    if k * k < 4:
+        pytest.skip("single-tap filters have no halo")
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(hash(case) % 1000)
+    OH, OW = H + 2 * pad - k + 1, W + 2 * pad - k + 1
+    kd = k * k * cg
+    ld = (kd + 7) // 8 * 8
+    x_full = torch.randn(B, H, W, Ct, device=dev, generator=gen).to(BF)
+    w = torch.zeros(og, ld, device=dev, dtype=BF)
+    w[:, :kd] = (torch.randn(og, kd, device=dev, generator=gen) / kd ** 0.5).to(BF)
+    bias = torch.randn(og, device=dev, generator=gen)
+    dy_full = torch.randn(B, OH, OW, Ot, device=dev, generator=gen).to(BF)
+    x = x_full[..., c_off:c_off + cg]
+    dy = dy_full[..., o_off:o_off + og]
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    xr = x.float().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    wr = w[:, :kd].float().view(og, k, k, cg).permute(0, 3, 1, 2).contiguous()
+    yr = torch.nn.functional.conv2d(xr, wr, bias, padding=pad)
+    yr.backward(dy.float().permute(0, 3, 1, 2))
+    y_ref = torch.relu(yr.detach()).permute(0, 2, 3, 1)
+    dx_ref = xr.grad.permute(0, 2, 3, 1)
+
+    y_full = torch.full((B, OH, OW, Ot), 7.0, device=dev, dtype=BF)
+    y = y_full[..., o_off:o_off + og]
+    F.conv_halo(F.CONV_FWD, x, y, w, k, pad, bias=bias, relu=True, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    assert _rel(y, y_ref) < 1e-2
+    if Ot != og:
+        rest = torch.cat([y_full[..., :o_off], y_full[..., o_off + og:]], dim=-1)
+        assert bool((rest == 7.0).all())
+    dx_full = torch.full((B, H, W, Ct), 3.0, device=dev, dtype=BF)
+    dx = dx_full[..., c_off:c_off + cg]
+    F.conv_halo(F.CONV_DGRAD, dx, dy, w, k, pad, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    assert _rel(dx, dx_ref) < 1e-2
+    if Ct != cg:
+        rest = torch.cat([dx_full[..., :c_off], dx_full[..., c_off + cg:]], dim=-1)
+        assert bool((rest == 3.0).all())
+
+
+@pytest.mark.parametrize("cpad", [None, 64])
+def test_space_to_depth_conv_matches_strided_torch_conv(cpad):
+    """Input(s2d) + Conv2d(s2d): an 11x11 stride-4 convolution run as a 3-tap stride-1 implicit GEMM; with cpad the
+    48-channel space-to-depth pixel is zero-padded to one 128-byte line."""
     from geeps_b200.ops.layers import Conv2d, Input
     dev = torch.device("cuda:0")
     gen = torch.Generator(device=dev).manual_seed(3)
     B, C, H, k, S, cout = 4, 3, 67, 11, 4, 32
     x = torch.randn(B, C, H, H, device=dev, generator=gen)
-    inp, conv = Input(s2d=S, s2d_k=k), Conv2d("c1", cout, k, stride=S, relu=True, need_dx=False, s2d=S)
+    inp = Input(s2d=S, s2d_k=k, cpad=cpad)
+    conv = Conv2d("c1", cout, k, stride=S, relu=True, need_dx=False, s2d=S, cin_valid=C if cpad else None)
     shape = conv.setup(inp.setup((B, C, H, H), dev), dev)
     OH = (H - k) // S + 1
     assert shape == (B, OH, OH, cout)
@@ -95,8 +153,9 @@ def test_space_to_depth_conv_matches_strided_torch_conv():
     y = conv.forward(inp.forward(x)).view(B, OH, OH, cout)
 
     # the same weights as a [cout, C, k, k] filter: column (a*T + b)*48 + (dy*S + dx)*C + c -> tap (a*S+dy, b*S+dx)
-    T, Cs = conv.k, S * S * C
-    wt = w32.to(BF).float()[:, :T * T * Cs].view(cout, T, T, S, S, C)       # [o, a, b, dy, dx, c]
+    T, Cs, Cp = conv.k, S * S * C, conv.in_shape[-1]
+    assert Cp == (cpad or Cs)
+    wt = w32.to(BF).float()[:, :T * T * Cp].view(cout, T, T, Cp)[..., :Cs].reshape(cout, T, T, S, S, C)   # [o, a, b, dy, dx, c]
     wfull = wt.permute(0, 5, 1, 3, 2, 4).reshape(cout, C, T * S, T * S)[:, :, :k, :k].contiguous().requires_grad_(True)
     xr = x.to(BF).float()
     yr = torch.nn.functional.conv2d(xr, wfull, bias, stride=S)
@@ -106,7 +165,9 @@ def test_space_to_depth_conv_matches_strided_torch_conv():
     conv.backward(dy.view(-1, cout))
     mask = (yr > 0).float()
     yr.backward(dy.float().permute(0, 3, 1, 2) * mask)
-    gw = conv.g32["weight"][:, :T * T * Cs].view(cout, T, T, S, S, C).permute(0, 5, 1, 3, 2, 4).reshape(cout, C, T * S, T * S)
+    gfull = conv.g32["weight"][:, :T * T * Cp].view(cout, T, T, Cp)
+    assert float(gfull[..., Cs:].abs().max()) == 0 if Cp > Cs else True      # padding channels receive no gradient
+    gw = gfull[..., :Cs].reshape(cout, T, T, S, S, C).permute(0, 5, 1, 3, 2, 4).reshape(cout, C, T * S, T * S)
     assert _rel(gw[:, :, :k, :k], wfull.grad) < 1e-2
     # taps past the 11 x 11 filter receive no gradient, so they stay zero under SGD
     assert float(gw[:, :, k:, :].abs().max()) == 0 and float(gw[:, :, :, k:].abs().max()) == 0
