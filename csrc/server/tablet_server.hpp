@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "core/common_util.hpp"
+#include "core/relaxed.hpp"
 #include "core/row_op_util.hpp"
 #include "geeps.hpp"
 
@@ -21,8 +22,9 @@ namespace geeps_b200 {
 class ServerClientEncode;
 
 struct TabletStats {
-  uint64_t nr_update = 0, nr_local_update = 0, nr_rows = 0, nr_clock = 0, nr_broadcast = 0, nr_errors = 0;
-  double apply_time = 0, clock_time = 0, send_time = 0;
+  // written by the shard's server thread, read by GetStats() on the application thread
+  Relaxed<uint64_t> nr_update = 0, nr_local_update = 0, nr_rows = 0, nr_clock = 0, nr_broadcast = 0, nr_errors = 0;
+  Relaxed<double> apply_time = 0, clock_time = 0, send_time = 0;
   std::string to_json() const;
 };
 
