@@ -368,7 +368,7 @@ HaloPlan plan_halo(const GeepsConvTcParams* p) {
   hp.util = 0;
   HaloDev& d = hp.d;
   memset(&d, 0, sizeof(d));
-  if (p->mode != MODE_FWD && p->mode != MODE_DGRAD) return hp;
+  if ((p->mode != MODE_FWD && p->mode != MODE_DGRAD) || p->stride > 1) return hp;
   const bool fwd = p->mode == MODE_FWD;
   const int GW = fwd ? p->OW : p->W, GH = fwd ? p->OH : p->H;
   d.KH = p->KH; d.KW = p->KW; d.taps = p->KH * p->KW;

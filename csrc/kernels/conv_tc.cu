@@ -49,6 +49,7 @@ struct ConvDev {
   int relu, zero_fill_c;          // wgrad: a channel coordinate outside X, for panels past the last one
   int ch_valid;                   // wgrad: channels per tap (cg)
   int narrow;                     // fwd / dgrad: result leaves in 32-channel (64-byte) slabs, see the host code
+  int stride;                     // fwd / wgrad: pixel stride of the layer (the X boxes are loaded with this element stride)
 };
 
 struct SmemCtl {
@@ -159,7 +160,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint64_t* bar = &ctl->full[s];
           tc05::mbar_expect_tx(bar, tx_bytes);
           if (MODE == MODE_FWD) {
-            tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 + kw - d.pad, mb.h0 + kh - d.pad, mb.b0);
+            tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 * d.stride + kw - d.pad, mb.h0 * d.stride + kh - d.pad, mb.b0);
             tc05::tma_load_3d(sb, &tmB, bar, cc * 64, tap, ni * BN);
           } else if (MODE == MODE_DGRAD) {
             tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 + d.pad - kw, mb.h0 + d.pad - kh, mb.b0);
@@ -169,7 +170,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int h = 0; h < 2; ++h)
               tc05::tma_load_4d(sa + h * PANEL_BYTES, &tmA, bar, mi * BM + 64 * h, kb.w0, kb.h0, kb.b0);
             for (int j = 0; j < BN / 64; ++j)
-              tc05::tma_load_4d(sb + j * PANEL_BYTES, &tmB, bar, pc[j], kb.w0 + pdw[j], kb.h0 + pdh[j], kb.b0);
+              tc05::tma_load_4d(sb + j * PANEL_BYTES, &tmB, bar, pc[j], kb.w0 * d.stride + pdw[j], kb.h0 * d.stride + pdh[j], kb.b0);
           }
           if (MODE == MODE_WGRAD) {
             kb.w0 += d.bw;
@@ -336,25 +337,33 @@ EncodeTiledFn encode_fn() {
 
 // rank-N map (128-byte swizzle unless told otherwise); dims / box innermost first, strides (bytes) for dims 1..rank-1
 bool make_map(CUtensorMap* map, const void* base, int rank, const long long* dims, const long long* strides_bytes,
-              const int* box, bool fp32, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+              const int* box, bool fp32, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B,
+              const int* elem_strides = nullptr) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gd[4], gs[3];
   cuuint32_t bx[4], es[4];
-  for (int i = 0; i < rank; ++i) { gd[i] = (cuuint64_t)dims[i]; bx[i] = (cuuint32_t)box[i]; es[i] = 1; }
+  for (int i = 0; i < rank; ++i) {
+    gd[i] = (cuuint64_t)dims[i]; bx[i] = (cuuint32_t)box[i];
+    es[i] = elem_strides ? (cuuint32_t)elem_strides[i] : 1;
+  }
   for (int i = 0; i + 1 < rank; ++i) gs[i] = (cuuint64_t)strides_bytes[i];
   return fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
             const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// NHWC activation tensor as (channels, W, H, B) with a pixel pitch of `pitch` channels
+// NHWC activation tensor as (channels, W, H, B) with a pixel pitch of `pitch` channels.  stride > 1: a box of
+// bw x bh pixels takes every stride-th pixel (TMA element strides; the box extent is given in traversed elements,
+// of which ceil(extent / stride) are loaded).
 bool make_act_map(CUtensorMap* map, const void* base, int ch, int W, int H, int B, long long pitch, int bw, int bh,
-                  int bnb, bool narrow = false) {
+                  int bnb, bool narrow = false, int stride = 1) {
   const long long dims[4] = {ch, W, H, B};
   const long long st[3] = {pitch * 2, pitch * 2 * W, pitch * 2 * W * H};
-  const int box[4] = {narrow ? 32 : 64, bw, bh, bnb};
-  return make_map(map, base, 4, dims, st, box, false, narrow ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+  const int box[4] = {narrow ? 32 : 64, bw * stride, bh * stride, bnb};
+  const int es[4] = {1, stride, stride, 1};
+  return make_map(map, base, 4, dims, st, box, false, narrow ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  es);
 }
 
 // Pick the pixel box (bw, bh, bnb) with at most `cap` pixels that covers the W x H x B grid with the fewest
@@ -404,7 +413,9 @@ extern "C" {
 
 int geeps_conv_tc_supported(const GeepsConvTcParams* p) {
   if (p->B <= 0 || p->H <= 0 || p->W <= 0 || p->cg <= 0 || p->og <= 0 || p->KH <= 0 || p->KW <= 0) return 0;
-  if (p->OH != p->H + 2 * p->pad - p->KH + 1 || p->OW != p->W + 2 * p->pad - p->KW + 1) return 0;   // stride 1 only
+  const int s = p->stride > 1 ? p->stride : 1;
+  if (s > 8 || (s > 1 && p->mode == MODE_DGRAD)) return 0;
+  if (p->OH != (p->H + 2 * p->pad - p->KH) / s + 1 || p->OW != (p->W + 2 * p->pad - p->KW) / s + 1) return 0;
   if (p->OH <= 0 || p->OW <= 0) return 0;
   if (((uintptr_t)p->x & 15) || ((uintptr_t)p->y & 15) || ((uintptr_t)p->w & 15)) return 0;
   if ((p->x_pitch & 7) || (p->y_pitch & 7) || (p->cg & 7) || (p->og & 7)) return 0;
@@ -428,6 +439,7 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   d.zero_fill_c = 0;
   d.ch_valid = p->cg;
   d.narrow = 0;
+  d.stride = p->stride > 1 ? p->stride : 1;
   CUtensorMap ta, tb, tc;
   bool ok = true;
   const long long wdims[3] = {p->cg, d.taps, p->og};
@@ -451,7 +463,7 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
     d.n_tiles = (nch + bn - 1) / bn;
     const long long wst[2] = {(long long)p->cg * 2, p->ldw * 2};
     if (fwd) {
-      ok = make_act_map(&ta, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb);
+      ok = make_act_map(&ta, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb, false, d.stride);
       const int wbox[3] = {64, 1, bn};
       ok = ok && make_map(&tb, p->w, 3, wdims, wst, wbox, false);
       d.narrow = narrow_store(p->og, p->y_pitch);
@@ -485,7 +497,7 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
     d.n_tiles = (panels + per - 1) / per;
     d.zero_fill_c = d.cchunks * 64;
     ok = make_act_map(&ta, p->y, p->og, p->OW, p->OH, p->B, p->y_pitch, d.bw, d.bh, d.bnb);
-    ok = ok && make_act_map(&tb, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb);
+    ok = ok && make_act_map(&tb, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb, false, d.stride);
     const long long wst[2] = {(long long)p->cg * 4, p->ldw * 4};
     const int wbox[3] = {32, 1, BM};
     ok = ok && make_map(&tc, p->w, 3, wdims, wst, wbox, true);

@@ -157,6 +157,8 @@ typedef struct GeepsConvTcParams {
   void* x; void* y; void* w; const float* bias; int* status;
   long long x_pitch, y_pitch, ldw;
   int B, H, W, cg, OH, OW, og, KH, KW, pad, relu, mode, split_k;
+  int stride;   // 0 or 1: stride 1; 2 .. 8: forward and weight gradient only (the activation boxes are loaded with
+                // that TMA element stride), the data gradient of a strided layer is not an implicit GEMM here
 } GeepsConvTcParams;
 int geeps_conv_tc(const GeepsConvTcParams* p, void* stream);
 int geeps_conv_tc_supported(const GeepsConvTcParams* p);

@@ -330,6 +330,25 @@ relu_backward_2d_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
     st8(dx + p * lddx + c, o);
   }
 }
+// dst = bf16(relu ? max(src, 0) : src) over a [P][C] fp32 matrix with row pitches: the finishing pass of a split-K
+// GEMM whose partial sums were reduce-added in fp32
+__global__ void __launch_bounds__(256)
+f32_to_bf16_2d_kernel(const float* __restrict__ src, bf16* __restrict__ dst, long long P, int C, long long lds,
+                      long long ldd, int relu) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float lo = relu ? 0.f : -INFINITY;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long p = i / cv;
+    const float4 a = *reinterpret_cast<const float4*>(src + p * lds + c);
+    const float4 b = *reinterpret_cast<const float4*>(src + p * lds + c + 4);
+    *reinterpret_cast<uint4*>(dst + p * ldd + c) =
+        make_uint4(pack_bf16x2(fmaxf(a.x, lo), fmaxf(a.y, lo)), pack_bf16x2(fmaxf(a.z, lo), fmaxf(a.w, lo)),
+                   pack_bf16x2(fmaxf(b.x, lo), fmaxf(b.y, lo)), pack_bf16x2(fmaxf(b.z, lo), fmaxf(b.w, lo)));
+  }
+}
 // ReLU backward fused with the per-channel sums of its result (the bias gradient of the layer whose output y is):
 // dx = y > 0 ? dy : 0, out[c] += sum over pixels of dx.  Every thread keeps one 8-channel slot and strides over
 // the pixels, as in channel_reduce_kernel.
@@ -1101,6 +1120,12 @@ int geeps_relu_backward_colsum(const void* dy, const void* y, void* dx, float* c
   if (want < min_blocks) want = min_blocks;
   relu_backward_colsum_kernel<<<(int)(want < 1 ? 1 : want), 256, C * sizeof(float), st>>>(
       (const bf16*)dy, (const bf16*)y, (bf16*)dx, colsum, P, C, lddy, ldy, lddx);
+  return CK();
+}
+int geeps_f32_to_bf16_2d(const float* src, void* dst, long long P, int C, long long lds, long long ldd, int relu,
+                         void* stream) {
+  if (C % 8 || lds % 4 || ldd % 8 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15)) return (int)cudaErrorInvalidValue;
+  f32_to_bf16_2d_kernel<<<grid_1d(P * (C / 8)), 256, 0, (cudaStream_t)stream>>>(src, (bf16*)dst, P, C, lds, ldd, relu);
   return CK();
 }
 int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long ldd, long long lds, void* stream) {

@@ -46,6 +46,9 @@ int geeps_colsum(const void* x, float* out, long long P, int C, long long ldx, f
 int geeps_relu_backward(const void* dy, const void* y, void* dx, long long n, void* stream);
 int geeps_relu_backward_2d(const void* dy, const void* y, void* dx, long long P, int C, long long lddy, long long ldy,
                            long long lddx, void* stream);
+// dst[P][C] (bf16) = src[P][C] (fp32), optionally through ReLU; row pitches in elements
+int geeps_f32_to_bf16_2d(const float* src, void* dst, long long P, int C, long long lds, long long ldd, int relu,
+                         void* stream);
 int geeps_add_bf16_2d(void* dst, const void* src, long long P, int C, long long ldd, long long lds, void* stream);
 int geeps_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, void* stream);
 // the same with the seed taken as seed + *step_ref when the kernel runs (a device-resident step counter: the launch

@@ -32,7 +32,7 @@ class ConvTcParams(C.Structure):
         ("x_pitch", C.c_longlong), ("y_pitch", C.c_longlong), ("ldw", C.c_longlong),
         ("B", C.c_int), ("H", C.c_int), ("W", C.c_int), ("cg", C.c_int), ("OH", C.c_int), ("OW", C.c_int),
         ("og", C.c_int), ("KH", C.c_int), ("KW", C.c_int), ("pad", C.c_int), ("relu", C.c_int),
-        ("mode", C.c_int), ("split_k", C.c_int),
+        ("mode", C.c_int), ("split_k", C.c_int), ("stride", C.c_int),
     ]
 
 

@@ -70,8 +70,9 @@ CONV_FWD, CONV_DGRAD, CONV_WGRAD = 0, 1, 2
 
 def conv_tc_params(mode: int, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, k: int, pad: int, *,
                    bias: torch.Tensor | None = None, relu: bool = False, split_k: int = 0,
-                   status: torch.Tensor | None = None) -> ConvTcParams:
-    """Arguments of the implicit-GEMM convolution (stride 1).  x: [B, H, W, cg] and y: [B, OH, OW, og] are NHWC
+                   status: torch.Tensor | None = None, stride: int = 1) -> ConvTcParams:
+    """Arguments of the implicit-GEMM convolution (any stride up to 8 for forward and weight gradient, stride 1 for
+    the data gradient).  x: [B, H, W, cg] and y: [B, OH, OW, og] are NHWC
     bf16 tensors or channel slices of wider ones (last-dim stride 1, dense pixels); w: [og, ldw] with column
     (kh * k + kw) * cg + ci, bf16 for forward / data gradient, fp32 (the gradient) for the weight gradient."""
     B, H, W, cg = x.shape
@@ -87,6 +88,7 @@ def conv_tc_params(mode: int, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor,
     p.x_pitch, p.y_pitch, p.ldw = xp, yp, w.stride(0)
     p.B, p.H, p.W, p.cg, p.OH, p.OW, p.og = B, H, W, cg, OH, OW, og
     p.KH, p.KW, p.pad, p.relu, p.mode, p.split_k = k, k, pad, int(relu), mode, split_k
+    p.stride = stride
     return p
 
 
@@ -95,8 +97,9 @@ def conv_tc_supported(p: ConvTcParams) -> bool:
 
 
 def conv_tc(mode: int, x, y, w, k: int, pad: int, **kw) -> None:
-    """Stride-1 convolution without a patch matrix (tcgen05 + 4-D TMA): forward writes y, CONV_DGRAD writes x
-    (y holds dY), CONV_WGRAD writes w (fp32, y holds dY)."""
+    """Convolution without a patch matrix (tcgen05 + 4-D TMA): forward writes y, CONV_DGRAD writes x (y holds dY;
+    stride 1 only), CONV_WGRAD writes w (fp32, y holds dY).  stride=s loads the activation boxes with TMA element
+    stride s."""
     L.require_cuda()
     assert x.dtype == bf16 and y.dtype == bf16
     assert w.dtype == (torch.float32 if mode == CONV_WGRAD else bf16)
@@ -223,6 +226,14 @@ def add_2d(dst2d, src2d) -> None:
     P, Cc = dst2d.shape
     launch(lib().geeps_add_bf16_2d, "add_bf16_2d", ptr(dst2d), ptr(src2d), C.c_longlong(P), Cc, C.c_longlong(_ld(dst2d)),
                                   C.c_longlong(_ld(src2d)), stream_ptr())
+
+
+def f32_to_bf16_2d(src2d, dst2d, relu: bool = False) -> None:
+    """dst (bf16) = src (fp32), optionally through ReLU; both may be column slices of wider matrices."""
+    P, Cc = src2d.shape
+    assert src2d.dtype == torch.float32 and dst2d.dtype == bf16 and dst2d.shape == src2d.shape
+    launch(lib().geeps_f32_to_bf16_2d, "f32_to_bf16_2d", ptr(src2d), ptr(dst2d), C.c_longlong(P), Cc,
+           C.c_longlong(_ld(src2d)), C.c_longlong(_ld(dst2d)), int(relu), stream_ptr())
 
 
 def dropout(x, y, p: float, seed: int, step_ref: int | None = None) -> None:

@@ -22,6 +22,8 @@ from . import functional as F
 BF = torch.bfloat16
 # stride-1 convolutions as implicit GEMM (GEEPS_IMPLICIT_CONV=0 keeps the im2col + GEMM + col2im formulation)
 IMPLICIT_CONV = os.environ.get("GEEPS_IMPLICIT_CONV", "1") != "0"
+# fully-connected layers at batch <= 256 split their k range over the SMs (GEEPS_SPLIT_K_LINEAR=0: one wide tile row)
+SPLIT_K_LINEAR = os.environ.get("GEEPS_SPLIT_K_LINEAR", "0") != "0"
 
 
 def _pad8(n: int) -> int:
@@ -176,11 +178,20 @@ class Conv2d(Layer):
         self.pointwise = self.k == 1 and self.stride == 1 and self.pad == 0 and G == 1 and C % 8 == 0
         # stride-1 layers run as an implicit GEMM (no patch matrix); the final say comes from the kernel's own
         # alignment check on the first forward, when the output binding is known
-        self.implicit = (IMPLICIT_CONV and not self.pointwise and self.stride == 1 and self.cg % 8 == 0
+        self.implicit = (IMPLICIT_CONV and not self.pointwise and 1 <= self.stride <= 8 and self.cg % 8 == 0
                          and self.og % 8 == 0 and C % 8 == 0)
+        if self.stride > 1 and self.cg < 32:
+            # every tap is a k-step of 64 channels: with 8 channels (the 7 x 7 stride-2 first layer of the 22K net)
+            # 49 mostly-zero k-steps lose to 7 dense ones over a patch matrix (6.8 against 5.8 ms per step)
+            self.implicit = False
+        # a strided layer's data gradient still goes through GEMM + col2im (its forward and weight gradient load
+        # the activation boxes with a TMA element stride and build no patch matrix)
+        self.implicit_dgrad = self.implicit and self.stride == 1
         self.cols = self.dcol = None
         if not self.pointwise and not self.implicit:
             self._alloc_patch_buffers()
+        elif self.implicit and not self.implicit_dgrad and self.need_dx:
+            self.dcol = torch.empty(self.M, self.ld, dtype=BF, device=device)
         self.y = None
         self.dx = torch.empty(in_shape, dtype=BF, device=device) if self.need_dx else None
         self.out_shape = (B, self.OH, self.OW, self.cout)
@@ -220,7 +231,8 @@ class Conv2d(Layer):
         if self.implicit and self.cols is None and not getattr(self, "_implicit_checked", False):
             self._implicit_checked = True
             ok = all(F.conv_tc_supported(F.conv_tc_params(F.CONV_FWD, self._x4(x, g), self._y4(self.y, g),
-                                                          w16[g * self.og:(g + 1) * self.og], self.k, self.pad))
+                                                          w16[g * self.og:(g + 1) * self.og], self.k, self.pad,
+                                                          stride=self.stride))
                      for g in range(self.groups))
             if not ok:
                 self.implicit = False
@@ -229,7 +241,7 @@ class Conv2d(Layer):
             if self.implicit:
                 F.conv_tc(F.CONV_FWD, self._x4(x, g), self._y4(self.y, g), w16[g * self.og:(g + 1) * self.og],
                           self.k, self.pad, bias=None if bias is None else bias[g * self.og:(g + 1) * self.og],
-                          relu=self.relu)
+                          relu=self.relu, stride=self.stride)
                 continue
             if self.pointwise:
                 a = x.view(self.M, -1)
@@ -261,10 +273,14 @@ class Conv2d(Layer):
         for g in range(self.groups):
             if self.implicit:
                 xg, dy4 = self._x4(self.x, g), self._y4(dy, g)
-                F.conv_tc(F.CONV_WGRAD, xg, dy4, gw[g * self.og:(g + 1) * self.og], self.k, self.pad)
-                if self.need_dx:
+                F.conv_tc(F.CONV_WGRAD, xg, dy4, gw[g * self.og:(g + 1) * self.og], self.k, self.pad,
+                          stride=self.stride)
+                if self.need_dx and self.implicit_dgrad:
                     F.conv_tc(F.CONV_DGRAD, self._x4(self.dx, g), dy4, w16[g * self.og:(g + 1) * self.og],
                               self.k, self.pad)
+                elif self.need_dx:
+                    F.gemm(dy[:, g * self.og:(g + 1) * self.og], w16[g * self.og:(g + 1) * self.og], self.dcol, b_mn=True)
+                    F.col2im(self.dcol, self.dx, self.geoms[g])
                 continue
             dyg = dy[:, g * self.og:(g + 1) * self.og]
             a = self.x.view(self.M, -1) if self.pointwise else self.cols[g]
@@ -327,9 +343,28 @@ class Linear(Layer):
             shards, n_start = pull
             F.pull_gemm(self.x, shards, n_start, self.y, ldw=self.ld, bias=self.p32["bias"], relu=self.relu,
                         w_local=self.p16["weight"])
+        elif self._split_k():
+            # batch-sized M: two or four wide output tiles would leave most SMs idle while the weights stream, so the
+            # k range is split over the SMs (partial sums reduce-added in fp32) and a finishing pass converts
+            if self.fp32_out:
+                F.gemm(self.x, self.p16["weight"], self.y, bias=self.p32["bias"], split_k=0)
+            else:
+                ws = self._workspace(self.out_ld)[:, :self.out]
+                F.gemm(self.x, self.p16["weight"], ws, bias=self.p32["bias"], split_k=0)
+                F.f32_to_bf16_2d(ws, self.y, relu=self.relu)
         else:
             F.gemm(self.x, self.p16["weight"], self.y, bias=self.p32["bias"], relu=self.relu)
         return self.y
+
+    def _split_k(self) -> bool:
+        return SPLIT_K_LINEAR and self.B <= 256 and self.out % 8 == 0
+
+    def _workspace(self, width):
+        """fp32 [B, width] scratch shared by the forward and the data gradient of this layer."""
+        w = max(self.out_ld, self.k_in)
+        if getattr(self, "_ws", None) is None:
+            self._ws = torch.empty(self.B, w, dtype=torch.float32, device=self.device)
+        return self._ws.view(-1)[:self.B * width].view(self.B, width)
 
     def backward(self, dy):
         if self.relu:
@@ -346,7 +381,12 @@ class Linear(Layer):
         # dW[out, in] = dy^T @ x ; dx[B, in] = dy @ W
         F.gemm(dy, self.x, self.g32["weight"], a_mn=True, b_mn=True, split_k=0)
         if self.need_dx:
-            F.gemm(dy, self.p16["weight"], self.dx, b_mn=True)
+            if self._split_k():
+                ws = self._workspace(self.k_in)
+                F.gemm(dy, self.p16["weight"], ws, b_mn=True, split_k=0)
+                F.f32_to_bf16_2d(ws, self.dx)
+            else:
+                F.gemm(dy, self.p16["weight"], self.dx, b_mn=True)
             return self.dx.view(self.in_shape)
         return None
 

@@ -75,6 +75,49 @@ def test_conv_tc_forward_dgrad_wgrad_match_torch(case):
     assert status.tolist()[0] == 0
 
 
+STRIDED = [
+    # B, H, W, cg, og, k, pad, stride
+    (4, 28, 28, 64, 96, 3, 1, 2),        # Inception down-sampling branch
+    (2, 64, 64, 8, 64, 7, 3, 2),         # first layer of the 22K net (3 channels padded to 8), scaled down
+    (3, 17, 17, 32, 32, 3, 0, 2),        # no padding, odd size
+    (2, 23, 23, 16, 48, 5, 2, 3),        # stride 3
+]
+
+
+@pytest.mark.parametrize("case", STRIDED)
+def test_strided_conv_forward_and_weight_gradient_match_torch(case):
+    """Strided layers: the activation boxes are loaded with a TMA element stride, no patch matrix."""
+    from geeps_b200.ops import functional as F
+    B, H, W, cg, og, k, pad, st = case
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(5)
+    OH, OW = (H + 2 * pad - k) // st + 1, (W + 2 * pad - k) // st + 1
+    kd = k * k * cg
+    ld = (kd + 7) // 8 * 8
+    x = torch.randn(B, H, W, cg, device=dev, generator=gen).to(BF)
+    w = torch.zeros(og, ld, device=dev, dtype=BF)
+    w[:, :kd] = (torch.randn(og, kd, device=dev, generator=gen) / kd ** 0.5).to(BF)
+    bias = torch.randn(og, device=dev, generator=gen)
+    dy = torch.randn(B, OH, OW, og, device=dev, generator=gen).to(BF)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    xr = x.float().permute(0, 3, 1, 2).contiguous()
+    wr = w[:, :kd].float().view(og, k, k, cg).permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    yr = torch.nn.functional.conv2d(xr, wr, bias, stride=st, padding=pad)
+    yr.backward(dy.float().permute(0, 3, 1, 2))
+    y = torch.empty(B, OH, OW, og, device=dev, dtype=BF)
+    assert F.conv_tc_supported(F.conv_tc_params(F.CONV_FWD, x, y, w, k, pad, stride=st))
+    assert not F.conv_tc_supported(F.conv_tc_params(F.CONV_DGRAD, x, y, w, k, pad, stride=st))
+    F.conv_tc(F.CONV_FWD, x, y, w, k, pad, bias=bias, relu=True, status=status, stride=st)
+    assert _rel(y, torch.relu(yr.detach()).permute(0, 2, 3, 1)) < 1e-2
+    dw_ref = wr.grad.permute(0, 2, 3, 1).reshape(og, kd)
+    for split in (0, 1):
+        dw = torch.full((og, ld), 5.0, device=dev)
+        F.conv_tc(F.CONV_WGRAD, x, dy, dw, k, pad, split_k=split, status=status, stride=st)
+        assert _rel(dw[:, :kd], dw_ref) < 1e-2, split
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+
+
 HALO_CASES = CASES + [
     (3, 57, 57, 48, 0, 48, 96, 0, 96, 3, 0),            # AlexNet conv1 after space-to-depth: 96 channels leave in 32-wide slabs
     (3, 28, 28, 192, 0, 192, 96, 0, 96, 3, 1),          # three chunks, rows split 4 + 4 per tile, last tile short

@@ -310,3 +310,34 @@ def test_colsum_relu_backward_dropout():
     assert torch.equal(o1, o2)
     keep = (o1 > 0).float().mean().item()
     assert abs(keep - 0.5) < 0.01 and o1.max().item() == 2.0
+
+
+@pytest.mark.parametrize("relu,fp32_out", [(True, False), (False, False), (False, True)])
+def test_linear_with_the_k_range_split_over_the_sms_matches_fp32(relu, fp32_out, monkeypatch):
+    """Batch-sized M: split-K GEMM into an fp32 workspace plus the converting pass, forward and data gradient,
+    against torch in fp32 on the bf16-rounded operands."""
+    from geeps_b200.ops import layers as GL
+    monkeypatch.setattr(GL, "SPLIT_K_LINEAR", True)
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(11)
+    B, K, N = 64, 1024, 264
+    lin = GL.Linear("fc", N, relu=relu, fp32_out=fp32_out)
+    lin.setup((B, K), dev)
+    w = (torch.randn(N, K, device=dev, generator=gen) * 0.05).to(BF)
+    bias = torch.randn(N, device=dev, generator=gen)
+    lin.p16, lin.p32 = {"weight": w}, {"bias": bias}
+    lin.g32 = {"weight": torch.zeros(N, K, device=dev), "bias": torch.zeros(N, device=dev)}
+    x = torch.randn(B, K, device=dev, generator=gen).to(BF)
+    y = lin.forward(x)
+    ref = x.float() @ w.float().t() + bias
+    if relu:
+        ref = torch.relu(ref)
+    assert y.dtype == (torch.float32 if fp32_out else BF)
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+    dy = torch.randn(B, N, device=dev, generator=gen).to(torch.float32 if fp32_out else BF)
+    dyb = dy.to(BF)
+    dx = lin.backward(dyb)
+    mask = (ref > 0).float() if relu else torch.ones_like(ref)
+    dx_ref = (dyb.float() * mask) @ w.float()
+    assert ((dx.float() - dx_ref).norm() / dx_ref.norm()).item() < 1e-2
+    torch.cuda.synchronize()
