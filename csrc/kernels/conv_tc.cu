@@ -50,6 +50,10 @@ struct ConvDev {
   int ch_valid;                   // wgrad: channels per tap (cg)
   int narrow;                     // fwd / dgrad: result leaves in 32-channel (64-byte) slabs, see the host code
   int stride;                     // fwd / wgrad: pixel stride of the layer (the X boxes are loaded with this element stride)
+  int pad_w, pad_h;               // dgrad: dY offset of tap (0, 0); equal to pad for a stride-1 layer
+  int tap0, tap_dw, tap_dh;       // dgrad: weight tap of loop position (kh, kw) = tap0 + kh * tap_dh + kw * tap_dw
+                                  // (a strided layer's data gradient runs one parity class of dX at a time, each
+                                  // with the sub-filter of the taps that reach it)
 };
 
 struct SmemCtl {
@@ -120,9 +124,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      tc05::tma_prefetch_desc(&tmA);
-      tc05::tma_prefetch_desc(&tmB);
+    // the loop runs with the whole warp converged; the elected lane issues the copies
+    {
+      const bool leader = tc05::elect_one();
+      if (leader) { tc05::tma_prefetch_desc(&tmA); tc05::tma_prefetch_desc(&tmB); }
       // every index below advances incrementally: this one thread's latency is the producer's throughput,
       // and an integer division costs more than the TMA issue itself
       int s = 0;
@@ -137,7 +142,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         Box mb = {0, 0, 0};
         if (MODE != MODE_WGRAD) mb = decode_box(d, mi);
         // fwd / dgrad: k-tile = (kh, kw, channel chunk), starting at 0 (no split)
-        int kh = 0, kw = 0, cc = 0, tap = 0;
+        int kh = 0, kw = 0, cc = 0, tap = 0, wtap = d.tap0;
         // wgrad: k-tile = pixel box; the N panels of this tile are fixed
         Box kb = {0, 0, 0};
         int pc[4] = {0, 0, 0, 0}, pdw[4] = {0, 0, 0, 0}, pdh[4] = {0, 0, 0, 0};
@@ -154,23 +159,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         for (int kt = kt_begin; kt < kt_end; ++kt) {
-          if (!tc05::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+          if (!tc05::mbar_wait_warp(&ctl->empty[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           uint8_t* sa = tiles + (size_t)s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           uint64_t* bar = &ctl->full[s];
+          if (leader) {
           tc05::mbar_expect_tx(bar, tx_bytes);
           if (MODE == MODE_FWD) {
             tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 * d.stride + kw - d.pad, mb.h0 * d.stride + kh - d.pad, mb.b0);
             tc05::tma_load_3d(sb, &tmB, bar, cc * 64, tap, ni * BN);
           } else if (MODE == MODE_DGRAD) {
-            tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 + d.pad - kw, mb.h0 + d.pad - kh, mb.b0);
+            tc05::tma_load_4d(sa, &tmA, bar, cc * 64, mb.w0 + d.pad_w - kw, mb.h0 + d.pad_h - kh, mb.b0);
             for (int h = 0; h < BN / 64; ++h)
-              tc05::tma_load_3d(sb + h * PANEL_BYTES, &tmB, bar, ni * BN + 64 * h, tap, cc * 64);
+              tc05::tma_load_3d(sb + h * PANEL_BYTES, &tmB, bar, ni * BN + 64 * h, wtap, cc * 64);
           } else {
             for (int h = 0; h < 2; ++h)
               tc05::tma_load_4d(sa + h * PANEL_BYTES, &tmA, bar, mi * BM + 64 * h, kb.w0, kb.h0, kb.b0);
             for (int j = 0; j < BN / 64; ++j)
               tc05::tma_load_4d(sb + j * PANEL_BYTES, &tmB, bar, pc[j], kb.w0 * d.stride + pdw[j], kb.h0 * d.stride + pdh[j], kb.b0);
+          }
           }
           if (MODE == MODE_WGRAD) {
             kb.w0 += d.bw;
@@ -179,8 +186,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               if (kb.h0 >= d.ht * d.bh) { kb.h0 = 0; kb.b0 += d.bnb; }
             }
           } else if (++cc == d.cchunks) {
-            cc = 0; ++tap;
-            if (++kw == d.KW) { kw = 0; ++kh; }
+            cc = 0; ++tap; wtap += d.tap_dw;
+            if (++kw == d.KW) { kw = 0; ++kh; wtap += d.tap_dh - d.KW * d.tap_dw; }
           }
           if (++s == S) { s = 0; ph ^= 1u; }
         }
@@ -188,7 +195,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    {
+      const bool leader = tc05::elect_one();
       const uint32_t idesc = tc05::make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t tile_i = 0, ph = 0;
       int s = 0;
@@ -197,14 +205,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int z = t / tiles_mn;
         const int kt_begin = z * kt_per, kt_end = min(d.kt_total, kt_begin + kt_per);
         const uint32_t acc = tile_i & 1u, acc_ph = (tile_i >> 1) & 1u;
-        if (!tc05::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+        if (!tc05::mbar_wait_warp(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
         tc05::fence_after_sync();
         const uint32_t tacc = tmem + acc * (uint32_t)acc_stride;
         for (int kt = kt_begin; kt < kt_end; ++kt) {
-          if (!tc05::mbar_wait(&ctl->full[s], ph, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+          if (!tc05::mbar_wait_warp(&ctl->full[s], ph, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           tc05::fence_after_sync();
           const uint32_t sa = tc05::smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
+          if (leader) {
           // descriptors as 32-bit halves: per MMA this one thread spends an add per operand, not a rebuild
           const uint32_t a_lo = tc05::desc_lo(sa, A_MN ? PANEL_BYTES : 16), b_lo = tc05::desc_lo(sb, B_MN ? PANEL_BYTES : 16);
           constexpr uint32_t d_hi = tc05::desc_hi(1024);
@@ -213,9 +222,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc05::mma_bf16_ss_lohi(tacc, a_lo + (A_MN ? 128 : 2) * k, d_hi, b_lo + (B_MN ? 128 : 2) * k, d_hi, idesc,
                                    (kt > kt_begin || k > 0) ? 1u : 0u);
           tc05::mma_commit(&ctl->empty[s]);
+          }
           if (++s == S) { s = 0; ph ^= 1u; }
         }
-        if (ok) tc05::mma_commit(&ctl->tmem_full[acc]);
+        if (ok && leader) tc05::mma_commit(&ctl->tmem_full[acc]);
       }
     }
   } else {
@@ -366,6 +376,16 @@ bool make_act_map(CUtensorMap* map, const void* base, int ch, int W, int H, int 
                   es);
 }
 
+// A parity class of an NHWC tensor: pixels (s * i + a, s * j + b) as a dense (channels, W2, H2, B) tensor
+bool make_act_view(CUtensorMap* map, const void* base, int ch, int W, int H, int B, long long pitch, int s, int a,
+                   int b, int W2, int H2, int bw, int bh, int bnb, bool narrow) {
+  const long long dims[4] = {ch, W2, H2, B};
+  const long long st[3] = {pitch * 2 * s, pitch * 2 * W * s, pitch * 2 * W * H};
+  const int box[4] = {narrow ? 32 : 64, bw, bh, bnb};
+  const char* origin = (const char*)base + ((long long)a * W + b) * pitch * 2;
+  return make_map(map, origin, 4, dims, st, box, false, narrow ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 // Pick the pixel box (bw, bh, bnb) with at most `cap` pixels that covers the W x H x B grid with the fewest
 // boxes; ties go to the wider box (longer contiguous runs).
 void pick_box(int W, int H, int B, int cap, int* bw, int* bh, int* bnb) {
@@ -414,7 +434,9 @@ extern "C" {
 int geeps_conv_tc_supported(const GeepsConvTcParams* p) {
   if (p->B <= 0 || p->H <= 0 || p->W <= 0 || p->cg <= 0 || p->og <= 0 || p->KH <= 0 || p->KW <= 0) return 0;
   const int s = p->stride > 1 ? p->stride : 1;
-  if (s > 8 || (s > 1 && p->mode == MODE_DGRAD)) return 0;
+  // a strided data gradient runs per parity class of dX; a class without taps (filter narrower than the stride)
+  // would have to be zeroed instead and is left to the caller
+  if (s > 8 || (s > 1 && p->mode == MODE_DGRAD && (p->KH < s || p->KW < s))) return 0;
   if (p->OH != (p->H + 2 * p->pad - p->KH) / s + 1 || p->OW != (p->W + 2 * p->pad - p->KW) / s + 1) return 0;
   if (p->OH <= 0 || p->OW <= 0) return 0;
   if (((uintptr_t)p->x & 15) || ((uintptr_t)p->y & 15) || ((uintptr_t)p->w & 15)) return 0;
@@ -425,9 +447,38 @@ int geeps_conv_tc_supported(const GeepsConvTcParams* p) {
   return 1;
 }
 
+}  // extern "C"
+
+namespace {
+// one parity class (a, b) of a strided layer's data gradient, or {s = 1}: the whole problem
+struct DgradClass { int s, a, b; };
+int conv_tc_run(const GeepsConvTcParams* p, DgradClass cls, void* stream);
+}  // namespace
+
+extern "C" {
+
 int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   if (!geeps_conv_tc_supported(p)) return (int)cudaErrorInvalidValue;
   if (p->mode != MODE_WGRAD && p->split_k >= 0 && geeps_conv_halo_applicable(p)) return geeps_conv_halo(p, stream);
+  if (p->mode == MODE_DGRAD && p->stride > 1) {
+    // dX[s i + a, s j + b] = sum over u, v of dY[i + oh0 - u, j + ow0 - v] * W[kh0 + s u, kw0 + s v]: s * s
+    // stride-1 problems over dense views of dX, each with its sub-filter
+    for (int a = 0; a < p->stride; ++a)
+      for (int b = 0; b < p->stride; ++b) {
+        if (a >= p->H || b >= p->W) continue;
+        const int e = conv_tc_run(p, DgradClass{p->stride, a, b}, stream);
+        if (e) return e;
+      }
+    return 0;
+  }
+  return conv_tc_run(p, DgradClass{1, 0, 0}, stream);
+}
+
+}  // extern "C"
+
+namespace {
+
+int conv_tc_run(const GeepsConvTcParams* p, DgradClass cls, void* stream) {
   const int kSMs = geeps_sm_count();
   cudaStream_t st = (cudaStream_t)stream;
   ConvDev d;
@@ -440,13 +491,25 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   d.ch_valid = p->cg;
   d.narrow = 0;
   d.stride = p->stride > 1 ? p->stride : 1;
+  d.pad_w = d.pad_h = p->pad;
+  d.tap0 = 0; d.tap_dw = 1; d.tap_dh = p->KW;
   CUtensorMap ta, tb, tc;
   bool ok = true;
   const long long wdims[3] = {p->cg, d.taps, p->og};
   if (p->mode == MODE_FWD || p->mode == MODE_DGRAD) {
     const bool fwd = p->mode == MODE_FWD;
     // rows of the tile: pixels of the output (fwd) or of the input gradient (dgrad)
-    const int GW = fwd ? p->OW : p->W, GH = fwd ? p->OH : p->H;
+    int GW = fwd ? p->OW : p->W, GH = fwd ? p->OH : p->H;
+    if (cls.s > 1) {
+      const int sd = cls.s;
+      GW = (p->W - cls.b + sd - 1) / sd; GH = (p->H - cls.a + sd - 1) / sd;
+      const int kh0 = (cls.a + p->pad) % sd, kw0 = (cls.b + p->pad) % sd;
+      const int khs = (p->KH - kh0 + sd - 1) / sd, kws = (p->KW - kw0 + sd - 1) / sd;    // >= 1: KH, KW >= s
+      d.pad_h = (cls.a + p->pad - kh0) / sd; d.pad_w = (cls.b + p->pad - kw0) / sd;
+      d.tap0 = kh0 * p->KW + kw0; d.tap_dw = sd; d.tap_dh = sd * p->KW;
+      d.KW = kws; d.taps = khs * kws;
+      d.stride = 1;
+    }
     pick_box(GW, GH, p->B, BM, &d.bw, &d.bh, &d.bnb);
     d.rows = d.bw * d.bh * d.bnb;
     d.wt = (GW + d.bw - 1) / d.bw; d.ht = (GH + d.bh - 1) / d.bh;
@@ -473,7 +536,11 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
       const int wbox[3] = {64, 1, 64};
       ok = ok && make_map(&tb, p->w, 3, wdims, wst, wbox, false);
       d.narrow = narrow_store(p->cg, p->x_pitch);
-      ok = ok && make_act_map(&tc, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb, d.narrow != 0);
+      if (cls.s > 1)
+        ok = ok && make_act_view(&tc, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, cls.s, cls.a, cls.b, GW, GH, d.bw,
+                                 d.bh, d.bnb, d.narrow != 0);
+      else
+        ok = ok && make_act_map(&tc, p->x, p->cg, p->W, p->H, p->B, p->x_pitch, d.bw, d.bh, d.bnb, d.narrow != 0);
     }
   } else {
     // reduction over output pixels in boxes of up to 64
@@ -544,4 +611,4 @@ int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   return launch<MODE_WGRAD>(ta, tb, tc, d, grid, st);
 }
 
-}  // extern "C"
+}  // namespace

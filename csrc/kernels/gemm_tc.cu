@@ -94,9 +94,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      tc05::tma_prefetch_desc(&tmA);
-      tc05::tma_prefetch_desc(&tmB);
+    // the loop runs with the whole warp converged; the elected lane issues the copies
+    {
+      const bool leader = tc05::elect_one();
+      if (leader) { tc05::tma_prefetch_desc(&tmA); tc05::tma_prefetch_desc(&tmB); }
       // ring slot and phase advance incrementally: a division per k-tile in this single thread would cost
       // more than issuing the loads
       int s = 0;
@@ -107,10 +108,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = (mn % d.m_tiles) * BM, n0 = (mn / d.m_tiles) * BN;
         const int kt_begin = z * kt_per, kt_end = min(d.kt_total, kt_begin + kt_per);
         for (int kt = kt_begin; kt < kt_end; ++kt) {
-          if (!tc05::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+          if (!tc05::mbar_wait_warp(&ctl->empty[s], ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           uint8_t* sa = tiles + (size_t)s * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           const int k0 = kt * BK;
+          if (leader) {
           tc05::mbar_expect_tx(&ctl->full[s], STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
@@ -125,13 +127,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           } else {
             tc05::tma_load_2d(sb, &tmB, &ctl->full[s], k0, n0);
           }
+          }
           if (++s == S) { s = 0; ph ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    {
+      const bool leader = tc05::elect_one();
       const uint32_t idesc = tc05::make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t tile_i = 0, ph = 0;
       int s = 0;
@@ -141,14 +145,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int kt_begin = z * kt_per, kt_end = min(d.kt_total, kt_begin + kt_per);
         const uint32_t acc = tile_i & 1u, acc_ph = (tile_i >> 1) & 1u;
         // the epilogue must have drained this accumulator (two tiles ago)
-        if (!tc05::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+        if (!tc05::mbar_wait_warp(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
         tc05::fence_after_sync();
         const uint32_t tacc = tmem + acc * (uint32_t)acc_stride;
         for (int kt = kt_begin; kt < kt_end; ++kt) {
-          if (!tc05::mbar_wait(&ctl->full[s], ph, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+          if (!tc05::mbar_wait_warp(&ctl->full[s], ph, abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
           tc05::fence_after_sync();
           const uint32_t sa = tc05::smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
+          if (leader) {
           // descriptors as 32-bit halves: per MMA this one thread spends an add per operand, not a rebuild.
           // K-major: 16 k-elements = 32 bytes inside the 128-byte swizzle row (2 units of 16 bytes);
           // MN-major: 16 k-rows of 128 bytes = two 8-row groups of 1024 bytes (128 units).
@@ -159,9 +164,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc05::mma_bf16_ss_lohi(tacc, a_lo + (A_MN ? 128 : 2) * k, d_hi, b_lo + (B_MN ? 128 : 2) * k, d_hi, idesc,
                                    (kt > kt_begin || k > 0) ? 1u : 0u);
           tc05::mma_commit(&ctl->empty[s]);  // frees the stage when these MMAs have read it
+          }
           if (++s == S) { s = 0; ph ^= 1u; }
         }
-        if (ok) tc05::mma_commit(&ctl->tmem_full[acc]);
+        if (ok && leader) tc05::mma_commit(&ctl->tmem_full[acc]);
       }
     }
   } else {

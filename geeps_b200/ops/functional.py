@@ -71,8 +71,8 @@ CONV_FWD, CONV_DGRAD, CONV_WGRAD = 0, 1, 2
 def conv_tc_params(mode: int, x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, k: int, pad: int, *,
                    bias: torch.Tensor | None = None, relu: bool = False, split_k: int = 0,
                    status: torch.Tensor | None = None, stride: int = 1) -> ConvTcParams:
-    """Arguments of the implicit-GEMM convolution (any stride up to 8 for forward and weight gradient, stride 1 for
-    the data gradient).  x: [B, H, W, cg] and y: [B, OH, OW, og] are NHWC
+    """Arguments of the implicit-GEMM convolution (stride 1 .. 8; the data gradient of a strided layer needs a
+    filter at least as wide as the stride).  x: [B, H, W, cg] and y: [B, OH, OW, og] are NHWC
     bf16 tensors or channel slices of wider ones (last-dim stride 1, dense pixels); w: [og, ldw] with column
     (kh * k + kw) * cg + ci, bf16 for forward / data gradient, fp32 (the gradient) for the weight gradient."""
     B, H, W, cg = x.shape
@@ -97,9 +97,9 @@ def conv_tc_supported(p: ConvTcParams) -> bool:
 
 
 def conv_tc(mode: int, x, y, w, k: int, pad: int, **kw) -> None:
-    """Convolution without a patch matrix (tcgen05 + 4-D TMA): forward writes y, CONV_DGRAD writes x (y holds dY;
-    stride 1 only), CONV_WGRAD writes w (fp32, y holds dY).  stride=s loads the activation boxes with TMA element
-    stride s."""
+    """Convolution without a patch matrix (tcgen05 + 4-D TMA): forward writes y, CONV_DGRAD writes x (y holds dY),
+    CONV_WGRAD writes w (fp32, y holds dY).  stride=s: forward and weight gradient load the activation boxes with
+    TMA element stride s; the data gradient runs s * s stride-1 problems, one per parity class of x."""
     L.require_cuda()
     assert x.dtype == bf16 and y.dtype == bf16
     assert w.dtype == (torch.float32 if mode == CONV_WGRAD else bf16)

@@ -184,9 +184,10 @@ class Conv2d(Layer):
             # every tap is a k-step of 64 channels: with 8 channels (the 7 x 7 stride-2 first layer of the 22K net)
             # 49 mostly-zero k-steps lose to 7 dense ones over a patch matrix (6.8 against 5.8 ms per step)
             self.implicit = False
-        # a strided layer's data gradient still goes through GEMM + col2im (its forward and weight gradient load
-        # the activation boxes with a TMA element stride and build no patch matrix)
-        self.implicit_dgrad = self.implicit and self.stride == 1
+        # a strided layer's forward and weight gradient load the activation boxes with a TMA element stride; its data
+        # gradient runs one parity class of dX at a time (stride^2 stride-1 problems with sub-filters), unless the
+        # filter is narrower than the stride (then some classes have no taps): GEMM + col2im for those
+        self.implicit_dgrad = self.implicit and (self.stride == 1 or self.k >= self.stride)
         self.cols = self.dcol = None
         if not self.pointwise and not self.implicit:
             self._alloc_patch_buffers()
@@ -277,7 +278,7 @@ class Conv2d(Layer):
                           stride=self.stride)
                 if self.need_dx and self.implicit_dgrad:
                     F.conv_tc(F.CONV_DGRAD, self._x4(self.dx, g), dy4, w16[g * self.og:(g + 1) * self.og],
-                              self.k, self.pad)
+                              self.k, self.pad, stride=self.stride)
                 elif self.need_dx:
                     F.gemm(dy[:, g * self.og:(g + 1) * self.og], w16[g * self.og:(g + 1) * self.og], self.dcol, b_mn=True)
                     F.col2im(self.dcol, self.dx, self.geoms[g])

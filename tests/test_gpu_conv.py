@@ -85,8 +85,9 @@ STRIDED = [
 
 
 @pytest.mark.parametrize("case", STRIDED)
-def test_strided_conv_forward_and_weight_gradient_match_torch(case):
-    """Strided layers: the activation boxes are loaded with a TMA element stride, no patch matrix."""
+def test_strided_conv_forward_and_gradients_match_torch(case):
+    """Strided layers: the activation boxes are loaded with a TMA element stride, the data gradient runs per parity
+    class of the input; no patch matrix."""
     from geeps_b200.ops import functional as F
     B, H, W, cg, og, k, pad, st = case
     dev = torch.device("cuda:0")
@@ -100,13 +101,14 @@ def test_strided_conv_forward_and_weight_gradient_match_torch(case):
     bias = torch.randn(og, device=dev, generator=gen)
     dy = torch.randn(B, OH, OW, og, device=dev, generator=gen).to(BF)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
-    xr = x.float().permute(0, 3, 1, 2).contiguous()
+    xr = x.float().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
     wr = w[:, :kd].float().view(og, k, k, cg).permute(0, 3, 1, 2).contiguous().requires_grad_(True)
     yr = torch.nn.functional.conv2d(xr, wr, bias, stride=st, padding=pad)
     yr.backward(dy.float().permute(0, 3, 1, 2))
     y = torch.empty(B, OH, OW, og, device=dev, dtype=BF)
     assert F.conv_tc_supported(F.conv_tc_params(F.CONV_FWD, x, y, w, k, pad, stride=st))
-    assert not F.conv_tc_supported(F.conv_tc_params(F.CONV_DGRAD, x, y, w, k, pad, stride=st))
+    assert F.conv_tc_supported(F.conv_tc_params(F.CONV_DGRAD, x, y, w, k, pad, stride=st))
+    assert not F.conv_tc_supported(F.conv_tc_params(F.CONV_DGRAD, x, y, w[:, :cg], 1, 0, stride=st))
     F.conv_tc(F.CONV_FWD, x, y, w, k, pad, bias=bias, relu=True, status=status, stride=st)
     assert _rel(y, torch.relu(yr.detach()).permute(0, 2, 3, 1)) < 1e-2
     dw_ref = wr.grad.permute(0, 2, 3, 1).reshape(og, kd)
@@ -114,6 +116,9 @@ def test_strided_conv_forward_and_weight_gradient_match_torch(case):
         dw = torch.full((og, ld), 5.0, device=dev)
         F.conv_tc(F.CONV_WGRAD, x, dy, dw, k, pad, split_k=split, status=status, stride=st)
         assert _rel(dw[:, :kd], dw_ref) < 1e-2, split
+    dx = torch.full((B, H, W, cg), 3.0, device=dev, dtype=BF)
+    F.conv_tc(F.CONV_DGRAD, dx, dy, w, k, pad, status=status, stride=st)
+    assert _rel(dx, xr.grad.permute(0, 2, 3, 1)) < 1e-2
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0
 
