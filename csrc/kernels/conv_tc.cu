@@ -460,6 +460,8 @@ extern "C" {
 int geeps_conv_tc(const GeepsConvTcParams* p, void* stream) {
   if (!geeps_conv_tc_supported(p)) return (int)cudaErrorInvalidValue;
   if (p->mode != MODE_WGRAD && p->split_k >= 0 && geeps_conv_halo_applicable(p)) return geeps_conv_halo(p, stream);
+  if (p->mode == MODE_WGRAD && p->split_k >= 0 && geeps_conv_wgrad_halo_applicable(p))
+    return geeps_conv_wgrad_halo(p, stream);
   if (p->mode == MODE_DGRAD && p->stride > 1) {
     // dX[s i + a, s j + b] = sum over u, v of dY[i + oh0 - u, j + ow0 - v] * W[kh0 + s u, kw0 + s v]: s * s
     // stride-1 problems over dense views of dX, each with its sub-filter

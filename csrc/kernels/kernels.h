@@ -167,6 +167,9 @@ int geeps_conv_tc_supported(const GeepsConvTcParams* p);
 // (a negative split_k on a forward / data-gradient call keeps the call on the box kernel).
 int geeps_conv_halo_applicable(const GeepsConvTcParams* p);
 int geeps_conv_halo(const GeepsConvTcParams* p, void* stream);
+// Weight gradient with the taps of a filter row served by one activation tile (conv_wgrad_halo.cu); same routing.
+int geeps_conv_wgrad_halo_applicable(const GeepsConvTcParams* p);
+int geeps_conv_wgrad_halo(const GeepsConvTcParams* p, void* stream);
 
 // ---------------- parameter pull fused with the consuming GEMM ----------------
 // Y[M,N] = X[M,K] * W[N,K]^T + bias (+ReLU), M <= 256, K a multiple of 64.  W's rows live on the server

@@ -120,6 +120,14 @@ def conv_halo(mode: int, x, y, w, k: int, pad: int, **kw) -> None:
     launch(lib().geeps_conv_halo, "conv_halo", C.byref(p), stream_ptr())
 
 
+def conv_wgrad_halo(x, dy, dw, k: int, pad: int, **kw) -> None:
+    """The filter-row weight-gradient kernel called directly (dw fp32 [og, ldw], overwritten)."""
+    L.require_cuda()
+    assert x.dtype == bf16 and dy.dtype == bf16 and dw.dtype == torch.float32
+    p = conv_tc_params(CONV_WGRAD, x, dy, dw, k, pad, **kw)
+    launch(lib().geeps_conv_wgrad_halo, "conv_wgrad_halo", C.byref(p), stream_ptr())
+
+
 def nchw_to_nhwc_bf16(x: torch.Tensor, cpad: int | None = None) -> torch.Tensor:
     L.require_cuda()
     B, Cc, H, W = x.shape

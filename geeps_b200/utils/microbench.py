@@ -171,6 +171,12 @@ def bench_conv():
                               "halo_frac_of_peak": round(flops / t_halo / 1e9 / peak, 3), "peak_source": src,
                               "routed_to_halo": bool(F.conv_halo_applicable(F.conv_tc_params(mode, x, y, w, k, pad)))}),
                   flush=True)
+        dw = torch.empty(og, (kd + 7) // 8 * 8, device=dev)
+        t_box = timeit(lambda: F.conv_tc(F.CONV_WGRAD, x, y, dw, k, pad, split_k=-1), flush=flush)
+        t_halo = timeit(lambda: F.conv_wgrad_halo(x, y, dw, k, pad), flush=flush)
+        print(json.dumps({"kernel": f"{name} wgrad", "box_ms": round(t_box, 4), "halo_ms": round(t_halo, 4),
+                          "halo_tflops": round(flops / t_halo / 1e9, 1),
+                          "halo_frac_of_peak": round(flops / t_halo / 1e9 / peak, 3), "peak_source": src}), flush=True)
 
 
 def main():

@@ -179,6 +179,33 @@ def test_conv_halo_forward_dgrad_match_torch(case):
 
 
 @pytest.mark.parametrize("cpad", [None, 64])
+@pytest.mark.parametrize("case", [c for c in HALO_CASES if c[9] > 1 and c[9] <= 8])
+def test_conv_wgrad_halo_matches_torch(case):
+    """The filter-row weight-gradient kernel (one activation tile serves the taps of a row through overlapping
+    N panels) called directly on every shape it accepts."""
+    from geeps_b200.ops import functional as F
+    B, H, W, Ct, c_off, cg, Ot, o_off, og, k, pad = case
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(hash(case) % 1000)
+    OH, OW = H + 2 * pad - k + 1, W + 2 * pad - k + 1
+    kd = k * k * cg
+    ld = (kd + 7) // 8 * 8
+    x = torch.randn(B, H, W, Ct, device=dev, generator=gen).to(BF)[..., c_off:c_off + cg]
+    dy = torch.randn(B, OH, OW, Ot, device=dev, generator=gen).to(BF)[..., o_off:o_off + og]
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    xr = x.float().permute(0, 3, 1, 2).contiguous()
+    wr = torch.zeros(og, cg, k, k, device=dev, requires_grad=True)
+    torch.nn.functional.conv2d(xr, wr, None, padding=pad).backward(dy.float().permute(0, 3, 1, 2))
+    dw_ref = wr.grad.permute(0, 2, 3, 1).reshape(og, kd)
+    dw = torch.full((og, ld), 5.0, device=dev)
+    F.conv_wgrad_halo(x, dy, dw, k, pad, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    assert _rel(dw[:, :kd], dw_ref) < 1e-2
+    assert bool((dw[:, kd:] == 0).all())
+
+
+@pytest.mark.parametrize("cpad", [None, 64])
 def test_space_to_depth_conv_matches_strided_torch_conv(cpad):
     """Input(s2d) + Conv2d(s2d): an 11x11 stride-4 convolution run as a 3-tap stride-1 implicit GEMM; with cpad the
     48-channel space-to-depth pixel is zero-padded to one 128-byte line."""
