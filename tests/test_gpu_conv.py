@@ -178,7 +178,6 @@ def test_conv_halo_forward_dgrad_match_torch(case):
         assert bool((rest == 3.0).all())
 
 
-@pytest.mark.parametrize("cpad", [None, 64])
 @pytest.mark.parametrize("case", [c for c in HALO_CASES if c[9] > 1 and c[9] <= 8])
 def test_conv_wgrad_halo_matches_torch(case):
     """The filter-row weight-gradient kernel (one activation tile serves the taps of a row through overlapping
