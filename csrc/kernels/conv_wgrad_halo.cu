@@ -323,11 +323,7 @@ WgPlan plan_wgrad(const GeepsConvTcParams* p) {
 
 int halo_mode() {
   static int m = -1;
-  if (m < 0) {
-    const char* e = getenv("GEEPS_HALO_CONV");
-    const char* w = getenv("GEEPS_WGRAD_HALO");
-    m = (e ? atoi(e) : 1) && (w ? atoi(w) : 0);
-  }
+  if (m < 0) { const char* e = getenv("GEEPS_HALO_CONV"); m = e ? atoi(e) : 1; }
   return m;
 }
 
@@ -335,16 +331,19 @@ int halo_mode() {
 
 extern "C" {
 
-// 1 when conv_tc() should route this weight-gradient call here: filter rows of at least 3 taps (the saving is the
-// activation panels of a row's taps), at least 32 input channels per 64-channel panel, little position padding, and
-// enough position blocks to slice.  Fitted to timings of both kernels (python -m geeps_b200.utils.microbench conv).
+// 1 when conv_tc() should route this weight-gradient call here.  Fitted to timings of both kernels at batch 128 .. 256
+// (python -m geeps_b200.utils.microbench conv): filter rows of 5 taps or more always win (AlexNet conv2 0.103 ->
+// 0.087 ms per group, Inception 5 x 5 0.054 -> 0.050 ms); 3-tap rows only when the layer is one item wide (one block
+// of output channels, one chunk of input channels: AlexNet conv1 0.120 -> 0.112 ms) - wider 3 x 3 layers are faster
+// on the box kernel, which covers four (tap, chunk) panels per MMA whatever the filter's shape.
 int geeps_conv_wgrad_halo_applicable(const GeepsConvTcParams* p) {
   if (!halo_mode()) return 0;
   if (!geeps_conv_tc_supported(p)) return 0;
   const WgPlan wp = plan_wgrad(p);
   if (!wp.ok) return 0;
   const int tail = p->cg - (wp.d.cchunks - 1) * 64;
-  return p->KW >= 3 && tail >= 32 && wp.util >= 0.6 && wp.d.n_blocks >= 4 * geeps_sm_count() ? 1 : 0;
+  if (tail < 32 || wp.util < 0.6 || wp.d.n_blocks < 4 * geeps_sm_count()) return 0;
+  return p->KW >= 5 || (p->KW >= 3 && wp.d.m_tiles == 1 && wp.d.cchunks == 1) ? 1 : 0;
 }
 
 int geeps_conv_wgrad_halo(const GeepsConvTcParams* p, void* stream) {

@@ -15,6 +15,7 @@ once and launches the kernel of interest three times.
   conv1_fwd   AlexNet conv1 after space-to-depth (256 x 57 x 57 x 64 (48 + 16 zero) -> 96, 3x3, no padding);
               routed to the halo-tile kernel, like conv2_fwd / conv2_dgrad (GEEPS_HALO_CONV=0: the box kernel)
   conv2_fwd / conv2_dgrad   one group of AlexNet conv2 (256 x 27 x 27, 48 of 96 -> 128 of 256 channels, 5x5)
+  conv1_wgrad / conv2_wgrad   the weight gradients of the same two layers (filter-row kernel, conv_wgrad_halo.cu)
 """
 from __future__ import annotations
 
@@ -124,8 +125,8 @@ def main():
                 F.conv_tc(F.CONV_DGRAD, x, y, w, k, pad)
             else:
                 F.conv_tc(F.CONV_WGRAD, x, y, dw, k, pad)
-    elif case in ("conv1_fwd", "conv2_fwd", "conv2_dgrad"):
-        if case == "conv1_fwd":
+    elif case in ("conv1_fwd", "conv2_fwd", "conv2_dgrad", "conv1_wgrad", "conv2_wgrad"):
+        if case.startswith("conv1"):
             B, H, ct, cg, ot, og, k, pad = 256, 57, 64, 64, 96, 96, 3, 0
         else:
             B, H, ct, cg, ot, og, k, pad = 256, 27, 96, 48, 256, 128, 5, 2
@@ -133,8 +134,13 @@ def main():
         x = (torch.randn(B, H, H, ct, device=dev) * 0.5).to(BF)[..., :cg]
         y = (torch.randn(B, OH, OH, ot, device=dev) * 0.5).to(BF)[..., :og]
         w = (torch.randn(og, k * k * cg, device=dev) * 0.02).to(BF)
-        for _ in range(4):
-            F.conv_tc(F.CONV_DGRAD if case == "conv2_dgrad" else F.CONV_FWD, x, y, w, k, pad)
+        if case.endswith("wgrad"):
+            dw = torch.empty(og, k * k * cg, device=dev)
+            for _ in range(4):
+                F.conv_tc(F.CONV_WGRAD, x, y, dw, k, pad)
+        else:
+            for _ in range(4):
+                F.conv_tc(F.CONV_DGRAD if case == "conv2_dgrad" else F.CONV_FWD, x, y, w, k, pad)
     else:
         raise SystemExit(f"unknown case {case}")
     torch.cuda.synchronize()
