@@ -544,7 +544,6 @@ lrn_backward_v8_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, c
       }
     }
     Bf8 xv = ld8(x + base + c), o;
-#pragma unroll
     float acc = 0.f;
 #pragma unroll
     for (int j = 8 - HALF; j <= 8 + HALF; ++j) acc += ratio[j];
@@ -623,6 +622,45 @@ nchw_to_s2d_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int H, 
     if ((N & 7) == 0)
       for (; j + 8 <= Cpad; j += 8) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0, 0, 0, 0);
     for (; j < Cpad; ++j) dst[j] = __float2bfloat16(j < N ? v[j] : 0.f);
+  }
+}
+
+// The same layout for S = 4, C = 3 with coalesced traffic on both sides: a block of four warps converts 32
+// consecutive output pixels of one output row.  Warp dy reads, for each colour, the 128 consecutive input elements of
+// image row 4 hs + dy that those pixels cover (one 4-element group per lane), the values meet in a [32 pixels][Cpad]
+// tile in shared memory, and the tile leaves as one contiguous run of 32 * Cpad * 2 bytes in 16-byte stores.
+template <typename T>
+__global__ void __launch_bounds__(128)
+nchw_to_s2d43_tile_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int H, int W, int Hs, int Ws, int Cpad,
+                          int segs) {
+  constexpr int S = 4, C = 3, PIX = 32, PITCH = 72;      // tile row pitch in elements: 144 bytes staggers the banks
+  __shared__ __align__(16) bf16 tile[PIX * PITCH];
+  const int lane = threadIdx.x & 31, dy = threadIdx.x >> 5;
+  long long blk = blockIdx.x;
+  const int seg = (int)(blk % segs); blk /= segs;
+  const int hs = (int)(blk % Hs);
+  const long long b = blk / Hs;
+  const int ws0 = seg * PIX;
+  // channels past S * S * C are zero (this warp's share of them: pixel `lane`, slots 48 + 4 dy .. + 4, when they exist)
+  for (int j = S * S * C + dy * 4; j < Cpad && j < S * S * C + dy * 4 + 4; ++j) tile[lane * PITCH + j] = __float2bfloat16(0.f);
+  const int h = hs * S + dy;
+  const int w0 = (ws0 + lane) * S;
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const T* row = x + ((b * C + c) * H + h) * (long long)W;
+#pragma unroll
+    for (int dx = 0; dx < S; ++dx) {
+      const float v = (h < H && w0 + dx < W) ? in_val(row + w0 + dx) : 0.f;
+      tile[lane * PITCH + (dy * S + dx) * C + c] = __float2bfloat16(v);
+    }
+  }
+  __syncthreads();
+  const int per_pix = Cpad >> 3;                          // 16-byte pieces per pixel
+  const int npix = min(PIX, Ws - ws0);
+  bf16* dst = y + ((b * Hs + hs) * (long long)Ws + ws0) * Cpad;
+  for (int i = threadIdx.x; i < npix * per_pix; i += blockDim.x) {
+    const int px = i / per_pix, piece = i - px * per_pix;
+    *reinterpret_cast<uint4*>(dst + (long long)i * 8) = *reinterpret_cast<const uint4*>(tile + px * PITCH + piece * 8);
   }
 }
 
@@ -985,7 +1023,11 @@ static int nchw_to_nhwc_launch(const T* x, void* y, int B, int C, int H, int W, 
 template <typename T>
 static int nchw_to_s2d_launch(const T* x, void* y, int B, int C, int H, int W, int S, int Hs, int Ws, int Cpad,
                               cudaStream_t st) {
-  if (S == 4 && C == 3)
+  if (S == 4 && C == 3 && Cpad % 8 == 0 && Cpad >= 48 && Cpad <= 64 && (((uintptr_t)y) & 15) == 0) {
+    const int segs = (Ws + 31) / 32;
+    nchw_to_s2d43_tile_kernel<T><<<(unsigned)((long long)B * Hs * segs), 128, 0, st>>>(x, (bf16*)y, B, H, W, Hs, Ws, Cpad,
+                                                                                      segs);
+  } else if (S == 4 && C == 3)
     nchw_to_s2d_kernel<4, 3, T><<<grid_1d((long long)B * Hs * Ws), 256, 0, st>>>(x, (bf16*)y, B, H, W, Hs, Ws, Cpad);
   else
     nchw_to_s2d_generic_kernel<T><<<grid_1d((long long)B * Hs * Ws * Cpad), 256, 0, st>>>(x, (bf16*)y, B, C, H, W, S,
