@@ -186,13 +186,16 @@ lrn_maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ p, uin
 //   dx = as - 2 alpha beta / n * x * (window sum of rs)
 // The host picks blockDim as a multiple of C/8, so a thread keeps its channel vector for every item it visits and
 // sums the bias gradient in registers.
-template <int HALF>
+// K3S2: the pooling window is 3 x 3 with stride 2 (AlexNet): window size and stride become constants, so the four
+// divisions per pixel vector that find the windows covering it are shifts.
+template <int HALF, bool K3S2>
 __global__ void __launch_bounds__(512, 2)
 lrn_maxpool_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dp, const uint8_t* __restrict__ argmax,
                             bf16* __restrict__ dx, const GeepsPoolGeom g, int R, int max_oh, const LrnCoef cf, float coef,
                             int relu_mask, float* __restrict__ colsum) {
   extern __shared__ __align__(16) uint8_t lp_smem[];
   const int C = g.C, cv = C >> 3, W = g.W, OW = g.OW;
+  const int PK = K3S2 ? 3 : g.K, PS = K3S2 ? 2 : g.stride;
   const int row_elems = W * C, orow_elems = OW * C;
   bf16* as = reinterpret_cast<bf16*>(lp_smem);
   bf16* rs = as + (size_t)R * row_elems;
@@ -211,8 +214,8 @@ lrn_maxpool_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__
   for (int blk = blockIdx.x; blk < total_blocks; blk += gridDim.x) {
     const int b = blk / row_blocks, h0 = (blk - b * row_blocks) * R;
     const int nr = min(R, g.H - h0);
-    const int oh_lo = max(0, (h0 + g.pad - g.K + g.stride) / g.stride);
-    const int oh_hi = min(g.OH - 1, (h0 + nr - 1 + g.pad) / g.stride);
+    const int oh_lo = max(0, (h0 + g.pad - PK + PS) / PS);
+    const int oh_hi = min(g.OH - 1, (h0 + nr - 1 + g.pad) / PS);
     __syncthreads();                                   // the previous block's readers are done with the buffers
     {
       const long long opix0 = ((long long)b * g.OH + oh_lo) * OW;
@@ -231,16 +234,16 @@ lrn_maxpool_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__
     for (ItemWalk it(tid, nt, W, cv); it.r < nr; it.next(W, cv)) {
       const int c = it.cvi * 8;
       const int th = h0 + it.r + g.pad, tw = it.w + g.pad;
-      const int roh_lo = max(oh_lo, (th - g.K + g.stride) / g.stride), roh_hi = min(oh_hi, th / g.stride);
-      const int ow_lo = max(0, (tw - g.K + g.stride) / g.stride), ow_hi = min(OW - 1, tw / g.stride);
+      const int roh_lo = max(oh_lo, (th - PK + PS) / PS), roh_hi = min(oh_hi, th / PS);
+      const int ow_lo = max(0, (tw - PK + PS) / PS), ow_hi = min(OW - 1, tw / PS);
       float dy[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) dy[e] = 0.f;
       bool any = false;
       for (int oh = roh_lo; oh <= roh_hi; ++oh) {
-        const uint32_t code_h = (uint32_t)((th - oh * g.stride) * g.K + tw);
+        const uint32_t code_h = (uint32_t)((th - oh * PS) * PK + tw);
         for (int ow = ow_lo; ow <= ow_hi; ++ow) {
-          const uint32_t code = code_h - (uint32_t)(ow * g.stride);
+          const uint32_t code = code_h - (uint32_t)(ow * PS);
           const size_t o = (size_t)(oh - oh_lo) * orow_elems + (size_t)ow * C + c;
           const uint2 pk = *reinterpret_cast<const uint2*>(args + o);
           const uint32_t c4 = code * 0x01010101u;
@@ -435,20 +438,23 @@ int geeps_lrn_maxpool_backward(const void* x, const void* dp, const void* argmax
   int grid = geeps_sm_count() * per_sm;
   if (grid > total) grid = (int)total;
   if (colsum != nullptr) cudaMemsetAsync(colsum, 0, sizeof(float) * g->C, st);
-#define LP_BWD(HALF)                                                                                               \
+#define LP_BWD(HALF, K3S2)                                                                                         \
   do {                                                                                                             \
     static bool attr_set = false;                                                                                  \
     if (!attr_set) {                                                                                               \
-      cudaError_t e = cudaFuncSetAttribute(lrn_maxpool_backward_kernel<HALF>,                                      \
+      cudaError_t e = cudaFuncSetAttribute(lrn_maxpool_backward_kernel<HALF, K3S2>,                                \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLpMaxSmem);          \
       if (e != cudaSuccess) return (int)e;                                                                         \
       attr_set = true;                                                                                             \
     }                                                                                                              \
-    lrn_maxpool_backward_kernel<HALF><<<grid, block, smem, st>>>((const bf16*)x, (const bf16*)dp,                   \
+    lrn_maxpool_backward_kernel<HALF, K3S2><<<grid, block, smem, st>>>((const bf16*)x, (const bf16*)dp,             \
                                                                  (const uint8_t*)argmax, (bf16*)dx, *g, R, max_oh,  \
                                                                  cf, coef, relu_mask, colsum);                     \
   } while (0)
-  if (size == 3) LP_BWD(1); else if (size == 5) LP_BWD(2); else LP_BWD(3);
+  const bool k3s2 = g->K == 3 && g->stride == 2;
+  if (size == 3) { if (k3s2) LP_BWD(1, true); else LP_BWD(1, false); }
+  else if (size == 5) { if (k3s2) LP_BWD(2, true); else LP_BWD(2, false); }
+  else { if (k3s2) LP_BWD(3, true); else LP_BWD(3, false); }
 #undef LP_BWD
   return (int)cudaGetLastError();
 }
