@@ -443,8 +443,10 @@ int geeps_conv_halo_applicable(const GeepsConvTcParams* p) {
   const double chn = (double)d.n_valid / ((double)d.m_tiles * BM);
   if (pos < 0.6) return 0;
   // its tiles are large (up to 256 positions x 128 channels): with fewer than two per SM the box kernel's smaller
-  // tiles spread better (Inception at batch 32 .. 100: 5.60 against 5.79 ms per step of the 22K net)
-  if ((long long)d.m_tiles * d.n_images * d.row_tiles < 2LL * geeps_sm_count()) return 0;
+  // tiles spread better (Inception at batch 32 .. 100: 5.60 against 5.79 ms per step of the 22K net); a layer of one
+  // channel block still wins from 1.7 tiles per SM on (AlexNet conv5 per group, 256 tiles: 0.030 against 0.038 ms)
+  const long long tiles = (long long)d.m_tiles * d.n_images * d.row_tiles;
+  if (tiles * 10 < (d.m_tiles == 1 ? 17LL : 20LL) * geeps_sm_count()) return 0;
   if (p->mode == MODE_FWD) return (d.m_tiles == 1 && d.n_valid >= 96) || (chn >= 0.85 && pos >= 0.8) ? 1 : 0;
   return d.taps >= 25 || (d.n_valid >= 64 && (d.n_valid <= 128 || chn >= 0.85)) ? 1 : 0;
 }

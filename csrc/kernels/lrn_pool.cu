@@ -24,10 +24,6 @@
 namespace {
 
 typedef __nv_bfloat16 bf16;
-__device__ __forceinline__ float bf(const bf16 v) { return __bfloat162float(v); }
-struct alignas(16) Bf8 { bf16 v[8]; };
-__device__ __forceinline__ Bf8 ld8(const bf16* p) { Bf8 r; *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p); return r; }
-__device__ __forceinline__ void st8(bf16* p, const Bf8& r) { *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r); }
 
 // ---- arithmetic of the normalisation ----
 // scale = k + alpha/n * w = k * (1 + eps), w = window sum of x^2, eps = alpha / (n k) * w.  The two powers the
@@ -102,20 +98,22 @@ struct ItemWalk {
 // grid = B * ceil(OH / RO); one CTA produces RO pooled rows from the (RO-1)*stride + K input rows under them.
 // The input is read from global memory (one 16-byte and two 8-byte loads per 8 outputs), normalised once per
 // element into shared memory ([n_in][W][C] bf16), and pooled from there.
-template <int HALF>
+// K3S2: 3 x 3 windows with stride 2 (window size and stride are then constants of the pooling loops)
+template <int HALF, bool K3S2>
 __global__ void __launch_bounds__(512)
 lrn_maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ p, uint8_t* __restrict__ argmax,
                            const GeepsPoolGeom g, const LrnCoef cf, int RO) {
   extern __shared__ __align__(16) uint8_t lp_smem[];
   const int C = g.C, cv = C >> 3, W = g.W;
+  const int PK = K3S2 ? 3 : g.K, PS = K3S2 ? 2 : g.stride;
   const int row_elems = W * C;
   bf16* ys = reinterpret_cast<bf16*>(lp_smem);
   const int oh_blocks = (g.OH + RO - 1) / RO;
   const int b = blockIdx.x / oh_blocks, oh0 = (blockIdx.x - b * oh_blocks) * RO;
   const int n_out = min(RO, g.OH - oh0);
-  const int ih_base = oh0 * g.stride - g.pad;                    // input row of shared-memory row 0 (may be < 0)
+  const int ih_base = oh0 * PS - g.pad;                    // input row of shared-memory row 0 (may be < 0)
   const int r_lo = max(0, -ih_base);
-  const int r_hi = min((n_out - 1) * g.stride + g.K, g.H - ih_base);   // rows [r_lo, r_hi) exist
+  const int r_hi = min((n_out - 1) * PS + PK, g.H - ih_base);   // rows [r_lo, r_hi) exist
   const int tid = threadIdx.x, nt = blockDim.x;
   {
     const bf16* xbase = x + ((long long)b * g.H + ih_base + r_lo) * row_elems;
@@ -123,7 +121,7 @@ lrn_maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ p, uin
     const int nrows = r_hi - r_lo;
     for (ItemWalk it(tid, nt, W, cv); it.r < nrows; it.next(W, cv)) {
       const int c = it.cvi * 8;
-      const size_t pix = (size_t)it.r * row_elems + (size_t)it.w * C;
+      const int pix = it.r * row_elems + it.w * C;          // offsets inside a block of a few rows: 32 bits
       float v[16], t[16], ws[8], o[8];
       load16(xbase + pix, c, C, v);
 #pragma unroll
@@ -142,10 +140,10 @@ lrn_maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ p, uin
   __syncthreads();
   for (ItemWalk it(tid, nt, g.OW, cv); it.r < n_out; it.next(g.OW, cv)) {
     const int oh = oh0 + it.r, ow = it.w, c = it.cvi * 8;
-    const int ih0 = oh * g.stride - g.pad;
-    const int kh_lo = max(0, -ih0), kh_hi = min(g.K, g.H - ih0);
-    const int iw0 = ow * g.stride - g.pad;
-    const int kw_lo = max(0, -iw0), kw_hi = min(g.K, W - iw0);
+    const int ih0 = oh * PS - g.pad;
+    const int kh_lo = max(0, -ih0), kh_hi = min(PK, g.H - ih0);
+    const int iw0 = ow * PS - g.pad;
+    const int kw_lo = max(0, -iw0), kw_hi = min(PK, W - iw0);
     // packed: best value and window code per 16-bit lane; strict > keeps the first maximum
     const uint32_t neg = 0xff7fff7fu;                 // two bf16 lowest finite values
     __nv_bfloat162 best[4];
@@ -153,11 +151,11 @@ lrn_maxpool_forward_kernel(const bf16* __restrict__ x, bf16* __restrict__ p, uin
 #pragma unroll
     for (int j = 0; j < 4; ++j) { best[j] = *reinterpret_cast<const __nv_bfloat162*>(&neg); arg[j] = 0x00ff00ffu; }
     for (int kh = kh_lo; kh < kh_hi; ++kh) {
-      const bf16* yr = ys + (size_t)(ih0 + kh - ih_base) * row_elems + c;
+      const bf16* yr = ys + (ih0 + kh - ih_base) * row_elems + c;
       for (int kw = kw_lo; kw < kw_hi; ++kw) {
-        const uint4 v = *reinterpret_cast<const uint4*>(yr + (size_t)(iw0 + kw) * C);
+        const uint4 v = *reinterpret_cast<const uint4*>(yr + (iw0 + kw) * C);
         const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
-        const uint32_t code1 = (uint32_t)(kh * g.K + kw);
+        const uint32_t code1 = (uint32_t)(kh * PK + kw);
         const uint32_t code = code1 | (code1 << 16);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -244,7 +242,7 @@ lrn_maxpool_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__
         const uint32_t code_h = (uint32_t)((th - oh * PS) * PK + tw);
         for (int ow = ow_lo; ow <= ow_hi; ++ow) {
           const uint32_t code = code_h - (uint32_t)(ow * PS);
-          const size_t o = (size_t)(oh - oh_lo) * orow_elems + (size_t)ow * C + c;
+          const int o = (oh - oh_lo) * orow_elems + ow * C + c;
           const uint2 pk = *reinterpret_cast<const uint2*>(args + o);
           const uint32_t c4 = code * 0x01010101u;
           const uint32_t m0 = __vcmpeq4(pk.x, c4), m1 = __vcmpeq4(pk.y, c4);      // 0xff per matching channel
@@ -258,7 +256,7 @@ lrn_maxpool_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__
           dy[4] += bf_lo(k2); dy[5] += bf_hi(k2); dy[6] += bf_lo(k3); dy[7] += bf_hi(k3);
         }
       }
-      const size_t pix = (size_t)it.r * row_elems + (size_t)it.w * C;
+      const int pix = it.r * row_elems + it.w * C;          // offsets inside a block of a few rows: 32 bits
       uint4 oa = make_uint4(0u, 0u, 0u, 0u), orat = make_uint4(0u, 0u, 0u, 0u);
       if (any) {
         float v[16], t[16], ws[8], a[8], rt[8];
@@ -291,7 +289,7 @@ lrn_maxpool_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__
     bf16* dblk = dx + ((long long)b * g.H + h0) * row_elems;
     for (ItemWalk it(tid, nt, W, cv); it.r < nr; it.next(W, cv)) {
       const int c = it.cvi * 8;
-      const size_t pix = (size_t)it.r * row_elems + (size_t)it.w * C;
+      const int pix = it.r * row_elems + it.w * C;          // offsets inside a block of a few rows: 32 bits
       float rt[16], ws[8], o[8];
       load16(rs + pix, c, C, rt);
       window8<HALF>(rt, ws);
@@ -404,19 +402,22 @@ int geeps_lrn_maxpool_forward(const void* x, void* p, void* argmax, const GeepsP
   const int RO = lp_fwd_rows(g);
   const int grid = g->B * ((g->OH + RO - 1) / RO);
   cudaStream_t st = (cudaStream_t)stream;
-#define LP_FWD(HALF)                                                                                               \
+#define LP_FWD(HALF, K3S2)                                                                                         \
   do {                                                                                                             \
     static bool attr_set = false;                                                                                  \
     if (!attr_set) {                                                                                               \
-      cudaError_t e = cudaFuncSetAttribute(lrn_maxpool_forward_kernel<HALF>,                                       \
+      cudaError_t e = cudaFuncSetAttribute(lrn_maxpool_forward_kernel<HALF, K3S2>,                                 \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLpMaxSmem);          \
       if (e != cudaSuccess) return (int)e;                                                                         \
       attr_set = true;                                                                                             \
     }                                                                                                              \
-    lrn_maxpool_forward_kernel<HALF><<<grid, block, smem, st>>>((const bf16*)x, (bf16*)p, (uint8_t*)argmax, *g, cf, \
-                                                                 RO);                                              \
+    lrn_maxpool_forward_kernel<HALF, K3S2><<<grid, block, smem, st>>>((const bf16*)x, (bf16*)p, (uint8_t*)argmax,   \
+                                                                       *g, cf, RO);                                \
   } while (0)
-  if (size == 3) LP_FWD(1); else if (size == 5) LP_FWD(2); else LP_FWD(3);
+  const bool k3s2 = g->K == 3 && g->stride == 2;
+  if (size == 3) { if (k3s2) LP_FWD(1, true); else LP_FWD(1, false); }
+  else if (size == 5) { if (k3s2) LP_FWD(2, true); else LP_FWD(2, false); }
+  else { if (k3s2) LP_FWD(3, true); else LP_FWD(3, false); }
 #undef LP_FWD
   return (int)cudaGetLastError();
 }
