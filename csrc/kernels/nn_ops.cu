@@ -627,7 +627,7 @@ nchw_to_s2d_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, int H, 
 
 // The same layout for S = 4, C = 3 with coalesced traffic on both sides: a block of four warps converts 32
 // consecutive output pixels of one output row.  Warp dy reads, for each colour, the 128 consecutive input elements of
-// image row 4 hs + dy that those pixels cover (one 4-element group per lane), the values meet in a [32 pixels][Cpad]
+// image row 4 hs + dy that those pixels cover (32 consecutive elements per load), the values meet in a [32 pixels][Cpad]
 // tile in shared memory, and the tile leaves as one contiguous run of 32 * Cpad * 2 bytes in 16-byte stores.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -644,14 +644,18 @@ nchw_to_s2d43_tile_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B, 
   // channels past S * S * C are zero (this warp's share of them: pixel `lane`, slots 48 + 4 dy .. + 4, when they exist)
   for (int j = S * S * C + dy * 4; j < Cpad && j < S * S * C + dy * 4 + 4; ++j) tile[lane * PITCH + j] = __float2bfloat16(0.f);
   const int h = hs * S + dy;
-  const int w0 = (ws0 + lane) * S;
+  // the 128 consecutive input elements of this image row that the 32 pixels cover, 32 at a time: every load
+  // instruction of the warp is one contiguous run (also when x is pinned host memory read over PCIe)
+  const int wbase = ws0 * S;
 #pragma unroll
   for (int c = 0; c < C; ++c) {
     const T* row = x + ((b * C + c) * H + h) * (long long)W;
 #pragma unroll
-    for (int dx = 0; dx < S; ++dx) {
-      const float v = (h < H && w0 + dx < W) ? in_val(row + w0 + dx) : 0.f;
-      tile[lane * PITCH + (dy * S + dx) * C + c] = __float2bfloat16(v);
+    for (int i = 0; i < S; ++i) {
+      const int e = i * 32 + lane;                      // element of the run: pixel e / 4, column offset e % 4
+      const int w = wbase + e;
+      const float v = (h < H && w < W) ? in_val(row + w) : 0.f;
+      tile[(e >> 2) * PITCH + (dy * S + (e & 3)) * C + c] = __float2bfloat16(v);
     }
   }
   __syncthreads();

@@ -127,6 +127,8 @@ class Input(Layer):
         return self.out_shape
 
     def forward(self, x):
+        if x.dtype == BF and tuple(x.shape) == tuple(self.out_shape) and x.is_contiguous():
+            return x           # already in this layer's output layout (HostFeeder(layout=...) converts while it copies)
         if self.s2d:
             return F.nchw_to_s2d_bf16(x, self.y, self.s2d)
         return F.nchw_to_nhwc_bf16(x, self.cpad)
