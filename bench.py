@@ -135,9 +135,6 @@ def main() -> None:
     ap.add_argument("--multicast", type=int, default=0, choices=[0, 1],
                     help="1: the parameter-server arena is bound to an NVSwitch multicast object and large tables are "
                          "reduced / published through it (multimem) from 4 GPUs on")
-    ap.add_argument("--kernel-input", type=int, default=0, choices=[0, 1],
-                    help="end-to-end runs: 1 = a kernel on the copy stream reads each pinned host batch over PCIe and writes "
-                         "the model's input layout (AlexNet: space-to-depth) into the device slot; 0 = copy engine + input layer")
     ap.add_argument("--no-graph", action="store_true",
                     help="replay the recorded native calls one launch at a time instead of one CUDA graph per step")
     args = ap.parse_args()
@@ -297,21 +294,15 @@ def main() -> None:
         barrier()
         e2e = e2e_other = diag = None
         if not args.no_e2e:
-            il = mod.net.input_layer
-            kernel_input = bool(args.kernel_input) and getattr(il, "s2d", 0) == 4 and in_dtype == torch.bfloat16
-            feeder = HostFeeder((B,) + image, (B,), dev, x_dtype=in_dtype, timed=True,
-                                s2d_layout=(il.s2d, il.out_shape) if kernel_input else None)
+            feeder = HostFeeder((B,) + image, (B,), dev, x_dtype=in_dtype, timed=True)
             e2e = e2e_record(make_e2e(feeder, x_host), feeder)
-            e2e["input_path"] = ("kernel reads pinned host memory, writes the input layout" if kernel_input
-                                 else "copy engine, then the input layer's conversion kernel")
             # all ranks copy at once with nothing else running: what the host-to-device path gives each GPU
             barrier()
             c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             with torch.cuda.stream(feeder.copy_stream):
                 c0.record(feeder.copy_stream)
-                stage = feeder.x[0] if feeder.s2d_layout is None else torch.empty_like(x_host, device=dev)
                 for _ in range(8):
-                    stage.copy_(x_host, non_blocking=True)
+                    feeder.x[0].copy_(x_host, non_blocking=True)
                 c1.record(feeder.copy_stream)
             c1.synchronize()
             alone_ms = max_over_ranks(c0.elapsed_time(c1) / 8)

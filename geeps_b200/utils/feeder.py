@@ -7,31 +7,20 @@ import torch
 
 
 class HostFeeder:
-    def __init__(self, x_shape, y_shape, device, depth: int = 2, x_dtype=torch.float32, timed: bool = False,
-                 s2d_layout=None):
+    def __init__(self, x_shape, y_shape, device, depth: int = 2, x_dtype=torch.float32, timed: bool = False):
         """x_dtype: dtype of the batches on the host and in the device slots (fp32, or bf16 to halve the
         host-to-device bytes; the input layer converts either to bf16 NHWC).  timed: bracket every copy with
-        timing events on the copy stream (copy_times_ms() returns their durations).
-        s2d_layout = (S, out_shape): no copy engine is used; a kernel on the copy stream reads the pinned host batch
-        over PCIe and writes the model's space-to-depth input layout (bf16 [B, Hs, Ws, C']) straight into the device
-        slot, which the input layer then passes through.  The bytes that cross PCIe per step are the same."""
+        timing events on the copy stream (copy_times_ms() returns their durations)."""
         self.device = torch.device(device)
-        self.s2d_layout = s2d_layout
         self.copy_stream = torch.cuda.Stream(device=self.device)
         self.timed = timed
         self._timing = []          # (begin, end) event pairs of submitted copies
-        if s2d_layout is None:
-            self.x = [torch.empty(x_shape, dtype=x_dtype, device=self.device) for _ in range(depth)]
-        else:
-            self.x = [torch.zeros(s2d_layout[1], dtype=torch.bfloat16, device=self.device) for _ in range(depth)]
+        self.x = [torch.empty(x_shape, dtype=x_dtype, device=self.device) for _ in range(depth)]
         self.y = [torch.empty(y_shape, dtype=torch.int64, device=self.device) for _ in range(depth)]
         self.ready = [torch.cuda.Event() for _ in range(depth)]
         self.free = [torch.cuda.Event() for _ in range(depth)]
         self.depth, self.put_i, self.get_i = depth, 0, 0
-        n_x = 1
-        for d in x_shape:
-            n_x *= d
-        self.bytes_per_batch = n_x * torch.empty(0, dtype=x_dtype).element_size() + self.y[0].numel() * 8
+        self.bytes_per_batch = self.x[0].numel() * self.x[0].element_size() + self.y[0].numel() * 8
         for e in self.free:
             e.record(torch.cuda.current_stream(self.device))
 
@@ -43,12 +32,7 @@ class HostFeeder:
             if self.timed:
                 t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 t0.record(self.copy_stream)
-            if self.s2d_layout is None:
-                self.x[s].copy_(x_host, non_blocking=True)
-            else:
-                from ..ops import functional as F
-                assert x_host.is_pinned(), "the batch must live in pinned host memory"
-                F.nchw_to_s2d_bf16(x_host, self.x[s], self.s2d_layout[0])
+            self.x[s].copy_(x_host, non_blocking=True)
             self.y[s].copy_(y_host, non_blocking=True)
             if self.timed:
                 t1.record(self.copy_stream)
