@@ -270,12 +270,54 @@ bn_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* _
   }
 }
 
+// Normalisation with the statistics finalised inside: every thread derives mean and 1/std of its eight channels from
+// the channel sums (no separate finalisation launch); the threads of the first pixel also store mean / rstd for the
+// backward pass, update the running statistics and zero `zero_after` (2 C floats: the scratch of the NEXT reduction
+// of this layer, e.g. the backward one, so that no memset node sits in front of it).
+__global__ void __launch_bounds__(256)
+bn_apply_fused_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ sums,
+                      float* __restrict__ mean_rstd, float* running_mean, float* running_var,
+                      const float* __restrict__ gamma, const float* __restrict__ beta, float* zero_after, long long P,
+                      int C, long long ldx, long long ldy, int relu, float inv_count, float eps, float momentum) {
+  const int cv = C >> 3;
+  const long long total = P * cv;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % cv) * 8;
+    const long long p = i / cv;
+    float m[8], r[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      m[e] = sums[c + e] * inv_count;
+      const float var = fmaxf(sums[C + c + e] * inv_count - m[e] * m[e], 0.f);
+      r[e] = rsqrtf(var + eps);
+      if (p == 0) {
+        mean_rstd[c + e] = m[e];
+        mean_rstd[C + c + e] = r[e];
+        if (running_mean) {
+          running_mean[c + e] = (1.f - momentum) * running_mean[c + e] + momentum * m[e];
+          running_var[c + e] = (1.f - momentum) * running_var[c + e] + momentum * var;
+        }
+        if (zero_after) { zero_after[c + e] = 0.f; zero_after[C + c + e] = 0.f; }
+      }
+    }
+    Bf8 v = ld8(x + p * ldx + c), o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float f = (bf(v.v[e]) - m[e]) * r[e] * gamma[c + e] + beta[c + e];
+      if (relu) f = fmaxf(f, 0.f);
+      o.v[e] = __float2bfloat16(f);
+    }
+    st8(y + p * ldy + c, o);
+  }
+}
+
 // dx = gamma * rstd * (dy' - sum_dy/P - xhat * sum_dy_xhat/P); also emits dgamma, dbeta (scaled).
 __global__ void __launch_bounds__(256)
 bn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
                    bf16* __restrict__ dx, const float* __restrict__ mean_rstd, const float* __restrict__ gamma,
                    const float* __restrict__ sums, float* dgamma, float* dbeta, long long P, int C,
-                   long long ldx, long long lddy, long long lddx, int relu, float grad_scale) {
+                   long long ldx, long long lddy, long long lddx, int relu, float grad_scale, float* zero_after) {
   const int cv = C >> 3;
   const long long total = P * cv;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -284,6 +326,8 @@ bn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, cons
   if (tid0 < C) {
     if (dbeta) dbeta[tid0] = sums[tid0] * grad_scale;
     if (dgamma) dgamma[tid0] = sums[C + tid0] * grad_scale;
+    // the scratch of this layer's next forward reduction (nobody reads it during the backward pass)
+    if (zero_after) { zero_after[tid0] = 0.f; zero_after[C + tid0] = 0.f; }
   }
   for (long long i = tid0; i < total; i += stride) {
     const int c = (int)(i % cv) * 8;
@@ -1120,7 +1164,36 @@ int geeps_bn_backward(const void* x, const void* dy, const void* y, void* dx, co
       (const bf16*)x, (const bf16*)dy, (const bf16*)y, mean_rstd, sums, P, C, ldx, lddy, relu, 1.f);
   bn_backward_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y,
                                                            (bf16*)dx, mean_rstd, gamma, sums, dgamma, dbeta, P, C,
-                                                           ldx, lddy, lddx, relu, grad_scale);
+                                                           ldx, lddy, lddx, relu, grad_scale, nullptr);
+  return CK();
+}
+
+// The training-loop forms: `sums` must be zero on entry (2 C floats) and `zero_after` (or NULL) is zeroed for the
+// layer's next reduction, so a BatchNorm layer that alternates forward and backward needs no memset and no separate
+// finalisation launch: 2 launches per direction instead of 4 and 3.
+int geeps_bn_forward_fused(const void* x, void* y, const float* gamma, const float* beta, float* sums,
+                           float* mean_rstd, float* running_mean, float* running_var, float* zero_after, long long P,
+                           int C, long long ldx, long long ldy, float eps, float momentum, int relu, void* stream) {
+  if (C % 8) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  channel_reduce_kernel<0><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
+      (const bf16*)x, nullptr, nullptr, nullptr, sums, P, C, ldx, 0, 0, 1.f);
+  bn_apply_fused_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (bf16*)y, sums, mean_rstd, running_mean,
+                                                              running_var, gamma, beta, zero_after, P, C, ldx, ldy, relu,
+                                                              1.f / (float)P, eps, momentum);
+  return CK();
+}
+int geeps_bn_backward_fused(const void* x, const void* dy, const void* y, void* dx, const float* mean_rstd,
+                            const float* gamma, float* sums, float* dgamma, float* dbeta, float* zero_after, long long P,
+                            int C, long long ldx, long long lddy, long long lddx, int relu, float grad_scale,
+                            void* stream) {
+  if (C % 8) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  channel_reduce_kernel<1><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
+      (const bf16*)x, (const bf16*)dy, (const bf16*)y, mean_rstd, sums, P, C, ldx, lddy, relu, 1.f);
+  bn_backward_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y,
+                                                           (bf16*)dx, mean_rstd, gamma, sums, dgamma, dbeta, P, C,
+                                                           ldx, lddy, lddx, relu, grad_scale, zero_after);
   return CK();
 }
 

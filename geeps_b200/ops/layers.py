@@ -405,7 +405,11 @@ class BatchNorm(Layer):
         self.P = 1
         for s in in_shape[:-1]:
             self.P *= s
-        self.sums = torch.empty(2 * self.C, device=device)
+        # reduction scratch of the two directions: each kernel pair leaves the other direction's scratch zeroed, so a
+        # training loop (forward, backward, forward, ...) needs no memset in front of a reduction
+        self.sums = torch.zeros(2 * self.C, device=device)
+        self.sums_b = torch.zeros(2 * self.C, device=device)
+        self._clean_f = self._clean_b = True
         self.mean_rstd = torch.empty(2 * self.C, device=device)
         self.running_mean = torch.zeros(self.C, device=device)
         self.running_var = torch.ones(self.C, device=device)
@@ -423,15 +427,26 @@ class BatchNorm(Layer):
 
     def forward(self, x):
         self.x = x if x.dim() == 2 else x.view(self.P, self.C)
-        F.bn_forward(self.x, self.y, self.p32["gamma"], self.p32["beta"], self.sums, self.mean_rstd, self.running_mean,
-                     self.running_var, eps=self.eps, momentum=self.momentum, relu=self.relu)
+        if not self._clean_f:       # two forward passes in a row (no backward in between zeroed the scratch)
+            F.bn_forward(self.x, self.y, self.p32["gamma"], self.p32["beta"], self.sums, self.mean_rstd,
+                         self.running_mean, self.running_var, eps=self.eps, momentum=self.momentum, relu=self.relu)
+            return self.y
+        F.bn_forward_fused(self.x, self.y, self.p32["gamma"], self.p32["beta"], self.sums, self.mean_rstd,
+                           self.running_mean, self.running_var, zero_after=self.sums_b, eps=self.eps,
+                           momentum=self.momentum, relu=self.relu)
+        self._clean_f, self._clean_b = False, True
         return self.y
 
     def backward(self, dy):
         if dy.dim() != 2:
             dy = dy.view(self.P, self.C)
-        F.bn_backward(self.x, dy, self.y, self.dx, self.mean_rstd, self.p32["gamma"], self.sums, self.g32["gamma"],
-                      self.g32["beta"], relu=self.relu)
+        if not self._clean_b:
+            F.bn_backward(self.x, dy, self.y, self.dx, self.mean_rstd, self.p32["gamma"], self.sums_b, self.g32["gamma"],
+                          self.g32["beta"], relu=self.relu)
+            return self.dx
+        F.bn_backward_fused(self.x, dy, self.y, self.dx, self.mean_rstd, self.p32["gamma"], self.sums_b,
+                            self.g32["gamma"], self.g32["beta"], zero_after=self.sums, relu=self.relu)
+        self._clean_b, self._clean_f = False, True
         return self.dx
 
 

@@ -142,6 +142,43 @@ def test_batchnorm_forward_backward(relu):
     assert torch.allclose(db, br.grad, atol=0.5, rtol=2e-2)
 
 
+@pytest.mark.parametrize("relu", [False, True])
+def test_batchnorm_layer_alternating_and_repeated_passes(relu):
+    """The BatchNorm layer's training-loop form (two launches per direction, each zeroing the other direction's
+    scratch) over forward / backward / forward / forward / backward: every result matches torch."""
+    from geeps_b200.ops import layers as GL
+    torch.manual_seed(4)
+    P, Cc = 2048, 64
+    bn = GL.BatchNorm("bn", relu=relu)
+    bn.setup((P, Cc), torch.device(DEV))
+    gamma = torch.rand(Cc, device=DEV) + 0.5
+    beta = torch.randn(Cc, device=DEV) * 0.1
+    bn.p32 = {"gamma": gamma, "beta": beta}
+    bn.g32 = {"gamma": torch.empty(Cc, device=DEV), "beta": torch.empty(Cc, device=DEV)}
+
+    def check(x, dy):
+        xr = x.float().requires_grad_(True)
+        gr, br = gamma.clone().requires_grad_(True), beta.clone().requires_grad_(True)
+        yr = TF.batch_norm(xr, None, None, gr, br, training=True, eps=bn.eps)
+        y = bn.forward(x)
+        assert torch.allclose(y.float(), torch.relu(yr) if relu else yr, atol=3e-2, rtol=2e-2)
+        if dy is None:
+            return
+        dx = bn.backward(dy)
+        (yr * (y.float() > 0) if relu else yr).backward(dy.float())
+        assert torch.allclose(dx.float(), xr.grad, atol=3e-2, rtol=3e-2)
+        assert torch.allclose(bn.g32["gamma"], gr.grad, atol=0.5, rtol=2e-2)
+        assert torch.allclose(bn.g32["beta"], br.grad, atol=0.5, rtol=2e-2)
+
+    mk = lambda: (torch.randn(P, Cc, device=DEV) * 2 + 1).to(BF)
+    check(mk(), torch.randn(P, Cc, device=DEV).to(BF))
+    check(mk(), None)                      # forward only ...
+    check(mk(), None)                      # ... twice in a row: the scratch was not zeroed by a backward pass
+    check(mk(), torch.randn(P, Cc, device=DEV).to(BF))
+    check(mk(), torch.randn(P, Cc, device=DEV).to(BF))
+    torch.cuda.synchronize()
+
+
 def test_lrn_forward_backward():
     torch.manual_seed(3)
     P, Cc = 500, 96
