@@ -170,10 +170,10 @@ col2im_kernel(const bf16* __restrict__ dcol, bf16* __restrict__ dx, const GeepsC
 // MODE 1: out[c] += sum dy', out[C+c] += sum dy' * xhat          (BN backward; dy' = dy masked by y>0 if relu)
 // MODE 2: out[c] += scale * sum x                                (bias gradient)
 template <int MODE>
-__global__ void __launch_bounds__(256)
-channel_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
-                      const float* __restrict__ mean_rstd, float* __restrict__ out, long long P, int C,
-                      long long ldx, long long lddy, int relu, float scale) {
+__device__ __forceinline__ void channel_reduce_body(const bf16* __restrict__ x, const bf16* __restrict__ dy,
+                                                    const bf16* __restrict__ y, const float* __restrict__ mean_rstd,
+                                                    float* __restrict__ out, long long P, int C, long long ldx,
+                                                    long long lddy, int relu, float scale) {
   extern __shared__ float sacc[];  // [2*C]
   for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sacc[i] = 0.f;
   __syncthreads();
@@ -220,6 +220,13 @@ channel_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, c
     const float v = sacc[i];
     if (v != 0.f) atomicAdd(out + i, MODE == 2 ? v * scale : v);
   }
+}
+template <int MODE>
+__global__ void __launch_bounds__(256)
+channel_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                      const float* __restrict__ mean_rstd, float* __restrict__ out, long long P, int C,
+                      long long ldx, long long lddy, int relu, float scale) {
+  channel_reduce_body<MODE>(x, dy, y, mean_rstd, out, P, C, ldx, lddy, relu, scale);
 }
 
 // any C, any pitch: one thread per column (small P: FC bias gradients with odd widths)
@@ -274,11 +281,12 @@ bn_apply_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* _
 // the channel sums (no separate finalisation launch); the threads of the first pixel also store mean / rstd for the
 // backward pass, update the running statistics and zero `zero_after` (2 C floats: the scratch of the NEXT reduction
 // of this layer, e.g. the backward one, so that no memset node sits in front of it).
-__global__ void __launch_bounds__(256)
-bn_apply_fused_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ sums,
-                      float* __restrict__ mean_rstd, float* running_mean, float* running_var,
-                      const float* __restrict__ gamma, const float* __restrict__ beta, float* zero_after, long long P,
-                      int C, long long ldx, long long ldy, int relu, float inv_count, float eps, float momentum) {
+__device__ __forceinline__ void bn_apply_fused_body(const bf16* __restrict__ x, bf16* __restrict__ y,
+                                                    const float* sums, float* mean_rstd,
+                                                    float* running_mean, float* running_var,
+                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                    float* zero_after, long long P, int C, long long ldx, long long ldy,
+                                                    int relu, float inv_count, float eps, float momentum) {
   const int cv = C >> 3;
   const long long total = P * cv;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -311,13 +319,22 @@ bn_apply_fused_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const fl
     st8(y + p * ldy + c, o);
   }
 }
+__global__ void __launch_bounds__(256)
+bn_apply_fused_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ sums,
+                      float* __restrict__ mean_rstd, float* running_mean, float* running_var,
+                      const float* __restrict__ gamma, const float* __restrict__ beta, float* zero_after, long long P,
+                      int C, long long ldx, long long ldy, int relu, float inv_count, float eps, float momentum) {
+  bn_apply_fused_body(x, y, sums, mean_rstd, running_mean, running_var, gamma, beta, zero_after, P, C, ldx, ldy, relu,
+                      inv_count, eps, momentum);
+}
 
 // dx = gamma * rstd * (dy' - sum_dy/P - xhat * sum_dy_xhat/P); also emits dgamma, dbeta (scaled).
-__global__ void __launch_bounds__(256)
-bn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
-                   bf16* __restrict__ dx, const float* __restrict__ mean_rstd, const float* __restrict__ gamma,
-                   const float* __restrict__ sums, float* dgamma, float* dbeta, long long P, int C,
-                   long long ldx, long long lddy, long long lddx, int relu, float grad_scale, float* zero_after) {
+__device__ __forceinline__ void bn_backward_body(const bf16* __restrict__ x, const bf16* __restrict__ dy,
+                                                 const bf16* __restrict__ y, bf16* __restrict__ dx,
+                                                 const float* mean_rstd, const float* __restrict__ gamma,
+                                                 const float* sums, float* dgamma, float* dbeta, long long P, int C,
+                                                 long long ldx, long long lddy, long long lddx, int relu,
+                                                 float grad_scale, float* zero_after) {
   const int cv = C >> 3;
   const long long total = P * cv;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -344,6 +361,62 @@ bn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, cons
     }
     st8(dx + p * lddx + c, o);
   }
+}
+__global__ void __launch_bounds__(256)
+bn_backward_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                   bf16* __restrict__ dx, const float* __restrict__ mean_rstd, const float* __restrict__ gamma,
+                   const float* __restrict__ sums, float* dgamma, float* dbeta, long long P, int C,
+                   long long ldx, long long lddy, long long lddx, int relu, float grad_scale, float* zero_after) {
+  bn_backward_body(x, dy, y, dx, mean_rstd, gamma, sums, dgamma, dbeta, P, C, ldx, lddy, lddx, relu, grad_scale,
+                   zero_after);
+}
+
+// ---- one launch per direction: reduction, grid barrier, normalisation (cooperative launch: all blocks resident) ----
+// bar[0] counts arrivals, bar[1] counts blocks that are done (the last one resets both for the next launch), bar[2]
+// is set when a block gave up waiting (it then skips the second phase: the output stays stale and mean_rstd[0] is
+// made NaN so that the failure shows in the loss).
+__device__ __forceinline__ bool bn_grid_barrier(int* bar, int nblocks) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(bar, 1);
+    s_ok = geeps_wait_ge(bar, nblocks, 1000000000ull, nullptr) ? 1 : 0;
+    __threadfence();
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+__device__ __forceinline__ void bn_grid_done(int* bar, int nblocks) {
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(bar + 1, 1) == nblocks - 1) {
+    bar[0] = 0; bar[1] = 0;
+    __threadfence();
+  }
+}
+__global__ void __launch_bounds__(256)
+bn_forward_coop_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, float* sums, float* mean_rstd,
+                       float* running_mean, float* running_var, const float* __restrict__ gamma,
+                       const float* __restrict__ beta, float* zero_after, int* bar, long long P, int C, long long ldx,
+                       long long ldy, int relu, float inv_count, float eps, float momentum) {
+  channel_reduce_body<0>(x, nullptr, nullptr, nullptr, sums, P, C, ldx, 0, 0, 1.f);
+  if (bn_grid_barrier(bar, (int)gridDim.x))
+    bn_apply_fused_body(x, y, sums, mean_rstd, running_mean, running_var, gamma, beta, zero_after, P, C, ldx, ldy, relu,
+                        inv_count, eps, momentum);
+  else if (threadIdx.x == 0) { bar[2] = 1; mean_rstd[0] = __int_as_float(0x7fc00000); }
+  bn_grid_done(bar, (int)gridDim.x);
+}
+__global__ void __launch_bounds__(256)
+bn_backward_coop_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                        bf16* __restrict__ dx, float* mean_rstd, const float* __restrict__ gamma, float* sums,
+                        float* dgamma, float* dbeta, float* zero_after, int* bar, long long P, int C, long long ldx,
+                        long long lddy, long long lddx, int relu, float grad_scale) {
+  channel_reduce_body<1>(x, dy, y, mean_rstd, sums, P, C, ldx, lddy, relu, 1.f);
+  if (bn_grid_barrier(bar, (int)gridDim.x))
+    bn_backward_body(x, dy, y, dx, mean_rstd, gamma, sums, dgamma, dbeta, P, C, ldx, lddy, lddx, relu, grad_scale,
+                     zero_after);
+  else if (threadIdx.x == 0) { bar[2] = 1; mean_rstd[0] = __int_as_float(0x7fc00000); }
+  bn_grid_done(bar, (int)gridDim.x);
 }
 
 // ---------------- ReLU backward / dropout ----------------
@@ -1171,11 +1244,36 @@ int geeps_bn_backward(const void* x, const void* dy, const void* y, void* dx, co
 // The training-loop forms: `sums` must be zero on entry (2 C floats) and `zero_after` (or NULL) is zeroed for the
 // layer's next reduction, so a BatchNorm layer that alternates forward and backward needs no memset and no separate
 // finalisation launch: 2 launches per direction instead of 4 and 3.
+// grid of a single-launch BatchNorm kernel: enough blocks for the reduction, never more than can be resident at
+// once beside other kernels (the blocks wait for one another at the grid barrier)
+static int bn_coop_grid(long long P, int C) {
+  int g = reduce_grid(P, C);
+  const int cap = geeps_sm_count();
+  return g > cap ? cap : g;
+}
+static bool bn_coop_enabled() {
+  static int v = -1;
+  // off by default: with at most one block per SM and a grid barrier the single launch is slower than two full-width
+  // launches (Inception-BN-22K 5.84 against 5.65 ms per step, small net 1.96 against 1.95 ms)
+  if (v < 0) { const char* e = getenv("GEEPS_BN_COOP"); v = e ? atoi(e) : 0; }
+  return v != 0;
+}
+
 int geeps_bn_forward_fused(const void* x, void* y, const float* gamma, const float* beta, float* sums,
-                           float* mean_rstd, float* running_mean, float* running_var, float* zero_after, long long P,
-                           int C, long long ldx, long long ldy, float eps, float momentum, int relu, void* stream) {
+                           float* mean_rstd, float* running_mean, float* running_var, float* zero_after, int* barrier,
+                           long long P, int C, long long ldx, long long ldy, float eps, float momentum, int relu,
+                           void* stream) {
   if (C % 8) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
+  if (barrier != nullptr && bn_coop_enabled()) {
+    const bf16* xx = (const bf16*)x; bf16* yy = (bf16*)y;
+    float inv_count = 1.f / (float)P;
+    void* args[] = {&xx, &yy, &sums, &mean_rstd, &running_mean, &running_var, &gamma, &beta, &zero_after, &barrier,
+                    &P, &C, &ldx, &ldy, &relu, &inv_count, &eps, &momentum};
+    cudaError_t e = cudaLaunchCooperativeKernel((void*)bn_forward_coop_kernel, dim3(bn_coop_grid(P, C)), dim3(256), args,
+                                                2 * C * sizeof(float), st);
+    return e == cudaSuccess ? CK() : (int)e;
+  }
   channel_reduce_kernel<0><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
       (const bf16*)x, nullptr, nullptr, nullptr, sums, P, C, ldx, 0, 0, 1.f);
   bn_apply_fused_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (bf16*)y, sums, mean_rstd, running_mean,
@@ -1183,12 +1281,21 @@ int geeps_bn_forward_fused(const void* x, void* y, const float* gamma, const flo
                                                               1.f / (float)P, eps, momentum);
   return CK();
 }
-int geeps_bn_backward_fused(const void* x, const void* dy, const void* y, void* dx, const float* mean_rstd,
-                            const float* gamma, float* sums, float* dgamma, float* dbeta, float* zero_after, long long P,
-                            int C, long long ldx, long long lddy, long long lddx, int relu, float grad_scale,
-                            void* stream) {
+int geeps_bn_backward_fused(const void* x, const void* dy, const void* y, void* dx, float* mean_rstd,
+                            const float* gamma, float* sums, float* dgamma, float* dbeta, float* zero_after,
+                            int* barrier, long long P, int C, long long ldx, long long lddy, long long lddx, int relu,
+                            float grad_scale, void* stream) {
   if (C % 8) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
+  if (barrier != nullptr && bn_coop_enabled()) {
+    const bf16* xx = (const bf16*)x; const bf16* dd = (const bf16*)dy; const bf16* yy = (const bf16*)y;
+    bf16* dxx = (bf16*)dx;
+    void* args[] = {&xx, &dd, &yy, &dxx, &mean_rstd, &gamma, &sums, &dgamma, &dbeta, &zero_after, &barrier,
+                    &P, &C, &ldx, &lddy, &lddx, &relu, &grad_scale};
+    cudaError_t e = cudaLaunchCooperativeKernel((void*)bn_backward_coop_kernel, dim3(bn_coop_grid(P, C)), dim3(256),
+                                                args, 2 * C * sizeof(float), st);
+    return e == cudaSuccess ? CK() : (int)e;
+  }
   channel_reduce_kernel<1><<<reduce_grid(P, C), 256, 2 * C * sizeof(float), st>>>(
       (const bf16*)x, (const bf16*)dy, (const bf16*)y, mean_rstd, sums, P, C, ldx, lddy, relu, 1.f);
   bn_backward_kernel<<<grid_1d(P * (C / 8)), 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y,

@@ -38,14 +38,18 @@ int geeps_bn_backward(const void* x, const void* dy, const void* y, void* dx, co
                       const float* gamma, float* sums, float* dgamma, float* dbeta, long long P, int C,
                       long long ldx, long long lddy, long long lddx, int relu, float grad_scale, void* stream);
 // Training-loop forms: `sums` (2 C floats) must be zero on entry; `zero_after` (2 C floats or NULL) is zeroed for the
-// layer's next reduction; the statistics are finalised inside the normalising kernel.  2 launches each.
+// layer's next reduction; the statistics are finalised inside the normalising kernel.  Two launches each, or - with
+// `barrier` (4 ints, zero at first use, private to this layer and direction) - ONE cooperative launch whose blocks meet
+// at a bounded grid barrier between the reduction and the normalisation, when GEEPS_BN_COOP=1 (measured slower than the
+// two launches, so it is off by default).
 int geeps_bn_forward_fused(const void* x, void* y, const float* gamma, const float* beta, float* sums,
-                           float* mean_rstd, float* running_mean, float* running_var, float* zero_after, long long P,
-                           int C, long long ldx, long long ldy, float eps, float momentum, int relu, void* stream);
-int geeps_bn_backward_fused(const void* x, const void* dy, const void* y, void* dx, const float* mean_rstd,
-                            const float* gamma, float* sums, float* dgamma, float* dbeta, float* zero_after, long long P,
-                            int C, long long ldx, long long lddy, long long lddx, int relu, float grad_scale,
-                            void* stream);
+                           float* mean_rstd, float* running_mean, float* running_var, float* zero_after, int* barrier,
+                           long long P, int C, long long ldx, long long ldy, float eps, float momentum, int relu,
+                           void* stream);
+int geeps_bn_backward_fused(const void* x, const void* dy, const void* y, void* dx, float* mean_rstd,
+                            const float* gamma, float* sums, float* dgamma, float* dbeta, float* zero_after,
+                            int* barrier, long long P, int C, long long ldx, long long lddy, long long lddx, int relu,
+                            float grad_scale, void* stream);
 // out[c] (+)= scale * sum_p x[p][c]
 // dx = y > 0 ? dy : 0 and colsum[c] = sum over the P pixels of dx (C % 8 == 0, C <= 8192), one pass
 int geeps_relu_backward_colsum(const void* dy, const void* y, void* dx, float* colsum, long long P, int C,

@@ -193,24 +193,26 @@ def bn_backward(x2d, dy2d, y2d, dx2d, mean_rstd, gamma, sums, dgamma, dbeta, rel
                                   C.c_float(grad_scale), stream_ptr())
 
 
-def bn_forward_fused(x2d, y2d, gamma, beta, sums, mean_rstd, running_mean, running_var, zero_after=None, eps=1e-5,
-                     momentum=0.1, relu=False) -> None:
-    """BatchNorm forward in two launches: `sums` (2 C floats) must be zero on entry, `zero_after` is zeroed for the
-    layer's next reduction (its backward scratch)."""
+def bn_forward_fused(x2d, y2d, gamma, beta, sums, mean_rstd, running_mean, running_var, zero_after=None, barrier=None,
+                     eps=1e-5, momentum=0.1, relu=False) -> None:
+    """BatchNorm forward in two launches, or one with `barrier` (4 int32, zero at first use, private to the layer and
+    direction): `sums` (2 C floats) must be zero on entry, `zero_after` is zeroed for the layer's next reduction (its
+    backward scratch)."""
     P, Cc = x2d.shape
     launch(lib().geeps_bn_forward_fused, "bn_forward_fused", ptr(x2d), ptr(y2d), ptr(gamma), ptr(beta), ptr(sums),
            ptr(mean_rstd), ptr(running_mean), ptr(running_var), ptr(zero_after) if zero_after is not None else None,
-           C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)), C.c_longlong(_ld(y2d)), C.c_float(eps), C.c_float(momentum),
+           ptr(barrier) if barrier is not None else None, C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)), C.c_longlong(_ld(y2d)), C.c_float(eps), C.c_float(momentum),
            int(relu), stream_ptr())
 
 
-def bn_backward_fused(x2d, dy2d, y2d, dx2d, mean_rstd, gamma, sums, dgamma, dbeta, zero_after=None, relu=False,
-                      grad_scale=1.0) -> None:
-    """BatchNorm backward in two launches: `sums` must be zero on entry, `zero_after` (the forward scratch) is zeroed."""
+def bn_backward_fused(x2d, dy2d, y2d, dx2d, mean_rstd, gamma, sums, dgamma, dbeta, zero_after=None, barrier=None,
+                      relu=False, grad_scale=1.0) -> None:
+    """BatchNorm backward in two launches (one with `barrier`): `sums` must be zero on entry, `zero_after` (the forward
+    scratch) is zeroed."""
     P, Cc = x2d.shape
     launch(lib().geeps_bn_backward_fused, "bn_backward_fused", ptr(x2d), ptr(dy2d), ptr(y2d), ptr(dx2d), ptr(mean_rstd),
            ptr(gamma), ptr(sums), ptr(dgamma), ptr(dbeta), ptr(zero_after) if zero_after is not None else None,
-           C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)), C.c_longlong(_ld(dy2d)), C.c_longlong(_ld(dx2d)), int(relu),
+           ptr(barrier) if barrier is not None else None, C.c_longlong(P), Cc, C.c_longlong(_ld(x2d)), C.c_longlong(_ld(dy2d)), C.c_longlong(_ld(dx2d)), int(relu),
            C.c_float(grad_scale), stream_ptr())
 
 

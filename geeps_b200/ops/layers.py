@@ -410,6 +410,7 @@ class BatchNorm(Layer):
         self.sums = torch.zeros(2 * self.C, device=device)
         self.sums_b = torch.zeros(2 * self.C, device=device)
         self._clean_f = self._clean_b = True
+        self.bar = torch.zeros(8, dtype=torch.int32, device=device)      # grid-barrier words: forward [0:4], backward [4:8]
         self.mean_rstd = torch.empty(2 * self.C, device=device)
         self.running_mean = torch.zeros(self.C, device=device)
         self.running_var = torch.ones(self.C, device=device)
@@ -432,7 +433,8 @@ class BatchNorm(Layer):
                          self.running_mean, self.running_var, eps=self.eps, momentum=self.momentum, relu=self.relu)
             return self.y
         F.bn_forward_fused(self.x, self.y, self.p32["gamma"], self.p32["beta"], self.sums, self.mean_rstd,
-                           self.running_mean, self.running_var, zero_after=self.sums_b, eps=self.eps,
+                           self.running_mean, self.running_var, zero_after=self.sums_b, barrier=self.bar[0:4],
+                           eps=self.eps,
                            momentum=self.momentum, relu=self.relu)
         self._clean_f, self._clean_b = False, True
         return self.y
@@ -445,7 +447,8 @@ class BatchNorm(Layer):
                           self.g32["beta"], relu=self.relu)
             return self.dx
         F.bn_backward_fused(self.x, dy, self.y, self.dx, self.mean_rstd, self.p32["gamma"], self.sums_b,
-                            self.g32["gamma"], self.g32["beta"], zero_after=self.sums, relu=self.relu)
+                            self.g32["gamma"], self.g32["beta"], zero_after=self.sums, barrier=self.bar[4:8],
+                            relu=self.relu)
         self._clean_b, self._clean_f = False, True
         return self.dx
 
