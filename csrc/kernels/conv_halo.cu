@@ -27,7 +27,10 @@
 // channel: it adds that channel's bias (one register), applies ReLU and writes bf16 into a [position][64 channels]
 // slab with the 128-byte swizzle - the 32 lanes of a warp write 64 contiguous bytes of one position per store - and
 // a 4-D TMA store (64 channels, PW, rows, 1) writes the slab to the NHWC tensor, clipping the dropped columns, the
-// rows past the image and the channels past the layer's extent.
+// rows past the image and the channels past the layer's extent.  A tile is two store blocks of Rb image rows; the
+// pitch PW is padded until a block has a multiple of 8 positions, which makes the swizzled chunk offsets of a
+// thread's channel constants; each block has its own pair of slabs; eight epilogue warps (two per TMEM lane quarter,
+// alternate column groups) share the conversion.
 //
 // conv_tc() routes a forward / data-gradient call here when the geometry wastes little (see
 // geeps_conv_halo_applicable); GEEPS_HALO_CONV=0 keeps every call on the box kernel.  Bounded waits and TMEM
