@@ -454,6 +454,23 @@ int geeps_conv_halo_applicable(const GeepsConvTcParams* p) {
   return d.taps >= 25 || (d.n_valid >= 64 && (d.n_valid <= 128 || chn >= 0.85)) ? 1 : 0;
 }
 
+int geeps_conv_halo_plan(const GeepsConvTcParams* p, GeepsHaloPlanInfo* out) {
+  memset(out, 0, sizeof(*out));
+  if (!geeps_conv_tc_supported(p)) return 0;
+  const HaloPlan hp = plan_halo(p);
+  if (!hp.ok) return 0;
+  const HaloDev& d = hp.d;
+  out->ok = 1;
+  out->routed = geeps_conv_halo_applicable(p);
+  out->PW = d.PW; out->R = d.Rb; out->row_tiles = d.row_tiles; out->m_tiles = d.m_tiles;
+  out->positions = d.split; out->ncols2 = d.ncols2; out->ncols1 = d.ncols1;
+  out->stages_x = d.stages_x; out->stages_w = d.stages_w; out->x_stage_bytes = d.x_stage_bytes;
+  out->tmem_cols = 2 * ACC_COLS;
+  out->smem_bytes = (long long)hp.smem;
+  out->util = hp.util;
+  return 1;
+}
+
 int geeps_conv_halo(const GeepsConvTcParams* p, void* stream) {
   if (!geeps_conv_tc_supported(p)) return (int)cudaErrorInvalidValue;
   HaloPlan hp = plan_halo(p);

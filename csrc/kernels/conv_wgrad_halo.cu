@@ -346,6 +346,24 @@ int geeps_conv_wgrad_halo_applicable(const GeepsConvTcParams* p) {
   return p->KW >= 5 || (p->KW >= 3 && wp.d.m_tiles == 1 && wp.d.cchunks == 1) ? 1 : 0;
 }
 
+int geeps_conv_wgrad_halo_plan(const GeepsConvTcParams* p, GeepsHaloPlanInfo* out) {
+  memset(out, 0, sizeof(*out));
+  if (!geeps_conv_tc_supported(p)) return 0;
+  const WgPlan wp = plan_wgrad(p);
+  if (!wp.ok) return 0;
+  const WgDev& d = wp.d;
+  out->ok = 1;
+  out->routed = geeps_conv_wgrad_halo_applicable(p);
+  out->PW = d.PW; out->R = d.R; out->row_tiles = d.row_tiles; out->m_tiles = d.m_tiles;
+  out->positions = d.kpos;
+  out->TY = d.TY; out->passes = d.passes; out->split = d.split; out->n_blocks = d.n_blocks;
+  out->stages_x = d.stages; out->stages_w = d.stages; out->x_stage_bytes = d.x_bytes;
+  out->tmem_cols = d.tmem_cols;
+  out->smem_bytes = (long long)wp.smem;
+  out->util = wp.util;
+  return 1;
+}
+
 int geeps_conv_wgrad_halo(const GeepsConvTcParams* p, void* stream) {
   if (!geeps_conv_tc_supported(p)) return (int)cudaErrorInvalidValue;
   WgPlan wp = plan_wgrad(p);

@@ -170,6 +170,19 @@ int geeps_conv_halo(const GeepsConvTcParams* p, void* stream);
 // Weight gradient with the taps of a filter row served by one activation tile (conv_wgrad_halo.cu); same routing.
 int geeps_conv_wgrad_halo_applicable(const GeepsConvTcParams* p);
 int geeps_conv_wgrad_halo(const GeepsConvTcParams* p, void* stream);
+// The geometry the two halo kernels would use for a call (host arithmetic only; for tests and tuning).  `ok` = 0 when
+// the kernel does not accept the call.
+typedef struct GeepsHaloPlanInfo {
+  int ok, routed;                       // accepted; geeps_conv_tc() would route the call to this kernel
+  int PW, R, row_tiles, m_tiles;        // flat pitch, image rows per block, row tiles per image, channel blocks
+  int positions, ncols2, ncols1;        // positions per block; MMA N of a two-block / one-block tile (forward, dgrad)
+  int TY, passes, split, n_blocks;      // weight gradient: filter rows per item, passes, position slices, blocks
+  int stages_x, stages_w, x_stage_bytes, tmem_cols;
+  long long smem_bytes;
+  double util;
+} GeepsHaloPlanInfo;
+int geeps_conv_halo_plan(const GeepsConvTcParams* p, GeepsHaloPlanInfo* out);
+int geeps_conv_wgrad_halo_plan(const GeepsConvTcParams* p, GeepsHaloPlanInfo* out);
 
 // ---------------- parameter pull fused with the consuming GEMM ----------------
 // Y[M,N] = X[M,K] * W[N,K]^T + bias (+ReLU), M <= 256, K a multiple of 64.  W's rows live on the server

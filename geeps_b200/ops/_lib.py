@@ -36,6 +36,17 @@ class ConvTcParams(C.Structure):
     ]
 
 
+class HaloPlanInfo(C.Structure):
+    _fields_ = [
+        ("ok", C.c_int), ("routed", C.c_int),
+        ("PW", C.c_int), ("R", C.c_int), ("row_tiles", C.c_int), ("m_tiles", C.c_int),
+        ("positions", C.c_int), ("ncols2", C.c_int), ("ncols1", C.c_int),
+        ("TY", C.c_int), ("passes", C.c_int), ("split", C.c_int), ("n_blocks", C.c_int),
+        ("stages_x", C.c_int), ("stages_w", C.c_int), ("x_stage_bytes", C.c_int), ("tmem_cols", C.c_int),
+        ("smem_bytes", C.c_longlong), ("util", C.c_double),
+    ]
+
+
 class PushApplyParams(C.Structure):
     _fields_ = [
         ("upd", C.c_void_p * MAX_RANKS), ("cache", C.c_void_p * MAX_RANKS),
