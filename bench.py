@@ -15,7 +15,9 @@ Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over 
 resident on the device; `e2e` runs the same public API call with a host->device copy of the step's batch
 from pinned memory and a device->host read of the loss in every step.  The synthetic batches are N(0,1)
 values stored as bf16 by default (79 MB per step; the input layer rounds to bf16 NHWC either way);
-`e2e_fp32_input` is the same end-to-end run with fp32 batches on the host (158 MB per step).  `diag`
+`e2e_fp32_input` is the same end-to-end run with fp32 batches on the host (158 MB per step), and
+`e2e_uint8_input` the one with 8-bit pixels on the host (40 MB per step; the values quantised to steps of
+1/40, mean-subtracted and scaled by the input layer on the device, as a pipeline fed by image files does).  `diag`
 gives the host time to enqueue a step and the host-to-device copy bandwidth per GPU with all ranks
 copying at once.
 """
@@ -36,6 +38,7 @@ MODEL = "alexnet"
 BATCH_PER_GPU = 256
 IMAGE = (3, 227, 227)
 CLASSES = 1000
+U8_MEAN, U8_STEPS = 128.0, 40.0      # uint8 input batches: pixel = round(U8_STEPS * z + U8_MEAN), z ~ N(0, 1)
 
 
 class ClockSampler:
@@ -60,6 +63,13 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.samples.append((time.time(), line.strip()))
+
+    def wait_first_sample(self, limit_s: float = 8.0) -> None:
+        """Block until nvidia-smi has printed its first line (its start can take over a second on a fresh machine,
+        longer than a short timed region) or the limit has passed."""
+        t_end = time.time() + limit_s
+        while self.proc is not None and not self.samples and self.proc.poll() is None and time.time() < t_end:
+            time.sleep(0.02)
 
     def mark_begin(self):
         self.t_begin = time.time()
@@ -121,9 +131,11 @@ def main() -> None:
     ap.add_argument("--cache-frac", type=float, default=None,
                     help="manage activations through the PS memory plan and cap the GPU budget at this fraction of the working set")
     ap.add_argument("--slack", type=int, default=0)
-    ap.add_argument("--input-dtype", default="bf16", choices=["fp32", "bf16"],
+    ap.add_argument("--input-dtype", default="bf16", choices=["fp32", "bf16", "uint8"],
                     help="dtype of the synthetic input batches on the host and on the device; the input layer rounds "
-                         "either to bf16 NHWC, so the results are identical and bf16 halves the host-to-device bytes")
+                         "fp32 and bf16 to bf16 NHWC, so the results are identical and bf16 halves the host-to-device "
+                         "bytes; uint8 = 8-bit pixels (the N(0,1) values quantised to steps of 1/40 around 128) that "
+                         "the input layer mean-subtracts and scales on the device")
     ap.add_argument("--fp32-weight-cache", action="store_true",
                     help="also refresh the workers' fp32 copies of the weights every clock (the layers read bf16 only)")
     ap.add_argument("--no-tape", action="store_true",
@@ -188,10 +200,18 @@ def main() -> None:
                        use_graph=not (args.no_graph or args.no_tape) and args.transport == "nvlink",
                        pull_fc=args.pull_fc, uncached=tuple(n for n in args.uncached.split(",") if n))
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
-        in_dtype = torch.bfloat16 if args.input_dtype == "bf16" else torch.float32
-        x_dev = torch.randn((B,) + image, device=dev, generator=gen).to(in_dtype)
+        in_dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "uint8": torch.uint8}[args.input_dtype]
+        # uint8 batches: pixel = round(40 z + 128) clipped to a byte, read back as (pixel - 128) / 40 by the input layer
+        mod.net.input_layer.set_transform((U8_MEAN,) * 3, 1.0 / U8_STEPS)
+
+        def synth(shape, dtype, **kw):
+            z = torch.randn(shape, **kw)
+            if dtype == torch.uint8:
+                return (z * U8_STEPS + U8_MEAN).round_().clamp_(0, 255).to(torch.uint8)
+            return z.to(dtype)
+        x_dev = synth((B,) + image, in_dtype, device=dev, generator=gen)
         y_dev = torch.randint(0, classes, (B,), device=dev, generator=gen)
-        x_host = torch.randn((B,) + image).to(in_dtype).pin_memory()
+        x_host = synth((B,) + image, in_dtype).pin_memory()
         y_host = torch.randint(0, classes, (B,)).pin_memory()
 
         def barrier():
@@ -212,6 +232,8 @@ def main() -> None:
             the launches of one block and the last loss."""
             sampler = ClockSampler(local_rank)
             sampler.start()
+            sampler.wait_first_sample()
+            barrier()                # the ranks leave the wait together
             for _ in range(3):       # keeps the GPU under load while nvidia-smi starts sampling (untimed)
                 step_fn()
             barrier()
@@ -292,7 +314,7 @@ def main() -> None:
             step_device()
         host_enqueue_ms = max_over_ranks((time.perf_counter() - t0) / 5 * 1e3)
         barrier()
-        e2e = e2e_other = diag = None
+        e2e = e2e_other = e2e_u8 = diag = None
         if not args.no_e2e:
             feeder = HostFeeder((B,) + image, (B,), dev, x_dtype=in_dtype, timed=True)
             e2e = e2e_record(make_e2e(feeder, x_host), feeder)
@@ -315,9 +337,19 @@ def main() -> None:
                 # input layer rounds it to bf16 either way, so a host pipeline may as well ship bf16)
                 other = torch.float32 if in_dtype == torch.bfloat16 else torch.bfloat16
                 feeder2 = HostFeeder((B,) + image, (B,), dev, x_dtype=other, timed=True)
-                x_host2 = x_host.to(other).pin_memory()
+                x_host2 = synth((B,) + image, other).pin_memory()
                 e2e_other = e2e_record(make_e2e(feeder2, x_host2), feeder2)
                 e2e_other["input_dtype"] = "fp32" if other == torch.float32 else "bf16"
+                del feeder2, x_host2
+                if in_dtype != torch.uint8:
+                    # and with 8-bit pixels on the host (a quarter of the fp32 bytes), transformed by the input layer
+                    try:
+                        feeder3 = HostFeeder((B,) + image, (B,), dev, x_dtype=torch.uint8, timed=True)
+                        x_host3 = synth((B,) + image, torch.uint8).pin_memory()
+                        e2e_u8 = e2e_record(make_e2e(feeder3, x_host3), feeder3)
+                        e2e_u8["input_dtype"] = "uint8"
+                    except Exception as e:      # the headline line is printed whatever happens to this extra run
+                        e2e_u8 = {"error": f"{type(e).__name__}: {e}"[:300]}
             e2e["input_dtype"] = args.input_dtype
         stats = mod.ps.get_stats()
         # kernels launched inside the runtime (flag signal + flag wait + push/apply per table per clock,
@@ -340,7 +372,7 @@ def main() -> None:
                            "host_replay_tapes": len(mod._tapes), "step_graphs": len(mod._graphs),
                            "graph_nodes": max([g.nodes for g in mod._graphs.values()] + [0]),
                            "tables": "fp32 master rows, momentum SGD on the owning shard",
-                           "l2": "no explicit flush: per step the input batch (79 MB bf16 / 158 MB fp32), the activations "
+                           "l2": "no explicit flush: per step the input batch (79 MB bf16 / 158 MB fp32 / 40 MB uint8), the activations "
                                  "(conv1 output alone 148 MB) and 122 MB of bf16 weights exceed the 126 MB L2"},
                 "memory_plan": ({"cache_fraction_of_activations": args.cache_frac, "budget_rows": mod.budget_rows,
                                  "working_set_rows": mod.working_set_rows, "managed_activation_rows": mod.managed_rows,
@@ -352,6 +384,7 @@ def main() -> None:
                                 if args.cache_frac is not None else None),
                 "clocks": clocks, "e2e": e2e,
                 ("e2e_fp32_input" if e2e_other and e2e_other.get("input_dtype") == "fp32" else "e2e_other_input"): e2e_other,
+                "e2e_uint8_input": e2e_u8,
                 "diag": diag,
                 "ps": {"device_push_ms_per_step": stats["bgthread"]["device_push_ms"] / max(1, stats["bgthread"]["device_push_samples"]) * len(mod.tables),
                        "device_push_gb_per_s": stats["bgthread"]["device_push_gb_per_s"],

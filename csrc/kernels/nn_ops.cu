@@ -808,6 +808,94 @@ nchw_to_s2d_generic_kernel(const T* __restrict__ x, bf16* __restrict__ y, int B,
   }
 }
 
+// ---- data transformer: uint8 NCHW source images -> cropped / mirrored / mean-subtracted / scaled bf16 activations ----
+// The work of Caffe's DataTransformer (crop_size, mirror, mean_value, scale), done on the device so that the host ships
+// one byte per value.  aug (NULL: centre crop, no mirror) holds {h_off, w_off, mirror} per image.
+struct XformDev {
+  const uint8_t* x;
+  const int* aug;
+  int Hin, Win;          // source image
+  int H, W;              // cropped image (what the network sees)
+  int h_off, w_off;      // centre crop, used when aug == NULL
+  float mean[4], scale;
+};
+
+__device__ __forceinline__ void xform_image(const XformDev& t, long long b, int& h_off, int& w_off, int& mirror) {
+  if (t.aug != nullptr) {
+    // out-of-range offsets are clamped: a bad entry reads a valid window instead of another image
+    h_off = min(max(t.aug[b * 3 + 0], 0), t.Hin - t.H);
+    w_off = min(max(t.aug[b * 3 + 1], 0), t.Win - t.W);
+    mirror = t.aug[b * 3 + 2] != 0;
+  } else {
+    h_off = t.h_off; w_off = t.w_off; mirror = 0;
+  }
+}
+
+// S = 4, C = 3 with the tile scheme of nchw_to_s2d43_tile_kernel: warp dy reads, for each colour, the 128 consecutive
+// source bytes that 32 output pixels cover (reversed when the image is mirrored, still one contiguous run per load)
+__global__ void __launch_bounds__(128)
+u8_xform_s2d43_tile_kernel(XformDev t, bf16* __restrict__ y, int Hs, int Ws, int Cpad, int segs) {
+  constexpr int S = 4, C = 3, PIX = 32, PITCH = 72;
+  __shared__ __align__(16) bf16 tile[PIX * PITCH];
+  const int lane = threadIdx.x & 31, dy = threadIdx.x >> 5;
+  long long blk = blockIdx.x;
+  const int seg = (int)(blk % segs); blk /= segs;
+  const int hs = (int)(blk % Hs);
+  const long long b = blk / Hs;
+  const int ws0 = seg * PIX;
+  int h_off, w_off, mirror;
+  xform_image(t, b, h_off, w_off, mirror);
+  for (int j = S * S * C + dy * 4; j < Cpad && j < S * S * C + dy * 4 + 4; ++j) tile[lane * PITCH + j] = __float2bfloat16(0.f);
+  const int h = hs * S + dy;
+  const int wbase = ws0 * S;
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const uint8_t* row = t.x + ((b * C + c) * t.Hin + (h + h_off)) * (long long)t.Win + w_off;
+#pragma unroll
+    for (int i = 0; i < S; ++i) {
+      const int e = i * 32 + lane;
+      const int w = wbase + e;
+      float v = 0.f;
+      if (h < t.H && w < t.W) v = ((float)__ldg(row + (mirror ? t.W - 1 - w : w)) - t.mean[c]) * t.scale;
+      tile[(e >> 2) * PITCH + (dy * S + (e & 3)) * C + c] = __float2bfloat16(v);
+    }
+  }
+  __syncthreads();
+  const int per_pix = Cpad >> 3;
+  const int npix = min(PIX, Ws - ws0);
+  bf16* dst = y + ((b * Hs + hs) * (long long)Ws + ws0) * Cpad;
+  for (int i = threadIdx.x; i < npix * per_pix; i += blockDim.x) {
+    const int px = i / per_pix, piece = i - px * per_pix;
+    *reinterpret_cast<uint4*>(dst + (long long)i * 8) = *reinterpret_cast<const uint4*>(tile + px * PITCH + piece * 8);
+  }
+}
+
+// any S >= 1 (S = 1: plain NHWC) and C <= 4: one thread per output element
+__global__ void __launch_bounds__(256)
+u8_xform_generic_kernel(XformDev t, bf16* __restrict__ y, int B, int C, int S, int Hs, int Ws, int Cpad) {
+  const long long total = (long long)B * Hs * Ws * Cpad;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int j = (int)(i % Cpad);
+    long long r = i / Cpad;
+    const int ws = (int)(r % Ws); r /= Ws;
+    const int hs = (int)(r % Hs);
+    const long long b = r / Hs;
+    float v = 0.f;
+    if (j < S * S * C) {
+      const int c = j % C, q = j / C, dx = q % S, dy = q / S;
+      const int h = hs * S + dy, w = ws * S + dx;
+      if (h < t.H && w < t.W) {
+        int h_off, w_off, mirror;
+        xform_image(t, b, h_off, w_off, mirror);
+        const uint8_t* row = t.x + ((b * C + c) * t.Hin + (h + h_off)) * (long long)t.Win + w_off;
+        v = ((float)__ldg(row + (mirror ? t.W - 1 - w : w)) - t.mean[c]) * t.scale;
+      }
+    }
+    y[i] = __float2bfloat16(v);
+  }
+}
+
 // g[r][c] = 0 where mask[c] == 0
 __global__ void __launch_bounds__(256)
 col_mask_kernel(float* __restrict__ g, const uint8_t* __restrict__ mask, long long rows, int cols, long long ld) {
@@ -1173,6 +1261,32 @@ int geeps_nchw_to_s2d_bf16(const void* x, int x_is_bf16, void* y, int B, int C, 
   cudaStream_t st = (cudaStream_t)stream;
   return x_is_bf16 ? nchw_to_s2d_launch((const bf16*)x, y, B, C, H, W, S, Hs, Ws, Cpad, st)
                    : nchw_to_s2d_launch((const float*)x, y, B, C, H, W, S, Hs, Ws, Cpad, st);
+}
+
+int geeps_u8_transform_bf16(const GeepsU8Transform* p, void* stream) {
+  if (p == nullptr || p->x == nullptr || p->y == nullptr) return (int)cudaErrorInvalidValue;
+  const int S = p->S < 1 ? 1 : p->S;
+  if (p->C < 1 || p->C > 4 || p->B < 1 || p->H < 1 || p->W < 1 || p->Hin < p->H || p->Win < p->W ||
+      p->Cpad < S * S * p->C || p->Hs < 1 || p->Ws < 1)
+    return (int)cudaErrorInvalidValue;
+  // every source element an output position can name lies inside the cropped image
+  if ((long long)(p->Hs - 1) * S >= p->H || (long long)(p->Ws - 1) * S >= p->W) return (int)cudaErrorInvalidValue;
+  XformDev t;
+  t.x = p->x; t.aug = p->aug;
+  t.Hin = p->Hin; t.Win = p->Win; t.H = p->H; t.W = p->W;
+  t.h_off = (p->Hin - p->H) / 2; t.w_off = (p->Win - p->W) / 2;
+  for (int c = 0; c < 4; ++c) t.mean[c] = p->mean[c];
+  t.scale = p->scale;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (S == 4 && p->C == 3 && p->Cpad % 8 == 0 && p->Cpad >= 48 && p->Cpad <= 64 && (((uintptr_t)p->y) & 15) == 0) {
+    const int segs = (p->Ws + 31) / 32;
+    u8_xform_s2d43_tile_kernel<<<(unsigned)((long long)p->B * p->Hs * segs), 128, 0, st>>>(t, (bf16*)p->y, p->Hs, p->Ws,
+                                                                                          p->Cpad, segs);
+  } else {
+    u8_xform_generic_kernel<<<grid_1d((long long)p->B * p->Hs * p->Ws * p->Cpad), 256, 0, st>>>(t, (bf16*)p->y, p->B, p->C,
+                                                                                              S, p->Hs, p->Ws, p->Cpad);
+  }
+  return CK();
 }
 
 int geeps_col_mask_f32(float* g, const unsigned char* mask, long long rows, int cols, long long ld, void* stream) {

@@ -25,6 +25,19 @@ int geeps_nchw_to_nhwc_bf16(const void* x, int x_is_bf16, void* y, int B, int C,
 // NCHW (fp32 or bf16) -> space-to-depth NHWC bf16 [B][Hs][Ws][Cpad], channel (dy*S + dx)*C + c, zero-padded
 int geeps_nchw_to_s2d_bf16(const void* x, int x_is_bf16, void* y, int B, int C, int H, int W, int S, int Hs, int Ws,
                            int Cpad, void* stream);
+// Data transformer: uint8 NCHW source images [B][C][Hin][Win] -> bf16 activations of the H x W crop, as NHWC
+// [B][Hs = H][Ws = W][Cpad] (S <= 1) or in the space-to-depth layout [B][Hs][Ws][Cpad] (S > 1); every value becomes
+// (pixel - mean[c]) * scale, channels past S*S*C and positions past the crop are zero.  aug: NULL (centre crop, no
+// mirror) or 3 ints per image on the device: {h_off, w_off, mirror}.  C <= 4.
+typedef struct GeepsU8Transform {
+  const unsigned char* x;
+  void* y;
+  const int* aug;
+  int B, C, Hin, Win, H, W, S, Hs, Ws, Cpad;
+  float mean[4];
+  float scale;
+} GeepsU8Transform;
+int geeps_u8_transform_bf16(const GeepsU8Transform* p, void* stream);
 // g[r][c] = 0 where mask[c] == 0 (fp32 matrix, pitch ld)
 int geeps_col_mask_f32(float* g, const unsigned char* mask, long long rows, int cols, long long ld, void* stream);
 int geeps_im2col(const void* x, void* col, const GeepsConvGeom* g, void* stream);

@@ -116,6 +116,12 @@ class PoolGeom(C.Structure):
                 ("B", "H", "W", "C", "K", "stride", "pad", "OH", "OW", "ldx", "ldy")]
 
 
+class U8Transform(C.Structure):
+    """Mirror of GeepsU8Transform (csrc/kernels/nn_ops.h)."""
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("aug", C.c_void_p)] + [(n, C.c_int) for n in
+                ("B", "C", "Hin", "Win", "H", "W", "S", "Hs", "Ws", "Cpad")] + [("mean", C.c_float * 4), ("scale", C.c_float)]
+
+
 _lib = None
 _launches = 0
 

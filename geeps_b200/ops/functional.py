@@ -150,6 +150,28 @@ def nchw_to_s2d_bf16(x: torch.Tensor, y: torch.Tensor, S: int) -> torch.Tensor:
     return y
 
 
+def u8_transform(x: torch.Tensor, y: torch.Tensor, crop, S: int = 0, aug: torch.Tensor | None = None,
+                 mean=(0.0, 0.0, 0.0, 0.0), scale: float = 1.0) -> torch.Tensor:
+    """Data transformer on the device: uint8 NCHW source images -> bf16 activations of the crop = (H, W) window, as
+    NHWC (S <= 1, y [B, H, W, cpad]) or space-to-depth (y [B, Hs, Ws, cpad]); value = (pixel - mean[c]) * scale.
+    aug: None (centre crop, no mirror) or int32 [B, 3] on the device: h_off, w_off, mirror per image."""
+    L.require_cuda()
+    B, Cc, Hin, Win = x.shape
+    H, W = crop
+    _, Hs, Ws, cpad = y.shape
+    assert x.dtype == torch.uint8 and y.dtype == bf16 and x.is_contiguous() and y.is_contiguous()
+    assert aug is None or (aug.dtype == torch.int32 and aug.is_contiguous() and aug.numel() == 3 * B and aug.is_cuda)
+    p = L.U8Transform()
+    p.x, p.y, p.aug = x.data_ptr(), y.data_ptr(), (aug.data_ptr() if aug is not None else None)
+    p.B, p.C, p.Hin, p.Win, p.H, p.W, p.S, p.Hs, p.Ws, p.Cpad = B, Cc, Hin, Win, H, W, S, Hs, Ws, cpad
+    m = list(mean) + [0.0] * 4
+    for c in range(4):
+        p.mean[c] = float(m[c])
+    p.scale = float(scale)
+    launch(lib().geeps_u8_transform_bf16, "u8_transform", C.byref(p), stream_ptr())
+    return y
+
+
 def col_mask(g: torch.Tensor, mask: torch.Tensor) -> None:
     """Zero the columns of the fp32 matrix g whose mask byte is 0."""
     assert g.dtype == torch.float32 and mask.dtype == torch.uint8 and g.stride(1) == 1

@@ -104,18 +104,25 @@ class Layer:
 
 
 class Input(Layer):
-    """fp32 NCHW batch -> NHWC bf16 (optionally zero-padding the channel count)."""
+    """NCHW batch -> NHWC bf16 (optionally zero-padding the channel count).  The batch is fp32 or bf16 (values as
+    they are), or uint8 source images that this layer crops, mirrors, mean-subtracts and scales on the device."""
 
-    def __init__(self, cpad: int | None = None, s2d: int = 0, s2d_k: int = 0):
+    def __init__(self, cpad: int | None = None, s2d: int = 0, s2d_k: int = 0, mean=(0.0, 0.0, 0.0), scale: float = 1.0):
         """s2d = S > 0: emit the space-to-depth layout [B, Hs, Ws, S*S*C] that turns the following k x k
         stride-S convolution (k = s2d_k, no padding) into a stride-1 convolution with ceil(k/S) taps.  cpad widens
         the pixel with zero channels (48 -> 64 makes every pixel one aligned 128-byte line, which the TMA loads of
-        the convolution reward: 0.26 -> 0.14 ms on the box kernel at batch 256)."""
+        the convolution reward: 0.26 -> 0.14 ms on the box kernel at batch 256).
+        mean, scale: for uint8 batches, value = (pixel - mean[channel]) * scale (Caffe's mean_value / scale)."""
         super().__init__()
         self.cpad, self.s2d, self.s2d_k = cpad, s2d, s2d_k
+        self.mean, self.scale = tuple(mean), float(scale)
+        self.aug = None            # int32 [B, 3] on the device: h_off, w_off, mirror of every image (uint8 batches)
+        self._src_hw = None        # source image size of the last uint8 batch that went through forward
+        self._centre = True        # aug holds the centre crop (no set_augmentation call in force)
 
     def setup(self, in_shape, device):
         B, C, H, W = in_shape
+        self.in_shape, self.device = tuple(in_shape), device
         if self.s2d:
             S, k = self.s2d, self.s2d_k
             taps = -(-k // S)
@@ -126,9 +133,53 @@ class Input(Layer):
             self.out_shape = (B, H, W, self.cpad or C)
         return self.out_shape
 
+    def set_transform(self, mean, scale: float) -> None:
+        """Mean per channel and scale applied to uint8 batches (takes effect on steps not yet recorded or captured)."""
+        self.mean, self.scale = tuple(mean), float(scale)
+
+    def _centre_crop(self) -> None:
+        B, _, H, W = self.in_shape
+        centre = torch.tensor([(self._src_hw[0] - H) // 2, (self._src_hw[1] - W) // 2, 0], dtype=torch.int32)
+        self.aug.copy_(centre.to(self.device).expand(B, 3))
+
+    def set_augmentation(self, aug: "torch.Tensor | None") -> None:
+        """Crop offsets and mirror flags of the next uint8 batch: int [B, 3] (h_off, w_off, mirror), host or device.
+        The values land in a buffer this layer owns (the one every uint8 step reads, recorded and captured steps
+        included).  None goes back to the centre crop without mirroring."""
+        B = self.in_shape[0]
+        self._centre = aug is None
+        if aug is None:
+            if self.aug is not None and self._src_hw is not None:
+                self._centre_crop()
+            return
+        if self.aug is None:
+            self.aug = torch.zeros(B, 3, dtype=torch.int32, device=self.device)
+        self.aug.copy_(aug.to(torch.int32).reshape(B, 3), non_blocking=True)
+
+    def randomize(self, src_hw, mirror: bool = True, generator=None) -> None:
+        """Random crop window (and mirror flag) per image for source images of size src_hw, drawn on the device."""
+        B, _, H, W = self.in_shape
+        Hin, Win = src_hw
+        dev = self.device
+        a = torch.stack([torch.randint(0, Hin - H + 1, (B,), device=dev, generator=generator),
+                         torch.randint(0, Win - W + 1, (B,), device=dev, generator=generator),
+                         torch.randint(0, 2 if mirror else 1, (B,), device=dev, generator=generator)], dim=1)
+        self.set_augmentation(a)
+
     def forward(self, x):
         if x.dtype == BF and tuple(x.shape) == tuple(self.out_shape) and x.is_contiguous():
             return x           # already in this layer's output layout (HostFeeder(layout=...) converts while it copies)
+        if x.dtype == torch.uint8:
+            B, C, H, W = self.in_shape
+            src_hw = (int(x.shape[2]), int(x.shape[3]))
+            if self.aug is None:
+                self.aug = torch.zeros(B, 3, dtype=torch.int32, device=self.device)
+            if self._centre and src_hw != self._src_hw:
+                self._src_hw = src_hw
+                self._centre_crop()
+            self._src_hw = src_hw
+            y = self.y if self.s2d else torch.empty(self.out_shape, dtype=BF, device=x.device)
+            return F.u8_transform(x, y, (H, W), self.s2d, self.aug, self.mean, self.scale)
         if self.s2d:
             return F.nchw_to_s2d_bf16(x, self.y, self.s2d)
         return F.nchw_to_nhwc_bf16(x, self.cpad)

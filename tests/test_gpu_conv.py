@@ -245,3 +245,43 @@ def test_space_to_depth_conv_matches_strided_torch_conv(cpad):
     assert _rel(gw[:, :, :k, :k], wfull.grad) < 1e-2
     # taps past the 11 x 11 filter receive no gradient, so they stay zero under SGD
     assert float(gw[:, :, k:, :].abs().max()) == 0 and float(gw[:, :, :, k:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("layout", ["s2d64", "s2d48", "nhwc8", "s2d2"])
+@pytest.mark.parametrize("mode", ["centre", "random"])
+def test_uint8_data_transformer_matches_torch(layout, mode):
+    """Input on uint8 source images: crop, mirror, mean subtraction and scale on the device give exactly what the
+    same arithmetic in torch followed by the fp32 input path gives (both round the same fp32 value to bf16)."""
+    from geeps_b200.ops.layers import Input
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev).manual_seed(11)
+    B, C, Hin, Win, H, W = 5, 3, 80, 90, 67, 71
+    mean, scale = (104.0, 117.0, 123.5), 1.0 / 57.0
+    kw = {"s2d64": dict(s2d=4, s2d_k=11, cpad=64), "s2d48": dict(s2d=4, s2d_k=11), "nhwc8": dict(cpad=8),
+          "s2d2": dict(s2d=2, s2d_k=7, cpad=16)}[layout]
+    inp, ref = Input(mean=mean, scale=scale, **kw), Input(**kw)
+    shape = inp.setup((B, C, H, W), dev)
+    assert ref.setup((B, C, H, W), dev) == shape
+    x = torch.randint(0, 256, (B, C, Hin, Win), device=dev, generator=gen, dtype=torch.uint8)
+    if mode == "random":
+        inp.randomize((Hin, Win), mirror=True, generator=gen)
+        aug = inp.aug.cpu()
+        assert int(aug[:, 2].max()) == 1 and int(aug[:, 2].min()) == 0      # both orientations are in the batch
+    else:
+        aug = torch.tensor([[(Hin - H) // 2, (Win - W) // 2, 0]] * B)
+    y = inp.forward(x).clone()
+    m = torch.tensor(mean, device=dev).view(1, C, 1, 1)
+    rows = []
+    for b in range(B):
+        ho, wo, mir = (int(v) for v in aug[b])
+        win = x[b:b + 1, :, ho:ho + H, wo:wo + W].float()
+        rows.append(win.flip(-1) if mir else win)
+    xr = (torch.cat(rows) - m) * scale
+    yr = ref.forward(xr.contiguous())
+    assert y.shape == yr.shape == shape
+    assert torch.equal(y, yr)
+    if mode == "random":
+        inp.set_augmentation(None)          # back to the centre crop, through the same buffer
+        y2 = inp.forward(x)
+        xc = (x[:, :, (Hin - H) // 2:(Hin - H) // 2 + H, (Win - W) // 2:(Win - W) // 2 + W].float() - m) * scale
+        assert torch.equal(y2, ref.forward(xc.contiguous()))
