@@ -220,6 +220,52 @@ def test_graph_replay_alexnet_with_dropout_trains():
         mod.close()
 
 
+def test_uint8_batches_with_augmentation_train_like_float_batches_under_graph_replay():
+    """8-bit source images, cropped / mirrored / normalised by the input layer with a new augmentation every step: the
+    captured step reads the augmentation from the layer's buffer, so replayed steps follow it and the losses equal
+    those of a module fed the same crops as float batches through the layer code."""
+    dev = torch.device("cuda:0")
+    B, Hin, Win, H, W, steps = 32, 20, 22, 16, 16, 12
+    mean, scale = (120.0, 128.0, 131.0), 1.0 / 64.0
+    gen = torch.Generator(device=dev).manual_seed(7)
+    x8 = torch.randint(0, 256, (B, 3, Hin, Win), device=dev, generator=gen, dtype=torch.uint8)
+    y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+    augs = [torch.stack([torch.randint(0, Hin - H + 1, (B,), generator=gen, device=dev),
+                         torch.randint(0, Win - W + 1, (B,), generator=gen, device=dev),
+                         torch.randint(0, 2, (B,), generator=gen, device=dev)], dim=1) for _ in range(steps)]
+    m = torch.tensor(mean, device=dev).view(1, 3, 1, 1)
+
+    def as_float(aug):
+        rows = []
+        for b in range(B):
+            ho, wo, mir = (int(v) for v in aug[b])
+            win = x8[b:b + 1, :, ho:ho + H, wo:wo + W].float()
+            rows.append(win.flip(-1) if mir else win)
+        return ((torch.cat(rows) - m) * scale).contiguous()
+
+    losses = {}
+    for u8 in (False, True):
+        with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+            mod = PSModule(tiny_net(), (B, 3, H, W), cfg(TRANSPORT_NVLINK, learning_rate=0.05), device=dev, seed=3,
+                           use_graph=u8)
+            inp = mod.net.input_layer
+            inp.set_transform(mean, scale)
+            out = []
+            for aug in augs:
+                if u8:
+                    inp.set_augmentation(aug)
+                    out.append(mod.step(x8, y).item())
+                else:
+                    out.append(mod.step(as_float(aug), y).item())
+            if u8:
+                assert len(mod._graphs) >= 1 and mod.ps.get_stats()["client"]["nr_replayed_clocks"] > 0
+            assert mod.ps.last_error() == 0
+            losses[u8] = out
+            mod.close()
+    assert losses[True] == pytest.approx(losses[False], rel=2e-3), losses
+    assert len(set(round(v, 5) for v in losses[True])) > steps // 2          # the batches did differ from step to step
+
+
 @pytest.mark.parametrize("mode", ["pull_fc", "uncached"])
 def test_uncached_tables_train_like_published_ones(mode):
     """Tables the shards do not publish: (pull_fc) the fully-connected layers pull their weight rows from the shards
