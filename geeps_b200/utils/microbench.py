@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: python -m geeps_b200.utils.microbench [gemm|conv|lrn_pool|rows|all]
+"""Kernel micro-benchmarks: python -m geeps_b200.utils.microbench [gemm|conv|lrn_pool|rows|input|all]
 
 Every number is a CUDA-event time on the launching stream after warm-up, with a buffer larger than
 L2 written between timed launches.  GEMM lines also give cuBLAS (torch.matmul) on the same shape and
@@ -179,6 +179,31 @@ def bench_conv():
                           "halo_frac_of_peak": round(flops / t_halo / 1e9 / peak, 3), "peak_source": src}), flush=True)
 
 
+def bench_input():
+    """The input layer of AlexNet at batch 256 (3 x 227 x 227 -> space-to-depth 57 x 57 x 64 bf16) from fp32, bf16 and
+    uint8 batches; the uint8 form also from 256 x 256 source images with a random crop and mirror per image."""
+    from ..ops.layers import Input
+    dev = torch.device("cuda")
+    _, hbm, src = _peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    B, H = 256, 227
+    for name, dtype, Hin in (("fp32 batch", torch.float32, H), ("bf16 batch", BF, H), ("uint8 batch", torch.uint8, H),
+                             ("uint8 256x256 source, random crop + mirror", torch.uint8, 256)):
+        inp = Input(s2d=4, s2d_k=11, cpad=64, mean=(104.0, 117.0, 123.0), scale=1.0 / 58.0)
+        out_shape = inp.setup((B, 3, H, H), dev)
+        if dtype == torch.uint8:
+            x = torch.randint(0, 256, (B, 3, Hin, Hin), device=dev, dtype=torch.uint8)
+            if Hin > H:
+                inp.randomize((Hin, Hin))
+        else:
+            x = torch.randn(B, 3, H, H, device=dev).to(dtype)
+        t = timeit(lambda: inp.forward(x), flush=flush)
+        nbytes = B * 3 * H * H * x.element_size() + 2 * out_shape[0] * out_shape[1] * out_shape[2] * out_shape[3]
+        gbs = nbytes / t / 1e6
+        print(json.dumps({"kernel": f"input layer, {name}", "ms": round(t, 4), "algorithmic_mb": round(nbytes / 1e6, 1),
+                          "gb_s": round(gbs, 1), "frac_of_hbm": round(gbs / hbm, 3), "peak_source": src}), flush=True)
+
+
 def main():
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     if what in ("conv", "all"):
@@ -189,6 +214,8 @@ def main():
         bench_gemm()
     if what in ("rows", "all"):
         bench_rows()
+    if what in ("input", "all"):
+        bench_input()
 
 
 if __name__ == "__main__":

@@ -110,3 +110,30 @@ def test_affinity_splits_a_mask_shared_by_all_gpus():
             assert got == [b]
     finally:
         os.sched_setaffinity(0, before)
+
+
+def test_input_layer_augmentation_buffer_bookkeeping():
+    """The augmentation of uint8 batches lives in one buffer the layer owns: random windows stay inside the source
+    image, explicit values land in the same storage (captured steps keep reading it), and None restores the centre
+    crop once the source size is known."""
+    import torch
+    from geeps_b200.ops.layers import Input
+    B, H, W, Hin, Win = 6, 16, 18, 24, 30
+    inp = Input(cpad=8, mean=(1.0, 2.0, 3.0), scale=0.5)
+    assert inp.setup((B, 3, H, W), "cpu") == (B, H, W, 8)
+    inp.randomize((Hin, Win), generator=torch.Generator().manual_seed(0))
+    a = inp.aug.clone()
+    assert a.shape == (B, 3) and a.dtype == torch.int32
+    assert int(a[:, 0].min()) >= 0 and int(a[:, 0].max()) <= Hin - H
+    assert int(a[:, 1].min()) >= 0 and int(a[:, 1].max()) <= Win - W
+    assert set(a[:, 2].tolist()) <= {0, 1}
+    ptr = inp.aug.data_ptr()
+    inp.set_augmentation(torch.tensor([[1, 2, 1]] * B))
+    assert inp.aug.data_ptr() == ptr and inp.aug.tolist() == [[1, 2, 1]] * B
+    inp._src_hw = (Hin, Win)                  # what a forward on a uint8 batch records
+    inp.set_augmentation(None)
+    assert inp.aug.data_ptr() == ptr and inp.aug.tolist() == [[(Hin - H) // 2, (Win - W) // 2, 0]] * B
+    inp.randomize((Hin, Win), mirror=False)
+    assert int(inp.aug[:, 2].max()) == 0
+    inp.set_transform((9.0, 8.0, 7.0), 2.0)
+    assert inp.mean == (9.0, 8.0, 7.0) and inp.scale == 2.0
