@@ -195,6 +195,12 @@ int geeps_graph_launch(void* exec, void* stream) { return (int)cudaGraphLaunch((
 void geeps_graph_destroy(void* exec) { if (exec) cudaGraphExecDestroy((cudaGraphExec_t)exec); }
 
 int geeps_current_clock(void* g) { return static_cast<GeePs*>(g)->CurrentClock(); }
+void geeps_set_hyper_params(void* g, float lr, float momentum, float weight_decay) {
+  static_cast<GeePs*>(g)->SetHyperParams(lr, momentum, weight_decay);
+}
+void geeps_get_hyper_params(void* g, float* out3) {
+  static_cast<GeePs*>(g)->GetHyperParams(out3, out3 + 1, out3 + 2);
+}
 int geeps_last_error(void* g) { return static_cast<GeePs*>(g)->LastError(); }
 int geeps_last_error_string(void* g, char* buf, int cap) { return copy_out(static_cast<GeePs*>(g)->LastErrorString(), buf, cap); }
 int geeps_get_stats(void* g, char* buf, int cap) { return copy_out(static_cast<GeePs*>(g)->GetStats(), buf, cap); }

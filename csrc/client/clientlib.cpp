@@ -78,6 +78,7 @@ ClientLib::ClientLib(uint process_id, const GeePsConfig& config) : process_id_(p
   pc.partition_align = config.table_partition_align;
   for (int v : config.table_pull) pc.pull_tables.push_back(nvlink_ && v ? 1 : 0);
   compiler_.reset(new PlanCompiler(pc));
+  hyper_.reset(new HyperSchedule(config.learning_rate, config.momentum, config.weight_decay));
   last_heartbeat_.assign(num_processes_, now_seconds());
   peer_clock_.assign(num_processes_, 0);
   peer_dead_.assign(num_processes_, 0);
@@ -109,6 +110,14 @@ void ClientLib::set_error(int code, const std::string& what) {
   global_cv_.notify_all();
 }
 
+// Takes effect for the updates of the iteration in progress (pushed by its Clock call under the number clock_) and
+// all later ones.  The TCP shard of this process applies an update of clock c only after this worker's own push of
+// clock c, which comes after this call, so the shard always finds the entry; the NVLINK push reads it when it
+// launches.  Steps captured in a CUDA graph carry the values of the time of capture: capture again after a change.
+void ClientLib::set_hyper_params(float lr, float momentum, float weight_decay) {
+  hyper_->set(clock_, lr, momentum, weight_decay);
+}
+
 std::string ClientLib::last_error_string() {
   std::lock_guard<std::mutex> lk(error_mu_);
   return error_text_;
@@ -121,6 +130,7 @@ bool ClientLib::open_channel(uint c, std::unique_ptr<ServerThreadEntry>* server,
                              std::string* err) {
   const uint nch = config_.num_comm_channels ? config_.num_comm_channels : 1;
   server->reset(new ServerThreadEntry(c, nch, process_id_, num_processes_, config_));
+  (*server)->hyper_schedule = hyper_;
   ClientLib* self = this;
   if (c == 0) {
     (*server)->control_hook = [self](const std::string& src, Message& msg) {

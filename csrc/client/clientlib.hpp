@@ -190,6 +190,10 @@ class ClientLib {
   bool load_snapshot(const std::string& dir);
   std::string plan_json() const { return plan_.to_json(); }
   iter_t current_clock() const { return clock_; }
+  // Learning rate, momentum and weight decay of the shard-side optimizer for the updates of the current iteration
+  // and all later ones.  Every worker makes the same call in the same iteration.
+  void set_hyper_params(float lr, float momentum, float weight_decay);
+  HyperSchedule::Entry hyper_params() const { return hyper_->at(clock_); }
   int last_error() const { return error_code_.load(); }
   std::string last_error_string();
   const Plan& plan() const { return plan_; }
@@ -284,6 +288,7 @@ class ClientLib {
   void* last_app_stream_ = nullptr;      // stream of the application's latest access call
   bool bootstrap_init_pushed_ = false;   // clock 0 was signalled before StartIterations: its updates are initial values
   iter_t clock_ = kInitialClock;
+  std::shared_ptr<HyperSchedule> hyper_;
   int last_handle_ = -1;
 
   // storage

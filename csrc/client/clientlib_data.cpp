@@ -108,7 +108,7 @@ FlatOps* ClientLib::create_oplog_entry(CachedTable& ct, ParamCache& pc, MemType,
 // the shard had not yet seen are re-applied the same way.
 float ClientLib::rmw_alpha_for(const CachedTable& ct, iter_t clock) const {
   const bool is_init = !started_ && clock == kInitialClock;
-  if (ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM && !is_init) return -config_.learning_rate * config_.grad_scale;
+  if (ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM && !is_init) return -hyper_->at(clock).lr * config_.grad_scale;
   return 1.f;
 }
 

@@ -399,9 +399,10 @@ void ClientLib::fabric_push(iter_t clock, uint table_id, bool is_init, void* str
   p.clock_ref = clock_ref();
   p.mode = is_init ? GEEPS_TABLE_ADDITIVE : ct.mode;
   p.publish = 1;
-  p.lr = config_.learning_rate;
-  p.momentum_coef = config_.momentum;
-  p.weight_decay = config_.weight_decay;
+  const HyperSchedule::Entry hyper = hyper_->at(clock);      // the values in force for the updates of this clock
+  p.lr = hyper.lr;
+  p.momentum_coef = hyper.momentum;
+  p.weight_decay = hyper.weight_decay;
   p.grad_scale = config_.grad_scale;
   p.fp32_from_row = (!is_init && config_.bf16_compute_cache && table_id < config_.table_fp32_from_row.size())
                         ? (long long)config_.table_fp32_from_row[table_id] : 0;
@@ -462,7 +463,7 @@ void ClientLib::fabric_read_rmw(const OpInfo& op, RowData* dst, void* stream) {
   p.clock = stamp_arg(clock_);
   p.clock_ref = clock_ref();
   p.additive_below_clock = bootstrap_init_pushed_ ? (int)kInitialClock + 1 : 0;
-  p.alpha = ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM ? -config_.learning_rate * config_.grad_scale : 1.f;
+  p.alpha = ct.mode == GeePsConfig::TABLE_SGD_MOMENTUM ? -hyper_->at(clock_).lr * config_.grad_scale : 1.f;
   geeps_row_gather_rmw(&p, stream);
   bg_stats_.nr_rmw_replay++;
 }

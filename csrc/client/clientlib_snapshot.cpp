@@ -71,10 +71,11 @@ bool ClientLib::save_snapshot(const std::string& dir) {
   ::mkdir(sdir.c_str(), 0777);
   bool ok = true;
   std::ostringstream man;
+  const HyperSchedule::Entry hyper = hyper_->at(clock_);
   man << "{\"clock\":" << clock_ << ",\"world_size\":" << num_processes_ << ",\"shard\":" << process_id_
       << ",\"partitioner\":" << config_.partitioner << ",\"num_tables\":" << config_.num_tables
-      << ",\"row_floats\":128,\"dtype\":\"fp32\",\"learning_rate\":" << config_.learning_rate
-      << ",\"momentum\":" << config_.momentum << ",\"weight_decay\":" << config_.weight_decay << ",\"tables\":[";
+      << ",\"row_floats\":128,\"dtype\":\"fp32\",\"learning_rate\":" << hyper.lr
+      << ",\"momentum\":" << hyper.momentum << ",\"weight_decay\":" << hyper.weight_decay << ",\"tables\":[";
   bool first = true;
   for (auto& kv : tables_) {
     CachedTable& ct = *kv.second;

@@ -52,3 +52,12 @@ bool GeePs::EnableDeviceClock() { return impl_->enable_device_clock(); }
 void GeePs::AdvanceReplayedClock() { impl_->advance_replayed_iteration(); }
 const int* GeePs::DeviceClockPtr() const { return impl_->device_clock_ptr(); }
 iter_t GeePs::CurrentClock() const { return impl_->current_clock(); }
+void GeePs::SetHyperParams(float learning_rate, float momentum, float weight_decay) {
+  impl_->set_hyper_params(learning_rate, momentum, weight_decay);
+}
+void GeePs::GetHyperParams(float* learning_rate, float* momentum, float* weight_decay) const {
+  const geeps_b200::HyperSchedule::Entry h = impl_->hyper_params();
+  if (learning_rate) *learning_rate = h.lr;
+  if (momentum) *momentum = h.momentum;
+  if (weight_decay) *weight_decay = h.weight_decay;
+}

@@ -20,6 +20,7 @@ bool ServerThreadEntry::start(std::string* err) {
   if (!router_->bind("*", port_for(config_, process_id_, channel_id_), err)) return false;
   encoder_.reset(new ServerClientEncode(router_, num_processes_, process_id_, config_));
   storage_.reset(new TabletStorage(channel_id_, num_channels_, process_id_, num_processes_, encoder_, config_));
+  if (hyper_schedule) storage_->hyper = hyper_schedule;
   metadata_.reset(new MetadataServer(process_id_, num_processes_, encoder_, config_));
   decoder_.reset(new ClientServerDecode(storage_, metadata_));
   decoder_->control_hook = control_hook;

@@ -24,6 +24,8 @@ class ServerThreadEntry {
   // Handler for the control-plane messages that reach this shard (heartbeats, barriers, handle exchange, lost
   // peers).  Set it before start(): a peer may deliver such a message the moment the port is bound.
   std::function<void(const std::string&, Message&)> control_hook;
+  // Optimizer hyper-parameters by clock, shared with the worker side of the process (set before start()).
+  std::shared_ptr<HyperSchedule> hyper_schedule;
   static unsigned port_for(const GeePsConfig& config, uint process_id, uint channel_id);
   std::shared_ptr<RouterHandler> router() { return router_; }
   std::shared_ptr<TabletStorage> storage() { return storage_; }

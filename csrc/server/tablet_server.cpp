@@ -30,6 +30,7 @@ TabletStorage::TabletStorage(uint channel_id, uint num_channels, uint process_id
   optimizer.momentum = config.momentum;
   optimizer.weight_decay = config.weight_decay;
   optimizer.grad_scale = config.grad_scale;
+  hyper.reset(new HyperSchedule(config.learning_rate, config.momentum, config.weight_decay));
 }
 
 bool TabletStorage::fail(const std::string& what) {
@@ -106,6 +107,8 @@ bool TabletStorage::clock(uint client_id, iter_t clock, uint table_id) {
     if (t.mode == GeePsConfig::TABLE_SGD_MOMENTUM) {
       auto it = t.pending.find(new_global);
       if (it != t.pending.end()) {   // every worker's update of this clock is in: one optimizer step
+        const HyperSchedule::Entry h = hyper->at(new_global);
+        optimizer.lr = h.lr; optimizer.momentum = h.momentum; optimizer.weight_decay = h.weight_decay;
         cpu_sgd_momentum(t.row_count * ROW_DATA_SIZE, t.store.floats(), t.momentum.floats(), it->second->floats(),
                          optimizer);
         t.pending.erase(it);

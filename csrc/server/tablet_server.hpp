@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "core/common_util.hpp"
+#include "core/hyper_schedule.hpp"
 #include "core/relaxed.hpp"
 #include "core/row_op_util.hpp"
 #include "geeps.hpp"
@@ -55,6 +56,9 @@ class TabletStorage {
   uint process_id() const { return process_id_; }
   const std::string& last_error() const { return last_error_; }
   OptimizerParams optimizer;
+  // learning rate, momentum and weight decay by clock; the worker side of the process shares the object and
+  // changes it (set before the handler thread starts; a schedule of its own, built from the config, otherwise)
+  std::shared_ptr<HyperSchedule> hyper;
 
  private:
   void apply_updates(DataTable& t, const RowOpVal* updates, size_t n);

@@ -43,6 +43,10 @@ def _lib():
         lib.geeps_new.restype = C.c_void_p
         lib.geeps_new.argtypes = [C.c_uint, C.c_void_p]
         lib.geeps_read_bf16.restype = C.c_void_p
+        lib.geeps_set_hyper_params.argtypes = [C.c_void_p, C.c_float, C.c_float, C.c_float]
+        lib.geeps_set_hyper_params.restype = None
+        lib.geeps_get_hyper_params.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
+        lib.geeps_get_hyper_params.restype = None
         lib.geeps_planner_new.restype = C.c_void_p
         lib.geeps_mtcache_new.restype = C.c_void_p
         lib.geeps_ringcache_new.restype = C.c_void_p
@@ -136,6 +140,20 @@ class GeePs:
     @property
     def clock_value(self) -> int:
         return self._l.geeps_current_clock(self._g)
+
+    def set_hyper_params(self, learning_rate=None, momentum=None, weight_decay=None) -> None:
+        """Learning rate, momentum and weight decay of the shard-side optimizer for the updates of the iteration in
+        progress and all later ones (None keeps a value).  Every worker makes the same call in the same iteration.
+        Iterations captured in a CUDA graph keep the values of the time of capture."""
+        lr, mom, wd = self.hyper_params()
+        self._l.geeps_set_hyper_params(self._g, lr if learning_rate is None else learning_rate,
+                                       mom if momentum is None else momentum, wd if weight_decay is None else weight_decay)
+
+    def hyper_params(self):
+        """(learning_rate, momentum, weight_decay) in force for the updates of the iteration in progress."""
+        out = (C.c_float * 3)()
+        self._l.geeps_get_hyper_params(self._g, out)
+        return float(out[0]), float(out[1]), float(out[2])
 
     # ---- virtual iteration ----
     def virtual_read(self, table: int, rows, slack: int = 0) -> int:

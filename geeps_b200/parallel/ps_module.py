@@ -50,7 +50,7 @@ class PSModule:
     def __init__(self, net, in_shape, ps_config: GeePsConfig, rank: int = 0, world: int = 1, device="cuda:0",
                  slack: int = 0, seed: int = 0, keep_init: bool = False, trace=None, manage_activations: bool = False,
                  cache_fraction: float | None = None, use_tape: bool = False, bf16_weights_only: bool = False,
-                 use_graph: bool = False, pull_fc: bool = False, uncached=()):
+                 use_graph: bool = False, pull_fc: bool = False, uncached=(), resume_from: str | None = None):
         """bf16_weights_only: with the NVLINK transport and the bf16 compute cache, weight rows are published to
         the workers' bf16 caches only (the layers never read weights in fp32; biases, BatchNorm scale / shift and
         the shard's master rows stay fp32).  The fp32 views of weights (`params_fp32`) then keep their initial
@@ -65,7 +65,11 @@ class PSModule:
         pass; the bias rows arrive through the table's fp32 tail.
         uncached: names of further layers whose tables are kept uncached (no worker-side copy; every Read fetches
         the whole table from the shards into the staging pool) - the device-side form of a parameter cache that
-        does not fit the GPU budget."""
+        does not fit the GPU budget.
+        resume_from: directory of table snapshots (`save_snapshot`): the tables (master rows, momentum, clocks) come
+        from its latest snapshot instead of the initial values, and training goes on at the snapshot's clock.  The
+        world size may differ from the one that wrote it.  Layer-local state (BatchNorm running statistics) is not
+        part of a table snapshot."""
         self.net, self.rank, self.world, self.slack = net, rank, world, slack
         self.device = torch.device(device)
         self.trace = trace or NullTrace()
@@ -153,9 +157,13 @@ class PSModule:
         self.initial_params = {} if keep_init else None
         self.captured = None
         self._declare()
-        self._bootstrap(seed)
+        if resume_from is not None:
+            if not self.ps.load_snapshot(resume_from):
+                raise RuntimeError(f"resume from {resume_from}: {self.ps.last_error_string()}")
+        else:
+            self._bootstrap(seed)
         self.ps.start_iterations()
-        self.steps = 0
+        self.steps = max(0, self.ps.clock_value - 1)      # clock 0 is the bootstrap clock
         if self.use_graph:
             ref = self.ps.enable_device_clock()
             for l in net.all_layers():
@@ -361,6 +369,23 @@ class PSModule:
         if self.use_graph and not self._graph_failed:
             return key in self._graphs
         return (not self.use_tape) or key in self._tapes
+
+    def save_snapshot(self, directory: str) -> None:
+        """Write every table (master rows, momentum, clocks) under directory/snapshot.<clock>; every rank calls it
+        before the same step."""
+        if not self.ps.save_snapshot(directory):
+            raise RuntimeError(f"snapshot to {directory}: {self.ps.last_error_string()}")
+
+    def set_hyper_params(self, learning_rate=None, momentum=None, weight_decay=None) -> None:
+        """Change the optimizer's learning rate / momentum / weight decay from the next step on (every rank makes the
+        same call before the same step).  Recorded and captured steps carry the old values in their push launches, so
+        they are dropped when a value changes: the next few steps run through the layer code and are captured again."""
+        old = self.ps.hyper_params()
+        self.ps.set_hyper_params(learning_rate, momentum, weight_decay)
+        if self.ps.hyper_params() != old:
+            if self.use_graph:
+                torch.cuda.synchronize(self.device)      # no replay in flight when its graph is destroyed
+            self.invalidate_tapes()
 
     def invalidate_tapes(self) -> None:
         """Forget the recorded steps (call after anything that changes what a step launches: switching layers

@@ -140,6 +140,12 @@ class GeePs {
   /* The compiled plan as JSON (placement, offsets, indices, per-shard ranges) */
   std::string PlanJson() const;
   iter_t CurrentClock() const;
+  /* Optimizer tables: learning rate, momentum and weight decay of the shard-side optimizer for the updates of the
+   * iteration in progress and all later ones (a learning-rate policy calls this between iterations).  Every worker
+   * makes the same call in the same iteration, so all shards switch at the same clock.  Iterations captured in a
+   * CUDA graph keep the values of the time of capture. */
+  void SetHyperParams(float learning_rate, float momentum, float weight_decay);
+  void GetHyperParams(float* learning_rate, float* momentum, float* weight_decay) const;
   /* NVLINK transport: keep the clock in a device word, so that the launches of one iteration carry no value that
    * changes from clock to clock and can be captured in a CUDA graph (one graph per phase of the update ring, i.e.
    * per clock modulo slack + 1).  From then on Clock() joins the runtime's streams into the stream of the latest

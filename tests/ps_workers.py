@@ -484,3 +484,54 @@ def multitable_worker(rank, world, base_port, clocks, q, kw):
         q.put((rank, "ok", vals, stats["channels"], stats["comm_channels"], None))
     except Exception as e:  # pragma: no cover
         q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))
+
+
+def lr_schedule_worker(rank, world, base_port, slack, q, kw):
+    """Momentum-SGD table whose learning rate, momentum and weight decay change while the run goes on: both workers
+    make the same set_hyper_params call before the same clock (rank 1 lags behind by a sleep, so the shards see the
+    calls at different wall-clock times) and return the fully applied table."""
+    try:
+        import time
+        import torch
+        from geeps_b200.parallel.ps import GeePs
+        from geeps_b200.utils.config import DEVICE_CPU, TABLE_SGD_MOMENTUM
+        kw = dict(kw)
+        kw.setdefault("device", DEVICE_CPU)
+        cfg = make_cfg(world, base_port, table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.1, momentum=0.9,
+                       weight_decay=0.0, grad_scale=1.0 / world, **kw)
+        g = GeePs(rank, cfg)
+        rows = list(range(40))
+        r = g.virtual_read(0, rows, slack)
+        u = g.virtual_pre_update(0, rows)
+        pr = g.virtual_post_read(r)
+        up = g.virtual_update(u)
+        g.virtual_clock()
+        r0 = g.virtual_read(0, rows, 0)
+        g.virtual_post_read(r0)
+        g.finish_virtual_iteration()
+        g.pre_update(u).fill_(1.0 / world)          # initial value 1.0
+        g.update(up)
+        g.clock()
+        g.start_iterations()
+        seen_hyper = []
+        for c in range(1, 9):
+            if c == 3:
+                g.set_hyper_params(learning_rate=0.05)
+            if c == 6:
+                g.set_hyper_params(learning_rate=0.01, momentum=0.5, weight_decay=0.1)
+            if rank == 1 and c in (3, 6):
+                time.sleep(0.7)
+            seen_hyper.append(g.hyper_params())
+            g.read(r, asynchronous=False)
+            b = g.pre_update(u)
+            g.post_read(pr)
+            b.fill_(float(c))                       # gradient c from every worker: mean c
+            g.update(up)
+            g.clock()
+        final = g.read(r0, asynchronous=False)
+        out = (float(final.min()), float(final.max()))
+        g.shutdown()
+        g.close()
+        q.put((rank, "ok", out, seen_hyper, None, None))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, "error", repr(e) + traceback.format_exc(), None, None, None))

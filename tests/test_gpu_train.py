@@ -266,6 +266,66 @@ def test_uint8_batches_with_augmentation_train_like_float_batches_under_graph_re
     assert len(set(round(v, 5) for v in losses[True])) > steps // 2          # the batches did differ from step to step
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_hyper_parameter_changes_take_effect_at_the_next_step(graph):
+    """set_hyper_params between steps on the NVLINK path: with learning rate and momentum at zero the shard's step
+    leaves the parameters where they are (the loss on a fixed batch stops moving), and training picks up again when
+    they come back.  Under graph replay the captured steps are dropped at every change and captured again."""
+    dev = torch.device("cuda:0")
+    B = 32
+    with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+        mod = PSModule(tiny_net(), (B, 3, 16, 16), cfg(TRANSPORT_NVLINK, learning_rate=0.05), device=dev, seed=3,
+                       use_graph=graph)
+        gen = torch.Generator(device=dev).manual_seed(5)
+        x = torch.randn(B, 3, 16, 16, device=dev, generator=gen)
+        y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+        assert mod.ps.hyper_params() == pytest.approx((0.05, 0.9, 0.0))
+        losses = []
+        for i in range(24):
+            if i == 8:
+                mod.set_hyper_params(learning_rate=0.0, momentum=0.0)
+                assert not mod._graphs and not mod._tapes
+            if i == 14:
+                mod.set_hyper_params(learning_rate=0.05, momentum=0.9)
+            losses.append(mod.step(x, y).item())
+        assert mod.ps.last_error() == 0
+        if graph:
+            assert len(mod._graphs) >= 1 and mod.ps.get_stats()["client"]["nr_replayed_clocks"] > 0
+        mod.close()
+    # (the loss is a sum of per-sample terms added in no fixed order: equal up to rounding)
+    assert abs(losses[8] - losses[7]) > 2e-5, losses                # the update of step 7 still moved the parameters
+    assert all(abs(v - losses[8]) <= 2e-6 * abs(losses[8]) for v in losses[9:15]), losses    # steps 8 .. 13 did not
+    assert abs(losses[15] - losses[14]) > 2e-5 and losses[-1] < losses[0], losses
+
+
+def test_snapshot_and_resume_on_the_nvlink_path(tmp_path):
+    """Table snapshot of a training run on the GPU transport (master rows, momentum, clocks read from the device
+    arena) and a new module resumed from it: the resumed run continues with the losses of the original one."""
+    dev = torch.device("cuda:0")
+    B = 32
+    gen = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(B, 3, 16, 16, device=dev, generator=gen)
+    y = torch.randint(0, 10, (B,), device=dev, generator=gen)
+    snap = str(tmp_path / "snap")
+    with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+        mod = PSModule(tiny_net(), (B, 3, 16, 16), cfg(TRANSPORT_NVLINK, learning_rate=0.05), device=dev, seed=3)
+        first = [mod.step(x, y).item() for _ in range(6)]
+        mod.save_snapshot(snap)
+        clock = mod.ps.clock_value
+        cont = [mod.step(x, y).item() for _ in range(4)]
+        assert mod.ps.last_error() == 0
+        mod.close()
+    with torch.cuda.stream(torch.cuda.Stream(device=dev)):
+        mod = PSModule(tiny_net(), (B, 3, 16, 16), cfg(TRANSPORT_NVLINK, learning_rate=0.05), device=dev, seed=99,
+                       resume_from=snap)
+        assert mod.ps.clock_value == clock and mod.steps == 6
+        resumed = [mod.step(x, y).item() for _ in range(4)]
+        assert mod.ps.last_error() == 0
+        mod.close()
+    assert resumed == pytest.approx(cont, rel=2e-3), (first, cont, resumed)
+    assert abs(resumed[0] - first[0]) > 1e-3          # not a fresh start
+
+
 @pytest.mark.parametrize("mode", ["pull_fc", "uncached"])
 def test_uncached_tables_train_like_published_ones(mode):
     """Tables the shards do not publish: (pull_fc) the fully-connected layers pull their weight rows from the shards

@@ -11,7 +11,7 @@ import torch
 from geeps_b200.parallel.ps import GeePs, GeePsError
 from geeps_b200.utils.config import (DEVICE_CPU, PARTITION_ROUND_ROBIN, TABLE_SGD_MOMENTUM, GeePsConfig)
 
-from ps_workers import helloworld_worker, multitable_worker, rmw_worker
+from ps_workers import helloworld_worker, lr_schedule_worker, multitable_worker, rmw_worker
 
 _port = [12000 + (os.getpid() % 300) * 40]   # below the ephemeral port range
 
@@ -151,6 +151,78 @@ def test_optimizer_table_matches_momentum_sgd():
         p = p - v
     g.shutdown()
     g.close()
+
+
+def test_optimizer_table_follows_hyper_parameter_changes():
+    """set_hyper_params between iterations: the shard applies the updates of that iteration and all later ones with
+    the new learning rate / momentum / weight decay, earlier ones with the old values."""
+    g = _single(dict(table_mode=TABLE_SGD_MOMENTUM, learning_rate=0.1, momentum=0.9, weight_decay=0.01))
+    rows = [5, 6, 7]
+    r = g.virtual_read(0, rows, 0)
+    u = g.virtual_pre_update(0, rows)
+    pr = g.virtual_post_read(r)
+    up = g.virtual_update(u)
+    g.virtual_clock()
+    g.finish_virtual_iteration()
+    torch.manual_seed(0)
+    w0 = torch.randn(3, 128)
+    g.pre_update(u).copy_(w0)
+    g.update(up)
+    g.clock()
+    g.start_iterations()
+    assert g.hyper_params() == pytest.approx((0.1, 0.9, 0.01))
+    p, v = w0.clone(), torch.zeros_like(w0)
+    lr, mom, wd = 0.1, 0.9, 0.01
+    for c in range(8):
+        if c == 2:
+            lr = 0.02
+            g.set_hyper_params(learning_rate=lr)
+        if c == 5:
+            lr, mom, wd = 0.5, 0.0, 0.0
+            g.set_hyper_params(lr, mom, wd)
+            g.set_hyper_params(lr, mom, wd)          # repeating a call changes nothing
+        assert g.hyper_params() == pytest.approx((lr, mom, wd))
+        x = g.read(r, asynchronous=False).clone()
+        assert torch.allclose(x, p, atol=1e-5), c
+        grad = torch.randn(3, 128)
+        b = g.pre_update(u)
+        g.post_read(pr)
+        b.copy_(grad)
+        g.update(up)
+        g.clock()
+        v = mom * v + lr * (grad + wd * p)
+        p = p - v
+    g.shutdown()
+    g.close()
+
+
+@pytest.mark.parametrize("slack", [0, 1])
+def test_all_shards_switch_hyper_parameters_at_the_same_clock(slack):
+    """Two workers, two shards, one worker lagging: the update of clock c is applied with the values that were in
+    force for clock c on every shard, so the table equals the single-process recurrence whatever the timing."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = next_port()
+    procs = [ctx.Process(target=lr_schedule_worker, args=(rk, 2, port, slack, q, {})) for rk in range(2)]
+    for pr in procs:
+        pr.start()
+    out = sorted(q.get(timeout=240) for _ in procs)
+    for pr in procs:
+        pr.join(timeout=60)
+    p, v = 1.0, 0.0
+    lr, mom, wd = 0.1, 0.9, 0.0
+    for c in range(1, 9):
+        if c == 3:
+            lr = 0.05
+        if c == 6:
+            lr, mom, wd = 0.01, 0.5, 0.1
+        v = mom * v + lr * (float(c) + wd * p)
+        p -= v
+    for o in out:
+        assert o[1] == "ok", o[2]
+        assert abs(o[2][0] - p) < 1e-4 and abs(o[2][1] - p) < 1e-4, (o[2], p)
+        assert o[3][1] == pytest.approx((0.1, 0.9, 0.0)) and o[3][2] == pytest.approx((0.05, 0.9, 0.0))
+        assert o[3][7] == pytest.approx((0.01, 0.5, 0.1))
 
 
 def test_call_order_is_enforced_and_reported():
