@@ -40,6 +40,11 @@ class HostFeeder:
             self.ready[s].record(self.copy_stream)
         self.put_i += 1
 
+    def wait_copied(self, slot: int) -> None:
+        """Host wait until the last copy submitted into `slot` has finished reading its host tensors (call before
+        overwriting a staging buffer that was handed to submit)."""
+        self.ready[slot].synchronize()
+
     def copy_times_ms(self, clear: bool = True) -> list:
         """Device time of every completed copy submitted since the last call (needs timed=True)."""
         out, keep = [], []
