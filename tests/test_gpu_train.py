@@ -294,7 +294,7 @@ def test_hyper_parameter_changes_take_effect_at_the_next_step(graph):
         mod.close()
     # (the loss is a sum of per-sample terms added in no fixed order: equal up to rounding)
     assert abs(losses[8] - losses[7]) > 2e-5, losses                # the update of step 7 still moved the parameters
-    assert all(abs(v - losses[8]) <= 2e-6 * abs(losses[8]) for v in losses[9:15]), losses    # steps 8 .. 13 did not
+    assert all(abs(v - losses[8]) <= 1e-5 * abs(losses[8]) for v in losses[9:15]), losses    # steps 8 .. 13 did not
     assert abs(losses[15] - losses[14]) > 2e-5 and losses[-1] < losses[0], losses
 
 
