@@ -134,7 +134,8 @@ class GeePs {
   /* 0 when healthy; otherwise the first error (expired wait, dead peer, ...) and its text */
   int LastError() const;
   std::string LastErrorString() const;
-  /* Table snapshots */
+  /* Table snapshots: rows, optimizer momentum and clocks.  The hyper-parameters of a resumed run come from its
+   * config and its own SetHyperParams calls (the manifest records the values in force for reference). */
   bool SaveSnapshot(const std::string& dir);
   bool LoadSnapshot(const std::string& dir);
   /* The compiled plan as JSON (placement, offsets, indices, per-shard ranges) */

@@ -295,14 +295,23 @@ def test_snapshot_roundtrip(tmp_path):
     g.pre_update(u).copy_(torch.ones(16, 128)); g.update(up); g.clock()
     g.start_iterations()
     for s in range(3):
+        if s == 2:
+            g.set_hyper_params(learning_rate=0.02)      # in force from this iteration on
         step(g, r, u, pr, up, s)
     assert g.save_snapshot(str(tmp_path))
+    import json
+    with open(os.path.join(str(tmp_path), "snapshot.4", "MANIFEST.0.json")) as f:
+        man = json.load(f)
+    assert man["clock"] == 4 and man["learning_rate"] == pytest.approx(0.02) and man["momentum"] == pytest.approx(0.9)
     after = [step(g, r, u, pr, up, 10 + s) for s in range(3)]
     g.shutdown(); g.close()
 
     g2, r, u, pr, up = build(next_port())
     assert g2.load_snapshot(str(tmp_path))
     g2.start_iterations()
+    # rows, momentum and clocks come from the snapshot; the hyper-parameters from the config and later calls
+    assert g2.hyper_params()[0] == pytest.approx(0.05)
+    g2.set_hyper_params(learning_rate=0.02)
     again = [step(g2, r, u, pr, up, 10 + s) for s in range(3)]
     for a, b in zip(after, again):
         assert torch.equal(a, b)      # parameters AND momentum came back
