@@ -100,6 +100,18 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def pcie_links() -> list:
+    """PCIe generation and width of every GPU's link as nvidia-smi reports them now (read only; explains what the
+    host-to-device copies of the end-to-end run can reach)."""
+    try:
+        out = subprocess.run(["nvidia-smi", "--query-gpu=index,pcie.link.gen.current,pcie.link.width.current,"
+                              "pcie.link.gen.max,pcie.link.width.max", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=20).stdout
+        return [[f.strip() for f in line.split(",")] for line in out.strip().splitlines()][:16]
+    except Exception:
+        return []
+
+
 def reference_arm(args) -> None:
     """The reference is a C++ library (SCons + ZeroMQ/boost/tbb/glog/gflags/cblas) with no Python
     package, and its Caffe application (the only program in it that trains AlexNet) is an empty submodule: the
@@ -332,6 +344,8 @@ def main() -> None:
             diag = {"host_enqueue_ms_per_step": host_enqueue_ms,
                     "h2d_copy_alone_ms": alone_ms,
                     "h2d_copy_alone_gb_per_s": x_host.numel() * x_host.element_size() / alone_ms / 1e6}
+            if rank == 0:
+                diag["pcie"] = pcie_links()
             if not args.single_e2e and model_name == "alexnet":
                 # the same run with the other input dtype on the host (the spec names an fp32 N(0,1) input; the
                 # input layer rounds it to bf16 either way, so a host pipeline may as well ship bf16)
