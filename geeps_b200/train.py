@@ -181,8 +181,10 @@ def main(argv=None) -> None:
         source = ArraySource(images, labels, B, rank, world, seed=args.seed, sets=feeder_depth)
         source.skip(solver.iter)       # a resumed run goes on with the batches that follow the ones already consumed
         feeder = HostFeeder((B, image[0]) + src_hw, (B,), dev, depth=feeder_depth, x_dtype=torch.uint8)
-        aug_gen = torch.Generator(device=dev).manual_seed(args.seed * 7919 + rank)
-        augment = None if args.no_augment else (lambda it: inp.randomize(src_hw, mirror=True, generator=aug_gen))
+        augment = None
+        if not args.no_augment:
+            aug_gen = torch.Generator(device=dev).manual_seed(args.seed * 7919 + rank)
+            augment = lambda it: inp.randomize(src_hw, mirror=True, generator=aug_gen)
         if rank == 0:
             print(f"{args.model}: batch {B} x {world} GPUs, {len(images)} images {src_hw[0]}x{src_hw[1]}, "
                   f"iterations {solver.iter} -> {args.max_iter}, lr policy {args.lr_policy}", flush=True)

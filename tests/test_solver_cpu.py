@@ -1,6 +1,7 @@
 """Training-loop pieces that need no GPU: learning-rate policies, the solver's bookkeeping (when the rate changes,
 what is displayed, when snapshots are written, where a resumed run starts) and the data walk of the trainer."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -152,3 +153,77 @@ def test_device_batches_keep_staging_sets_and_device_slots_in_step():
         i = feeder.log.index(subs[-1])
         assert feeder.log[i - 1] == ("wait", (k + 1) % 2)
     assert [e[1] for e in feeder.log if e[0] == "release"] == [0, 1, 0, 1, 0]
+
+
+def test_trainer_main_wires_model_data_feeder_and_solver(monkeypatch, tmp_path, capsys):
+    """python -m geeps_b200.train end to end with the GPU parts replaced by fakes (the module, the feeder, the CUDA
+    stream calls): arguments reach the right places, the data walk feeds the module batch by batch, the policy's
+    rate changes arrive before their iterations, snapshots are written, and a resumed run skips the consumed batches."""
+    import contextlib
+
+    import geeps_b200.parallel.ps_module as pm
+    import geeps_b200.train as train
+    import geeps_b200.utils.feeder as fd
+    made = []
+
+    class FakeInput:
+        def __init__(self):
+            self.transform, self.augs = None, 0
+
+        def set_transform(self, mean, scale):
+            self.transform = (tuple(mean), scale)
+
+    class FakePS(FakeModule):
+        def __init__(self, net, in_shape, cfg, rank=0, world=1, resume_from=None, **kw):
+            super().__init__(steps=4 if resume_from else 0)
+            self.in_shape, self.cfg, self.kw, self.resume_from = in_shape, cfg, kw, resume_from
+            self.net = type("N", (), {"input_layer": FakeInput()})()
+            self.labels_seen = []
+            made.append(self)
+
+        def step(self, x, labels):
+            assert x.dtype == torch.uint8 and tuple(x.shape) == (4, 3, 40, 40)
+            self.labels_seen.append(labels.tolist())
+            return super().step(x, labels)
+
+        def close(self):
+            self.calls.append(("close",))
+
+    class Feeder(FakeFeeder):
+        def __init__(self, x_shape, y_shape, device, depth=2, x_dtype=None, timed=False):
+            super().__init__(depth)
+            assert tuple(x_shape) == (4, 3, 40, 40) and x_dtype == torch.uint8
+
+    monkeypatch.setattr(pm, "PSModule", FakePS)
+    monkeypatch.setattr(fd, "HostFeeder", Feeder)
+    monkeypatch.setattr(torch.cuda, "set_device", lambda d: None)
+    monkeypatch.setattr(torch.cuda, "Stream", lambda **kw: object())
+    monkeypatch.setattr(torch.cuda, "stream", lambda s: contextlib.nullcontext())
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda d=None: None)
+    monkeypatch.setattr(torch.Tensor, "pin_memory", lambda t: t)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    snap = str(tmp_path / "snap")
+    common = ["--model", "inception_bn_small", "--batch", "4", "--synthetic-images", "24", "--source-size", "40",
+              "--no-augment", "--lr-policy", "step", "--stepsize", "3", "--base-lr", "0.1", "--display", "2",
+              "--snapshot", "4", "--snapshot-dir", snap, "--mean", "1", "2", "3", "--scale", "0.5"]
+    train.main(common + ["--max-iter", "8"])
+    mod = made[0]
+    assert mod.in_shape == (4, 3, 32, 32) and mod.resume_from is None and mod.kw["use_graph"] is True
+    assert mod.cfg.learning_rate == pytest.approx(0.1)
+    assert mod.net.input_layer.transform == ((1.0, 2.0, 3.0), 0.5)
+    assert [c[1] for c in mod.calls if c[0] == "step"] == list(range(8))
+    assert [(c[1], round(c[2], 6)) for c in mod.calls if c[0] == "hyper"] == [(0, 0.1), (3, 0.01), (6, 0.001)]
+    assert [c[1] for c in mod.calls if c[0] == "snapshot"] == [4, 8] and mod.calls[-1] == ("close",)
+    out = capsys.readouterr().out
+    assert "iteration 0  loss 100.00000  lr 0.1" in out and "iteration 6  loss 94.00000  lr 0.001" in out
+    # a resumed run (the fake resumes at iteration 4) goes on with the batches the first run saw from iteration 4 on
+    os.makedirs(snap, exist_ok=True)
+    with open(os.path.join(snap, "LATEST"), "w") as f:
+        f.write("5")
+    train.main(common + ["--max-iter", "8", "--resume"])
+    res = made[1]
+    assert res.resume_from == snap and [c[1] for c in res.calls if c[0] == "step"] == [4, 5, 6, 7]
+    assert res.labels_seen == mod.labels_seen[4:8]
+    with pytest.raises(SystemExit):
+        train.main(common + ["--max-iter", "8", "--resume", "--snapshot-dir", str(tmp_path / "none")])
