@@ -137,3 +137,37 @@ def test_input_layer_augmentation_buffer_bookkeeping():
     assert int(inp.aug[:, 2].max()) == 0
     inp.set_transform((9.0, 8.0, 7.0), 2.0)
     assert inp.mean == (9.0, 8.0, 7.0) and inp.scale == 2.0
+
+
+def test_bench_clock_sampler_reads_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The benchmark's clock record: the sampler waits for the tool's first line (its start can outlast a short timed
+    region), keeps the samples of the marked window and reports the median clock and the active throttle reasons."""
+    import os
+    import stat
+    import sys
+    import time
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\nsleep 0.4\nwhile true; do echo '1867, 1965, 930.5, Not Active, Not Active, Not Active, Active'; "
+                    "sleep 0.05; done\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    s = bench.ClockSampler(0)
+    s.start()
+    t0 = time.time()
+    s.wait_first_sample()
+    assert 0.3 < time.time() - t0 < 5.0 and s.samples          # blocked until the first line arrived
+    s.mark_begin()
+    time.sleep(0.3)
+    s.mark_end()
+    rec = s.stop()
+    assert rec["sm_mhz"] == 1867.0 and rec["sm_max_mhz"] == 1965.0 and rec["reasons"] == ["sw_power_cap"]
+    assert rec["samples"] >= 3
+    # without the tool the record says so instead of failing the run
+    monkeypatch.setenv("PATH", str(tmp_path / "empty"))
+    s2 = bench.ClockSampler(0)
+    s2.start()
+    s2.wait_first_sample(0.2)
+    assert s2.stop()["sm_mhz"] is None
+    assert bench.pcie_links() == []
