@@ -127,7 +127,6 @@ def main(argv=None) -> None:
 
     import numpy as np
     import torch
-    import torch.distributed as dist
 
     from .models.alexnet import alexnet
     from .models.inception_bn import inception_bn_22k, inception_bn_small
@@ -143,8 +142,8 @@ def main(argv=None) -> None:
     bind_to_gpu_cores(local_rank, int(os.environ.get("LOCAL_WORLD_SIZE", world)))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    # no torch.distributed process group: the parameter server's own control plane (TCP, host_list / port_list)
+    # connects the ranks, and its peer-memory fabric carries the data
 
     image, classes, default_batch = MODELS[args.model]
     B = args.batch or default_batch
@@ -191,8 +190,6 @@ def main(argv=None) -> None:
         solver.run(device_batches(source, feeder, stream), args.max_iter, before_step=augment)
         torch.cuda.synchronize(dev)
         mod.close()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
