@@ -17,8 +17,8 @@ import torch
 
 from ..ops import _lib as L
 from ..ops import functional as F
-from ..ops.layers import BF, ParamSpec
-from ..utils.config import TABLE_SGD_MOMENTUM, TRANSPORT_NVLINK, GeePsConfig
+from ..ops.layers import BF
+from ..utils.config import TRANSPORT_NVLINK, GeePsConfig
 from ..utils.trace import NullTrace
 from .ps import ROW_FLOATS, GeePs
 
